@@ -1,0 +1,490 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a.
+//
+//   D[M,N] = alpha * sum_k A[m,k] * B[n,k]   (fp32 accumulation in TMEM)
+//
+// Roles inside one 192-thread CTA (one CTA per SM, static round-robin over tiles):
+//   warp 0      : TMA producer  (cp.async.bulk.tensor -> 128B-swizzled smem ring)
+//   warp 1      : tcgen05.mma issuer + TMEM owner (two accumulator buffers)
+//   warps 2..5  : epilogue (tcgen05.ld -> bias / GELU / residual / dGELU -> global)
+// The accumulator is double-buffered in TMEM so the epilogue of tile i overlaps the
+// main loop of tile i+1.
+//
+// Operand layouts (all bf16, row-major in global memory, leading dims in elements):
+//   a_mn = 0 : A is [M, K]  (K contiguous)      a_mn = 1 : A is [K, M]  (M contiguous)
+//   b_mn = 0 : B is [N, K]  (K contiguous)      b_mn = 1 : B is [K, N]  (N contiguous)
+// which covers forward (0,0), data-gradient (0,1) and weight-gradient (1,1) of a
+// linear layer without any transposed copies.
+#include "tc05.cuh"
+#include "kernels.h"
+
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+using namespace tc05;
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kThreads = 192;
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
+};
+
+struct DevParams {
+  int M, N, K;
+  int tiles_m, tiles_n, batch, splits;
+  int kb_total;
+  float alpha;
+  int epi;
+  int out_f32;      // 1: fp32 output
+  int accumulate;   // 1: out += result (fp32 output only, uses red.add)
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  const __nv_bfloat16* aux;
+  void* out;
+  __nv_bfloat16* out2;
+  long long ldo, ldr, ldaux, ldo2;
+  long long bs_out, bs_res, bs_aux, bs_out2, bs_bias;
+  int* status;
+};
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float dgelu_erf(float x) {
+  const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752f));
+  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
+  return cdf + x * pdf;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const DevParams p) {
+  using L = SmemLayout<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint64_t* empty_bar = full_bar + L::kStages;
+  uint64_t* acc_full = empty_bar + L::kStages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t kTmemCols = 2 * BN;  // 256 or 512: powers of two
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 128);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;
+  const int total_work = tiles_per_batch * p.batch * p.splits;
+  const int kb_per_split = (p.kb_total + p.splits - 1) / p.splits;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (elect_one()) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        const int split = w % p.splits;
+        const int t = w / p.splits;
+        const int z = t / tiles_per_batch;
+        const int tt = t % tiles_per_batch;
+        const int m0 = (tt % p.tiles_m) * BM;
+        const int n0 = (tt / p.tiles_m) * BN;
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(p.kb_total, kb0 + kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.status, kErrEmptyWait)) { ok = false; break; }
+          uint8_t* sa = smem + stage * L::kStageBytes;
+          uint8_t* sb = sa + L::kABytes;
+          mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+          if (!A_MN) {
+            tma_load_3d(sa, &tmap_a, &full_bar[stage], kb * BK, m0, z);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_3d(sa + c * (BK * 128), &tmap_a, &full_bar[stage], m0 + c * 64, kb * BK, z);
+          }
+          if (!B_MN) {
+            if (BN == 256) {
+              tma_load_3d(sb, &tmap_b, &full_bar[stage], kb * BK, n0, z);
+              tma_load_3d(sb + 128 * 128, &tmap_b, &full_bar[stage], kb * BK, n0 + 128, z);
+            } else {
+              tma_load_3d(sb, &tmap_b, &full_bar[stage], kb * BK, n0, z);
+            }
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_3d(sb + c * (BK * 128), &tmap_b, &full_bar[stage], n0 + c * 64, kb * BK, z);
+          }
+          if (++stage == L::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ---------------------------------
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        const int split = w % p.splits;
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(p.kb_total, kb0 + kb_per_split);
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, kErrAccEmptyWait)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kErrFullWait)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // K-major: 16 bf16 of K = 32 bytes inside the 128-byte swizzled row.
+            // MN-major: 16 rows of K = two 1024-byte swizzle atoms.
+            const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, BK * 128, 1024)
+                                     : make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, BK * 128, 1024)
+                                     : make_smem_desc(sb + k * 32, 16, 1024);
+            umma_bf16(d_tmem, da, db, idesc, (kb > kb0) || (k > 0));
+          }
+          umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
+          if (++stage == L::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue -----------------------------------
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      const int t = w / p.splits;
+      const int z = t / tiles_per_batch;
+      const int tt = t % tiles_per_batch;
+      const int m0 = (tt % p.tiles_m) * BM;
+      const int n0 = (tt / p.tiles_m) * BN;
+      const int split = w % p.splits;
+      const bool empty_split = split * kb_per_split >= p.kb_total;
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.status, kErrAccFullWait)) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+      const __nv_bfloat16* bias = p.bias ? p.bias + z * p.bs_bias : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int nc = n0 + c * 32;
+        if (nc >= p.N) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        if (!row_ok || empty_split) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        const bool full = (nc + 32 <= p.N);
+        if (bias && split == 0) {
+          if (full) {
+            const uint4* bp = reinterpret_cast<const uint4*>(bias + nc);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 b = __ldg(bp + q);
+              const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                v[q * 8 + e * 2] += bf16_lo(bw[e]);
+                v[q * 8 + e * 2 + 1] += bf16_hi(bw[e]);
+              }
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (nc + j < p.N) v[j] += __bfloat162float(bias[nc + j]);
+          }
+        }
+        if (p.out_f32) {
+          float* o = reinterpret_cast<float*>(p.out) + z * p.bs_out + static_cast<long long>(row) * p.ldo + nc;
+          if (p.accumulate || p.splits > 1) {
+            if (full && (p.ldo % 4 == 0)) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + q * 4), "f"(v[q * 4]),
+                             "f"(v[q * 4 + 1]), "f"(v[q * 4 + 2]), "f"(v[q * 4 + 3])
+                             : "memory");
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (nc + j < p.N) atomicAdd(o + j, v[j]);
+            }
+          } else {
+            if (full && (p.ldo % 4 == 0)) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                reinterpret_cast<float4*>(o)[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (nc + j < p.N) o[j] = v[j];
+            }
+          }
+          continue;
+        }
+        // ---- bf16 outputs ----
+        const bool vec = full && (p.ldo % 8 == 0);
+        if (p.residual) {
+          const __nv_bfloat16* rp = p.residual + z * p.bs_res + static_cast<long long>(row) * p.ldr + nc;
+          if (full && (p.ldr % 8 == 0)) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 b = *reinterpret_cast<const uint4*>(rp + q * 8);
+              const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                v[q * 8 + e * 2] += bf16_lo(bw[e]);
+                v[q * 8 + e * 2 + 1] += bf16_hi(bw[e]);
+              }
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (nc + j < p.N) v[j] += __bfloat162float(rp[j]);
+          }
+        }
+        if (p.epi == EPI_DGELU) {
+          const __nv_bfloat16* ap = p.aux + z * p.bs_aux + static_cast<long long>(row) * p.ldaux + nc;
+          if (full && (p.ldaux % 8 == 0)) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 b = *reinterpret_cast<const uint4*>(ap + q * 8);
+              const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                v[q * 8 + e * 2] *= dgelu_erf(bf16_lo(bw[e]));
+                v[q * 8 + e * 2 + 1] *= dgelu_erf(bf16_hi(bw[e]));
+              }
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (nc + j < p.N) v[j] *= dgelu_erf(__bfloat162float(ap[j]));
+          }
+        }
+        __nv_bfloat16* o =
+            reinterpret_cast<__nv_bfloat16*>(p.out) + z * p.bs_out + static_cast<long long>(row) * p.ldo + nc;
+        if (vec) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 u;
+            u.x = pack_bf16(v[q * 8], v[q * 8 + 1]);
+            u.y = pack_bf16(v[q * 8 + 2], v[q * 8 + 3]);
+            u.z = pack_bf16(v[q * 8 + 4], v[q * 8 + 5]);
+            u.w = pack_bf16(v[q * 8 + 6], v[q * 8 + 7]);
+            reinterpret_cast<uint4*>(o)[q] = u;
+          }
+        } else {
+          for (int j = 0; j < 32; ++j)
+            if (nc + j < p.N) o[j] = __float2bfloat16(v[j]);
+        }
+        if (p.epi == EPI_GELU) {
+          // second output: GELU of the (bf16-rounded) pre-activation that was just stored
+          __nv_bfloat16* o2 = p.out2 + z * p.bs_out2 + static_cast<long long>(row) * p.ldo2 + nc;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = gelu_erf(__bfloat162float(__float2bfloat16(v[j])));
+          if (full && (p.ldo2 % 8 == 0)) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 u;
+              u.x = pack_bf16(v[q * 8], v[q * 8 + 1]);
+              u.y = pack_bf16(v[q * 8 + 2], v[q * 8 + 3]);
+              u.z = pack_bf16(v[q * 8 + 4], v[q * 8 + 5]);
+              u.w = pack_bf16(v[q * 8 + 6], v[q * 8 + 7]);
+              reinterpret_cast<uint4*>(o2)[q] = u;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (nc + j < p.N) o2[j] = __float2bfloat16(v[j]);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+int g_num_sms = 0;
+int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const DevParams& p, int grid, cudaStream_t stream) {
+  using L = SmemLayout<BN>;
+  static bool configured = false;
+  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess) return -3;
+    configured = true;
+  }
+  kern<<<grid, kThreads, L::kTotal, stream>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace
+
+// Build a 3-D bf16 tensor map {inner, rows, batch} with a {64, box_rows, 1} box and 128B swizzle.
+int db200_make_tmap_bf16(CUtensorMap* out, const void* ptr, long long inner, long long rows, long long batch,
+                         long long row_stride_elems, long long batch_stride_elems, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows),
+                        static_cast<cuuint64_t>(batch)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_stride_elems) * 2,
+                           static_cast<cuuint64_t>(batch > 1 ? batch_stride_elems : row_stride_elems * rows) * 2};
+  cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+extern "C" int db200_gemm_bf16(const GemmArgs* a, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0 || a->batch <= 0) return 0;
+  // TMA needs 16-byte aligned bases and strides.
+  if ((reinterpret_cast<uintptr_t>(a->A) & 15) || (reinterpret_cast<uintptr_t>(a->B) & 15) || (a->lda % 8) ||
+      (a->ldb % 8) || (a->bs_a % 8) || (a->bs_b % 8))
+    return -10;
+  const int BN = (a->N > 128) ? 256 : 128;
+  DevParams p{};
+  p.M = a->M; p.N = a->N; p.K = a->K;
+  p.tiles_m = (a->M + BM - 1) / BM;
+  p.tiles_n = (a->N + BN - 1) / BN;
+  p.batch = a->batch;
+  p.kb_total = (a->K + BK - 1) / BK;
+  p.alpha = a->alpha;
+  p.epi = a->epi;
+  p.out_f32 = a->out_f32;
+  p.accumulate = a->accumulate;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(a->bias);
+  p.residual = reinterpret_cast<const __nv_bfloat16*>(a->residual);
+  p.aux = reinterpret_cast<const __nv_bfloat16*>(a->aux);
+  p.out = a->out;
+  p.out2 = reinterpret_cast<__nv_bfloat16*>(a->out2);
+  p.ldo = a->ldo; p.ldr = a->ldr; p.ldaux = a->ldaux; p.ldo2 = a->ldo2;
+  p.bs_out = a->bs_out; p.bs_res = a->bs_res; p.bs_aux = a->bs_aux; p.bs_out2 = a->bs_out2; p.bs_bias = a->bs_bias;
+  p.status = db200_status_ptr();
+  if (p.epi == EPI_GELU && (p.out_f32 || !p.out2)) return -11;
+  if (p.epi == EPI_DGELU && (p.out_f32 || !p.aux)) return -11;
+
+  const int tiles = p.tiles_m * p.tiles_n * p.batch;
+  int splits = 1;
+  if (a->out_f32 && a->allow_split_k && a->residual == nullptr) {
+    // Fill the machine when the output grid is small (weight gradients: K = tokens).
+    const int sms = num_sms();
+    while (tiles * splits * 2 <= sms && p.kb_total / (splits * 2) >= 4) splits *= 2;
+    if (tiles * splits < sms && p.kb_total / (splits * 2) >= 8) splits *= 2;
+  }
+  p.splits = splits;
+  if (splits > 1 && !p.accumulate) {
+    // partial sums are combined with red.add, so the destination has to start at zero
+    for (int z = 0; z < a->batch; ++z) {
+      if (cudaMemset2DAsync(reinterpret_cast<float*>(a->out) + z * a->bs_out, a->ldo * sizeof(float), 0,
+                            static_cast<size_t>(a->N) * sizeof(float), a->M, stream) != cudaSuccess)
+        return -5;
+    }
+  }
+
+  CUtensorMap ta, tb;
+  int rc;
+  if (!a->a_mn) rc = db200_make_tmap_bf16(&ta, a->A, a->K, a->M, a->batch, a->lda, a->bs_a, BM);
+  else          rc = db200_make_tmap_bf16(&ta, a->A, a->M, a->K, a->batch, a->lda, a->bs_a, BK);
+  if (rc) return rc;
+  if (!a->b_mn) rc = db200_make_tmap_bf16(&tb, a->B, a->K, a->N, a->batch, a->ldb, a->bs_b, 128);
+  else          rc = db200_make_tmap_bf16(&tb, a->B, a->N, a->K, a->batch, a->ldb, a->bs_b, BK);
+  if (rc) return rc;
+
+  const int grid = min(tiles * splits, num_sms());
+#define DISPATCH(BN_, AM_, BM_) return launch<BN_, AM_, BM_>(ta, tb, p, grid, stream)
+  if (BN == 256) {
+    if (!a->a_mn && !a->b_mn) DISPATCH(256, false, false);
+    if (!a->a_mn && a->b_mn) DISPATCH(256, false, true);
+    if (a->a_mn && !a->b_mn) DISPATCH(256, true, false);
+    DISPATCH(256, true, true);
+  } else {
+    if (!a->a_mn && !a->b_mn) DISPATCH(128, false, false);
+    if (!a->a_mn && a->b_mn) DISPATCH(128, false, true);
+    if (a->a_mn && !a->b_mn) DISPATCH(128, true, false);
+    DISPATCH(128, true, true);
+  }
+#undef DISPATCH
+}

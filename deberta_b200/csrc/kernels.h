@@ -1,0 +1,38 @@
+// C ABI of the sm_100a kernel library. Every launcher takes raw device pointers and a
+// CUDA stream handle and returns 0 on success or a negative code when the arguments
+// are rejected before any launch. The Python bindings mirror these structs with ctypes.
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ----- status word written by kernels whose bounded waits ran out -------------------
+int* db200_status_ptr(void);          // device address of the status word (lazily allocated)
+int db200_status_read_and_clear(void);  // synchronises the device; 0 = no error recorded
+
+// ----- GEMM ---------------------------------------------------------------------------
+enum { EPI_NONE = 0, EPI_GELU = 1, EPI_DGELU = 2 };
+
+typedef struct GemmArgs {
+  const void* A;     // bf16
+  const void* B;     // bf16
+  void* out;         // bf16 or fp32 (out_f32)
+  void* out2;        // bf16, EPI_GELU: gelu(out)
+  const void* bias;  // bf16 [N] or null
+  const void* residual;  // bf16 [M, N] or null (added before the activation derivative)
+  const void* aux;       // bf16 [M, N] pre-activation for EPI_DGELU
+  int M, N, K, batch;
+  int a_mn, b_mn;    // operand majors, see gemm.cu
+  int epi, out_f32, accumulate, allow_split_k;
+  float alpha;
+  long long lda, ldb, ldo, ldo2, ldr, ldaux;                       // leading dims (elements)
+  long long bs_a, bs_b, bs_out, bs_out2, bs_res, bs_aux, bs_bias;  // batch strides (elements)
+} GemmArgs;
+
+int db200_gemm_bf16(const GemmArgs* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

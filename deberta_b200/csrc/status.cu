@@ -1,0 +1,34 @@
+// Device-side status word: kernels record here (first error wins) when a bounded wait
+// ran out, instead of trapping or spinning forever. The host reads it after a sync.
+#include "kernels.h"
+
+#include <cuda_runtime.h>
+
+namespace {
+__device__ int g_status_word = 0;
+constexpr int kMaxDevices = 16;
+int* g_status_addr[kMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" int* db200_status_ptr(void) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  if (!g_status_addr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+    g_status_addr[dev] = static_cast<int*>(p);
+  }
+  return g_status_addr[dev];
+}
+
+extern "C" int db200_status_read_and_clear(void) {
+  int* p = db200_status_ptr();
+  if (!p) return -1;
+  int v = 0;
+  if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
+  if (v != 0) {
+    int zero = 0;
+    cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice);
+  }
+  return v;
+}

@@ -1,0 +1,95 @@
+"""tcgen05 GEMM kernel vs. the fp32 PyTorch statement of the same contract."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from deberta_b200.ops import _lib
+from deberta_b200.ops.gemm import EPI_DGELU, EPI_GELU, gemm, gemm_reference
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda", dtype=torch.float32) * scale).to(torch.bfloat16)
+
+
+def _close(got, ref, tol=2e-2):
+    got = got.float()
+    ref = ref.float()
+    err = (got - ref).abs().max().item()
+    denom = ref.abs().max().item() + 1e-6
+    assert err / denom < tol, f"rel err {err / denom:.4g} (abs {err:.4g})"
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (304, 264, 136), (1024, 768, 768), (640, 96, 2048)])
+def test_gemm_majors(a_mn, b_mn, M, N, K):
+    torch.manual_seed(0)
+    a = _rand(K, M) if a_mn else _rand(M, K)
+    b = _rand(K, N) if b_mn else _rand(N, K)
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    _lib.check_status()
+    ref = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    _close(out, ref)
+
+
+def test_gemm_bias_residual_gelu():
+    torch.manual_seed(1)
+    M, N, K = 520, 3072, 768
+    a, w = _rand(M, K), _rand(N, K, scale=0.05)
+    bias, res = _rand(N), _rand(M, N)
+    out = gemm(a, w, bias=bias, residual=res)
+    _close(out, gemm_reference(a, w, bias=bias, residual=res, out_dtype=torch.float32))
+    z, act = gemm(a, w, bias=bias, epi=EPI_GELU)
+    zr, ar = gemm_reference(a, w, bias=bias, epi=EPI_GELU)
+    _close(z, zr)
+    _close(act, ar)
+    dz = gemm(a, w, epi=EPI_DGELU, aux=z)
+    _close(dz, gemm_reference(a, w, epi=EPI_DGELU, aux=z, out_dtype=torch.float32))
+    _lib.check_status()
+
+
+def test_gemm_fp32_accumulate_split_k():
+    torch.manual_seed(2)
+    T, O, I = 4096, 768, 768
+    dy, x = _rand(T, O, scale=0.1), _rand(T, I)
+    grad = torch.ones(O, I, device="cuda", dtype=torch.float32)
+    gemm(dy, x, a_mn=True, b_mn=True, out=grad, accumulate=True)
+    ref = 1.0 + dy.float().t() @ x.float()
+    _close(grad, ref, tol=5e-3)
+    fresh = gemm(dy, x, a_mn=True, b_mn=True, out_dtype=torch.float32)
+    _close(fresh, ref - 1.0, tol=5e-3)
+    _lib.check_status()
+
+
+def test_gemm_batched_strided():
+    torch.manual_seed(3)
+    B, T, H, d, P = 3, 256, 4, 64, 512
+    q = _rand(T, B * H * d).view(T, B, H * d)  # tokens x (batch of heads) with row stride
+    qh = q[:, 0, :].view(T, H, d).permute(1, 0, 2)  # [H, T, d], inner stride 1, ld = B*H*d
+    pos = _rand(P, H * d).view(P, H, d).permute(1, 0, 2)  # [H, P, d]
+    out = gemm(qh, pos)
+    ref = torch.einsum("htd,hpd->htp", qh.float(), pos.float())
+    _close(out, ref)
+    _lib.check_status()
+
+
+def test_gemm_speed_report():
+    """Not a pass/fail perf gate: prints achieved TFLOP/s next to cuBLAS for the log."""
+    M, N, K = 16384, 3072, 768
+    a, w = _rand(M, K), _rand(N, K, scale=0.05)
+    for fn, name in ((lambda: gemm(a, w), "tcgen05"), (lambda: a @ w.t(), "cublas")):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(10):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        ms = s.elapsed_time(e) / 10
+        print(f"\n[gemm {M}x{N}x{K}] {name}: {ms * 1e3:.1f} us, {2 * M * N * K / ms / 1e9:.1f} TFLOP/s")
+    _lib.check_status()
