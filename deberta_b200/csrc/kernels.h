@@ -33,6 +33,13 @@ typedef struct GemmArgs {
 
 int db200_gemm_bf16(const GemmArgs* args, void* stream);
 
+// ----- LayerNorm / RMSNorm (bf16 in/out, fp32 stats; row_keep: optional uint8 per-row multiplier) -----
+int db200_norm_fwd(const void* x, const void* gamma, const void* beta, const void* row_keep, void* y, float* mean,
+                   float* rstd, int rows, int H, float eps, int rms, void* stream);
+int db200_norm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+                   const void* row_keep, void* dx, float* dgamma, float* dbeta, int rows, int H, int rms,
+                   void* stream);
+
 #ifdef __cplusplus
 }
 #endif
