@@ -40,6 +40,12 @@ int db200_norm_bwd(const void* dy, const void* x, const void* gamma, const float
                    const void* row_keep, void* dx, float* dgamma, float* dbeta, int rows, int H, int rms,
                    void* stream);
 
+// ----- optimizer (flat fp32 ranges) ---------------------------------------------------------
+int db200_sumsq(const float* g, long long n, float* out_accum, void* stream);
+int db200_adamw(float* p, const float* g, float* m, float* v, void* shadow_bf16, long long n, float lr, float wd,
+                float b1, float b2, float eps, float inv_bc1, float inv_sqrt_bc2, const float* norm_sq,
+                float max_norm, float grad_scale, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

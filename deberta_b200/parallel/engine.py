@@ -1,0 +1,372 @@
+"""Flat-buffer training engine: parameter storage, gradient synchronisation and AdamW.
+
+This takes the place of ``accelerator.prepare`` + ``torch.optim.AdamW`` + DDP/FSDP of the
+reference (``training/entrypoint.py:531-566``, ``training/runtime.py:139-296``) with a
+layout chosen for a 180 GB GPU and NVSwitch:
+
+* every trainable parameter lives in ONE flat buffer per dtype role — fp32 master
+  weights, fp32 gradients, and (bf16 mode) the bf16 compute copy the kernels read.
+  ``param.data`` is a view of the compute buffer, ``param.main_grad`` a view of the
+  gradient buffer; weight-gradient GEMMs accumulate straight into it.
+* buffers are ordered generator-decay | generator-no-decay | discriminator-decay |
+  discriminator-no-decay, so each optimizer (and each phase of decoupled training)
+  owns one contiguous range: its gradient reduction is one collective over one range and
+  its update is one fused AdamW launch per decay group.
+* ``parallelism="ddp"`` all-reduces the range; ``"zero"`` (sharded optimizer state — what
+  FSDP full-shard buys on this model size, at a third of its traffic) reduce-scatters it,
+  updates the local shard and all-gathers the bf16 compute copy.
+* the clip coefficient and the non-finite guard are evaluated on the device inside the
+  AdamW kernel from the reduced squared norm, so a step needs no host synchronisation;
+  the host reads the norm afterwards (or a step later) for logging and LR back-off.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import math
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from deberta_b200.ops import _lib
+
+from .dist import DistContext
+
+__all__ = ["TrainEngine", "Segment", "OptimizerState", "partition_parameters", "param_order_digest"]
+
+_ALIGN = 64  # elements; keeps every parameter 128-byte (bf16) / 256-byte (fp32) aligned for TMA and vector IO
+
+
+def is_no_decay_param(name: str, param: torch.Tensor) -> bool:
+    """1-D biases, anything named like a norm, and all ≤1-D tensors skip weight decay (``runtime.py:35-52``).
+
+    Two-dimensional tensors called ``bias`` (the GDES embedding deltas) are decayed.
+    """
+    n = name.lower()
+    if n.endswith(".bias") and param.dim() <= 1:
+        return True
+    if any(k in n for k in ("layernorm", "layer_norm", "rmsnorm", "rms_norm")):
+        return True
+    return param.dim() <= 1
+
+
+def is_generator_param(name: str) -> bool:
+    return name.startswith(("generator.", "generator_lm_head.", "enhanced_mask_decoder."))
+
+
+GROUP_ORDER = ("gen_decay", "gen_no_decay", "disc_decay", "disc_no_decay")
+
+
+def partition_parameters(model: nn.Module) -> dict[str, list[tuple[str, nn.Parameter]]]:
+    """Trainable parameters in the four optimizer groups, each Parameter object once (``runtime.py:72-111``)."""
+    groups: dict[str, list[tuple[str, nn.Parameter]]] = {k: [] for k in GROUP_ORDER}
+    seen: set[int] = set()
+    for name, p in model.named_parameters():
+        if not p.requires_grad or id(p) in seen:
+            continue
+        seen.add(id(p))
+        key = ("gen" if is_generator_param(name) else "disc") + ("_no_decay" if is_no_decay_param(name, p) else "_decay")
+        groups[key].append((name, p))
+    return groups
+
+
+def param_order_digest(model: nn.Module, owners: tuple[str, ...] = ("gen", "disc")) -> str:
+    """Digest of parameter names in optimizer order; guards Adam state against silent re-mapping on resume."""
+    parts = partition_parameters(model)
+    names = [n for key in GROUP_ORDER if key.split("_")[0] in owners for n, _ in parts[key]]
+    return hashlib.sha256("\n".join(names).encode()).hexdigest()[:16]
+
+
+@dataclass
+class Segment:
+    group: str          # gen_decay | gen_no_decay | disc_decay | disc_no_decay
+    start: int
+    end: int
+    weight_decay: float
+    base_lr: float
+
+
+@dataclass
+class OptimizerState:
+    """One optimizer = one contiguous range of the flat buffers plus its moments."""
+
+    name: str
+    start: int
+    end: int
+    segments: list[Segment]
+    betas: tuple[float, float]
+    eps: float
+    step: int = 0
+    shard: tuple[int, int] = (0, 0)  # range (absolute) whose moments this rank holds
+    exp_avg: torch.Tensor | None = None
+    exp_avg_sq: torch.Tensor | None = None
+    norm_sq: torch.Tensor | None = None  # device float: squared global grad norm of the last sync
+    names: list[str] = field(default_factory=list)
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class TrainEngine:
+    """Owns parameter/gradient/optimizer memory of one model replica on one device."""
+
+    def __init__(self, model: nn.Module, ctx: DistContext, *, compute_dtype: torch.dtype = torch.float32,
+                 parallelism: str = "ddp", decoupled: bool = True, lr_generator: float = 5e-4,
+                 lr_discriminator: float = 5e-4, weight_decay: float = 0.01, betas: tuple[float, float] = (0.9, 0.999),
+                 eps: float = 1e-8) -> None:
+        if parallelism not in ("ddp", "zero"):
+            raise ValueError("parallelism must be 'ddp' or 'zero'")
+        self.model, self.ctx, self.parallelism = model, ctx, parallelism
+        self.compute_dtype = compute_dtype
+        self.device = ctx.device
+        self.use_kernels = self.device.type == "cuda"
+        model.to(self.device)
+        world = ctx.world_size
+        parts = partition_parameters(model)
+        # ---- layout -----------------------------------------------------------------------
+        self.layout: dict[str, tuple[int, int, torch.Size]] = {}
+        segs: list[Segment] = []
+        bounds: dict[str, tuple[int, int]] = {}
+        cursor = 0
+        for owner in ("gen", "disc"):
+            owner_start = cursor
+            for key in (f"{owner}_decay", f"{owner}_no_decay"):
+                seg_start = cursor
+                for name, p in parts[key]:
+                    self.layout[name] = (cursor, p.numel(), p.shape)
+                    cursor = _round_up(cursor + p.numel(), _ALIGN)
+                wd = weight_decay if key.endswith("_decay") and not key.endswith("no_decay") else 0.0
+                segs.append(Segment(key, seg_start, cursor, wd, lr_generator if owner == "gen" else lr_discriminator))
+            cursor = _round_up(cursor, _ALIGN * world)  # every optimizer range splits evenly into aligned shards
+            if decoupled and (cursor - owner_start) % (world * _ALIGN):
+                raise AssertionError("optimizer range is not shard-aligned")
+            bounds[owner] = (owner_start, cursor)
+        total = cursor
+        self.total_elems = total
+        dev = self.device
+        self.master = torch.zeros(total, dtype=torch.float32, device=dev)
+        self.grads = torch.zeros(total, dtype=torch.float32, device=dev)
+        self.compute = torch.zeros(total, dtype=compute_dtype, device=dev) if compute_dtype != torch.float32 else None
+        self._params: dict[str, nn.Parameter] = {}
+        for key in GROUP_ORDER:
+            for name, p in parts[key]:
+                off, n, shape = self.layout[name]
+                self.master[off : off + n].copy_(p.data.reshape(-1))
+                gview = self.grads[off : off + n].view(shape)
+                if self.compute is not None:
+                    cview = self.compute[off : off + n]
+                    cview.copy_(p.data.reshape(-1))
+                    p.data = cview.view(shape)
+                    p.grad = None
+                    p.main_grad = gview
+                    p.register_post_accumulate_grad_hook(_fold_grad_into_main)
+                else:
+                    p.data = self.master[off : off + n].view(shape)
+                    p.grad = gview
+                self._params[name] = p
+        self._alias_gdes_bases()
+        for p in model.parameters():  # remaining frozen parameters follow the compute dtype
+            if not p.requires_grad and p.is_floating_point() and p.dtype != compute_dtype and self.compute is not None:
+                p.data = p.data.to(compute_dtype)
+        # ---- optimizers ---------------------------------------------------------------------
+        self.optimizers: dict[str, OptimizerState] = {}
+        specs = ([("generator", "gen"), ("discriminator", "disc")] if decoupled else [("all", None)])
+        for opt_name, owner in specs:
+            if owner is None:
+                start, end = 0, total
+                my = segs
+            else:
+                start, end = bounds[owner]
+                my = [s for s in segs if s.group.startswith(owner)]
+            if parallelism == "zero" and world > 1:
+                per = (end - start) // world
+                shard = (start + ctx.rank * per, start + (ctx.rank + 1) * per)
+            else:
+                shard = (start, end)
+            n = shard[1] - shard[0]
+            names = [nm for s in my for nm, _ in parts[s.group]]
+            self.optimizers[opt_name] = OptimizerState(
+                opt_name, start, end, my, betas, eps, 0, shard,
+                torch.zeros(n, dtype=torch.float32, device=dev), torch.zeros(n, dtype=torch.float32, device=dev),
+                torch.zeros(1, dtype=torch.float32, device=dev), names,
+            )
+
+    # ---- GDES ---------------------------------------------------------------------------------
+    def _alias_gdes_bases(self) -> None:
+        """Point every frozen GDES ``base_weight`` at the generator table it mirrors.
+
+        The base is by definition a copy of the generator embedding refreshed after each
+        generator step, and nothing reads it between that step and the refresh; sharing
+        the storage makes the refresh (and under sharding its all-gather) disappear.
+        """
+        for _attr, disc_mod, gen_mod in getattr(self.model, "_gdes_synced_embeddings", []):
+            disc_mod.base_weight.data = gen_mod.weight.data
+
+    # ---- gradients ------------------------------------------------------------------------------
+    def zero_grad(self, opt_name: str | None = None) -> None:
+        if opt_name is None:
+            self.grads.zero_()
+        else:
+            o = self.optimizers[opt_name]
+            self.grads[o.start : o.end].zero_()
+
+    def sync_grads(self, opt_name: str) -> torch.Tensor:
+        """Average the optimizer's gradient range over ranks; returns the squared global norm (device scalar)."""
+        o = self.optimizers[opt_name]
+        world = self.ctx.world_size
+        g = self.grads[o.start : o.end]
+        if world > 1:
+            avg = dist.ReduceOp.AVG if self.ctx.backend == "nccl" else dist.ReduceOp.SUM
+            if self.parallelism == "zero":
+                out = self.grads[o.shard[0] : o.shard[1]]
+                if self.ctx.backend == "nccl":
+                    dist.reduce_scatter_tensor(out, g, op=avg)
+                else:  # gloo has no reduce-scatter: all-reduce and keep the local shard
+                    dist.all_reduce(g, op=avg)
+            else:
+                dist.all_reduce(g, op=avg)
+            if avg == dist.ReduceOp.SUM:
+                (self.grads[o.shard[0] : o.shard[1]] if self.parallelism == "zero" else g).mul_(1.0 / world)
+        local = self.grads[o.shard[0] : o.shard[1]]
+        o.norm_sq.zero_()
+        if self.use_kernels:
+            _lib.call("db200_sumsq", _lib.ptr(local), ctypes.c_longlong(local.numel()), _lib.ptr(o.norm_sq),
+                      _lib.stream_ptr())
+        else:
+            o.norm_sq.add_(local.double().pow(2).sum().float())
+        if world > 1 and self.parallelism == "zero":
+            dist.all_reduce(o.norm_sq, op=dist.ReduceOp.SUM)
+        return o.norm_sq
+
+    def grad_norm(self, opt_name: str) -> torch.Tensor:
+        return self.optimizers[opt_name].norm_sq.sqrt().squeeze(0)
+
+    # ---- update ---------------------------------------------------------------------------------
+    def step(self, opt_name: str, *, lr_scale: float = 1.0, max_grad_norm: float = 0.0) -> None:
+        """AdamW over the optimizer's (local shard of the) range, clip + finite guard on the device."""
+        o = self.optimizers[opt_name]
+        o.step += 1
+        b1, b2 = o.betas
+        inv_bc1 = 1.0 / (1.0 - b1 ** o.step)
+        inv_sqrt_bc2 = 1.0 / math.sqrt(1.0 - b2 ** o.step)
+        s0, s1 = o.shard
+        skipped = False
+        if not self.use_kernels:
+            norm = float(o.norm_sq.sqrt())
+            if not math.isfinite(norm):
+                skipped = True
+            coef = min(1.0, max_grad_norm / (norm + 1e-6)) if (max_grad_norm > 0 and not skipped) else 1.0
+        for seg in o.segments:
+            a, b = max(seg.start, s0), min(seg.end, s1)
+            if a >= b:
+                continue
+            lr = seg.base_lr * lr_scale
+            p, g = self.master[a:b], self.grads[a:b]
+            m, v = o.exp_avg[a - s0 : b - s0], o.exp_avg_sq[a - s0 : b - s0]
+            shadow = self.compute[a:b] if self.compute is not None else None
+            if self.use_kernels:
+                c_f = ctypes.c_float
+                _lib.call("db200_adamw", _lib.ptr(p), _lib.ptr(g), _lib.ptr(m), _lib.ptr(v), _lib.ptr(shadow),
+                          ctypes.c_longlong(b - a), c_f(lr), c_f(seg.weight_decay), c_f(b1), c_f(b2), c_f(o.eps),
+                          c_f(inv_bc1), c_f(inv_sqrt_bc2), _lib.ptr(o.norm_sq), c_f(max_grad_norm), c_f(1.0),
+                          _lib.stream_ptr())
+            elif not skipped:
+                gg = g * coef if coef != 1.0 else g
+                p.mul_(1.0 - lr * seg.weight_decay)
+                m.lerp_(gg, 1.0 - b1)
+                v.mul_(b2).addcmul_(gg, gg, value=1.0 - b2)
+                denom = (v.sqrt() * inv_sqrt_bc2).add_(o.eps)
+                p.addcdiv_(m, denom, value=-lr * inv_bc1)
+                if shadow is not None:
+                    shadow.copy_(p)
+        if skipped:
+            o.step -= 1
+        if self.ctx.world_size > 1 and self.parallelism == "zero":
+            buf = self.compute if self.compute is not None else self.master
+            dist.all_gather_into_tensor(buf[o.start : o.end], buf[s0:s1])
+            if self.compute is not None:
+                pass  # masters stay sharded: only the owner's slice is authoritative
+
+    def reset_optimizer_state(self, opt_name: str | None = None) -> None:
+        for name, o in self.optimizers.items():
+            if opt_name in (None, name):
+                o.exp_avg.zero_()
+                o.exp_avg_sq.zero_()
+                o.step = 0
+
+    # ---- state ----------------------------------------------------------------------------------
+    def gather_master(self) -> None:
+        """Make every rank's fp32 master buffer complete (needed before saving under sharded optimizers)."""
+        if self.ctx.world_size > 1 and self.parallelism == "zero":
+            for o in self.optimizers.values():
+                dist.all_gather_into_tensor(self.master[o.start : o.end], self.master[o.shard[0] : o.shard[1]].clone())
+
+    def model_state_dict(self) -> dict[str, torch.Tensor]:
+        """``model.state_dict()`` with trainable tensors replaced by their fp32 masters (CPU copies)."""
+        self.gather_master()
+        out: dict[str, torch.Tensor] = {}
+        alias = {id(p): n for n, p in self._params.items()}
+        for key, t in self.model.state_dict(keep_vars=True).items():
+            name = alias.get(id(t))
+            if name is not None:
+                off, n, shape = self.layout[name]
+                out[key] = self.master[off : off + n].view(shape).detach().cpu().clone()
+            else:
+                out[key] = t.detach().float().cpu().clone() if t.is_floating_point() else t.detach().cpu().clone()
+        # frozen GDES bases mirror the generator masters at full precision
+        for attr, disc_mod, gen_mod in getattr(self.model, "_gdes_synced_embeddings", []):
+            gname = alias.get(id(gen_mod.weight))
+            for key, t in self.model.state_dict(keep_vars=True).items():
+                if t is disc_mod.base_weight and gname is not None:
+                    off, n, shape = self.layout[gname]
+                    out[key] = self.master[off : off + n].view(shape).detach().cpu().clone()
+        return out
+
+    def load_model_state_dict(self, state: dict[str, torch.Tensor], strict: bool = True) -> None:
+        keys = self.model.state_dict(keep_vars=True)
+        missing = [k for k in keys if k not in state]
+        unexpected = [k for k in state if k not in keys]
+        if strict and (missing or unexpected):
+            raise RuntimeError(f"state dict mismatch: missing={missing[:5]} unexpected={unexpected[:5]}")
+        alias = {id(p): n for n, p in self._params.items()}
+        with torch.no_grad():
+            for key, t in keys.items():
+                if key not in state:
+                    continue
+                src = state[key].to(self.device)
+                name = alias.get(id(t))
+                if name is not None:
+                    off, n, _ = self.layout[name]
+                    self.master[off : off + n].copy_(src.reshape(-1).float())
+                    if self.compute is not None:
+                        self.compute[off : off + n].copy_(self.master[off : off + n])
+                elif any(t is m.base_weight for _, m, _ in getattr(self.model, "_gdes_synced_embeddings", [])):
+                    continue  # aliases of generator tables
+                else:
+                    t.data.copy_(src.to(t.dtype))
+
+    def optimizer_state_dict(self) -> dict[str, Any]:
+        return {name: {"step": o.step, "shard": list(o.shard), "range": [o.start, o.end], "names": list(o.names),
+                       "exp_avg": o.exp_avg.detach().cpu().clone(), "exp_avg_sq": o.exp_avg_sq.detach().cpu().clone()}
+                for name, o in self.optimizers.items()}
+
+    def load_optimizer_state_dict(self, state: dict[str, Any]) -> None:
+        for name, o in self.optimizers.items():
+            s = state[name]
+            if list(s["range"]) != [o.start, o.end] or list(s["shard"]) != list(o.shard) or list(s["names"]) != o.names:
+                raise RuntimeError(f"optimizer state for {name!r} does not match the current parameter layout")
+            o.step = int(s["step"])
+            o.exp_avg.copy_(s["exp_avg"].to(self.device))
+            o.exp_avg_sq.copy_(s["exp_avg_sq"].to(self.device))
+
+
+def _fold_grad_into_main(p: torch.Tensor) -> None:
+    """Autograd produced ``p.grad`` (ops without a fused weight-gradient path): add it to the fp32 buffer."""
+    if p.grad is not None:
+        p.main_grad.add_(p.grad)
+        p.grad = None
