@@ -1,0 +1,258 @@
+"""One optimizer step of RTD pretraining over a gradient-accumulation window.
+
+Semantics follow the hot loop of the reference (``training/entrypoint.py:1046-1884``):
+
+* decoupled (default): phase 1 runs the generator on every micro-batch, steps the generator
+  optimizer, refreshes the shared embeddings; phase 2 runs the discriminator on the cached
+  corrupted inputs and steps its optimizer. Coupled: one combined objective, one optimizer.
+* token-weighted accumulation (``loop_utils``), gradient clipping over the stepping optimizer's
+  parameters, schedulers advance on every window, a non-finite window is skipped with LR
+  back-off and periodic optimizer-state reset.
+
+What differs is *where* things happen: losses, token weights, the clip coefficient and the
+non-finite guard stay on the device, so the host never waits for the GPU inside a window; it
+learns the outcome of a step one window later from a pinned-memory copy. On CPU (tests, smoke
+runs) the same code resolves everything synchronously.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+
+from deberta_b200.models.mask_utils import AttnMask
+from deberta_b200.parallel.dist import DistContext
+from deberta_b200.parallel.engine import TrainEngine, param_order_digest
+
+from .loop_utils import (apply_nonfinite_recovery, count_input_tokens_for_batch, count_rtd_tokens_for_batch,
+                         micro_loss_scale, recover_lr_mult)
+from .schedulers import StepSchedule
+
+__all__ = ["Trainer", "WindowStats"]
+
+
+@dataclass
+class WindowStats:
+    """Device-side sums of one window; ``.item()`` them only when a log line is due."""
+
+    gen_loss_tokens: torch.Tensor   # Σ gen_loss_i · g_i
+    disc_loss_tokens: torch.Tensor  # Σ disc_loss_i · d_i
+    disc_acc_tokens: torch.Tensor   # Σ acc_i · d_i
+    disc_pos: torch.Tensor          # Σ positives
+    gen_tokens: float
+    disc_tokens: float
+    input_tokens: float
+    zero_gen_window: bool = False
+    zero_disc_window: bool = False
+    grad_norms: dict[str, torch.Tensor] = field(default_factory=dict)
+
+
+class _PendingOutcome:
+    """Squared grad norms of a finished step on their way to the host."""
+
+    def __init__(self, step: int, norms: dict[str, torch.Tensor], sync: bool) -> None:
+        self.step = step
+        self.names = list(norms)
+        stacked = torch.cat([norms[n].reshape(1) for n in self.names])
+        if stacked.is_cuda and not sync:
+            self.host = torch.empty(stacked.shape, dtype=stacked.dtype, pin_memory=True)
+            self.host.copy_(stacked, non_blocking=True)
+            self.event = torch.cuda.Event()
+            self.event.record()
+        else:
+            self.host = stacked.detach().cpu()
+            self.event = None
+
+    def resolve(self) -> dict[str, float]:
+        if self.event is not None:
+            self.event.synchronize()
+        return {n: math.sqrt(v) if (v == v and v >= 0) else float("nan")
+                for n, v in zip(self.names, self.host.tolist())}
+
+
+class Trainer:
+    """Holds the model/engine/schedules of a run and executes optimizer steps."""
+
+    def __init__(self, *, model: torch.nn.Module, engine: TrainEngine, ctx: DistContext, train_cfg: Any,
+                 optim_cfg: Any, pad_token_id: int | None, synchronous: bool | None = None) -> None:
+        self.model, self.engine, self.ctx = model, engine, ctx
+        self.train_cfg, self.optim_cfg = train_cfg, optim_cfg
+        self.pad_token_id = pad_token_id
+        self.decoupled = bool(train_cfg.decoupled_training)
+        self.ga_steps = int(train_cfg.gradient_accumulation_steps)
+        self.token_weighted = bool(train_cfg.token_weighted_gradient_accumulation)
+        o = train_cfg.objective
+        self.gen_w, self.disc_w = float(o.gen_loss_weight), float(o.disc_loss_weight)
+        self.temperature = float(o.sampling_temperature)
+        self.max_grad_norm = float(optim_cfg.max_grad_norm)
+        # CPU runs resolve step outcomes immediately; GPU runs defer them by one window
+        self.synchronous = (engine.device.type != "cuda") if synchronous is None else bool(synchronous)
+        kind, warm, total = optim_cfg.scheduler.type, int(optim_cfg.scheduler.warmup_steps), int(train_cfg.max_steps)
+        self.schedules = {name: StepSchedule(kind, warmup_steps=warm, total_steps=total,
+                                             base_lr=opt.segments[0].base_lr if opt.segments else 1.0)
+                          for name, opt in engine.optimizers.items()}
+        self.global_step = 0
+        self.lr_mult = 1.0
+        self.skip_streak = 0
+        self.skipped_steps = 0
+        self.consumed_micro_batches = 0
+        self._pending: _PendingOutcome | None = None
+        self.last_outcome: dict[str, float] = {}
+        self.on_nonfinite = None  # optional callback(step, norms) for debug artifacts
+        self.model.train()
+
+    # ---- helpers ----------------------------------------------------------------------------------
+    def optimizer_param_digest(self):
+        if self.decoupled:
+            return {"generator": param_order_digest(self.model, ("gen",)),
+                    "discriminator": param_order_digest(self.model, ("disc",))}
+        return param_order_digest(self.model)
+
+    def current_lrs(self) -> dict[str, float]:
+        return {n: s.get_last_lr()[0] * self.lr_mult for n, s in self.schedules.items()}
+
+    def _to_device(self, batch: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+        dev = self.engine.device
+        return {k: (v.to(dev, non_blocking=True) if isinstance(v, torch.Tensor) else v) for k, v in batch.items()}
+
+    @staticmethod
+    def _mask_of(batch: dict[str, torch.Tensor]):
+        if batch.get("doc_ids") is not None:
+            return AttnMask(doc_ids=batch["doc_ids"])
+        return batch.get("attention_mask")
+
+    def _window_denominators(self, gen_total: float, disc_total: float):
+        """(gen denom, disc denom, window has masked tokens anywhere) — device tensors when several ranks take part.
+
+        The denominators are the per-rank mean of the window token totals, floored at 1.
+        """
+        if self.ctx.world_size <= 1:
+            return max(gen_total, 1.0), max(disc_total, 1.0), gen_total > 0
+        t = torch.tensor([gen_total, disc_total], dtype=torch.float32, device=self.engine.device)
+        t = self.ctx.reduce(t, "mean")
+        return t[0].clamp(min=1.0), t[1].clamp(min=1.0), (t[0] > 0).to(torch.float32)
+
+    def _finish_optimizer(self, name: str, loss_guard: torch.Tensor | None) -> torch.Tensor:
+        """Reduce gradients, fold a non-finite loss into the norm, update, advance the schedule."""
+        eng = self.engine
+        norm_sq = eng.sync_grads(name)
+        if loss_guard is not None:
+            norm_sq.add_(torch.where(torch.isfinite(loss_guard), 0.0, float("inf")).to(norm_sq.dtype))
+        eng.step(name, lr_scale=self.schedules[name].scale() * self.lr_mult, max_grad_norm=self.max_grad_norm)
+        self.schedules[name].step()
+        return norm_sq.clone()
+
+    def _resolve_pending(self) -> None:
+        """Apply the host-side consequences of the previous step (LR back-off / recovery)."""
+        if self._pending is None:
+            return
+        norms = self._pending.resolve()
+        step = self._pending.step
+        self._pending = None
+        self.last_outcome = norms
+        if any(not math.isfinite(v) for v in norms.values()):
+            self.skip_streak += 1
+            self.skipped_steps += 1
+            self.lr_mult, reset = apply_nonfinite_recovery(lr_mult=self.lr_mult, skip_streak=self.skip_streak)
+            for name, v in norms.items():
+                if not math.isfinite(v) and self.engine.use_kernels:
+                    self.engine.optimizers[name].step -= 1  # the device guard skipped that update
+            if reset:
+                self.engine.reset_optimizer_state()
+            if self.on_nonfinite is not None:
+                self.on_nonfinite(step, norms)
+        else:
+            self.skip_streak = 0
+            self.lr_mult = recover_lr_mult(self.lr_mult)
+
+    # ---- one optimizer step -------------------------------------------------------------------------
+    def train_window(self, batches: list[dict[str, torch.Tensor]]) -> WindowStats:
+        """Run one gradient-accumulation window (``len(batches)`` micro-batches) and step the optimizer(s)."""
+        self._resolve_pending()
+        eng, model, dev = self.engine, self.model, self.engine.device
+        counts = [count_rtd_tokens_for_batch(b, pad_token_id=self.pad_token_id) for b in batches]
+        input_tokens = sum(count_input_tokens_for_batch(b) for b in batches)
+        gen_total, disc_total = sum(c[0] for c in counts), sum(c[1] for c in counts)
+        gen_den, disc_den, has_targets = self._window_denominators(gen_total, disc_total)
+        scale = micro_loss_scale(ga_steps=len(batches), token_weighted_ga=self.token_weighted)
+        zero = lambda: torch.zeros((), dtype=torch.float32, device=dev)  # noqa: E731
+        stats = WindowStats(zero(), zero(), zero(), zero(), gen_total, disc_total, input_tokens,
+                            zero_gen_window=gen_total <= 0, zero_disc_window=disc_total <= 0)
+        eng.zero_grad()
+        norms: dict[str, torch.Tensor] = {}
+        if self.decoupled:
+            cached = []
+            guard = zero()
+            for b, (g_i, d_i) in zip(batches, counts):
+                b = self._to_device(b)
+                mask = self._mask_of(b)
+                out = model(input_ids=b["input_ids"], attention_mask=mask, labels=b["labels"],
+                            token_type_ids=b.get("token_type_ids"), sampling_temperature=self.temperature,
+                            phase="generator")
+                w = (g_i / gen_den) if self.token_weighted else 1.0
+                (out.gen_loss_raw * (self.gen_w * scale) * w).backward()
+                guard = guard + out.gen_loss_raw.detach().float()
+                stats.gen_loss_tokens += out.gen_loss_raw.detach().float() * g_i
+                cached.append((b, mask, out.corrupted_input_ids, out.disc_labels, g_i, d_i))
+            norms["generator"] = self._finish_optimizer("generator", guard)
+            model.sync_discriminator_embeddings_from_generator()
+            eng.zero_grad("generator")
+            guard = zero()
+            for b, mask, corrupted, labels, g_i, d_i in cached:
+                out = model(input_ids=b["input_ids"], corrupted_input_ids=corrupted, disc_labels=labels,
+                            attention_mask=mask, token_type_ids=b.get("token_type_ids"), phase="discriminator")
+                w = (d_i / disc_den) if self.token_weighted else 1.0
+                w = w * (1.0 if g_i > 0 else 0.0) * has_targets  # micro-batches / windows without masked tokens carry no RTD signal
+                (out.disc_loss_raw * (self.disc_w * scale) * w).backward()
+                guard = guard + out.disc_loss_raw.detach().float()
+                stats.disc_loss_tokens += out.disc_loss_raw.detach().float() * d_i
+                stats.disc_acc_tokens += out.disc_accuracy.float() * d_i
+                stats.disc_pos += out.disc_positive_count.float()
+            norms["discriminator"] = self._finish_optimizer("discriminator", guard)
+            eng.zero_grad("discriminator")
+        else:
+            guard = zero()
+            for b, (g_i, d_i) in zip(batches, counts):
+                b = self._to_device(b)
+                out = model(input_ids=b["input_ids"], attention_mask=self._mask_of(b), labels=b["labels"],
+                            token_type_ids=b.get("token_type_ids"), sampling_temperature=self.temperature,
+                            gen_loss_weight=self.gen_w, disc_loss_weight=self.disc_w)
+                if self.token_weighted:
+                    obj = self.gen_w * (g_i / gen_den) * out.gen_loss_raw + self.disc_w * (d_i / disc_den) * out.disc_loss_raw
+                else:
+                    obj = out.loss
+                (obj * scale).backward()
+                guard = guard + obj.detach().float()
+                stats.gen_loss_tokens += out.gen_loss.float() * g_i
+                stats.disc_loss_tokens += out.disc_loss.float() * d_i
+                stats.disc_acc_tokens += out.disc_accuracy.float() * d_i
+                stats.disc_pos += out.disc_positive_count.float()
+            norms["all"] = self._finish_optimizer("all", guard)
+            model.sync_discriminator_embeddings_from_generator()
+            eng.zero_grad()
+        stats.grad_norms = {k: v.sqrt() for k, v in norms.items()}
+        self.global_step += 1
+        self.consumed_micro_batches += len(batches)
+        self._pending = _PendingOutcome(self.global_step, norms, self.synchronous)
+        if self.synchronous:
+            self._resolve_pending()
+        return stats
+
+    # ---- state ----------------------------------------------------------------------------------------
+    def state_dict(self) -> dict[str, Any]:
+        self._resolve_pending()
+        return {"global_step": self.global_step, "lr_mult": self.lr_mult, "skip_streak": self.skip_streak,
+                "consumed_micro_batches": self.consumed_micro_batches,
+                "schedules": {n: s.state_dict() for n, s in self.schedules.items()}}
+
+    def load_state_dict(self, state: dict[str, Any]) -> None:
+        self.global_step = int(state["global_step"])
+        self.lr_mult = float(state.get("lr_mult", 1.0))
+        self.skip_streak = int(state.get("skip_streak", 0))
+        self.consumed_micro_batches = int(state.get("consumed_micro_batches", 0))
+        for n, s in self.schedules.items():
+            if n in state.get("schedules", {}):
+                s.load_state_dict(state["schedules"][n])
