@@ -116,6 +116,11 @@ def check_status() -> None:
         raise KernelError(f"device status {code}: {STATUS_NAMES.get(code, 'unknown')}")
 
 
+LAUNCH_COUNT = 0
+
+
 def call(name: str, *args: Any) -> None:
+    global LAUNCH_COUNT
+    LAUNCH_COUNT += 1
     fn = getattr(lib(), name)
     check(int(fn(*args)), name)
