@@ -1,0 +1,779 @@
+// Flash-style attention for sm_100a with DeBERTa's disentangled position terms.
+//
+//   score[q,k] = ( Q[q]·K[k] + C2P[q, lut_c2p(q-k)] + P2C[k, lut_p2c(q-k)] ) / scale
+//
+// Q, K, V are token-major [B*S, ld] bf16 tensors (a head is a 64-column slice), read by TMA
+// into 128B-swizzled shared memory. Both GEMMs of a tile (Q·Kᵀ and P·V) run on tcgen05 with
+// accumulators in TMEM; one thread owns one query row (TMEM lane), so the softmax needs no
+// shuffles and the position gathers are plain per-row loads. C2P / P2C are the per-head
+// products of queries / keys with the projected relative-position table, computed once per
+// layer by the GEMM kernel; they are read through L1/L2 with the bucket lookup tables held in
+// shared memory. Masking: optional key-padding flags or packed-document ids; inactive queries
+// produce zero rows. The position terms are optional, which gives plain (rotary) attention.
+//
+// Forward : grid (q-tiles, heads, batch), 128 threads, 2 CTAs per SM overlap MMA and softmax.
+// Backward: grid (k-tiles, heads, batch); dK/dV accumulate in TMEM, dQ and the gradients of
+//           C2P / P2C are reduced into fp32 buffers with red.global.add.
+#include "tc05.cuh"
+#include "kernels.h"
+
+namespace {
+
+using namespace tc05;
+
+constexpr int kTile = 128;   // query rows and key rows per tile
+constexpr int kD = 64;       // head dimension
+constexpr int kTileBytes = kTile * kD * 2;  // 16 KB
+
+struct AttnDev {
+  int B, S, heads;
+  int span2;              // rows of the position tables (2 * att_span); 0 = no position terms
+  float scale_log2;       // log2(e) / scale
+  float inv_scale;        // 1 / scale
+  const __nv_bfloat16* c2p;   // [B*S, heads, span2] or null
+  const __nv_bfloat16* p2c;   // [B*S, heads, span2] or null
+  const unsigned short* lut_c2p;  // [2S-1], index q-k+S-1
+  const unsigned short* lut_p2c;
+  const unsigned char* key_keep;  // [B*S] or null
+  const int* doc_ids;             // [B*S] or null
+  const __nv_bfloat16* bias;      // [B, heads, S, ldb] pre-gathered position bias (unscaled) or null
+  long long ldb;
+  __nv_bfloat16* out;   // [B*S, ldo]
+  long long ldo;
+  float* lse;           // [B, heads, S] log2-domain log-sum-exp of the scaled scores
+  int* status;
+};
+
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ float bf16_elem(const uint4& u, int j) {
+  const uint32_t w = (j >> 1) == 0 ? u.x : (j >> 1) == 1 ? u.y : (j >> 1) == 2 ? u.z : u.w;
+  return (j & 1) ? bf16_hi(w) : bf16_lo(w);
+}
+
+// Write one row of a 128x128 bf16 tile (two 64-column, 128B-swizzled blocks) from fp32 values.
+__device__ __forceinline__ void store_row_bf16_sw128(uint8_t* tile, int row, const float* v) {
+#pragma unroll
+  for (int blk = 0; blk < 2; ++blk) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const float* s = v + blk * 64 + c * 8;
+      uint4 u;
+      u.x = pack_bf16(s[0], s[1]);
+      u.y = pack_bf16(s[2], s[3]);
+      u.z = pack_bf16(s[4], s[5]);
+      u.w = pack_bf16(s[6], s[7]);
+      *reinterpret_cast<uint4*>(tile + blk * kTileBytes + swz128(row, c)) = u;
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// forward
+// --------------------------------------------------------------------------------------------
+struct FwdSmem {
+  static constexpr int kQ = 0;
+  static constexpr int kK = kQ + kTileBytes;          // 2 buffers
+  static constexpr int kV = kK + 2 * kTileBytes;      // 1 buffer (keeps two CTAs resident per SM)
+  static constexpr int kP = kV + kTileBytes;          // 128x128 bf16
+  static constexpr int kBar = kP + 2 * kTileBytes;
+  static constexpr int kMeta = kBar + 128;            // 128 ints of key metadata
+  static constexpr int kLut = kMeta + 512;            // 2 * (2S-1) uint16
+  static int total(int S, bool pos) { return kLut + (pos ? 2 * (2 * S) * 2 : 0) + 1024; }
+};
+
+__global__ void __launch_bounds__(128, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const AttnDev p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + FwdSmem::kQ;
+  uint8_t* sK = smem + FwdSmem::kK;
+  uint8_t* sV = smem + FwdSmem::kV;
+  uint8_t* sP = smem + FwdSmem::kP;
+  uint64_t* bar_q = reinterpret_cast<uint64_t*>(smem + FwdSmem::kBar);
+  uint64_t* bar_k = bar_q + 1;  // [2]
+  uint64_t* bar_v = bar_q + 3;
+  uint64_t* bar_s = bar_q + 4;
+  uint64_t* bar_o = bar_q + 5;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 6);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* kmeta = reinterpret_cast<int*>(smem + FwdSmem::kMeta);
+  unsigned short* lutc = reinterpret_cast<unsigned short*>(smem + FwdSmem::kLut);
+  unsigned short* lutp = lutc + 2 * p.S;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int q0 = blockIdx.x * kTile;
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int S = p.S;
+  const bool pos = p.span2 > 0;
+  const int nkt = (S + kTile - 1) / kTile;
+
+  if (tid == 0) {
+    mbar_init(bar_q, 1);
+    mbar_init(&bar_k[0], 1);
+    mbar_init(&bar_k[1], 1);
+    mbar_init(bar_v, 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_o, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  if (pos) {
+    for (int i = tid; i < 2 * S - 1; i += 128) {
+      lutc[i] = p.lut_c2p[i];
+      lutp[i] = p.lut_p2c[i];
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_s = tmem_base;          // 128 columns: scores
+  const uint32_t t_o = tmem_base + 128;    // 64 columns: output accumulator
+  const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+
+  if (tid == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    mbar_expect_tx(bar_q, kTileBytes);
+    tma_load_3d(sQ, &tm_q, bar_q, h * kD, q0, b);
+    mbar_expect_tx(&bar_k[0], kTileBytes);
+    tma_load_3d(sK, &tm_k, &bar_k[0], h * kD, 0, b);
+    mbar_expect_tx(bar_v, kTileBytes);
+    tma_load_3d(sV, &tm_v, bar_v, h * kD, 0, b);
+  }
+
+  const int q = q0 + tid;
+  const bool q_valid = q < S;
+  const long long tq = static_cast<long long>(b) * S + (q_valid ? q : 0);
+  int q_doc = 1;
+  bool q_live = q_valid;
+  if (q_valid && p.key_keep) q_live = p.key_keep[tq] != 0;
+  if (q_valid && p.doc_ids) {
+    q_doc = p.doc_ids[tq];
+    q_live = q_doc != 0;
+  }
+  const long long pos_row = static_cast<long long>(p.heads) * p.span2;
+  const __nv_bfloat16* c2p_row = p.c2p ? p.c2p + tq * pos_row + static_cast<long long>(h) * p.span2 : nullptr;
+
+  const uint4* bias_row = p.bias ? reinterpret_cast<const uint4*>(
+                                       p.bias + ((static_cast<long long>(b) * p.heads + h) * S + (q_valid ? q : 0)) * p.ldb)
+                                 : nullptr;
+
+  constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+  constexpr uint32_t idesc_o = make_idesc_bf16(128, 64, false, true);
+  bool ok = true;
+
+  // first score tile
+  if (tid == 0) {
+    ok = mbar_wait(bar_q, 0, abort_flag, p.status, kErrFullWait) &&
+         mbar_wait(&bar_k[0], 0, abort_flag, p.status, kErrFullWait);
+    if (ok) {
+      tc_fence_after();
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks)
+        umma_bf16(t_s, make_smem_desc(smem_u32(sQ) + ks * 32, 16, 1024), make_smem_desc(smem_u32(sK) + ks * 32, 16, 1024),
+                  idesc_s, ks > 0);
+    }
+    umma_commit(bar_s);
+  }
+
+  float m_run = -INFINITY, l_run = 0.f;
+  for (int j = 0; j < nkt; ++j) {
+    const int k0 = j * kTile;
+    {  // key metadata of this tile: 0 = masked, otherwise doc id (or 1)
+      const int kk = k0 + tid;
+      int meta = 0;
+      if (kk < S) {
+        const long long tk = static_cast<long long>(b) * S + kk;
+        meta = 1;
+        if (p.key_keep) meta = p.key_keep[tk] ? 1 : 0;
+        if (p.doc_ids) meta = p.doc_ids[tk];
+      }
+      kmeta[tid] = meta;
+    }
+    __syncthreads();
+    if (!mbar_wait(bar_s, j & 1, abort_flag, p.status, kErrAccFullWait)) { ok = false; break; }
+    tc_fence_after();
+
+    float s[128];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(t_s + lane_addr + c * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]);
+    }
+    float tmax = -INFINITY;
+    {
+      const int dbase = q - k0 + S - 1;  // lut index for k = k0
+      uint4 bvec = make_uint4(0, 0, 0, 0);
+      const __nv_bfloat16* p2c_base =
+          p.p2c ? p.p2c + (static_cast<long long>(b) * S + k0) * pos_row + static_cast<long long>(h) * p.span2 : nullptr;
+#pragma unroll
+      for (int k = 0; k < 128; ++k) {
+        const int meta = kmeta[k];
+        bool keep = meta != 0;
+        if (p.doc_ids) keep = keep && (meta == q_doc);
+        float v = s[k];
+        if (bias_row) {
+          if ((k & 7) == 0) bvec = __ldg(bias_row + ((k0 + k) >> 3));
+          v += bf16_elem(bvec, k & 7);
+        } else if (pos && keep && q_valid) {
+          const int di = dbase - k;
+          if (c2p_row) v += __bfloat162float(c2p_row[lutc[di]]);
+          if (p2c_base) v += __bfloat162float(p2c_base[static_cast<long long>(k) * pos_row + lutp[di]]);
+        }
+        v = keep ? v * p.scale_log2 : -INFINITY;
+        s[k] = v;
+        tmax = fmaxf(tmax, v);
+      }
+    }
+    const float m_new = fmaxf(m_run, tmax);
+    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+    const float alpha = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_use);
+    float lsum = 0.f;
+#pragma unroll
+    for (int k = 0; k < 128; ++k) {
+      s[k] = ex2(s[k] - m_use);
+      lsum += s[k];
+    }
+    l_run = l_run * alpha + lsum;
+    m_run = m_new;
+
+    if (j > 0) {
+      if (!mbar_wait(bar_o, (j - 1) & 1, abort_flag, p.status, kErrAccFullWait)) { ok = false; break; }
+      tc_fence_after();
+      // rescale the running output when any row of this warp raised its maximum
+      if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_o + lane_addr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st_32x32b_x32(t_o + lane_addr + c * 32, r);
+        }
+        tmem_st_wait();
+      }
+    }
+    if (tid == 0) {
+      if (j > 0) {  // P·V of tile j-1 retired: its V tile can be replaced by this tile's
+        mbar_expect_tx(bar_v, kTileBytes);
+        tma_load_3d(sV, &tm_v, bar_v, h * kD, k0, b);
+      }
+      if (j + 1 < nkt) {  // the other K buffer was last read by the scores of tile j-1
+        const int nb = (j + 1) & 1;
+        mbar_expect_tx(&bar_k[nb], kTileBytes);
+        tma_load_3d(sK + nb * kTileBytes, &tm_k, &bar_k[nb], h * kD, k0 + kTile, b);
+      }
+    }
+    store_row_bf16_sw128(sP, tid, s);
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      const bool v_ok = mbar_wait(bar_v, j & 1, abort_flag, p.status, kErrFullWait);
+      tc_fence_after();
+      const uint32_t pv = smem_u32(sV);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        if (!v_ok) break;
+        umma_bf16(t_o, make_smem_desc(smem_u32(sP) + (ks >> 2) * kTileBytes + (ks & 3) * 32, 16, 1024),
+                  make_smem_desc(pv + ks * 2048, 8192, 1024), idesc_o, (j > 0) || (ks > 0));
+      }
+      umma_commit(bar_o);
+      if (j + 1 < nkt) {
+        const int nb = (j + 1) & 1;
+        if (mbar_wait(&bar_k[nb], ((j + 1) >> 1) & 1, abort_flag, p.status, kErrFullWait)) {
+          tc_fence_after();
+          const uint32_t kb = smem_u32(sK + nb * kTileBytes);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_bf16(t_s, make_smem_desc(smem_u32(sQ) + ks * 32, 16, 1024), make_smem_desc(kb + ks * 32, 16, 1024),
+                      idesc_s, ks > 0);
+        }
+        umma_commit(bar_s);
+      }
+    }
+  }
+
+  if (ok && mbar_wait(bar_o, (nkt - 1) & 1, abort_flag, p.status, kErrAccFullWait)) {
+    tc_fence_after();
+    const float inv = (q_live && l_run > 0.f) ? 1.f / l_run : 0.f;
+    __nv_bfloat16* o = p.out + tq * p.ldo + h * kD;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(t_o + lane_addr + c * 32, r);
+      tmem_ld_wait();
+      if (q_valid) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 u;
+          u.x = pack_bf16(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
+          u.y = pack_bf16(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
+          u.z = pack_bf16(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
+          u.w = pack_bf16(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
+          reinterpret_cast<uint4*>(o + c * 32)[g] = u;
+        }
+      }
+    }
+    if (q_valid && p.lse)
+      p.lse[(static_cast<long long>(b) * p.heads + h) * S + q] =
+          (q_live && l_run > 0.f) ? (m_run + log2f(l_run)) : INFINITY;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+
+// --------------------------------------------------------------------------------------------
+// backward
+// --------------------------------------------------------------------------------------------
+struct AttnBwdDev {
+  int B, S, heads, span2;
+  float scale_log2, inv_scale;
+  const __nv_bfloat16* c2p;
+  const __nv_bfloat16* p2c;
+  const unsigned short* lut_c2p;
+  const unsigned short* lut_p2c;
+  const unsigned char* key_keep;
+  const int* doc_ids;
+  const __nv_bfloat16* bias;  // [B, heads, S, ldb] or null
+  __nv_bfloat16* dbias;       // [B, heads, S, ldb] gradient of the bias (written when bias is given)
+  long long ldb;
+  const float* lse;     // [B, heads, S] (log2 domain)
+  const float* delta;   // [B, heads, S] rowsum(dO * O)
+  float* dq_acc;        // [B*S, heads*64] fp32, zero-initialised
+  __nv_bfloat16* dk;    // [B*S, ldk]
+  __nv_bfloat16* dv;
+  long long ldk, ldv;
+  float* d_c2p;         // [B*S, heads, span2] fp32, zero-initialised (or null)
+  float* d_p2c;
+  int* status;
+};
+
+struct BwdSmem {
+  static constexpr int kK = 0;
+  static constexpr int kV = kK + kTileBytes;
+  static constexpr int kQ = kV + kTileBytes;           // 2 buffers
+  static constexpr int kdO = kQ + 2 * kTileBytes;      // 2 buffers
+  static constexpr int kP = kdO + 2 * kTileBytes;      // 128x128 bf16
+  static constexpr int kdS = kP + 2 * kTileBytes;      // 128x128 bf16
+  static constexpr int kBar = kdS + 2 * kTileBytes;
+  static constexpr int kMeta = kBar + 128;
+  static constexpr int kLut = kMeta + 512;
+  static int total(int S, bool pos) { return kLut + (pos ? 2 * (2 * S) * 2 : 0) + 1024; }
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__global__ void __launch_bounds__(128, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                const AttnBwdDev p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem + BwdSmem::kK;
+  uint8_t* sV = smem + BwdSmem::kV;
+  uint8_t* sQ = smem + BwdSmem::kQ;
+  uint8_t* sdO = smem + BwdSmem::kdO;
+  uint8_t* sP = smem + BwdSmem::kP;
+  uint8_t* sdS = smem + BwdSmem::kdS;
+  uint64_t* bar_kv = reinterpret_cast<uint64_t*>(smem + BwdSmem::kBar);
+  uint64_t* bar_qd = bar_kv + 1;  // [2]
+  uint64_t* bar_s = bar_kv + 3;
+  uint64_t* bar_g = bar_kv + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_kv + 5);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* kmeta = reinterpret_cast<int*>(smem + BwdSmem::kMeta);
+  unsigned short* lutc = reinterpret_cast<unsigned short*>(smem + BwdSmem::kLut);
+  unsigned short* lutp = lutc + 2 * p.S;
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int k0 = blockIdx.x * kTile;
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int S = p.S;
+  const bool pos = p.span2 > 0;
+  const int nqt = (S + kTile - 1) / kTile;
+
+  if (tid == 0) {
+    mbar_init(bar_kv, 1);
+    mbar_init(&bar_qd[0], 1);
+    mbar_init(&bar_qd[1], 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_g, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  if (pos) {
+    for (int i = tid; i < 2 * S - 1; i += 128) {
+      lutc[i] = p.lut_c2p[i];
+      lutp[i] = p.lut_p2c[i];
+    }
+  }
+  {
+    const int kk = k0 + tid;
+    int meta = 0;
+    if (kk < S) {
+      const long long tk = static_cast<long long>(b) * S + kk;
+      meta = 1;
+      if (p.key_keep) meta = p.key_keep[tk] ? 1 : 0;
+      if (p.doc_ids) meta = p.doc_ids[tk];
+    }
+    kmeta[tid] = meta;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 320,
+                 t_dq = tmem_base + 384;
+  const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+  const long long pos_row = static_cast<long long>(p.heads) * p.span2;
+
+  constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);    // Q·Kᵀ, dO·Vᵀ
+  constexpr uint32_t idesc_t = make_idesc_bf16(128, 64, true, true);       // Pᵀ·dO, dSᵀ·Q
+  constexpr uint32_t idesc_q = make_idesc_bf16(128, 64, false, true);      // dS·K
+
+  auto issue_scores = [&](int buf) {
+    const uint32_t q = smem_u32(sQ + buf * kTileBytes), d = smem_u32(sdO + buf * kTileBytes);
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+      umma_bf16(t_s, make_smem_desc(q + ks * 32, 16, 1024), make_smem_desc(smem_u32(sK) + ks * 32, 16, 1024), idesc_s,
+                ks > 0);
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+      umma_bf16(t_dp, make_smem_desc(d + ks * 32, 16, 1024), make_smem_desc(smem_u32(sV) + ks * 32, 16, 1024), idesc_s,
+                ks > 0);
+    umma_commit(bar_s);
+  };
+
+  if (tid == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_do);
+    mbar_expect_tx(bar_kv, 2 * kTileBytes);
+    tma_load_3d(sK, &tm_k, bar_kv, h * kD, k0, b);
+    tma_load_3d(sV, &tm_v, bar_kv, h * kD, k0, b);
+    mbar_expect_tx(&bar_qd[0], 2 * kTileBytes);
+    tma_load_3d(sQ, &tm_q, &bar_qd[0], h * kD, 0, b);
+    tma_load_3d(sdO, &tm_do, &bar_qd[0], h * kD, 0, b);
+    if (mbar_wait(bar_kv, 0, abort_flag, p.status, kErrFullWait) &&
+        mbar_wait(&bar_qd[0], 0, abort_flag, p.status, kErrFullWait)) {
+      tc_fence_after();
+      issue_scores(0);
+    } else {
+      umma_commit(bar_s);
+    }
+  }
+
+  auto flush_dq = [&](int qt) {  // dQ of q-tile `qt` from TMEM into the fp32 accumulator
+    const int q = qt * kTile + tid;
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(t_dq + lane_addr + c * 32, r);
+      tmem_ld_wait();
+      if (q < S) {
+        float* dst = p.dq_acc + (static_cast<long long>(b) * S + q) * (static_cast<long long>(p.heads) * kD) + h * kD + c * 32;
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+          red_add_v4(dst + g * 4, __uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]), __uint_as_float(r[g * 4 + 2]),
+                     __uint_as_float(r[g * 4 + 3]));
+      }
+    }
+  };
+
+  bool ok = true;
+  for (int i = 0; i < nqt; ++i) {
+    const int buf = i & 1;
+    const int q0 = i * kTile;
+    if (!mbar_wait(bar_s, i & 1, abort_flag, p.status, kErrAccFullWait)) { ok = false; break; }
+    if (i > 0 && !mbar_wait(bar_g, (i - 1) & 1, abort_flag, p.status, kErrAccFullWait)) { ok = false; break; }
+    tc_fence_after();
+    if (tid == 0 && i + 1 < nqt) {  // tile i-1 retired: its Q / dO buffers can take tile i+1
+      const int nb = (i + 1) & 1;
+      mbar_expect_tx(&bar_qd[nb], 2 * kTileBytes);
+      tma_load_3d(sQ + nb * kTileBytes, &tm_q, &bar_qd[nb], h * kD, q0 + kTile, b);
+      tma_load_3d(sdO + nb * kTileBytes, &tm_do, &bar_qd[nb], h * kD, q0 + kTile, b);
+    }
+    if (i > 0) flush_dq(i - 1);
+
+    const int q = q0 + tid;
+    const bool q_valid = q < S;
+    const long long tq = static_cast<long long>(b) * S + (q_valid ? q : 0);
+    int q_doc = 1;
+    if (q_valid && p.doc_ids) q_doc = p.doc_ids[tq];
+    const long long stat = (static_cast<long long>(b) * p.heads + h) * S + (q_valid ? q : 0);
+    const float lse = q_valid ? p.lse[stat] : INFINITY;
+    const float delta = q_valid ? p.delta[stat] : 0.f;
+    const __nv_bfloat16* c2p_row = p.c2p ? p.c2p + tq * pos_row + static_cast<long long>(h) * p.span2 : nullptr;
+    float* dc2p_row = p.d_c2p ? p.d_c2p + tq * pos_row + static_cast<long long>(h) * p.span2 : nullptr;
+    const long long kbase = (static_cast<long long>(b) * S + k0) * pos_row + static_cast<long long>(h) * p.span2;
+    const int dbase = q - k0 + S - 1;
+    const long long brow_off = ((static_cast<long long>(b) * p.heads + h) * S + (q_valid ? q : 0)) * p.ldb + k0;
+    const uint4* bias_row = p.bias ? reinterpret_cast<const uint4*>(p.bias + brow_off) : nullptr;
+    uint4* dbias_row = (p.dbias && q_valid) ? reinterpret_cast<uint4*>(p.dbias + brow_off) : nullptr;
+
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t rs[32], rd[32];
+      tmem_ld_32x32b_x32(t_s + lane_addr + c * 32, rs);
+      tmem_ld_32x32b_x32(t_dp + lane_addr + c * 32, rd);
+      tmem_ld_wait();
+      float pv[32], gv[32];
+      uint4 bvec = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const int k = c * 32 + e;
+        const int meta = kmeta[k];
+        bool keep = (meta != 0) && q_valid;
+        if (p.doc_ids) keep = keep && (meta == q_doc);
+        float v = __uint_as_float(rs[e]);
+        int ic = 0, ip = 0;
+        if (bias_row) {
+          if ((e & 7) == 0) bvec = __ldg(bias_row + c * 4 + (e >> 3));
+          v += bf16_elem(bvec, e & 7);
+        } else if (pos && keep) {
+          const int di = dbase - k;
+          ic = lutc[di];
+          ip = lutp[di];
+          if (c2p_row) v += __bfloat162float(c2p_row[ic]);
+          if (p.p2c) v += __bfloat162float(p.p2c[kbase + static_cast<long long>(k) * pos_row + ip]);
+        }
+        const float prob = keep ? ex2(v * p.scale_log2 - lse) : 0.f;
+        const float g = prob * (__uint_as_float(rd[e]) - delta) * p.inv_scale;
+        pv[e] = prob;
+        gv[e] = g;
+        if (!bias_row && pos && keep && g != 0.f) {
+          if (dc2p_row) atomicAdd(dc2p_row + ic, g);
+          if (p.d_p2c) atomicAdd(p.d_p2c + kbase + static_cast<long long>(k) * pos_row + ip, g);
+        }
+      }
+      // rows of P and dS for these 32 keys: 4 chunks of 8 bf16 inside 64-key block (c >> 1)
+#pragma unroll
+      for (int g4 = 0; g4 < 4; ++g4) {
+        const int chunk = (c & 1) * 4 + g4;
+        const uint32_t off = (c >> 1) * kTileBytes + swz128(tid, chunk);
+        uint4 u;
+        u.x = pack_bf16(pv[g4 * 8 + 0], pv[g4 * 8 + 1]);
+        u.y = pack_bf16(pv[g4 * 8 + 2], pv[g4 * 8 + 3]);
+        u.z = pack_bf16(pv[g4 * 8 + 4], pv[g4 * 8 + 5]);
+        u.w = pack_bf16(pv[g4 * 8 + 6], pv[g4 * 8 + 7]);
+        *reinterpret_cast<uint4*>(sP + off) = u;
+        u.x = pack_bf16(gv[g4 * 8 + 0], gv[g4 * 8 + 1]);
+        u.y = pack_bf16(gv[g4 * 8 + 2], gv[g4 * 8 + 3]);
+        u.z = pack_bf16(gv[g4 * 8 + 4], gv[g4 * 8 + 5]);
+        u.w = pack_bf16(gv[g4 * 8 + 6], gv[g4 * 8 + 7]);
+        *reinterpret_cast<uint4*>(sdS + off) = u;
+        if (dbias_row) dbias_row[c * 4 + g4] = u;
+      }
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t sp = smem_u32(sP), sds = smem_u32(sdS), sq = smem_u32(sQ + buf * kTileBytes),
+                     sdo = smem_u32(sdO + buf * kTileBytes), sk = smem_u32(sK);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)  // dV[k,d] += sum_q P[q,k] dO[q,d]
+        umma_bf16(t_dv, make_smem_desc(sp + ks * 2048, kTileBytes, 1024), make_smem_desc(sdo + ks * 2048, 8192, 1024),
+                  idesc_t, (i > 0) || (ks > 0));
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)  // dK[k,d] += sum_q dS[q,k] Q[q,d]
+        umma_bf16(t_dk, make_smem_desc(sds + ks * 2048, kTileBytes, 1024), make_smem_desc(sq + ks * 2048, 8192, 1024),
+                  idesc_t, (i > 0) || (ks > 0));
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)  // dQ[q,d] = sum_k dS[q,k] K[k,d]
+        umma_bf16(t_dq, make_smem_desc(sds + (ks >> 2) * kTileBytes + (ks & 3) * 32, 16, 1024),
+                  make_smem_desc(sk + ks * 2048, 8192, 1024), idesc_q, ks > 0);
+      umma_commit(bar_g);
+      if (i + 1 < nqt) {
+        const int nb = (i + 1) & 1;
+        if (mbar_wait(&bar_qd[nb], ((i + 1) >> 1) & 1, abort_flag, p.status, kErrFullWait)) {
+          tc_fence_after();
+          issue_scores(nb);
+        } else {
+          umma_commit(bar_s);
+        }
+      }
+    }
+  }
+
+  if (ok && mbar_wait(bar_g, (nqt - 1) & 1, abort_flag, p.status, kErrAccFullWait)) {
+    tc_fence_after();
+    flush_dq(nqt - 1);
+    const int kk = k0 + tid;
+    const long long tk = static_cast<long long>(b) * S + kk;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      __nv_bfloat16* dst = which == 0 ? p.dv + tk * p.ldv + h * kD : p.dk + tk * p.ldk + h * kD;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32((which == 0 ? t_dv : t_dk) + lane_addr + c * 32, r);
+        tmem_ld_wait();
+        if (kk < S) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 u;
+            u.x = pack_bf16(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
+            u.y = pack_bf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
+            u.z = pack_bf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
+            u.w = pack_bf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
+            reinterpret_cast<uint4*>(dst + c * 32)[g] = u;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+
+int make_head_map(CUtensorMap* m, const void* ptr, const AttnArgs* a, long long ld) {
+  return db200_make_tmap_bf16(m, ptr, static_cast<long long>(a->heads) * kD, a->S, a->B, ld,
+                              static_cast<long long>(a->S) * ld, kTile);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+extern "C" int db200_attn_fwd(const AttnArgs* a, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (a->B <= 0 || a->S <= 0 || a->heads <= 0) return 0;
+  const bool pos = a->span2 > 0;
+  if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->out) || (a->ldq % 8) || (a->ldk % 8) ||
+      (a->ldv % 8) || (a->ldo % 8))
+    return -10;
+  if (pos && (a->S > 4096 || a->span2 > 65535 || !a->lut_c2p || !a->lut_p2c)) return -12;
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_head_map(&tq, a->q, a, a->ldq))) return rc;
+  if ((rc = make_head_map(&tk, a->k, a, a->ldk))) return rc;
+  if ((rc = make_head_map(&tv, a->v, a, a->ldv))) return rc;
+  AttnDev d{};
+  d.B = a->B; d.S = a->S; d.heads = a->heads; d.span2 = a->span2;
+  d.scale_log2 = 1.4426950408889634f / a->scale;
+  d.inv_scale = 1.f / a->scale;
+  d.c2p = static_cast<const __nv_bfloat16*>(a->c2p);
+  d.p2c = static_cast<const __nv_bfloat16*>(a->p2c);
+  d.lut_c2p = static_cast<const unsigned short*>(a->lut_c2p);
+  d.lut_p2c = static_cast<const unsigned short*>(a->lut_p2c);
+  d.key_keep = static_cast<const unsigned char*>(a->key_keep);
+  d.doc_ids = static_cast<const int*>(a->doc_ids);
+  d.bias = static_cast<const __nv_bfloat16*>(a->bias);
+  d.ldb = a->ldb;
+  if (d.bias && ((a->ldb % 128) || !aligned16(a->bias))) return -10;
+  d.out = static_cast<__nv_bfloat16*>(a->out);
+  d.ldo = a->ldo;
+  d.lse = a->lse;
+  d.status = db200_status_ptr();
+  const int smem = FwdSmem::total(a->S, pos);
+  static int configured = 0;
+  if (configured < smem) {
+    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
+    configured = smem;
+  }
+  dim3 grid((a->S + kTile - 1) / kTile, a->heads, a->B);
+  attn_fwd_kernel<<<grid, 128, smem, stream>>>(tq, tk, tv, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int db200_attn_bwd(const AttnArgs* a, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (a->B <= 0 || a->S <= 0 || a->heads <= 0) return 0;
+  const bool pos = a->span2 > 0;
+  if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->dout) || !aligned16(a->dk) ||
+      !aligned16(a->dv) || !aligned16(a->dq_acc) || (a->ldq % 8) || (a->ldk % 8) || (a->ldv % 8) || (a->ld_do % 8) ||
+      (a->ld_dk % 8) || (a->ld_dv % 8))
+    return -10;
+  if (pos && (a->S > 4096 || a->span2 > 65535 || !a->lut_c2p || !a->lut_p2c)) return -12;
+  CUtensorMap tq, tk, tv, tdo;
+  int rc;
+  if ((rc = make_head_map(&tq, a->q, a, a->ldq))) return rc;
+  if ((rc = make_head_map(&tk, a->k, a, a->ldk))) return rc;
+  if ((rc = make_head_map(&tv, a->v, a, a->ldv))) return rc;
+  if ((rc = make_head_map(&tdo, a->dout, a, a->ld_do))) return rc;
+  AttnBwdDev d{};
+  d.B = a->B; d.S = a->S; d.heads = a->heads; d.span2 = a->span2;
+  d.scale_log2 = 1.4426950408889634f / a->scale;
+  d.inv_scale = 1.f / a->scale;
+  d.c2p = static_cast<const __nv_bfloat16*>(a->c2p);
+  d.p2c = static_cast<const __nv_bfloat16*>(a->p2c);
+  d.lut_c2p = static_cast<const unsigned short*>(a->lut_c2p);
+  d.lut_p2c = static_cast<const unsigned short*>(a->lut_p2c);
+  d.key_keep = static_cast<const unsigned char*>(a->key_keep);
+  d.doc_ids = static_cast<const int*>(a->doc_ids);
+  d.bias = static_cast<const __nv_bfloat16*>(a->bias);
+  d.dbias = static_cast<__nv_bfloat16*>(a->dbias);
+  d.ldb = a->ldb;
+  if (d.bias && ((a->ldb % 128) || !aligned16(a->bias) || !d.dbias || !aligned16(a->dbias))) return -10;
+  d.lse = a->lse;
+  d.delta = a->delta;
+  d.dq_acc = a->dq_acc;
+  d.dk = static_cast<__nv_bfloat16*>(a->dk);
+  d.dv = static_cast<__nv_bfloat16*>(a->dv);
+  d.ldk = a->ld_dk; d.ldv = a->ld_dv;
+  d.d_c2p = a->d_c2p;
+  d.d_p2c = a->d_p2c;
+  d.status = db200_status_ptr();
+  const int smem = BwdSmem::total(a->S, pos);
+  static int configured = 0;
+  if (configured < smem) {
+    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
+    configured = smem;
+  }
+  dim3 grid((a->S + kTile - 1) / kTile, a->heads, a->B);
+  attn_bwd_kernel<<<grid, 128, smem, stream>>>(tq, tk, tv, tdo, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

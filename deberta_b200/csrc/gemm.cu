@@ -54,7 +54,26 @@ struct DevParams {
   long long ldo, ldr, ldaux, ldo2;
   long long bs_out, bs_res, bs_aux, bs_out2, bs_bias;
   int* status;
+  // vocabulary cross-entropy epilogues (EPI_CE_FWD / EPI_CE_BWD)
+  const long long* labels;          // [M]
+  const unsigned char* forbidden;   // [N] ids that may not be sampled, or null
+  float inv_temp;                   // 1 / sampling temperature
+  unsigned long long seed;
+  float* ce_part;                   // [4, tiles_n, M]: tile max, tile sum-exp, best noisy logit, its index
+  float* label_logit;               // [M]
+  const float* row_lse;             // [M] natural-log log-sum-exp (backward)
+  float gscale;                     // dLoss/dlogit scale (backward)
+  const float* gscale_ptr;          // optional device scalar multiplied into gscale
 };
+
+// Counter-based uniform in (0,1): two rounds of a 64-bit mix of (seed, row, column).
+__device__ __forceinline__ float hash_uniform(unsigned long long seed, unsigned int row, unsigned int col) {
+  unsigned long long x = seed ^ (static_cast<unsigned long long>(row) << 32 | col);
+  x ^= x >> 33; x *= 0xff51afd7ed558ccdULL;
+  x ^= x >> 33; x *= 0xc4ceb9fe1a85ec53ULL;
+  x ^= x >> 33;
+  return (static_cast<float>(x >> 40) + 0.5f) * (1.0f / 16777216.0f);
+}
 
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
 __device__ __forceinline__ float dgelu_erf(float x) {
@@ -210,6 +229,91 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
       const __nv_bfloat16* bias = p.bias ? p.bias + z * p.bs_bias : nullptr;
+      if (p.epi == EPI_CE_FWD || p.epi == EPI_CE_BWD) {
+        // One thread owns one row of logits. Forward: tile-local max / sum-exp / label logit and the
+        // Gumbel-max candidate (logit/T + noise, forbidden ids excluded); partial results of every
+        // vocabulary tile are combined by a second small kernel. Backward: softmax minus one-hot.
+        const long long label = row_ok ? p.labels[row] : -1;
+        const float lse = (p.epi == EPI_CE_BWD && row_ok) ? p.row_lse[row] : 0.f;
+        const float gs = p.gscale * ((p.epi == EPI_CE_BWD && p.gscale_ptr) ? *p.gscale_ptr : 1.f);
+        float t_max = -INFINITY, t_sum = 0.f, best = -INFINITY;
+        int best_idx = 0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int nc = n0 + c * 32;
+          if (nc >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_row + c * 32, r);
+          tmem_ld_wait();
+          if (!row_ok) continue;
+          float v[32];
+          float cmax = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int n = nc + j;
+            float x = __uint_as_float(r[j]);
+            if (n < p.N) {
+              if (bias) x += __bfloat162float(bias[n]);
+            } else {
+              x = -INFINITY;
+            }
+            v[j] = x;
+            cmax = fmaxf(cmax, x);
+          }
+          if (p.epi == EPI_CE_FWD) {
+            const float m_new = fmaxf(t_max, cmax);
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int n = nc + j;
+              acc += __expf(v[j] - m_new);
+              if (n == label) p.label_logit[row] = v[j];
+              if (n < p.N) {
+                const bool banned = p.forbidden && p.forbidden[n];
+                float u = hash_uniform(p.seed, static_cast<unsigned int>(row), static_cast<unsigned int>(n));
+                u = fminf(fmaxf(u, 1e-6f), 1.f - 1e-6f);
+                const float cand = (banned ? -1e9f : v[j] * p.inv_temp) - __logf(-__logf(u));
+                if (cand > best) { best = cand; best_idx = n; }
+              }
+            }
+            t_sum = t_sum * __expf(t_max - m_new) + acc;
+            t_max = m_new;
+          } else {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldo + nc;
+            const bool vec = (nc + 32 <= p.N) && (p.ldo % 8 == 0);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              v[j] = (__expf(v[j] - lse) - ((nc + j) == label ? 1.f : 0.f)) * gs;
+            if (vec) {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                uint4 u;
+                u.x = pack_bf16(v[q4 * 8], v[q4 * 8 + 1]);
+                u.y = pack_bf16(v[q4 * 8 + 2], v[q4 * 8 + 3]);
+                u.z = pack_bf16(v[q4 * 8 + 4], v[q4 * 8 + 5]);
+                u.w = pack_bf16(v[q4 * 8 + 6], v[q4 * 8 + 7]);
+                reinterpret_cast<uint4*>(o)[q4] = u;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (nc + j < p.N) o[j] = __float2bfloat16(v[j]);
+            }
+          }
+        }
+        if (p.epi == EPI_CE_FWD && row_ok) {
+          const long long tn = n0 / BN;
+          const long long plane = static_cast<long long>(p.tiles_n) * p.M;
+          float* dst = p.ce_part + tn * p.M + row;
+          dst[0] = t_max;
+          dst[plane] = t_sum;
+          dst[2 * plane] = best;
+          dst[3 * plane] = __int_as_float(best_idx);
+        }
+        tc_fence_before();
+        mbar_arrive(&acc_empty[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int nc = n0 + c * 32;
@@ -417,6 +521,40 @@ int db200_make_tmap_bf16(CUtensorMap* out, const void* ptr, long long inner, lon
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
+extern "C" int db200_gemm_tile_n(int N) { return (N > 128) ? 256 : 128; }
+
+// Combine the per-vocabulary-tile partials of EPI_CE_FWD: per row log-sum-exp (natural log),
+// cross-entropy against the label logit, and the arg-max of the noisy logits (the sample).
+__global__ void ce_combine_kernel(const float* __restrict__ part, const float* __restrict__ label_logit, int tiles_n,
+                                  int M, float* __restrict__ lse_out, float* __restrict__ loss_rows,
+                                  long long* __restrict__ sampled) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= M) return;
+  const long long plane = static_cast<long long>(tiles_n) * M;
+  float m = -INFINITY;
+  for (int t = 0; t < tiles_n; ++t) m = fmaxf(m, part[static_cast<long long>(t) * M + row]);
+  float s = 0.f, best = -INFINITY;
+  int idx = 0;
+  for (int t = 0; t < tiles_n; ++t) {
+    const long long o = static_cast<long long>(t) * M + row;
+    s += part[plane + o] * __expf(part[o] - m);
+    const float b = part[2 * plane + o];
+    if (b > best) { best = b; idx = __float_as_int(part[3 * plane + o]); }
+  }
+  const float lse = m + logf(s);
+  lse_out[row] = lse;
+  loss_rows[row] = lse - label_logit[row];
+  sampled[row] = idx;
+}
+
+extern "C" int db200_ce_combine(const float* part, const float* label_logit, int tiles_n, int M, float* lse,
+                                float* loss_rows, long long* sampled, void* stream) {
+  if (M <= 0) return 0;
+  ce_combine_kernel<<<(M + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(part, label_logit, tiles_n, M, lse,
+                                                                                     loss_rows, sampled);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
 extern "C" int db200_gemm_bf16(const GemmArgs* a, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (a->M <= 0 || a->N <= 0 || a->K <= 0 || a->batch <= 0) return 0;
@@ -443,6 +581,17 @@ extern "C" int db200_gemm_bf16(const GemmArgs* a, void* stream_) {
   p.ldo = a->ldo; p.ldr = a->ldr; p.ldaux = a->ldaux; p.ldo2 = a->ldo2;
   p.bs_out = a->bs_out; p.bs_res = a->bs_res; p.bs_aux = a->bs_aux; p.bs_out2 = a->bs_out2; p.bs_bias = a->bs_bias;
   p.status = db200_status_ptr();
+  p.labels = reinterpret_cast<const long long*>(a->labels);
+  p.forbidden = reinterpret_cast<const unsigned char*>(a->forbidden);
+  p.inv_temp = a->inv_temp;
+  p.seed = a->seed;
+  p.ce_part = a->ce_part;
+  p.label_logit = a->label_logit;
+  p.row_lse = a->row_lse;
+  p.gscale = a->gscale;
+  p.gscale_ptr = a->gscale_ptr;
+  if ((p.epi == EPI_CE_FWD) && (!p.labels || !p.ce_part || !p.label_logit || a->batch != 1)) return -11;
+  if ((p.epi == EPI_CE_BWD) && (!p.labels || !p.row_lse || p.out_f32 || a->batch != 1)) return -11;
   if (p.epi == EPI_GELU && (p.out_f32 || !p.out2)) return -11;
   if (p.epi == EPI_DGELU && (p.out_f32 || !p.aux)) return -11;
 

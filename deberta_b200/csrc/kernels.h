@@ -13,7 +13,7 @@ int* db200_status_ptr(void);          // device address of the status word (lazi
 int db200_status_read_and_clear(void);  // synchronises the device; 0 = no error recorded
 
 // ----- GEMM ---------------------------------------------------------------------------
-enum { EPI_NONE = 0, EPI_GELU = 1, EPI_DGELU = 2 };
+enum { EPI_NONE = 0, EPI_GELU = 1, EPI_DGELU = 2, EPI_CE_FWD = 3, EPI_CE_BWD = 4 };
 
 typedef struct GemmArgs {
   const void* A;     // bf16
@@ -29,9 +29,22 @@ typedef struct GemmArgs {
   float alpha;
   long long lda, ldb, ldo, ldo2, ldr, ldaux;                       // leading dims (elements)
   long long bs_a, bs_b, bs_out, bs_out2, bs_res, bs_aux, bs_bias;  // batch strides (elements)
+  // vocabulary cross-entropy epilogues: A = hidden rows [M,K], B = embedding table [N,K], bias [N]
+  const void* labels;        // int64 [M]
+  const void* forbidden;     // uint8 [N] or null
+  float inv_temp;
+  unsigned long long seed;
+  float* ce_part;            // fp32 [4, ceil(N / tile_n), M] scratch (EPI_CE_FWD)
+  float* label_logit;        // fp32 [M]                       (EPI_CE_FWD)
+  const float* row_lse;      // fp32 [M]                       (EPI_CE_BWD)
+  float gscale;              // scale of the logit gradient     (EPI_CE_BWD)
+  const float* gscale_ptr;   // optional device scalar multiplied into gscale
 } GemmArgs;
 
 int db200_gemm_bf16(const GemmArgs* args, void* stream);
+int db200_gemm_tile_n(int N);  // vocabulary-tile width the GEMM uses for N columns
+int db200_ce_combine(const float* part, const float* label_logit, int tiles_n, int M, float* lse, float* loss_rows,
+                     long long* sampled, void* stream);
 
 // ----- LayerNorm / RMSNorm (bf16 in/out, fp32 stats; row_keep: optional uint8 per-row multiplier) -----
 int db200_norm_fwd(const void* x, const void* gamma, const void* beta, const void* row_keep, void* y, float* mean,
@@ -46,6 +59,44 @@ int db200_adamw(float* p, const float* g, float* m, float* v, void* shadow_bf16,
                 float b1, float b2, float eps, float inv_bc1, float inv_sqrt_bc2, const float* norm_sq,
                 float max_norm, float grad_scale, void* stream);
 
+// ----- attention (head dim 64; token-major bf16 operands; see attention.cu) -------------------------
+typedef struct AttnArgs {
+  const void *q, *k, *v;          // bf16 [B*S, ld*]
+  long long ldq, ldk, ldv;
+  void* out;                      // bf16 [B*S, ldo]           (forward)
+  long long ldo;
+  float* lse;                     // fp32 [B, heads, S], log2 domain
+  int B, S, heads, span2;         // span2 = rows of the position score tables, 0 = none
+  float scale;                    // scores are divided by this
+  const void *c2p, *p2c;          // bf16 [B*S, heads, span2] or null
+  const void *lut_c2p, *lut_p2c;  // uint16 [2S-1]
+  const void* key_keep;           // uint8 [B*S] or null
+  const void* doc_ids;            // int32 [B*S] or null
+  const void* dout;               // bf16 [B*S, ld_do]         (backward)
+  long long ld_do;
+  const float* delta;             // fp32 [B, heads, S]
+  float* dq_acc;                  // fp32 [B*S, heads*64], zeroed by the caller
+  void *dk, *dv;                  // bf16 [B*S, ld_dk / ld_dv]
+  long long ld_dk, ld_dv;
+  float *d_c2p, *d_p2c;           // fp32 [B*S, heads, span2], zeroed by the caller, or null
+  const void* bias;               // bf16 [B, heads, S, ldb] pre-gathered position bias (then span2 = 0), or null
+  void* dbias;                    // bf16 [B, heads, S, ldb] its gradient (backward)
+  long long ldb;                  // multiple of 128
+} AttnArgs;
+
+// key-indexed position bias: build from / scatter back to the bucket-indexed score tables (posbias.cu)
+int db200_posbias_build(const void* c2p, const void* p2c, const void* lut_c2p, const void* lut_p2c, void* bias, int B,
+                        int S, int ldb, int heads, int span2, void* stream);
+int db200_posbias_scatter(const void* dbias, const void* lut, void* dtab, int rows_are_keys, int B, int S, int ldb,
+                          int heads, int span2, void* stream);
+
+int db200_attn_fwd(const AttnArgs* args, void* stream);
+int db200_attn_bwd(const AttnArgs* args, void* stream);
+
 #ifdef __cplusplus
 }
+// internal: 3-D bf16 tensor map {inner, rows, batch}, box {64, box_rows, 1}, 128B swizzle
+#include <cuda.h>
+int db200_make_tmap_bf16(CUtensorMap* out, const void* ptr, long long inner, long long rows, long long batch,
+                         long long row_stride_elems, long long batch_stride_elems, int box_rows);
 #endif

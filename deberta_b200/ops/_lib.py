@@ -21,7 +21,7 @@ c_int = ctypes.c_int
 c_ll = ctypes.c_longlong
 c_float = ctypes.c_float
 
-EPI_NONE, EPI_GELU, EPI_DGELU = 0, 1, 2
+EPI_NONE, EPI_GELU, EPI_DGELU, EPI_CE_FWD, EPI_CE_BWD = 0, 1, 2, 3, 4
 
 STATUS_NAMES = {
     0: "ok",
@@ -71,6 +71,15 @@ class GemmArgs(ctypes.Structure):
         ("bs_res", c_ll),
         ("bs_aux", c_ll),
         ("bs_bias", c_ll),
+        ("labels", c_void_p),
+        ("forbidden", c_void_p),
+        ("inv_temp", c_float),
+        ("seed", ctypes.c_ulonglong),
+        ("ce_part", c_void_p),
+        ("label_logit", c_void_p),
+        ("row_lse", c_void_p),
+        ("gscale", c_float),
+        ("gscale_ptr", c_void_p),
     ]
 
 

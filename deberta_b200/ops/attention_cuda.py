@@ -1,21 +1,228 @@
-"""Dispatch predicates and launchers for the sm_100a attention kernels."""
+"""Launchers and autograd glue for the sm_100a attention kernels (``csrc/attention.cu``).
+
+The position terms of disentangled attention enter the kernels as two per-head score tables
+(``C2P = Q·PosKᵀ``, ``P2C = K·PosQᵀ``, both ``[tokens, heads, 2·span]``) produced by the batched
+tcgen05 GEMM; the kernels gather from them with the log-bucket lookup tables. The backward
+kernel returns the gradients of those tables, which two more batched GEMMs turn into the
+gradients of Q/K and of the projected position embeddings.
+"""
 
 from __future__ import annotations
 
+import ctypes
+import math
+
 import torch
+
+from . import _lib
+from .gemm import gemm
+
+c_void_p, c_int, c_ll, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+
+class AttnArgs(ctypes.Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p),
+        ("ldq", c_ll), ("ldk", c_ll), ("ldv", c_ll),
+        ("out", c_void_p), ("ldo", c_ll), ("lse", c_void_p),
+        ("B", c_int), ("S", c_int), ("heads", c_int), ("span2", c_int),
+        ("scale", c_float),
+        ("c2p", c_void_p), ("p2c", c_void_p), ("lut_c2p", c_void_p), ("lut_p2c", c_void_p),
+        ("key_keep", c_void_p), ("doc_ids", c_void_p),
+        ("dout", c_void_p), ("ld_do", c_ll), ("delta", c_void_p), ("dq_acc", c_void_p),
+        ("dk", c_void_p), ("dv", c_void_p), ("ld_dk", c_ll), ("ld_dv", c_ll),
+        ("d_c2p", c_void_p), ("d_p2c", c_void_p),
+        ("bias", c_void_p), ("dbias", c_void_p), ("ldb", c_ll),
+    ]
+
+# Up to this sequence length the position terms are pre-gathered into a key-indexed
+# [B, heads, S, S] bf16 bias (contiguous vector loads in the attention kernels); beyond it the
+# kernels gather from the bucket-indexed tables directly, which needs no S x S storage.
+BIAS_MODE_MAX_SEQ = 1024
+
+
+_LUT_CACHE: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _luts(S: int, bucket_size: int, max_position: int, att_span: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+    key = (S, bucket_size, max_position, att_span, str(device))
+    hit = _LUT_CACHE.get(key)
+    if hit is None:
+        from .attention import relative_position_luts
+
+        c2p, p2c = relative_position_luts(S, S, bucket_size, max_position, att_span)
+        hit = (c2p.to(torch.int16).to(device), p2c.to(torch.int16).to(device))
+        _LUT_CACHE[key] = hit
+    return hit
+
+
+def _token_major(x: torch.Tensor) -> torch.Tensor:
+    """[B,S,H] with unit inner stride, 16-byte aligned rows and batch stride = S · row stride (else a copy)."""
+    B, S, H = x.shape
+    if x.stride(2) != 1 or x.stride(0) != S * x.stride(1) or x.stride(1) % 8 or x.data_ptr() % 16:
+        return x.contiguous()
+    return x
+
+
+def _heads_view(x2: torch.Tensor, heads: int) -> torch.Tensor:
+    """[rows, H] (row stride ld) → [heads, rows, 64] view for the batched GEMM."""
+    rows, H = x2.shape
+    return x2.as_strided((heads, rows, H // heads), (H // heads, x2.stride(0), 1), x2.storage_offset())
+
+
+def _common_ok(q, k, v, heads, pair_keep, dropout_p, training) -> bool:
+    return (
+        q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16
+        and pair_keep is None and not (training and dropout_p > 0.0)
+        and q.dim() == 3 and q.shape == k.shape == v.shape and q.shape[-1] == heads * 64
+    )
 
 
 def disentangled_supported(q, k, v, pos_k, pos_q, heads, pair_keep, dropout_p, training, rel_pos) -> bool:
-    return False
+    if not _common_ok(q, k, v, heads, pair_keep, dropout_p, training) or rel_pos is not None:
+        return False
+    has_pos = pos_k is not None or pos_q is not None
+    return not has_pos or (q.shape[1] <= 4096 and all(t is None or t.shape[0] <= 32767 for t in (pos_k, pos_q)))
 
 
 def rope_supported(q, k, v, heads, rotary_dim, pair_keep, dropout_p, training) -> bool:
-    return False
+    return _common_ok(q, k, v, heads, pair_keep, dropout_p, training)
 
 
-def disentangled_attention_cuda(*args, **kwargs) -> torch.Tensor:  # pragma: no cover
-    raise NotImplementedError
+class _FlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, pos_k, pos_q, heads, scale, luts, key_keep, doc_ids):
+        q, k, v = _token_major(q), _token_major(k), _token_major(v)
+        B, S, H = q.shape
+        T = B * S
+        out = torch.empty((B, S, H), dtype=torch.bfloat16, device=q.device)
+        lse = torch.empty((B, heads, S), dtype=torch.float32, device=q.device)
+        q2, k2 = q.as_strided((T, H), (q.stride(1), 1), q.storage_offset()), k.as_strided((T, H), (k.stride(1), 1), k.storage_offset())
+        c2p = p2c = None
+        span2 = 0
+        if pos_k is not None:
+            span2 = pos_k.shape[0]
+            c2p = torch.empty((T, heads, span2), dtype=torch.bfloat16, device=q.device)
+            gemm(_heads_view(q2, heads), _heads_view(pos_k, heads), out=c2p.permute(1, 0, 2))
+        if pos_q is not None:
+            span2 = pos_q.shape[0]
+            p2c = torch.empty((T, heads, span2), dtype=torch.bfloat16, device=q.device)
+            gemm(_heads_view(k2, heads), _heads_view(pos_q, heads), out=p2c.permute(1, 0, 2))
+        kk = None if key_keep is None else key_keep.to(torch.uint8).contiguous()
+        dd = None if doc_ids is None else doc_ids.to(torch.int32).contiguous()
+        bias = None
+        ldb = (S + 127) // 128 * 128
+        if span2 and S <= BIAS_MODE_MAX_SEQ:
+            bias = torch.empty((B, heads, S, ldb), dtype=torch.bfloat16, device=q.device)
+            _lib.call("db200_posbias_build", _lib.ptr(c2p), _lib.ptr(p2c), _lib.ptr(luts[0]), _lib.ptr(luts[1]),
+                      _lib.ptr(bias), c_int(B), c_int(S), c_int(ldb), c_int(heads), c_int(span2), _lib.stream_ptr())
+            c2p = p2c = None  # only the key-indexed form is needed from here on
+        a = AttnArgs()
+        a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+        a.ldq, a.ldk, a.ldv = q.stride(1), k.stride(1), v.stride(1)
+        a.out, a.ldo, a.lse = out.data_ptr(), H, lse.data_ptr()
+        a.B, a.S, a.heads, a.span2, a.scale = B, S, heads, (0 if bias is not None else span2), scale
+        a.c2p = None if c2p is None else c2p.data_ptr()
+        a.p2c = None if p2c is None else p2c.data_ptr()
+        if bias is not None:
+            a.bias, a.ldb = bias.data_ptr(), ldb
+        elif span2:
+            a.lut_c2p, a.lut_p2c = luts[0].data_ptr(), luts[1].data_ptr()
+        a.key_keep = None if kk is None else kk.data_ptr()
+        a.doc_ids = None if dd is None else dd.data_ptr()
+        _lib.call("db200_attn_fwd", ctypes.byref(a), _lib.stream_ptr())
+        ctx.save_for_backward(q, k, v, out, lse, c2p, p2c, pos_k, pos_q, kk, dd, bias)
+        ctx.meta = (heads, scale, luts, span2)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse, c2p, p2c, pos_k, pos_q, kk, dd, bias = ctx.saved_tensors
+        heads, scale, luts, span2 = ctx.meta
+        B, S, H = q.shape
+        T = B * S
+        dev = q.device
+        dout = dout.contiguous()
+        delta = (dout.float() * out.float()).view(B, S, heads, 64).sum(-1).permute(0, 2, 1).contiguous()
+        dq_acc = torch.zeros((T, H), dtype=torch.float32, device=dev)
+        dk = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        dv = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        d_c2p = torch.zeros((T, heads, span2), dtype=torch.float32, device=dev) if c2p is not None else None
+        d_p2c = torch.zeros((T, heads, span2), dtype=torch.float32, device=dev) if p2c is not None else None
+        dbias = torch.empty_like(bias) if bias is not None else None
+        a = AttnArgs()
+        a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+        a.ldq, a.ldk, a.ldv = q.stride(1), k.stride(1), v.stride(1)
+        a.lse = lse.data_ptr()
+        a.B, a.S, a.heads, a.span2, a.scale = B, S, heads, (0 if bias is not None else span2), scale
+        a.c2p = None if c2p is None else c2p.data_ptr()
+        a.p2c = None if p2c is None else p2c.data_ptr()
+        if bias is not None:
+            a.bias, a.dbias, a.ldb = bias.data_ptr(), dbias.data_ptr(), bias.shape[-1]
+        elif span2:
+            a.lut_c2p, a.lut_p2c = luts[0].data_ptr(), luts[1].data_ptr()
+        a.key_keep = None if kk is None else kk.data_ptr()
+        a.doc_ids = None if dd is None else dd.data_ptr()
+        a.dout, a.ld_do, a.delta = dout.data_ptr(), H, delta.data_ptr()
+        a.dq_acc, a.dk, a.dv, a.ld_dk, a.ld_dv = dq_acc.data_ptr(), dk.data_ptr(), dv.data_ptr(), H, H
+        a.d_c2p = None if d_c2p is None else d_c2p.data_ptr()
+        a.d_p2c = None if d_p2c is None else d_p2c.data_ptr()
+        _lib.call("db200_attn_bwd", ctypes.byref(a), _lib.stream_ptr())
+        d_pos_k = d_pos_q = None
+        g_c2p = None if d_c2p is None else d_c2p.to(torch.bfloat16)
+        g_p2c = None if d_p2c is None else d_p2c.to(torch.bfloat16)
+        if bias is not None:  # reduce the key-indexed bias gradient back onto the bucket-indexed tables
+            for which, tab in ((0, pos_k), (1, pos_q)):
+                if tab is None:
+                    continue
+                gt = torch.empty((T, heads, span2), dtype=torch.bfloat16, device=dev)
+                _lib.call("db200_posbias_scatter", _lib.ptr(dbias), _lib.ptr(luts[which]), _lib.ptr(gt), c_int(which),
+                          c_int(B), c_int(S), c_int(bias.shape[-1]), c_int(heads), c_int(span2), _lib.stream_ptr())
+                if which == 0:
+                    g_c2p = gt
+                else:
+                    g_p2c = gt
+        q2 = q.as_strided((T, H), (q.stride(1), 1), q.storage_offset())
+        k2 = k.as_strided((T, H), (k.stride(1), 1), k.storage_offset())
+        if g_c2p is not None:
+            g = g_c2p.permute(1, 0, 2)  # [heads, T, span2]
+            # dQ += dC2P · PosK ; dPosK = dC2Pᵀ · Q   (per head)
+            gemm(g, _heads_view(pos_k, heads), b_mn=True, out=_heads_view(dq_acc, heads), accumulate=True)
+            d_pos_k = torch.zeros(pos_k.shape, dtype=torch.float32, device=dev)
+            gemm(g, _heads_view(q2, heads), a_mn=True, b_mn=True, out=_heads_view(d_pos_k, heads), accumulate=True)
+            d_pos_k = d_pos_k.to(pos_k.dtype)
+        if g_p2c is not None:
+            g = g_p2c.permute(1, 0, 2)
+            dk_extra = torch.zeros((T, H), dtype=torch.float32, device=dev)
+            gemm(g, _heads_view(pos_q, heads), b_mn=True, out=_heads_view(dk_extra, heads), accumulate=True)
+            dk = (dk.float() + dk_extra).to(torch.bfloat16)
+            d_pos_q = torch.zeros(pos_q.shape, dtype=torch.float32, device=dev)
+            gemm(g, _heads_view(k2, heads), a_mn=True, b_mn=True, out=_heads_view(d_pos_q, heads), accumulate=True)
+            d_pos_q = d_pos_q.to(pos_q.dtype)
+        dq = dq_acc.to(torch.bfloat16).view(B, S, H)
+        return dq, dk.view(B, S, H), dv.view(B, S, H), d_pos_k, d_pos_q, None, None, None, None, None
 
 
-def rope_attention_cuda(*args, **kwargs) -> torch.Tensor:  # pragma: no cover
-    raise NotImplementedError
+def disentangled_attention_cuda(q, k, v, pos_k, pos_q, *, heads, scale_factor, bucket_size, max_position, att_span,
+                                key_keep=None, doc_ids=None) -> torch.Tensor:
+    d = q.shape[-1] // heads
+    scale = math.sqrt(float(d * scale_factor))
+    luts = None
+    if pos_k is not None or pos_q is not None:
+        luts = _luts(q.shape[1], bucket_size, max_position, att_span, q.device)
+        pos_k = None if pos_k is None else pos_k[: 2 * att_span].contiguous()
+        pos_q = None if pos_q is None else pos_q[: 2 * att_span].contiguous()
+    return _FlashAttention.apply(q, k, v, pos_k, pos_q, heads, scale, luts, key_keep, doc_ids)
+
+
+def rope_attention_cuda(q, k, v, cos, sin, *, heads, rotary_dim, key_keep=None, doc_ids=None) -> torch.Tensor:
+    """Rotary attention: interleaved-pair rotation of q and k, then the same flash kernel without position tables."""
+    B, S, H = q.shape
+    d = H // heads
+    if rotary_dim > 0:
+        from .attention import rotate_interleaved
+
+        c, s = cos.to(q.dtype)[None, :, None, :], sin.to(q.dtype)[None, :, None, :]
+        q = rotate_interleaved(q.reshape(B, S, heads, d), c, s, rotary_dim).reshape(B, S, H)
+        k = rotate_interleaved(k.reshape(B, S, heads, d), c, s, rotary_dim).reshape(B, S, H)
+    return _FlashAttention.apply(q, k, v, None, None, heads, math.sqrt(float(d)), None, key_keep, doc_ids)

@@ -1,0 +1,111 @@
+"""sm_100a attention kernels vs. the fp32 PyTorch statements of the same operators (forward and gradients)."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from deberta_b200.ops import _lib
+from deberta_b200.ops.attention import (disentangled_attention, disentangled_attention_reference, relative_positions,
+                                        rope_attention, rope_attention_reference)
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel_err(got, ref):
+    return (got.float() - ref.float()).abs().max().item() / (ref.float().abs().max().item() + 1e-6)
+
+
+def _inputs(B, S, heads, span, seed=0, scale=0.5):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    H = heads * 64
+    mk = lambda *s: (torch.randn(*s, device="cuda", generator=g) * scale).to(torch.bfloat16).requires_grad_(True)  # noqa: E731
+    return mk(B, S, H), mk(B, S, H), mk(B, S, H), mk(2 * span, H), mk(2 * span, H)
+
+
+@pytest.mark.parametrize("mode", ["bias", "gather"])
+@pytest.mark.parametrize("B,S,heads,mask", [(2, 512, 2, "none"), (2, 200, 3, "pad"), (1, 384, 2, "doc"), (2, 128, 1, "none")])
+def test_disentangled_forward_backward(B, S, heads, mask, mode, monkeypatch):
+    from deberta_b200.ops import attention_cuda
+
+    # "bias": position terms pre-gathered to [q, k] form; "gather": bucket tables read inside the kernels
+    monkeypatch.setattr(attention_cuda, "BIAS_MODE_MAX_SEQ", 1024 if mode == "bias" else 0)
+    span, buckets, maxpos = 256, 256, 512
+    q, k, v, pk, pq = _inputs(B, S, heads, span)
+    kw = {}
+    if mask == "pad":
+        keep = torch.ones(B, S, dtype=torch.bool, device="cuda")
+        keep[0, S - 37:] = False
+        kw["key_keep"] = keep
+    elif mask == "doc":
+        doc = torch.ones(B, S, dtype=torch.long, device="cuda")
+        doc[:, 100:] = 2
+        doc[:, 300:] = 3
+        doc[:, S - 20:] = 0
+        kw["doc_ids"] = doc
+    out = disentangled_attention(q, k, v, pk, pq, heads=heads, scale_factor=3, bucket_size=buckets, max_position=maxpos,
+                                 att_span=span, **kw)
+    ref_in = [t.detach().float().requires_grad_(True) for t in (q, k, v, pk, pq)]
+    ref = disentangled_attention_reference(*ref_in, heads=heads, scale_factor=3,
+                                           rel_pos=relative_positions(S, S, buckets, maxpos, device="cuda"),
+                                           att_span=span, **kw)
+    _lib.check_status()
+    assert _rel_err(out, ref) < 2e-2
+    w = torch.randn_like(ref)
+    (out.float() * w).sum().backward()
+    (ref * w).sum().backward()
+    _lib.check_status()
+    for name, a, b in zip("q k v pos_k pos_q".split(), (q, k, v, pk, pq), ref_in):
+        assert _rel_err(a.grad, b.grad) < 4e-2, name
+
+
+@pytest.mark.parametrize("S,mask", [(256, "none"), (1000, "doc"), (320, "pad")])
+def test_rope_forward_backward(S, mask):
+    B, heads = 2, 2
+    q, k, v, _, _ = _inputs(B, S, heads, 8, seed=3)
+    inv = 1.0 / (10000 ** (torch.arange(0, 64, 2, device="cuda").float() / 64))
+    ang = torch.repeat_interleave(torch.outer(torch.arange(S, device="cuda").float(), inv), 2, dim=-1)
+    cos, sin = ang.cos(), ang.sin()
+    kw = {}
+    if mask == "doc":
+        doc = torch.ones(B, S, dtype=torch.long, device="cuda")
+        doc[:, 333:] = 2
+        doc[1, 700:] = 3
+        doc[0, 990:] = 0
+        kw["doc_ids"] = doc
+    elif mask == "pad":
+        keep = torch.ones(B, S, dtype=torch.bool, device="cuda")
+        keep[1, 250:] = False
+        kw["key_keep"] = keep
+    out = rope_attention(q, k, v, cos, sin, heads=heads, rotary_dim=64, **kw)
+    ref_in = [t.detach().float().requires_grad_(True) for t in (q, k, v)]
+    ref = rope_attention_reference(*ref_in, cos, sin, heads=heads, rotary_dim=64, **kw)
+    _lib.check_status()
+    assert _rel_err(out, ref) < 2e-2
+    w = torch.randn_like(ref)
+    (out.float() * w).sum().backward()
+    (ref * w).sum().backward()
+    _lib.check_status()
+    for name, a, b in zip("qkv", (q, k, v), ref_in):
+        assert _rel_err(a.grad, b.grad) < 4e-2, name
+
+
+def test_attention_speed_report():
+    B, S, heads, span = 32, 512, 12, 256
+    q, k, v, pk, pq = _inputs(B, S, heads, span, scale=0.3)
+    fn = lambda: disentangled_attention(q, k, v, pk, pq, heads=heads, scale_factor=3, bucket_size=256,  # noqa: E731
+                                        max_position=512, att_span=span)
+    out = fn()
+    g = torch.randn_like(out)
+    for label, f in (("fwd", fn), ("fwd+bwd", lambda: fn().backward(g))):
+        for _ in range(2):
+            f()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(5):
+            f()
+        e.record()
+        torch.cuda.synchronize()
+        print(f"\n[disentangled attention B={B} S={S} h={heads}] {label}: {s.elapsed_time(e) / 5 * 1e3:.0f} us")
+    _lib.check_status()
