@@ -1,0 +1,104 @@
+"""Operator micro-benchmarks: ``python -m deberta_b200.ops.microbench <op> [--batch B] [--seq S] [--iters N]``.
+
+Times one operator with CUDA events after warm-up (inputs of the DeBERTa-v3-base shapes are far
+larger than the 126 MB L2) and prints achieved throughput. Used for the kernel profiles:
+the same command line runs under ``ncu`` to capture a single kernel.
+"""
+
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+
+def _time(fn, iters: int, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / iters * 1e3  # microseconds
+
+
+def _rand(*shape, scale=0.3, grad=False):
+    t = (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+    return t.requires_grad_(True) if grad else t
+
+
+def bench_gemm(a) -> None:
+    from deberta_b200.ops.gemm import gemm
+
+    M = a.batch * a.seq
+    for N, K in ((768, 768), (3072, 768), (768, 3072)):
+        x, w = _rand(M, K), _rand(N, K, scale=0.05)
+        us = _time(lambda: gemm(x, w), a.iters)
+        ref = _time(lambda: x @ w.t(), a.iters)
+        print(f"gemm {M}x{N}x{K}: tcgen05 {us:.1f} us ({2 * M * N * K / us / 1e6:.0f} TFLOP/s) | cuBLAS {ref:.1f} us")
+
+
+def bench_attention(a) -> None:
+    from deberta_b200.ops.attention import disentangled_attention
+
+    h, span = a.heads, 256
+    H = h * 64
+    q, k, v = (_rand(a.batch, a.seq, H, grad=True) for _ in range(3))
+    pk, pq = (_rand(2 * span, H, grad=True) for _ in range(2))
+    kw = dict(heads=h, scale_factor=3, bucket_size=256, max_position=512, att_span=span)
+    for name, pkk, pqq in (("content only", None, None), ("disentangled", pk, pq)):
+        f = lambda: disentangled_attention(q, k, v, pkk, pqq, **kw)  # noqa: E731
+        g = torch.randn_like(f())
+        fwd = _time(f, a.iters)
+        both = _time(lambda: f().backward(g), a.iters)
+        flops = 4 * a.batch * h * a.seq * a.seq * 64
+        print(f"attention [{name}] B={a.batch} S={a.seq} h={h}: fwd {fwd:.0f} us ({flops / fwd / 1e6:.0f} TFLOP/s), "
+              f"fwd+bwd {both:.0f} us")
+
+
+def bench_vocab_ce(a) -> None:
+    from deberta_b200.ops.heads import mlm_loss_and_sample, mlm_loss_and_sample_reference
+
+    N, V, E = a.batch * 77, 128100, 768
+    x, w, b = _rand(N, E, grad=True), _rand(V, E, scale=0.02, grad=True), _rand(V, scale=0.01, grad=True)
+    labels = torch.randint(5, V, (N,), device="cuda")
+    forb = torch.zeros(V, dtype=torch.bool, device="cuda")
+    for name, fn in (("fused", mlm_loss_and_sample), ("aten", mlm_loss_and_sample_reference)):
+        f = lambda: fn(x, w, b, labels, forb, 1.0)  # noqa: E731
+        fwd = _time(f, a.iters)
+        both = _time(lambda: f()[0].backward(), a.iters)
+        print(f"vocab CE+sample [{name}] N={N} V={V}: fwd {fwd:.0f} us, fwd+bwd {both:.0f} us")
+
+
+def bench_layer(a) -> None:
+    from deberta_b200.models.deberta_v2 import DebertaV2Layer
+    from deberta_b200.models.builder import build_repo_hf_deberta_v2_config
+
+    cfg = build_repo_hf_deberta_v2_config("base")
+    cfg.hidden_dropout_prob = cfg.attention_probs_dropout_prob = 0.0
+    layer = DebertaV2Layer(cfg).cuda().to(torch.bfloat16)
+    x = _rand(a.batch, a.seq, 768, scale=1.0, grad=True)
+    rel = _rand(512, 768, scale=1.0)
+    f = lambda: layer(x, None, rel_embeddings=rel)[0]  # noqa: E731
+    g = torch.randn_like(f())
+    fwd = _time(f, a.iters)
+    both = _time(lambda: f().backward(g), a.iters)
+    print(f"DeBERTa-v3-base layer B={a.batch} S={a.seq}: fwd {fwd:.0f} us, fwd+bwd {both:.0f} us")
+
+
+def main() -> None:
+    p = argparse.ArgumentParser()
+    p.add_argument("op", choices=("gemm", "attention", "vocab_ce", "layer"))
+    p.add_argument("--batch", type=int, default=32)
+    p.add_argument("--seq", type=int, default=512)
+    p.add_argument("--heads", type=int, default=12)
+    p.add_argument("--iters", type=int, default=5)
+    a = p.parse_args()
+    {"gemm": bench_gemm, "attention": bench_attention, "vocab_ce": bench_vocab_ce, "layer": bench_layer}[a.op](a)
+
+
+if __name__ == "__main__":
+    main()

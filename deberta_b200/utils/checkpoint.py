@@ -1,0 +1,148 @@
+"""Checkpoint payload I/O.
+
+A training checkpoint directory holds (names follow what Accelerate writes for the reference,
+``utils/checkpoint.py`` / ``training/run_management.py`` there, so its tools can read our runs):
+
+* ``model.safetensors``   — full fp32 model state (rank 0)
+* ``optimizer.bin`` / ``optimizer_1.bin`` — generator (or single) / discriminator optimizer state; with
+  sharded optimizer state every rank writes ``optimizer_shard<rank>.bin`` instead
+* ``scheduler.bin`` / ``scheduler_1.bin``, ``trainer_state.bin``, ``random_states_<rank>.pkl``
+
+Model weights can also be read from the other layouts the reference accepts: ``model.bin`` /
+``pytorch_model.bin`` and torch-DCP sharded directories ``pytorch_model_fsdp*`` (state nested under
+``"model"``), with ``_orig_mod.`` prefixes of compiled modules stripped.
+"""
+
+from __future__ import annotations
+
+import logging
+import pickle
+import random
+from pathlib import Path
+from typing import Any
+
+import numpy as np
+import torch
+
+logger = logging.getLogger(__name__)
+
+MODEL_SAFETENSORS = "model.safetensors"
+
+
+def canonicalize_state_dict_keys(state: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    """Strip ``_orig_mod.`` (torch.compile wrappers) and a leading ``model.`` / ``module.`` prefix shared by all keys."""
+    out = {k.replace("_orig_mod.", ""): v for k, v in state.items()}
+    for prefix in ("model.", "module."):
+        if out and all(k.startswith(prefix) for k in out):
+            out = {k[len(prefix):]: v for k, v in out.items()}
+    return out
+
+
+def _load_dcp_dir(path: Path) -> dict[str, torch.Tensor]:
+    """Read a torch distributed-checkpoint directory without a process group."""
+    from torch.distributed.checkpoint import FileSystemReader
+    from torch.distributed.checkpoint.state_dict_loader import _load_state_dict_from_keys
+
+    state = _load_state_dict_from_keys(storage_reader=FileSystemReader(str(path)))
+    flat: dict[str, torch.Tensor] = {}
+
+    def walk(prefix: str, obj: Any) -> None:
+        if isinstance(obj, dict):
+            for k, v in obj.items():
+                walk(f"{prefix}.{k}" if prefix else str(k), v)
+        elif isinstance(obj, torch.Tensor):
+            flat[prefix] = obj
+
+    walk("", state)
+    return flat
+
+
+def load_model_state_dict(checkpoint_dir: str | Path) -> dict[str, torch.Tensor]:
+    """Model tensors of a checkpoint directory, whichever supported layout it uses (keys canonicalised)."""
+    ck = Path(checkpoint_dir)
+    st = ck / MODEL_SAFETENSORS
+    if st.exists():
+        from safetensors.torch import load_file
+
+        return canonicalize_state_dict_keys(load_file(str(st)))
+    for name in ("model.bin", "pytorch_model.bin"):
+        if (ck / name).exists():
+            return canonicalize_state_dict_keys(torch.load(ck / name, map_location="cpu", weights_only=True))
+    for sub in sorted(ck.glob("pytorch_model_fsdp*")):
+        if sub.is_dir():
+            return canonicalize_state_dict_keys(_load_dcp_dir(sub))
+    raise FileNotFoundError(f"No model weights found in checkpoint directory: {ck}")
+
+
+def save_model_state_dict(state: dict[str, torch.Tensor], checkpoint_dir: str | Path) -> Path:
+    """Write ``model.safetensors`` (tensors made contiguous and un-aliased first)."""
+    from safetensors.torch import save_file
+
+    path = Path(checkpoint_dir) / MODEL_SAFETENSORS
+    save_file({k: v.detach().cpu().contiguous().clone() for k, v in state.items()}, str(path))
+    return path
+
+
+def capture_rng_state() -> dict[str, Any]:
+    out: dict[str, Any] = {"python": random.getstate(), "numpy": np.random.get_state(), "torch": torch.get_rng_state()}
+    if torch.cuda.is_available():
+        out["cuda"] = torch.cuda.get_rng_state_all()
+    return out
+
+
+def restore_rng_state(state: dict[str, Any]) -> None:
+    random.setstate(state["python"])
+    np.random.set_state(state["numpy"])
+    torch.set_rng_state(state["torch"])
+    if "cuda" in state and torch.cuda.is_available():
+        try:
+            torch.cuda.set_rng_state_all(state["cuda"])
+        except Exception as e:  # different GPU count on resume
+            logger.warning("Could not restore CUDA RNG state: %s", e)
+
+
+def save_training_state(directory: str | Path, *, engine: Any, trainer: Any, ctx: Any) -> None:
+    """Every rank's part of a checkpoint (collective: gathers fp32 masters under sharded optimizers)."""
+    d = Path(directory)
+    model_state = engine.model_state_dict()  # collective
+    sharded = engine.parallelism == "zero" and ctx.world_size > 1
+    if ctx.is_main_process:
+        save_model_state_dict(model_state, d)
+        tstate = trainer.state_dict()
+        names = list(engine.optimizers)
+        for i, name in enumerate(names):
+            suffix = "" if i == 0 else f"_{i}"
+            torch.save(tstate["schedules"][name], d / f"scheduler{suffix}.bin")
+        torch.save(tstate, d / "trainer_state.bin")
+    opt_state = engine.optimizer_state_dict()
+    if sharded:
+        torch.save(opt_state, d / f"optimizer_shard{ctx.rank}.bin")
+    elif ctx.is_main_process:
+        for i, (name, st) in enumerate(opt_state.items()):
+            torch.save({name: st}, d / ("optimizer.bin" if i == 0 else f"optimizer_{i}.bin"))
+    with open(d / f"random_states_{ctx.rank}.pkl", "wb") as f:
+        pickle.dump(capture_rng_state(), f)
+
+
+def load_training_state(directory: str | Path, *, engine: Any, trainer: Any, ctx: Any, strict: bool = True) -> None:
+    d = Path(directory)
+    engine.load_model_state_dict(load_model_state_dict(d), strict=strict)
+    sharded = engine.parallelism == "zero" and ctx.world_size > 1
+    if sharded:
+        path = d / f"optimizer_shard{ctx.rank}.bin"
+        if not path.exists():
+            raise FileNotFoundError(f"{path} is missing: sharded optimizer state needs the same number of ranks on resume.")
+        engine.load_optimizer_state_dict(torch.load(path, map_location="cpu", weights_only=False))
+    else:
+        merged: dict[str, Any] = {}
+        for i in range(len(engine.optimizers)):
+            path = d / ("optimizer.bin" if i == 0 else f"optimizer_{i}.bin")
+            merged.update(torch.load(path, map_location="cpu", weights_only=False))
+        engine.load_optimizer_state_dict(merged)
+    ts = d / "trainer_state.bin"
+    if ts.exists():
+        trainer.load_state_dict(torch.load(ts, map_location="cpu", weights_only=False))
+    rng = d / f"random_states_{ctx.rank}.pkl"
+    if rng.exists():
+        with open(rng, "rb") as f:
+            restore_rng_state(pickle.load(f))
