@@ -415,18 +415,15 @@ class DebertaV2PreTrainedModel(PreTrainedModel):
 
     def _init_weights(self, module: nn.Module) -> None:
         """N(0, initializer_range) for matrices, zero biases and pad row, unit LayerNorm."""
+        from ._hf_init import init_embedding_, init_linear_, init_norm_
+
         std = float(self.config.initializer_range)
         if isinstance(module, nn.Linear):
-            module.weight.data.normal_(mean=0.0, std=std)
-            if module.bias is not None:
-                module.bias.data.zero_()
+            init_linear_(module, std)
         elif isinstance(module, nn.Embedding):
-            module.weight.data.normal_(mean=0.0, std=std)
-            if module.padding_idx is not None:
-                module.weight.data[module.padding_idx].zero_()
+            init_embedding_(module, std)
         elif isinstance(module, nn.LayerNorm):
-            module.weight.data.fill_(1.0)
-            module.bias.data.zero_()
+            init_norm_(module.weight, module.bias)
 
     def _set_gradient_checkpointing(self, module: nn.Module = None, value: bool = False, **_: Any) -> None:
         for m in self.modules():

@@ -231,17 +231,15 @@ class DebertaRoPEPreTrainedModel(PreTrainedModel):
     supports_gradient_checkpointing = True
 
     def _init_weights(self, module: nn.Module) -> None:
+        from ._hf_init import init_embedding_, init_linear_, init_norm_
+
         std = float(self.config.initializer_range)
         if isinstance(module, nn.Linear):
-            module.weight.data.normal_(mean=0.0, std=std)
-            if module.bias is not None:
-                module.bias.data.zero_()
+            init_linear_(module, std)
         elif isinstance(module, nn.Embedding):
-            module.weight.data.normal_(mean=0.0, std=std)
-            if module.padding_idx is not None:
-                module.weight.data[module.padding_idx].zero_()
+            init_embedding_(module, std)
         elif isinstance(module, RMSNorm):
-            module.weight.data.fill_(1.0)
+            init_norm_(module.weight)
 
     def _set_gradient_checkpointing(self, module: nn.Module = None, value: bool = False, **_: Any) -> None:
         for m in self.modules():

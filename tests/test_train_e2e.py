@@ -1,0 +1,96 @@
+"""End-to-end CPU runs through the public CLI: train → checkpoint → resume → export, and 2-rank gloo runs."""
+
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+CFG = ROOT / "configs" / "tiny_cpu_smoke_synthetic.yaml"
+
+
+def _train(args: list[str], env: dict | None = None, nproc: int = 1, port: int = 29611) -> subprocess.CompletedProcess:
+    base = [sys.executable]
+    if nproc > 1:
+        base += ["-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+                 "--master-port", str(port)]
+        base += ["-m", "deberta_b200"]
+    else:
+        base += ["-m", "deberta_b200"]
+    e = dict(os.environ, DEBERTA_FAST_EXIT_AFTER_TRAIN="0", PYTHONPATH=str(ROOT), CUDA_VISIBLE_DEVICES="")
+    e.update(env or {})
+    return subprocess.run(base + ["train", str(CFG), *args], capture_output=True, text=True, cwd=ROOT, env=e, timeout=600)
+
+
+def test_train_resume_export(tmp_path):
+    out = tmp_path / "run"
+    common = ["--train.checkpoint.output_dir", str(out), "--train.checkpoint.save_steps", "2", "--logging.logging_steps", "1",
+              "--train.checkpoint.save_total_limit", "2", "--logging.debug.metrics", "true"]
+    r = _train([*common, "--train.max_steps", "4", "--train.checkpoint.export_hf_final", "false"])
+    assert r.returncode == 0, r.stderr[-3000:]
+    assert (out / "checkpoint-4" / ".complete").read_text() == "ok\n"
+    assert sorted(p.name for p in out.glob("checkpoint-*")) == ["checkpoint-2", "checkpoint-4"]
+    state = json.loads((out / "checkpoint-4" / "data_state.json").read_text())
+    assert state["global_step"] == 4 and state["consumed_micro_batches"] == 4 and state["gradient_accumulation_steps"] == 1
+    assert set(state["optimizer_param_digest"]) == {"generator", "discriminator"}
+    assert json.loads((out / "run_metadata.json").read_text())["config_schema_version"] == 4
+    for name in ("model", "data", "train", "optim", "logging"):
+        assert (out / f"{name}_config.json").exists()
+    assert (out / "logs" / "config_original.yaml").exists() and (out / "logs" / "config_resolved.yaml").exists()
+    # resume: overwrite must be off, output dir is reused
+    r = _train([*common, "--train.max_steps", "6", "--train.checkpoint.overwrite_output_dir", "false",
+                "--train.checkpoint.resume_from_checkpoint", "auto"])
+    assert r.returncode == 0, r.stderr[-3000:]
+    assert "Resumed from" in r.stderr and (out / "checkpoint-6" / ".complete").exists()
+    assert sorted(p.name for p in out.glob("checkpoint-*")) == ["checkpoint-4", "checkpoint-6"]  # rotation keeps 2
+    hf = out / "final_hf"
+    assert (hf / "model.safetensors").exists() and (hf / "README.md").exists() and (hf / "export_meta.json").exists()
+    cfg = json.loads((hf / "config.json").read_text())
+    assert "use_rmsnorm_heads" not in cfg and cfg["model_type"] == "deberta-rope"
+    # the exported backbone loads and its word embeddings are generator table + discriminator delta
+    from safetensors.torch import load_file
+
+    from deberta_b200.models import DebertaRoPEModel
+
+    model = DebertaRoPEModel.from_pretrained(str(hf))
+    ck = load_file(str(out / "checkpoint-6" / "model.safetensors"))
+    want = ck["generator.embeddings.word_embeddings.weight"] + ck["discriminator.embeddings.word_embeddings.bias"]
+    torch.testing.assert_close(model.embeddings.word_embeddings.weight.data, want)
+    # a resume with a changed model must be refused
+    r = _train([*common, "--train.max_steps", "8", "--train.checkpoint.overwrite_output_dir", "false",
+                "--train.checkpoint.resume_from_checkpoint", "auto", "--model.rope.num_hidden_layers", "3"])
+    assert r.returncode != 0 and "Resume config mismatch" in r.stderr
+
+
+@pytest.mark.parametrize("parallelism", ["ddp", "zero"])
+def test_two_rank_gloo_matches_layout(tmp_path, parallelism):
+    out = tmp_path / f"run_{parallelism}"
+    r = _train(["--train.checkpoint.output_dir", str(out), "--train.max_steps", "3", "--train.checkpoint.save_steps", "0",
+                "--train.checkpoint.export_hf_final", "false", "--train.gradient_accumulation_steps", "2",
+                "--logging.logging_steps", "1"], env={"DEBERTA_PARALLELISM": parallelism}, nproc=2,
+               port=29611 + (parallelism == "zero"))
+    assert r.returncode == 0, r.stderr[-3000:]
+    ck = out / "checkpoint-3"
+    assert (ck / ".complete").exists() and (ck / "model.safetensors").exists()
+    names = {p.name for p in ck.iterdir()}
+    if parallelism == "zero":
+        assert {"optimizer_shard0.bin", "optimizer_shard1.bin"} <= names
+    else:
+        assert {"optimizer.bin", "optimizer_1.bin"} <= names
+    assert {"random_states_0.pkl", "random_states_1.pkl"} <= names
+    assert "step 3" in r.stderr
+
+
+def test_dry_run_reports_batch_shape(tmp_path, capsys):
+    from deberta_b200.cli import main
+
+    main(["train", str(CFG), "--dry-run", "--train.checkpoint.output_dir", str(tmp_path / "never")])
+    text = capsys.readouterr().out
+    assert "Dry-run preflight OK" in text and "sample_batch_shape=(4, 128)" in text
+    assert not (tmp_path / "never").exists()
