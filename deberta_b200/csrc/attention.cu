@@ -11,7 +11,8 @@
 // shared memory. Masking: optional key-padding flags or packed-document ids; inactive queries
 // produce zero rows. The position terms are optional, which gives plain (rotary) attention.
 //
-// Forward : grid (q-tiles, heads, batch), 128 threads, 2 CTAs per SM overlap MMA and softmax.
+// Forward : grid (q-tiles, heads, batch), 512 threads: four threads share a query row so that
+//           16 warps hide the latency of the softmax arithmetic.
 // Backward: grid (k-tiles, heads, batch); dK/dV accumulate in TMEM, dQ and the gradients of
 //           C2P / P2C are reduced into fp32 buffers with red.global.add.
 #include "tc05.cuh"
@@ -95,11 +96,34 @@ struct FwdSmem {
   static constexpr int kP = kV + kTileBytes;          // 128x128 bf16
   static constexpr int kBar = kP + 2 * kTileBytes;
   static constexpr int kMeta = kBar + 128;            // 128 ints of key metadata
-  static constexpr int kLut = kMeta + 512;            // 2 * (2S-1) uint16
+  static constexpr int kRed = kMeta + 512;            // 4 x 128 floats: per column-group row statistics
+  static constexpr int kLut = kRed + 2048;            // 2 * (2S-1) uint16
   static int total(int S, bool pos) { return kLut + (pos ? 2 * (2 * S) * 2 : 0) + 1024; }
 };
 
-__global__ void __launch_bounds__(128, 2)
+constexpr int kFwdThreads = 512;  // 16 warps: warp w owns rows of TMEM quadrant (w & 3), key columns 32*(w >> 2)...
+
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+// Four threads share a query row (one per 32-key column group of the tile); the row maximum is
+// exchanged through shared memory, the running sum stays per thread until the end.
+__global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnDev p) {
   extern __shared__ uint8_t smem_raw[];
@@ -116,11 +140,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* kmeta = reinterpret_cast<int*>(smem + FwdSmem::kMeta);
+  float* red = reinterpret_cast<float*>(smem + FwdSmem::kRed);  // [4][128] row maxima / sums per column group
   unsigned short* lutc = reinterpret_cast<unsigned short*>(smem + FwdSmem::kLut);
   unsigned short* lutp = lutc + 2 * p.S;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int quad = warp & 3;
+  const int part = warp >> 2;       // which 32 keys of the tile
+  const int row = quad * 32 + lane; // query row inside the tile
   const int q0 = blockIdx.x * kTile;
   const int h = blockIdx.y;
   const int b = blockIdx.z;
@@ -143,7 +172,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tmem_relinquish();
   }
   if (pos) {
-    for (int i = tid; i < 2 * S - 1; i += 128) {
+    for (int i = tid; i < 2 * S - 1; i += kFwdThreads) {
       lutc[i] = p.lut_c2p[i];
       lutp[i] = p.lut_p2c[i];
     }
@@ -154,7 +183,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_s = tmem_base;          // 128 columns: scores
   const uint32_t t_o = tmem_base + 128;    // 64 columns: output accumulator
-  const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+  const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
 
   if (tid == 0) {
     tma_prefetch_desc(&tm_q);
@@ -168,7 +197,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tma_load_3d(sV, &tm_v, bar_v, h * kD, 0, b);
   }
 
-  const int q = q0 + tid;
+  const int q = q0 + row;
   const bool q_valid = q < S;
   const long long tq = static_cast<long long>(b) * S + (q_valid ? q : 0);
   int q_doc = 1;
@@ -180,7 +209,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   const long long pos_row = static_cast<long long>(p.heads) * p.span2;
   const __nv_bfloat16* c2p_row = p.c2p ? p.c2p + tq * pos_row + static_cast<long long>(h) * p.span2 : nullptr;
-
   const uint4* bias_row = p.bias ? reinterpret_cast<const uint4*>(
                                        p.bias + ((static_cast<long long>(b) * p.heads + h) * S + (q_valid ? q : 0)) * p.ldb)
                                  : nullptr;
@@ -189,8 +217,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   constexpr uint32_t idesc_o = make_idesc_bf16(128, 64, false, true);
   bool ok = true;
 
-  // first score tile
-  if (tid == 0) {
+  if (tid == 0) {  // first score tile
     ok = mbar_wait(bar_q, 0, abort_flag, p.status, kErrFullWait) &&
          mbar_wait(&bar_k[0], 0, abort_flag, p.status, kErrFullWait);
     if (ok) {
@@ -203,10 +230,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     umma_commit(bar_s);
   }
 
-  float m_run = -INFINITY, l_run = 0.f;
+  float m_run = -INFINITY, l_part = 0.f;
   for (int j = 0; j < nkt; ++j) {
     const int k0 = j * kTile;
-    {  // key metadata of this tile: 0 = masked, otherwise doc id (or 1)
+    if (tid < kTile) {  // key metadata of this tile: 0 = masked, otherwise doc id (or 1)
       const int kk = k0 + tid;
       int meta = 0;
       if (kk < S) {
@@ -221,29 +248,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (!mbar_wait(bar_s, j & 1, abort_flag, p.status, kErrAccFullWait)) { ok = false; break; }
     tc_fence_after();
 
-    float s[128];
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    float s[32];
+    {
       uint32_t r[32];
-      tmem_ld_32x32b_x32(t_s + lane_addr + c * 32, r);
+      tmem_ld_32x32b_x32(t_s + lane_addr + part * 32, r);
       tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]);
+      for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(r[i]);
     }
     float tmax = -INFINITY;
     {
-      const int dbase = q - k0 + S - 1;  // lut index for k = k0
+      const int kb = k0 + part * 32;           // first key of this thread's column group
+      const int dbase = q - kb + S - 1;        // lut index for that key
       uint4 bvec = make_uint4(0, 0, 0, 0);
       const __nv_bfloat16* p2c_base =
-          p.p2c ? p.p2c + (static_cast<long long>(b) * S + k0) * pos_row + static_cast<long long>(h) * p.span2 : nullptr;
+          p.p2c ? p.p2c + (static_cast<long long>(b) * S + kb) * pos_row + static_cast<long long>(h) * p.span2 : nullptr;
 #pragma unroll
-      for (int k = 0; k < 128; ++k) {
-        const int meta = kmeta[k];
+      for (int k = 0; k < 32; ++k) {
+        const int meta = kmeta[part * 32 + k];
         bool keep = meta != 0;
         if (p.doc_ids) keep = keep && (meta == q_doc);
         float v = s[k];
         if (bias_row) {
-          if ((k & 7) == 0) bvec = __ldg(bias_row + ((k0 + k) >> 3));
+          if ((k & 7) == 0) bvec = __ldg(bias_row + ((kb + k) >> 3));
           v += bf16_elem(bvec, k & 7);
         } else if (pos && keep && q_valid) {
           const int di = dbase - k;
@@ -255,32 +282,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmax = fmaxf(tmax, v);
       }
     }
+    red[part * kTile + row] = tmax;
+    __syncthreads();
+    tmax = fmaxf(fmaxf(red[row], red[kTile + row]), fmaxf(red[2 * kTile + row], red[3 * kTile + row]));
     const float m_new = fmaxf(m_run, tmax);
     const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
     const float alpha = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_use);
     float lsum = 0.f;
 #pragma unroll
-    for (int k = 0; k < 128; ++k) {
+    for (int k = 0; k < 32; ++k) {
       s[k] = ex2(s[k] - m_use);
       lsum += s[k];
     }
-    l_run = l_run * alpha + lsum;
+    l_part = l_part * alpha + lsum;
     m_run = m_new;
 
     if (j > 0) {
       if (!mbar_wait(bar_o, (j - 1) & 1, abort_flag, p.status, kErrAccFullWait)) { ok = false; break; }
       tc_fence_after();
-      // rescale the running output when any row of this warp raised its maximum
+      // rescale the running output (16 of its 64 columns per thread) when a row of this warp raised its maximum
       if (__any_sync(0xffffffffu, alpha != 1.f)) {
+        uint32_t r[16];
+        tmem_ld_32x32b_x16(t_o + lane_addr + part * 16, r);
+        tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(t_o + lane_addr + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st_32x32b_x32(t_o + lane_addr + c * 32, r);
-        }
+        for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+        tmem_st_32x32b_x16(t_o + lane_addr + part * 16, r);
         tmem_st_wait();
       }
     }
@@ -295,7 +322,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tma_load_3d(sK + nb * kTileBytes, &tm_k, &bar_k[nb], h * kD, k0 + kTile, b);
       }
     }
-    store_row_bf16_sw128(sP, tid, s);
+    // this thread's 32 probabilities: 4 chunks of 8 bf16 in 64-key block (part >> 1)
+#pragma unroll
+    for (int g4 = 0; g4 < 4; ++g4) {
+      uint4 u;
+      u.x = pack_bf16(s[g4 * 8 + 0], s[g4 * 8 + 1]);
+      u.y = pack_bf16(s[g4 * 8 + 2], s[g4 * 8 + 3]);
+      u.z = pack_bf16(s[g4 * 8 + 4], s[g4 * 8 + 5]);
+      u.w = pack_bf16(s[g4 * 8 + 6], s[g4 * 8 + 7]);
+      *reinterpret_cast<uint4*>(sP + (part >> 1) * kTileBytes + swz128(row, (part & 1) * 4 + g4)) = u;
+    }
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
@@ -325,28 +361,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   }
 
+  // row sums: combine the four column groups
+  __syncthreads();
+  red[part * kTile + row] = l_part;
+  __syncthreads();
+  const float l_run = red[row] + red[kTile + row] + red[2 * kTile + row] + red[3 * kTile + row];
   if (ok && mbar_wait(bar_o, (nkt - 1) & 1, abort_flag, p.status, kErrAccFullWait)) {
     tc_fence_after();
     const float inv = (q_live && l_run > 0.f) ? 1.f / l_run : 0.f;
-    __nv_bfloat16* o = p.out + tq * p.ldo + h * kD;
+    __nv_bfloat16* o = p.out + tq * p.ldo + h * kD + part * 16;
+    uint32_t r[16];
+    tmem_ld_32x32b_x16(t_o + lane_addr + part * 16, r);
+    tmem_ld_wait();
+    if (q_valid) {
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      uint32_t r[32];
-      tmem_ld_32x32b_x32(t_o + lane_addr + c * 32, r);
-      tmem_ld_wait();
-      if (q_valid) {
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 u;
-          u.x = pack_bf16(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
-          u.y = pack_bf16(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
-          u.z = pack_bf16(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
-          u.w = pack_bf16(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
-          reinterpret_cast<uint4*>(o + c * 32)[g] = u;
-        }
+      for (int g = 0; g < 2; ++g) {
+        uint4 u;
+        u.x = pack_bf16(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
+        u.y = pack_bf16(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
+        u.z = pack_bf16(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
+        u.w = pack_bf16(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
+        reinterpret_cast<uint4*>(o)[g] = u;
       }
     }
-    if (q_valid && p.lse)
+    if (q_valid && part == 0 && p.lse)
       p.lse[(static_cast<long long>(b) * p.heads + h) * S + q] =
           (q_live && l_run > 0.f) ? (m_run + log2f(l_run)) : INFINITY;
   }
@@ -357,7 +395,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tmem_dealloc(tmem_base, 256);
   }
 }
-
 
 // --------------------------------------------------------------------------------------------
 // backward
@@ -402,7 +439,9 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-__global__ void __launch_bounds__(128, 1)
+constexpr int kBwdThreads = 512;  // warp w: TMEM lane quadrant (w & 3), 32-key column group (w >> 2)
+
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                 const AttnBwdDev p) {
@@ -426,6 +465,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int quad = warp & 3;
+  const int part = warp >> 2;
+  const int row = quad * 32 + lane;  // row of the tile this thread works on (query row, or key row at the end)
   const int k0 = blockIdx.x * kTile;
   const int h = blockIdx.y;
   const int b = blockIdx.z;
@@ -447,12 +490,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tmem_relinquish();
   }
   if (pos) {
-    for (int i = tid; i < 2 * S - 1; i += 128) {
+    for (int i = tid; i < 2 * S - 1; i += kBwdThreads) {
       lutc[i] = p.lut_c2p[i];
       lutp[i] = p.lut_p2c[i];
     }
   }
-  {
+  if (tid < kTile) {
     const int kk = k0 + tid;
     int meta = 0;
     if (kk < S) {
@@ -469,7 +512,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 320,
                  t_dq = tmem_base + 384;
-  const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+  const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
   const long long pos_row = static_cast<long long>(p.heads) * p.span2;
 
   constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);    // Q·Kᵀ, dO·Vᵀ
@@ -509,20 +552,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   }
 
-  auto flush_dq = [&](int qt) {  // dQ of q-tile `qt` from TMEM into the fp32 accumulator
-    const int q = qt * kTile + tid;
+  auto flush_dq = [&](int qt) {  // dQ of q-tile `qt` from TMEM into the fp32 accumulator (16 columns per thread)
+    const int q = qt * kTile + row;
+    uint32_t r[16];
+    tmem_ld_32x32b_x16(t_dq + lane_addr + part * 16, r);
+    tmem_ld_wait();
+    if (q < S) {
+      float* dst = p.dq_acc + (static_cast<long long>(b) * S + q) * (static_cast<long long>(p.heads) * kD) + h * kD + part * 16;
 #pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      uint32_t r[32];
-      tmem_ld_32x32b_x32(t_dq + lane_addr + c * 32, r);
-      tmem_ld_wait();
-      if (q < S) {
-        float* dst = p.dq_acc + (static_cast<long long>(b) * S + q) * (static_cast<long long>(p.heads) * kD) + h * kD + c * 32;
-#pragma unroll
-        for (int g = 0; g < 8; ++g)
-          red_add_v4(dst + g * 4, __uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]), __uint_as_float(r[g * 4 + 2]),
-                     __uint_as_float(r[g * 4 + 3]));
-      }
+      for (int g = 0; g < 4; ++g)
+        red_add_v4(dst + g * 4, __uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]), __uint_as_float(r[g * 4 + 2]),
+                   __uint_as_float(r[g * 4 + 3]));
     }
   };
 
@@ -541,7 +581,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     if (i > 0) flush_dq(i - 1);
 
-    const int q = q0 + tid;
+    const int q = q0 + row;
     const bool q_valid = q < S;
     const long long tq = static_cast<long long>(b) * S + (q_valid ? q : 0);
     int q_doc = 1;
@@ -557,8 +597,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint4* bias_row = p.bias ? reinterpret_cast<const uint4*>(p.bias + brow_off) : nullptr;
     uint4* dbias_row = (p.dbias && q_valid) ? reinterpret_cast<uint4*>(p.dbias + brow_off) : nullptr;
 
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    {
+      const int c = part;  // this thread's 32 keys of the tile
       uint32_t rs[32], rd[32];
       tmem_ld_32x32b_x32(t_s + lane_addr + c * 32, rs);
       tmem_ld_32x32b_x32(t_dp + lane_addr + c * 32, rd);
@@ -596,7 +636,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
       for (int g4 = 0; g4 < 4; ++g4) {
         const int chunk = (c & 1) * 4 + g4;
-        const uint32_t off = (c >> 1) * kTileBytes + swz128(tid, chunk);
+        const uint32_t off = (c >> 1) * kTileBytes + swz128(row, chunk);
         uint4 u;
         u.x = pack_bf16(pv[g4 * 8 + 0], pv[g4 * 8 + 1]);
         u.y = pack_bf16(pv[g4 * 8 + 2], pv[g4 * 8 + 3]);
@@ -646,26 +686,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (ok && mbar_wait(bar_g, (nqt - 1) & 1, abort_flag, p.status, kErrAccFullWait)) {
     tc_fence_after();
     flush_dq(nqt - 1);
-    const int kk = k0 + tid;
+    const int kk = k0 + row;
     const long long tk = static_cast<long long>(b) * S + kk;
 #pragma unroll
     for (int which = 0; which < 2; ++which) {
-      __nv_bfloat16* dst = which == 0 ? p.dv + tk * p.ldv + h * kD : p.dk + tk * p.ldk + h * kD;
+      __nv_bfloat16* dst = (which == 0 ? p.dv + tk * p.ldv : p.dk + tk * p.ldk) + h * kD + part * 16;
+      uint32_t r[16];
+      tmem_ld_32x32b_x16((which == 0 ? t_dv : t_dk) + lane_addr + part * 16, r);
+      tmem_ld_wait();
+      if (kk < S) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32((which == 0 ? t_dv : t_dk) + lane_addr + c * 32, r);
-        tmem_ld_wait();
-        if (kk < S) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 u;
-            u.x = pack_bf16(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
-            u.y = pack_bf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
-            u.z = pack_bf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
-            u.w = pack_bf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
-            reinterpret_cast<uint4*>(dst + c * 32)[g] = u;
-          }
+        for (int g = 0; g < 2; ++g) {
+          uint4 u;
+          u.x = pack_bf16(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
+          u.y = pack_bf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
+          u.z = pack_bf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
+          u.w = pack_bf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
+          reinterpret_cast<uint4*>(dst)[g] = u;
         }
       }
     }
@@ -725,7 +762,7 @@ extern "C" int db200_attn_fwd(const AttnArgs* a, void* stream_) {
     configured = smem;
   }
   dim3 grid((a->S + kTile - 1) / kTile, a->heads, a->B);
-  attn_fwd_kernel<<<grid, 128, smem, stream>>>(tq, tk, tv, d);
+  attn_fwd_kernel<<<grid, kFwdThreads, smem, stream>>>(tq, tk, tv, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -774,6 +811,6 @@ extern "C" int db200_attn_bwd(const AttnArgs* a, void* stream_) {
     configured = smem;
   }
   dim3 grid((a->S + kTile - 1) / kTile, a->heads, a->B);
-  attn_bwd_kernel<<<grid, 128, smem, stream>>>(tq, tk, tv, tdo, d);
+  attn_bwd_kernel<<<grid, kBwdThreads, smem, stream>>>(tq, tk, tv, tdo, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -2,10 +2,11 @@
 //
 //   D[M,N] = alpha * sum_k A[m,k] * B[n,k]   (fp32 accumulation in TMEM)
 //
-// Roles inside one 192-thread CTA (one CTA per SM, static round-robin over tiles):
+// Roles inside one 320-thread CTA (one CTA per SM, static round-robin over tiles):
 //   warp 0      : TMA producer  (cp.async.bulk.tensor -> 128B-swizzled smem ring)
 //   warp 1      : tcgen05.mma issuer + TMEM owner (two accumulator buffers)
-//   warps 2..5  : epilogue (tcgen05.ld -> bias / GELU / residual / dGELU -> global)
+//   warps 2..9  : epilogue (tcgen05.ld -> bias / GELU / residual / dGELU -> global); two warps per
+//                 TMEM lane quadrant split the tile's columns so the epilogue is not latency-bound
 // The accumulator is double-buffered in TMEM so the epilogue of tile i overlaps the
 // main loop of tile i+1.
 //
@@ -26,7 +27,8 @@ using namespace tc05;
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 8;  // two per TMEM lane quadrant, each owning half of the tile's columns
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 
 template <int BN>
 struct SmemLayout {
@@ -107,7 +109,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 128);
+      mbar_init(&acc_empty[a], 32 * kEpilogueWarps);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -212,6 +214,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else {
     // ------------------------------- epilogue -----------------------------------
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;  // which half of the tile's columns
+    constexpr int kChunksPerHalf = BN / 64;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -239,7 +243,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         float t_max = -INFINITY, t_sum = 0.f, best = -INFINITY;
         int best_idx = 0;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = half * kChunksPerHalf; c < (half + 1) * kChunksPerHalf; ++c) {
           const int nc = n0 + c * 32;
           if (nc >= p.N) break;
           uint32_t r[32];
@@ -300,9 +304,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
           }
         }
-        if (p.epi == EPI_CE_FWD && row_ok) {
-          const long long tn = n0 / BN;
-          const long long plane = static_cast<long long>(p.tiles_n) * p.M;
+        if (p.epi == EPI_CE_FWD && row_ok && (n0 + half * (BN / 2) < p.N)) {
+          // partial results are kept per half tile: ceil(N / (BN/2)) entries per row
+          const long long tn = (n0 / BN) * 2 + half;
+          const long long plane = static_cast<long long>((p.N + BN / 2 - 1) / (BN / 2)) * p.M;
           float* dst = p.ce_part + tn * p.M + row;
           dst[0] = t_max;
           dst[plane] = t_sum;
@@ -315,7 +320,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         continue;
       }
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * kChunksPerHalf; c < (half + 1) * kChunksPerHalf; ++c) {
         const int nc = n0 + c * 32;
         if (nc >= p.N) break;  // warp-uniform
         uint32_t r[32];
@@ -521,7 +526,8 @@ int db200_make_tmap_bf16(CUtensorMap* out, const void* ptr, long long inner, lon
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
-extern "C" int db200_gemm_tile_n(int N) { return (N > 128) ? 256 : 128; }
+// Width of the column range one partial result of EPI_CE_FWD covers (half of the GEMM tile).
+extern "C" int db200_gemm_tile_n(int N) { return (N > 128) ? 128 : 64; }
 
 // Combine the per-vocabulary-tile partials of EPI_CE_FWD: per row log-sum-exp (natural log),
 // cross-entropy against the label logit, and the arg-max of the noisy logits (the sample).

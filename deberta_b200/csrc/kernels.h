@@ -34,7 +34,7 @@ typedef struct GemmArgs {
   const void* forbidden;     // uint8 [N] or null
   float inv_temp;
   unsigned long long seed;
-  float* ce_part;            // fp32 [4, ceil(N / tile_n), M] scratch (EPI_CE_FWD)
+  float* ce_part;            // fp32 [4, ceil(N / db200_gemm_tile_n(N)), M] scratch (EPI_CE_FWD)
   float* label_logit;        // fp32 [M]                       (EPI_CE_FWD)
   const float* row_lse;      // fp32 [M]                       (EPI_CE_BWD)
   float gscale;              // scale of the logit gradient     (EPI_CE_BWD)
@@ -42,7 +42,7 @@ typedef struct GemmArgs {
 } GemmArgs;
 
 int db200_gemm_bf16(const GemmArgs* args, void* stream);
-int db200_gemm_tile_n(int N);  // vocabulary-tile width the GEMM uses for N columns
+int db200_gemm_tile_n(int N);  // width of the vocabulary range one EPI_CE_FWD partial covers
 int db200_ce_combine(const float* part, const float* label_logit, int tiles_n, int M, float* lse, float* loss_rows,
                      long long* sampled, void* stream);
 
@@ -52,6 +52,10 @@ int db200_norm_fwd(const void* x, const void* gamma, const void* beta, const voi
 int db200_norm_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
                    const void* row_keep, void* dx, float* dgamma, float* dbeta, int rows, int H, int rms,
                    void* stream);
+
+// ----- reductions ----------------------------------------------------------------------------
+// out_accum[n] += sum_m x[m, n]   (x bf16 [M, N] with leading dim ld, out fp32 [N])
+int db200_colsum_bf16(const void* x, long long ld, int M, int N, float* out_accum, void* stream);
 
 // ----- optimizer (flat fp32 ranges) ---------------------------------------------------------
 int db200_sumsq(const float* g, long long n, float* out_accum, void* stream);

@@ -86,11 +86,12 @@ class _VocabCE(torch.autograd.Function):
         dw = _weight_grad(dlogits, x, weight) if weight.requires_grad else None
         db = None
         if bias is not None and bias.requires_grad:
-            gb = dlogits.sum(dim=0, dtype=torch.float32)
+            from .linear import colsum_into
+
             main = getattr(bias, "main_grad", None)
-            if main is not None:
-                main.add_(gb)
-            else:
+            gb = main if main is not None else torch.zeros(V, dtype=torch.float32, device=x.device)
+            colsum_into(dlogits, gb)
+            if main is None:
                 db = gb.to(bias.dtype)
         return dx, dw, db, None, None, None
 

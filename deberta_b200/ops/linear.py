@@ -31,11 +31,29 @@ def _weight_grad(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Te
     return gemm(dy, x, a_mn=True, b_mn=True, out_dtype=torch.float32).to(w.dtype)
 
 
+def colsum_into(dy: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[n] += Σ_m dy[m, n]`` (bf16 in, fp32 accumulate) on the column-sum kernel."""
+    import ctypes
+
+    from . import _lib
+
+    _lib.call("db200_colsum_bf16", _lib.ptr(dy), ctypes.c_longlong(dy.stride(0)), ctypes.c_int(dy.shape[0]),
+              ctypes.c_int(dy.shape[1]), _lib.ptr(out), _lib.stream_ptr())
+
+
 def _bias_grad(dy: torch.Tensor, b: torch.Tensor | None) -> torch.Tensor | None:
     if b is None:
         return None
-    g = dy.sum(dim=0, dtype=torch.float32)
     main = getattr(b, "main_grad", None)
+    kernel_ok = dy.is_cuda and dy.dtype == torch.bfloat16 and dy.stride(1) == 1 and dy.stride(0) % 8 == 0 and dy.data_ptr() % 16 == 0
+    if main is not None and kernel_ok:
+        colsum_into(dy, main)
+        return None
+    if kernel_ok:
+        g = torch.zeros(dy.shape[1], dtype=torch.float32, device=dy.device)
+        colsum_into(dy, g)
+    else:
+        g = dy.sum(dim=0, dtype=torch.float32)
     if main is not None:
         main.add_(g)
         return None
