@@ -92,8 +92,8 @@ __device__ __forceinline__ void store_row_bf16_sw128(uint8_t* tile, int row, con
 struct FwdSmem {
   static constexpr int kQ = 0;
   static constexpr int kK = kQ + kTileBytes;          // 2 buffers
-  static constexpr int kV = kK + 2 * kTileBytes;      // 1 buffer (keeps two CTAs resident per SM)
-  static constexpr int kP = kV + kTileBytes;          // 128x128 bf16
+  static constexpr int kV = kK + 2 * kTileBytes;      // 2 buffers
+  static constexpr int kP = kV + 2 * kTileBytes;      // 128x128 bf16
   static constexpr int kBar = kP + 2 * kTileBytes;
   static constexpr int kMeta = kBar + 128;            // 128 ints of key metadata
   static constexpr int kRed = kMeta + 512;            // 4 x 128 floats: per column-group row statistics
@@ -134,10 +134,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* sP = smem + FwdSmem::kP;
   uint64_t* bar_q = reinterpret_cast<uint64_t*>(smem + FwdSmem::kBar);
   uint64_t* bar_k = bar_q + 1;  // [2]
-  uint64_t* bar_v = bar_q + 3;
-  uint64_t* bar_s = bar_q + 4;
-  uint64_t* bar_o = bar_q + 5;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 6);
+  uint64_t* bar_v = bar_q + 3;  // [2]
+  uint64_t* bar_s = bar_q + 5;
+  uint64_t* bar_o = bar_q + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 7);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* kmeta = reinterpret_cast<int*>(smem + FwdSmem::kMeta);
   float* red = reinterpret_cast<float*>(smem + FwdSmem::kRed);  // [4][128] row maxima / sums per column group
@@ -161,7 +161,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(bar_q, 1);
     mbar_init(&bar_k[0], 1);
     mbar_init(&bar_k[1], 1);
-    mbar_init(bar_v, 1);
+    mbar_init(&bar_v[0], 1);
+    mbar_init(&bar_v[1], 1);
     mbar_init(bar_s, 1);
     mbar_init(bar_o, 1);
     *abort_flag = 0;
@@ -193,8 +194,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tma_load_3d(sQ, &tm_q, bar_q, h * kD, q0, b);
     mbar_expect_tx(&bar_k[0], kTileBytes);
     tma_load_3d(sK, &tm_k, &bar_k[0], h * kD, 0, b);
-    mbar_expect_tx(bar_v, kTileBytes);
-    tma_load_3d(sV, &tm_v, bar_v, h * kD, 0, b);
+    mbar_expect_tx(&bar_v[0], kTileBytes);
+    tma_load_3d(sV, &tm_v, &bar_v[0], h * kD, 0, b);
+    if (nkt > 1) {  // second tile of K and V straight away: both buffers start empty
+      mbar_expect_tx(&bar_k[1], kTileBytes);
+      tma_load_3d(sK + kTileBytes, &tm_k, &bar_k[1], h * kD, kTile, b);
+      mbar_expect_tx(&bar_v[1], kTileBytes);
+      tma_load_3d(sV + kTileBytes, &tm_v, &bar_v[1], h * kD, kTile, b);
+    }
   }
 
   const int q = q0 + row;
@@ -283,7 +290,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
     red[part * kTile + row] = tmax;
-    __syncthreads();
+    tc_fence_before();
+    __syncthreads();  // every thread has read its scores of tile j: the score accumulator is free again
+    if (tid == 0 && j + 1 < nkt) {  // scores of the next tile run on the tensor core during this tile's softmax
+      const int nb = (j + 1) & 1;
+      if (mbar_wait(&bar_k[nb], ((j + 1) >> 1) & 1, abort_flag, p.status, kErrFullWait)) {
+        tc_fence_after();
+        const uint32_t kb2 = smem_u32(sK + nb * kTileBytes);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_bf16(t_s, make_smem_desc(smem_u32(sQ) + ks * 32, 16, 1024), make_smem_desc(kb2 + ks * 32, 16, 1024),
+                    idesc_s, ks > 0);
+      }
+      umma_commit(bar_s);
+    }
     tmax = fmaxf(fmaxf(red[row], red[kTile + row]), fmaxf(red[2 * kTile + row], red[3 * kTile + row]));
     const float m_new = fmaxf(m_run, tmax);
     const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
@@ -311,16 +331,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmem_st_wait();
       }
     }
-    if (tid == 0) {
-      if (j > 0) {  // P·V of tile j-1 retired: its V tile can be replaced by this tile's
-        mbar_expect_tx(bar_v, kTileBytes);
-        tma_load_3d(sV, &tm_v, bar_v, h * kD, k0, b);
-      }
-      if (j + 1 < nkt) {  // the other K buffer was last read by the scores of tile j-1
-        const int nb = (j + 1) & 1;
-        mbar_expect_tx(&bar_k[nb], kTileBytes);
-        tma_load_3d(sK + nb * kTileBytes, &tm_k, &bar_k[nb], h * kD, k0 + kTile, b);
-      }
+    if (tid == 0 && j > 0 && j + 1 < nkt) {
+      // P·V of tile j-1 and the scores of tile j have retired: buffer (j+1)&1 of V and of K is free for tile j+1
+      const int nb = (j + 1) & 1;
+      mbar_expect_tx(&bar_v[nb], kTileBytes);
+      tma_load_3d(sV + nb * kTileBytes, &tm_v, &bar_v[nb], h * kD, k0 + kTile, b);
     }
     // this thread's 32 probabilities: 4 chunks of 8 bf16 in 64-key block (part >> 1)
 #pragma unroll
@@ -336,9 +351,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     if (tid == 0) {
-      const bool v_ok = mbar_wait(bar_v, j & 1, abort_flag, p.status, kErrFullWait);
+      const bool v_ok = mbar_wait(&bar_v[j & 1], (j >> 1) & 1, abort_flag, p.status, kErrFullWait);
       tc_fence_after();
-      const uint32_t pv = smem_u32(sV);
+      const uint32_t pv = smem_u32(sV + (j & 1) * kTileBytes);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         if (!v_ok) break;
@@ -346,17 +361,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                   make_smem_desc(pv + ks * 2048, 8192, 1024), idesc_o, (j > 0) || (ks > 0));
       }
       umma_commit(bar_o);
-      if (j + 1 < nkt) {
-        const int nb = (j + 1) & 1;
-        if (mbar_wait(&bar_k[nb], ((j + 1) >> 1) & 1, abort_flag, p.status, kErrFullWait)) {
-          tc_fence_after();
-          const uint32_t kb = smem_u32(sK + nb * kTileBytes);
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_bf16(t_s, make_smem_desc(smem_u32(sQ) + ks * 32, 16, 1024), make_smem_desc(kb + ks * 32, 16, 1024),
-                      idesc_s, ks > 0);
-        }
-        umma_commit(bar_s);
+      if (j + 2 < nkt) {  // K buffer j&1 was read by the scores of tile j (retired before this tile's softmax ended)
+        mbar_expect_tx(&bar_k[j & 1], kTileBytes);
+        tma_load_3d(sK + (j & 1) * kTileBytes, &tm_k, &bar_k[j & 1], h * kD, k0 + 2 * kTile, b);
       }
     }
   }
@@ -425,9 +432,9 @@ struct AttnBwdDev {
 struct BwdSmem {
   static constexpr int kK = 0;
   static constexpr int kV = kK + kTileBytes;
-  static constexpr int kQ = kV + kTileBytes;           // 2 buffers
-  static constexpr int kdO = kQ + 2 * kTileBytes;      // 2 buffers
-  static constexpr int kP = kdO + 2 * kTileBytes;      // 128x128 bf16
+  static constexpr int kQ = kV + kTileBytes;           // 3 buffers
+  static constexpr int kdO = kQ + 3 * kTileBytes;      // 3 buffers
+  static constexpr int kP = kdO + 3 * kTileBytes;      // 128x128 bf16
   static constexpr int kdS = kP + 2 * kTileBytes;      // 128x128 bf16
   static constexpr int kBar = kdS + 2 * kTileBytes;
   static constexpr int kMeta = kBar + 128;
@@ -454,10 +461,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* sP = smem + BwdSmem::kP;
   uint8_t* sdS = smem + BwdSmem::kdS;
   uint64_t* bar_kv = reinterpret_cast<uint64_t*>(smem + BwdSmem::kBar);
-  uint64_t* bar_qd = bar_kv + 1;  // [2]
-  uint64_t* bar_s = bar_kv + 3;
-  uint64_t* bar_g = bar_kv + 4;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_kv + 5);
+  uint64_t* bar_qd = bar_kv + 1;  // [3]
+  uint64_t* bar_s = bar_kv + 4;
+  uint64_t* bar_g = bar_kv + 5;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_kv + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* kmeta = reinterpret_cast<int*>(smem + BwdSmem::kMeta);
   unsigned short* lutc = reinterpret_cast<unsigned short*>(smem + BwdSmem::kLut);
@@ -480,6 +487,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(bar_kv, 1);
     mbar_init(&bar_qd[0], 1);
     mbar_init(&bar_qd[1], 1);
+    mbar_init(&bar_qd[2], 1);
     mbar_init(bar_s, 1);
     mbar_init(bar_g, 1);
     *abort_flag = 0;
@@ -543,6 +551,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_expect_tx(&bar_qd[0], 2 * kTileBytes);
     tma_load_3d(sQ, &tm_q, &bar_qd[0], h * kD, 0, b);
     tma_load_3d(sdO, &tm_do, &bar_qd[0], h * kD, 0, b);
+    if (nqt > 1) {
+      mbar_expect_tx(&bar_qd[1], 2 * kTileBytes);
+      tma_load_3d(sQ + kTileBytes, &tm_q, &bar_qd[1], h * kD, kTile, b);
+      tma_load_3d(sdO + kTileBytes, &tm_do, &bar_qd[1], h * kD, kTile, b);
+    }
     if (mbar_wait(bar_kv, 0, abort_flag, p.status, kErrFullWait) &&
         mbar_wait(&bar_qd[0], 0, abort_flag, p.status, kErrFullWait)) {
       tc_fence_after();
@@ -568,18 +581,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   bool ok = true;
   for (int i = 0; i < nqt; ++i) {
-    const int buf = i & 1;
+    const int buf = i % 3;
     const int q0 = i * kTile;
     if (!mbar_wait(bar_s, i & 1, abort_flag, p.status, kErrAccFullWait)) { ok = false; break; }
-    if (i > 0 && !mbar_wait(bar_g, (i - 1) & 1, abort_flag, p.status, kErrAccFullWait)) { ok = false; break; }
     tc_fence_after();
-    if (tid == 0 && i + 1 < nqt) {  // tile i-1 retired: its Q / dO buffers can take tile i+1
-      const int nb = (i + 1) & 1;
-      mbar_expect_tx(&bar_qd[nb], 2 * kTileBytes);
-      tma_load_3d(sQ + nb * kTileBytes, &tm_q, &bar_qd[nb], h * kD, q0 + kTile, b);
-      tma_load_3d(sdO + nb * kTileBytes, &tm_do, &bar_qd[nb], h * kD, q0 + kTile, b);
+    uint32_t rs[32], rd[32];  // this thread's 32 scores and 32 dP values of tile i
+    tmem_ld_32x32b_x32(t_s + lane_addr + part * 32, rs);
+    tmem_ld_32x32b_x32(t_dp + lane_addr + part * 32, rd);
+    tmem_ld_wait();
+    tc_fence_before();
+    __syncthreads();  // both accumulators are in registers: the tensor core may start on tile i+1
+    if (tid == 0 && i + 1 < nqt) {
+      const int nb = (i + 1) % 3;
+      if (mbar_wait(&bar_qd[nb], ((i + 1) / 3) & 1, abort_flag, p.status, kErrFullWait)) {
+        tc_fence_after();
+        issue_scores(nb);
+      } else {
+        umma_commit(bar_s);
+      }
     }
-    if (i > 0) flush_dq(i - 1);
 
     const int q = q0 + row;
     const bool q_valid = q < S;
@@ -599,10 +619,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
     {
       const int c = part;  // this thread's 32 keys of the tile
-      uint32_t rs[32], rd[32];
-      tmem_ld_32x32b_x32(t_s + lane_addr + c * 32, rs);
-      tmem_ld_32x32b_x32(t_dp + lane_addr + c * 32, rd);
-      tmem_ld_wait();
       float pv[32], gv[32];
       uint4 bvec = make_uint4(0, 0, 0, 0);
 #pragma unroll
@@ -631,6 +647,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (dc2p_row) atomicAdd(dc2p_row + ic, g);
           if (p.d_p2c) atomicAdd(p.d_p2c + kbase + static_cast<long long>(k) * pos_row + ip, g);
         }
+      }
+      // the previous tile's gradient MMAs must retire before its P / dS tiles and dQ accumulator are reused
+      if (i > 0) {
+        if (!mbar_wait(bar_g, (i - 1) & 1, abort_flag, p.status, kErrAccFullWait)) { ok = false; break; }
+        tc_fence_after();
+        if (tid == 0 && i + 2 < nqt) {  // buffer (i+2)%3 held tile i-1
+          const int nb = (i + 2) % 3;
+          mbar_expect_tx(&bar_qd[nb], 2 * kTileBytes);
+          tma_load_3d(sQ + nb * kTileBytes, &tm_q, &bar_qd[nb], h * kD, q0 + 2 * kTile, b);
+          tma_load_3d(sdO + nb * kTileBytes, &tm_do, &bar_qd[nb], h * kD, q0 + 2 * kTile, b);
+        }
+        flush_dq(i - 1);
+      } else if (tid == 0 && nqt > 2) {
+        mbar_expect_tx(&bar_qd[2], 2 * kTileBytes);
+        tma_load_3d(sQ + 2 * kTileBytes, &tm_q, &bar_qd[2], h * kD, 2 * kTile, b);
+        tma_load_3d(sdO + 2 * kTileBytes, &tm_do, &bar_qd[2], h * kD, 2 * kTile, b);
       }
       // rows of P and dS for these 32 keys: 4 chunks of 8 bf16 inside 64-key block (c >> 1)
 #pragma unroll
@@ -671,15 +703,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         umma_bf16(t_dq, make_smem_desc(sds + (ks >> 2) * kTileBytes + (ks & 3) * 32, 16, 1024),
                   make_smem_desc(sk + ks * 2048, 8192, 1024), idesc_q, ks > 0);
       umma_commit(bar_g);
-      if (i + 1 < nqt) {
-        const int nb = (i + 1) & 1;
-        if (mbar_wait(&bar_qd[nb], ((i + 1) >> 1) & 1, abort_flag, p.status, kErrFullWait)) {
-          tc_fence_after();
-          issue_scores(nb);
-        } else {
-          umma_commit(bar_s);
-        }
-      }
     }
   }
 
