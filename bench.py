@@ -205,7 +205,10 @@ def run_ours(args: argparse.Namespace) -> dict:
         "config": {"model": f"deberta-v3-{args.model_size} RTD (12L disc + 6L gen, GDES, EMD)",
                    "global_batch": args.micro_batch * args.ga * ctx.world_size, "micro_batch": args.micro_batch,
                    "grad_accum": args.ga, "seq_len": args.seq_len,
-                   "parallelism": f"{args.parallelism}{ctx.world_size}",
+                   "parallelism": f"dp{ctx.world_size}" + ("-zero1" if args.parallelism == "zero" else "-replicated"),
+                   "collectives": ("none (1 GPU)" if ctx.world_size == 1 else
+                                   ("fused peer-memory kernels" + (" (multimem)" if engine.comm.multicast else "")
+                                    if getattr(engine, "comm", None) is not None else "NCCL")),
                    "l2": "activations of one micro-batch (>1 GB) exceed the 126 MB L2 between kernels"},
         "clocks": clocks,
         "e2e": {"value": tokens_per_step * ctx.world_size * args.steps / e2e_s, "unit": "tokens/s",

@@ -63,6 +63,36 @@ int db200_adamw(float* p, const float* g, float* m, float* v, void* shadow_bf16,
                 float b1, float b2, float eps, float inv_bc1, float inv_sqrt_bc2, const float* norm_sq,
                 float max_norm, float grad_scale, void* stream);
 
+// ----- fused gradient collectives over NVLink peer memory (see comm.cu) -----------------------
+#define DB200_COMM_MAX_WORLD 8
+#define DB200_COMM_VEC_MAX 128      // longest vector db200_comm_vector_sum takes
+#define DB200_COMM_PAD_WORDS 2048   // 32-bit words of the symmetric flag pad every rank allocates (zeroed once)
+typedef struct Db200CommCtx {
+  int world, rank;
+  void* grads[DB200_COMM_MAX_WORLD];   // every rank's fp32 gradient buffer as mapped into this process
+  void* params[DB200_COMM_MAX_WORLD];  // every rank's bf16 parameter buffer (only db200_comm_adamw needs it)
+  void* pads[DB200_COMM_MAX_WORLD];    // every rank's flag pad
+  void* mc_grads;                      // multicast address covering all gradient buffers, or null: plain peer loads/stores
+  void* mc_params;                     // the same for the parameter buffers
+  unsigned long long timeout_ns;       // longest wait for a peer flag; 0 = 20 s
+} Db200CommCtx;
+typedef struct Db200AdamSegment {
+  long long begin, end;  // element range inside the slab (multiples of 8)
+  float lr, weight_decay;
+} Db200AdamSegment;
+// Sum `count` gradients at `offset` (this rank's slab) over all ranks, times `scale`. to_all = 0: result in this
+// rank's buffer only, squared-norm share published to the peers (db200_comm_adamw picks it up). to_all = 1: result
+// in every rank's buffer, *norm_sq_out = squared norm over all slabs once all ranks are through. *extra_share (may
+// be null) is added to this rank's share of the squared norm (an infinity there makes every rank skip the update).
+int db200_comm_reduce(const Db200CommCtx* ctx, long long offset, long long count, float scale, int to_all,
+                      unsigned epoch, const float* extra_share, float* norm_sq_out, void* stream);
+// AdamW on this rank's slab after db200_comm_reduce(to_all = 0) with the same epoch; bf16 parameters go to all ranks.
+int db200_comm_adamw(const Db200CommCtx* ctx, long long offset, long long count, float* master, float* exp_avg,
+                     float* exp_avg_sq, const Db200AdamSegment* segs, int nseg, float b1, float b2, float eps,
+                     float inv_bc1, float inv_sqrt_bc2, float max_norm, unsigned epoch, float* norm_sq_out, void* stream);
+// out[i] = sum over ranks of in[i], i < n <= DB200_COMM_VEC_MAX (in/out: this rank's own device memory).
+int db200_comm_vector_sum(const Db200CommCtx* ctx, const float* in, float* out, int n, unsigned epoch, void* stream);
+
 // ----- attention (head dim 64; token-major bf16 operands; see attention.cu) -------------------------
 typedef struct AttnArgs {
   const void *q, *k, *v;          // bf16 [B*S, ld*]

@@ -27,6 +27,7 @@ class DistContext:
     device: torch.device = torch.device("cpu")
     backend: str | None = None
     owns_group: bool = False
+    fast_vector_sum: Any = None  # set by the engine: sums a short fp32 device vector over ranks in one kernel
 
     @property
     def is_main_process(self) -> bool:
@@ -45,6 +46,10 @@ class DistContext:
         """All-reduce a small tensor (sum or mean) and return it; identity for one process."""
         if not self.distributed:
             return tensor
+        if (self.fast_vector_sum is not None and tensor.dtype == torch.float32 and tensor.is_cuda
+                and 0 < tensor.numel() <= 128):
+            t = self.fast_vector_sum(tensor)
+            return t / self.world_size if reduction == "mean" else t
         t = tensor.clone()
         if t.device != self.device and self.backend == "nccl":
             t = t.to(self.device)

@@ -35,6 +35,7 @@ from torch import nn
 from deberta_b200.ops import _lib
 
 from .dist import DistContext
+from .peer import PeerComm, fused_comm_wanted
 
 __all__ = ["TrainEngine", "Segment", "OptimizerState", "partition_parameters", "param_order_digest"]
 
@@ -106,6 +107,7 @@ class OptimizerState:
     exp_avg_sq: torch.Tensor | None = None
     norm_sq: torch.Tensor | None = None  # device float: squared global grad norm of the last sync
     names: list[str] = field(default_factory=list)
+    epoch: int = 0  # call number of the last fused reduction (pairs it with the fused update)
 
 
 def _round_up(x: int, m: int) -> int:
@@ -150,8 +152,15 @@ class TrainEngine:
         self.total_elems = total
         dev = self.device
         self.master = torch.zeros(total, dtype=torch.float32, device=dev)
-        self.grads = torch.zeros(total, dtype=torch.float32, device=dev)
-        self.compute = torch.zeros(total, dtype=compute_dtype, device=dev) if compute_dtype != torch.float32 else None
+        self.comm = None
+        if compute_dtype == torch.bfloat16 and fused_comm_wanted(world, dev):
+            # gradient and parameter buffers live in memory every rank of the node can address
+            self.comm = PeerComm(total, rank=ctx.rank, world_size=world, device=dev)
+            self.grads, self.compute = self.comm.grads, self.comm.params
+            ctx.fast_vector_sum = self.comm.vector_sum
+        else:
+            self.grads = torch.zeros(total, dtype=torch.float32, device=dev)
+            self.compute = torch.zeros(total, dtype=compute_dtype, device=dev) if compute_dtype != torch.float32 else None
         self._params: dict[str, nn.Parameter] = {}
         for key in GROUP_ORDER:
             for name, p in parts[key]:
@@ -215,11 +224,25 @@ class TrainEngine:
             o = self.optimizers[opt_name]
             self.grads[o.start : o.end].zero_()
 
-    def sync_grads(self, opt_name: str) -> torch.Tensor:
-        """Average the optimizer's gradient range over ranks; returns the squared global norm (device scalar)."""
+    def sync_grads(self, opt_name: str, penalty: torch.Tensor | None = None) -> torch.Tensor:
+        """Average the optimizer's gradient range over ranks; returns the squared global norm (device scalar).
+
+        ``penalty`` (one device float, 0 or +inf) is added to this rank's share of the squared norm before
+        the shares are combined, so that a non-finite loss on any rank makes every rank skip the update.
+        Under the fused sharded path the returned scalar is filled in by the following ``step``.
+        """
         o = self.optimizers[opt_name]
         world = self.ctx.world_size
         g = self.grads[o.start : o.end]
+        if self.comm is not None:
+            if self.parallelism == "zero":
+                o.epoch = self.comm.reduce(o.shard[0], o.shard[1] - o.shard[0], scale=1.0 / world, to_all=False,
+                                           extra_share=penalty, norm_sq_out=None)
+            else:
+                per = (o.end - o.start) // world
+                o.epoch = self.comm.reduce(o.start + self.ctx.rank * per, per, scale=1.0 / world, to_all=True,
+                                           extra_share=penalty, norm_sq_out=o.norm_sq)
+            return o.norm_sq
         if world > 1:
             avg = dist.ReduceOp.AVG if self.ctx.backend == "nccl" else dist.ReduceOp.SUM
             if self.parallelism == "zero":
@@ -240,7 +263,14 @@ class TrainEngine:
         else:
             o.norm_sq.add_(local.double().pow(2).sum().float())
         if world > 1 and self.parallelism == "zero":
+            if penalty is not None:
+                o.norm_sq.add_(penalty.to(o.norm_sq.dtype).reshape(1))
             dist.all_reduce(o.norm_sq, op=dist.ReduceOp.SUM)
+        elif penalty is not None:
+            pen = penalty.to(o.norm_sq.dtype).reshape(1).clone()
+            if world > 1:
+                dist.all_reduce(pen, op=dist.ReduceOp.SUM)
+            o.norm_sq.add_(pen)
         return o.norm_sq
 
     def grad_norm(self, opt_name: str) -> torch.Tensor:
@@ -256,6 +286,13 @@ class TrainEngine:
         inv_sqrt_bc2 = 1.0 / math.sqrt(1.0 - b2 ** o.step)
         s0, s1 = o.shard
         skipped = False
+        if self.comm is not None and self.parallelism == "zero":
+            segs = [(max(sg.start, s0) - s0, min(sg.end, s1) - s0, sg.base_lr * lr_scale, sg.weight_decay)
+                    for sg in o.segments if max(sg.start, s0) < min(sg.end, s1)]
+            self.comm.adamw(s0, s1 - s0, master=self.master[s0:s1], exp_avg=o.exp_avg, exp_avg_sq=o.exp_avg_sq,
+                            segments=segs, betas=o.betas, eps=o.eps, inv_bc1=inv_bc1, inv_sqrt_bc2=inv_sqrt_bc2,
+                            max_norm=max_grad_norm, epoch=o.epoch, norm_sq_out=o.norm_sq)
+            return
         if not self.use_kernels:
             norm = float(o.norm_sq.sqrt())
             if not math.isfinite(norm):
@@ -287,10 +324,9 @@ class TrainEngine:
         if skipped:
             o.step -= 1
         if self.ctx.world_size > 1 and self.parallelism == "zero":
+            # masters stay sharded (only the owner's slice is authoritative); the compute copy is gathered
             buf = self.compute if self.compute is not None else self.master
             dist.all_gather_into_tensor(buf[o.start : o.end], buf[s0:s1])
-            if self.compute is not None:
-                pass  # masters stay sharded: only the owner's slice is authoritative
 
     def reset_optimizer_state(self, opt_name: str | None = None) -> None:
         for name, o in self.optimizers.items():

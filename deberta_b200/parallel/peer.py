@@ -1,0 +1,143 @@
+"""Symmetric buffers and the fused gradient collectives that run on them.
+
+``PeerComm`` owns three allocations that exist with the same size on every rank of a node and
+are mapped into every rank's address space (``torch.distributed._symmetric_memory`` does the
+handle exchange; nothing else of it is used):
+
+* the engine's flat fp32 gradient buffer,
+* the engine's flat bf16 parameter buffer,
+* a 8 KiB pad of flags and scalars the kernels use to order themselves between GPUs.
+
+On top of those it exposes the three launches of ``csrc/comm.cu``: slab reduction (+ squared
+norm), slab AdamW that stores the new bf16 parameters to all ranks, and a tiny vector sum.
+They stand in for the bucketed all-reduce / reduce-scatter / all-gather traffic that the
+reference gets from DDP and FSDP (``training/entrypoint.py:348-359``, the FSDP launch
+configs under ``configs/accelerate``), and for its scalar reductions
+(``training/steps.py:62-75,305-310``).
+
+Every call consumes one epoch number; all ranks must issue the same calls in the same order.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+
+__all__ = ["PeerComm", "CommCtx", "AdamSegment", "fused_comm_wanted", "MAX_WORLD", "VEC_MAX", "PAD_WORDS"]
+
+MAX_WORLD = 8
+VEC_MAX = 128
+PAD_WORDS = 2048
+
+
+class CommCtx(ctypes.Structure):
+    _fields_ = [
+        ("world", ctypes.c_int),
+        ("rank", ctypes.c_int),
+        ("grads", ctypes.c_void_p * MAX_WORLD),
+        ("params", ctypes.c_void_p * MAX_WORLD),
+        ("pads", ctypes.c_void_p * MAX_WORLD),
+        ("mc_grads", ctypes.c_void_p),
+        ("mc_params", ctypes.c_void_p),
+        ("timeout_ns", ctypes.c_ulonglong),
+    ]
+
+
+class AdamSegment(ctypes.Structure):
+    _fields_ = [("begin", ctypes.c_longlong), ("end", ctypes.c_longlong), ("lr", ctypes.c_float),
+                ("weight_decay", ctypes.c_float)]
+
+
+def fused_comm_wanted(world_size: int, device: torch.device) -> bool:
+    """Fused collectives are the default on 2..8 GPUs of one node; ``DEBERTA_FUSED_COMM=0`` keeps NCCL."""
+    if device.type != "cuda" or not (2 <= world_size <= MAX_WORLD):
+        return False
+    if os.environ.get("DEBERTA_FUSED_COMM", "1").strip().lower() in ("0", "false", "no", "off"):
+        return False
+    local_world = int(os.environ.get("LOCAL_WORLD_SIZE", str(world_size)))
+    return local_world == world_size  # peer mappings need all ranks on one node
+
+
+class PeerComm:
+    """Symmetric gradient / parameter buffers of one rank plus the launches that use them."""
+
+    def __init__(self, n_elems: int, *, rank: int, world_size: int, device: torch.device, want_params: bool = True,
+                 use_multicast: bool | None = None, timeout_s: float = 20.0) -> None:
+        import torch.distributed._symmetric_memory as symm
+
+        self.rank, self.world, self.device = rank, world_size, device
+        group = dist.group.WORLD
+        self.grads = symm.empty(n_elems, dtype=torch.float32, device=device)
+        self.params = symm.empty(n_elems, dtype=torch.bfloat16, device=device) if want_params else None
+        self.pad = symm.empty(PAD_WORDS, dtype=torch.int32, device=device)
+        self.grads.zero_()
+        self.pad.zero_()
+        if self.params is not None:
+            self.params.zero_()
+        torch.cuda.synchronize(device)
+        self._handles = [symm.rendezvous(t, group) for t in (self.grads, self.pad) + ((self.params,) if want_params else ())]
+        hg, hp = self._handles[0], self._handles[1]
+        hw = self._handles[2] if want_params else None
+        if use_multicast is None:
+            use_multicast = os.environ.get("DEBERTA_COMM_MULTICAST", "1").strip().lower() not in ("0", "false", "no", "off")
+        mc_g = int(getattr(hg, "multicast_ptr", 0) or 0) if use_multicast else 0
+        mc_w = int(getattr(hw, "multicast_ptr", 0) or 0) if (use_multicast and hw is not None) else 0
+        self.multicast = bool(mc_g)
+        ctx = CommCtx()
+        ctx.world, ctx.rank = world_size, rank
+        for r in range(world_size):
+            ctx.grads[r] = int(hg.buffer_ptrs[r])
+            ctx.pads[r] = int(hp.buffer_ptrs[r])
+            ctx.params[r] = int(hw.buffer_ptrs[r]) if hw is not None else 0
+        ctx.mc_grads = mc_g or None
+        ctx.mc_params = mc_w or None
+        ctx.timeout_ns = int(timeout_s * 1e9)
+        self.ctx = ctx
+        self.epoch = 0
+        dist.barrier()  # every pad is zeroed and mapped before the first flag is written
+
+    # ---- launches -------------------------------------------------------------------------------
+    def _next_epoch(self) -> ctypes.c_uint:
+        self.epoch += 1
+        return ctypes.c_uint(self.epoch & 0xFFFFFFFF)
+
+    def reduce(self, offset: int, count: int, *, scale: float, to_all: bool, extra_share: torch.Tensor | None,
+               norm_sq_out: torch.Tensor | None) -> int:
+        """Sum this rank's slab ``[offset, offset+count)`` over all ranks; returns the epoch that was used."""
+        e = self._next_epoch()
+        _lib.call("db200_comm_reduce", ctypes.byref(self.ctx), ctypes.c_longlong(offset), ctypes.c_longlong(count),
+                  ctypes.c_float(scale), ctypes.c_int(1 if to_all else 0), e, _lib.ptr(extra_share),
+                  _lib.ptr(norm_sq_out), _lib.stream_ptr())
+        return int(e.value)
+
+    def adamw(self, offset: int, count: int, *, master: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor,
+              segments: Sequence[tuple[int, int, float, float]], betas: tuple[float, float], eps: float, inv_bc1: float,
+              inv_sqrt_bc2: float, max_norm: float, epoch: int, norm_sq_out: torch.Tensor | None) -> None:
+        """AdamW on the slab reduced under ``epoch``; ``segments`` = (begin, end, lr, weight_decay) inside the slab."""
+        if self.params is None:
+            raise RuntimeError("PeerComm was built without a parameter buffer")
+        arr = (AdamSegment * max(1, len(segments)))()
+        for i, (b, en, lr, wd) in enumerate(segments):
+            arr[i] = AdamSegment(b, en, lr, wd)
+        cf = ctypes.c_float
+        _lib.call("db200_comm_adamw", ctypes.byref(self.ctx), ctypes.c_longlong(offset), ctypes.c_longlong(count),
+                  _lib.ptr(master), _lib.ptr(exp_avg), _lib.ptr(exp_avg_sq), arr, ctypes.c_int(len(segments)),
+                  cf(betas[0]), cf(betas[1]), cf(eps), cf(inv_bc1), cf(inv_sqrt_bc2), cf(max_norm),
+                  ctypes.c_uint(epoch & 0xFFFFFFFF), _lib.ptr(norm_sq_out), _lib.stream_ptr())
+
+    def vector_sum(self, values: torch.Tensor) -> torch.Tensor:
+        """Sum a float vector of at most ``VEC_MAX`` entries over all ranks (result on the device)."""
+        n = values.numel()
+        if n > VEC_MAX:
+            raise ValueError(f"vector_sum takes at most {VEC_MAX} values")
+        src = values.detach().to(device=self.device, dtype=torch.float32).reshape(-1).contiguous()
+        out = torch.empty(n, dtype=torch.float32, device=self.device)
+        _lib.call("db200_comm_vector_sum", ctypes.byref(self.ctx), _lib.ptr(src), _lib.ptr(out), ctypes.c_int(n),
+                  self._next_epoch(), _lib.stream_ptr())
+        return out.view(values.shape)

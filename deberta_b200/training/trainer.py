@@ -138,9 +138,10 @@ class Trainer:
     def _finish_optimizer(self, name: str, loss_guard: torch.Tensor | None) -> torch.Tensor:
         """Reduce gradients, fold a non-finite loss into the norm, update, advance the schedule."""
         eng = self.engine
-        norm_sq = eng.sync_grads(name)
-        if loss_guard is not None:
-            norm_sq.add_(torch.where(torch.isfinite(loss_guard), 0.0, float("inf")).to(norm_sq.dtype))
+        penalty = None
+        if loss_guard is not None:  # +inf when the window's loss was not finite: every rank then skips the update
+            penalty = torch.where(torch.isfinite(loss_guard), 0.0, float("inf")).to(torch.float32).reshape(1)
+        norm_sq = eng.sync_grads(name, penalty)
         eng.step(name, lr_scale=self.schedules[name].scale() * self.lr_mult, max_grad_norm=self.max_grad_norm)
         self.schedules[name].step()
         return norm_sq.clone()
