@@ -64,6 +64,16 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// 16 packed bf16 (32 contiguous bytes) of one row: one 256-bit store when aligned, else two 128-bit ones.
+__device__ __forceinline__ void store_bf16x16(__nv_bfloat16* dst, const uint32_t* w) {
+  if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+    st_global_32B(dst, w);
+  } else {
+    reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+}
+
 __device__ __forceinline__ float bf16_elem(const uint4& u, int j) {
   const uint32_t w = (j >> 1) == 0 ? u.x : (j >> 1) == 1 ? u.y : (j >> 1) == 2 ? u.z : u.w;
   return (j & 1) ? bf16_hi(w) : bf16_lo(w);
@@ -381,15 +391,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tmem_ld_32x32b_x16(t_o + lane_addr + part * 16, r);
     tmem_ld_wait();
     if (q_valid) {
+      uint32_t w[8];
 #pragma unroll
-      for (int g = 0; g < 2; ++g) {
-        uint4 u;
-        u.x = pack_bf16(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
-        u.y = pack_bf16(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
-        u.z = pack_bf16(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
-        u.w = pack_bf16(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
-        reinterpret_cast<uint4*>(o)[g] = u;
-      }
+      for (int g = 0; g < 8; ++g) w[g] = pack_bf16(__uint_as_float(r[2 * g]) * inv, __uint_as_float(r[2 * g + 1]) * inv);
+      store_bf16x16(o, w);
     }
     if (q_valid && part == 0 && p.lse)
       p.lse[(static_cast<long long>(b) * p.heads + h) * S + q] =
@@ -665,6 +670,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tma_load_3d(sdO + 2 * kTileBytes, &tm_do, &bar_qd[2], h * kD, 2 * kTile, b);
       }
       // rows of P and dS for these 32 keys: 4 chunks of 8 bf16 inside 64-key block (c >> 1)
+      uint32_t dsw[16];
 #pragma unroll
       for (int g4 = 0; g4 < 4; ++g4) {
         const int chunk = (c & 1) * 4 + g4;
@@ -680,7 +686,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         u.z = pack_bf16(gv[g4 * 8 + 4], gv[g4 * 8 + 5]);
         u.w = pack_bf16(gv[g4 * 8 + 6], gv[g4 * 8 + 7]);
         *reinterpret_cast<uint4*>(sdS + off) = u;
-        if (dbias_row) dbias_row[c * 4 + g4] = u;
+        dsw[g4 * 4] = u.x; dsw[g4 * 4 + 1] = u.y; dsw[g4 * 4 + 2] = u.z; dsw[g4 * 4 + 3] = u.w;
+      }
+      if (dbias_row) {  // 64 contiguous bytes of this query's row
+        st_global_32B(dbias_row + c * 4, dsw);
+        st_global_32B(dbias_row + c * 4 + 2, dsw + 8);
       }
     }
     fence_proxy_async();
@@ -718,15 +728,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_ld_32x32b_x16((which == 0 ? t_dv : t_dk) + lane_addr + part * 16, r);
       tmem_ld_wait();
       if (kk < S) {
+        uint32_t w[8];
 #pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          uint4 u;
-          u.x = pack_bf16(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
-          u.y = pack_bf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
-          u.z = pack_bf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
-          u.w = pack_bf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
-          reinterpret_cast<uint4*>(dst)[g] = u;
-        }
+        for (int g = 0; g < 8; ++g) w[g] = pack_bf16(__uint_as_float(r[2 * g]), __uint_as_float(r[2 * g + 1]));
+        store_bf16x16(dst, w);
       }
     }
   }
@@ -817,7 +822,7 @@ extern "C" int db200_attn_bwd(const AttnArgs* a, void* stream_) {
   d.bias = static_cast<const __nv_bfloat16*>(a->bias);
   d.dbias = static_cast<__nv_bfloat16*>(a->dbias);
   d.ldb = a->ldb;
-  if (d.bias && ((a->ldb % 128) || !aligned16(a->bias) || !d.dbias || !aligned16(a->dbias))) return -10;
+  if (d.bias && ((a->ldb % 128) || !aligned16(a->bias) || !d.dbias || (reinterpret_cast<uintptr_t>(a->dbias) & 31))) return -10;
   d.lse = a->lse;
   d.delta = a->delta;
   d.dq_acc = a->dq_acc;

@@ -289,15 +289,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             for (int j = 0; j < 32; ++j)
               v[j] = (__expf(v[j] - lse) - ((nc + j) == label ? 1.f : 0.f)) * gs;
             if (vec) {
-#pragma unroll
-              for (int q4 = 0; q4 < 4; ++q4) {
-                uint4 u;
-                u.x = pack_bf16(v[q4 * 8], v[q4 * 8 + 1]);
-                u.y = pack_bf16(v[q4 * 8 + 2], v[q4 * 8 + 3]);
-                u.z = pack_bf16(v[q4 * 8 + 4], v[q4 * 8 + 5]);
-                u.w = pack_bf16(v[q4 * 8 + 6], v[q4 * 8 + 7]);
-                reinterpret_cast<uint4*>(o)[q4] = u;
-              }
+              store_bf16x32(o, v);
             } else {
               for (int j = 0; j < 32; ++j)
                 if (nc + j < p.N) o[j] = __float2bfloat16(v[j]);
@@ -363,7 +355,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 if (nc + j < p.N) atomicAdd(o + j, v[j]);
             }
           } else {
-            if (full && (p.ldo % 4 == 0)) {
+            if (full && (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(o) & 31) == 0)) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) st_global_32B(o + q * 8, reinterpret_cast<const uint32_t*>(v) + q * 8);
+            } else if (full && (p.ldo % 4 == 0)) {
 #pragma unroll
               for (int q = 0; q < 8; ++q)
                 reinterpret_cast<float4*>(o)[q] = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
@@ -379,15 +374,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (p.residual) {
           const __nv_bfloat16* rp = p.residual + z * p.bs_res + static_cast<long long>(row) * p.ldr + nc;
           if (full && (p.ldr % 8 == 0)) {
+            uint32_t bw[16];
+            load_bf16x32(rp, bw);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 b = *reinterpret_cast<const uint4*>(rp + q * 8);
-              const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                v[q * 8 + e * 2] += bf16_lo(bw[e]);
-                v[q * 8 + e * 2 + 1] += bf16_hi(bw[e]);
-              }
+            for (int e = 0; e < 16; ++e) {
+              v[e * 2] += bf16_lo(bw[e]);
+              v[e * 2 + 1] += bf16_hi(bw[e]);
             }
           } else {
             for (int j = 0; j < 32; ++j)
@@ -397,15 +389,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (p.epi == EPI_DGELU) {
           const __nv_bfloat16* ap = p.aux + z * p.bs_aux + static_cast<long long>(row) * p.ldaux + nc;
           if (full && (p.ldaux % 8 == 0)) {
+            uint32_t bw[16];
+            load_bf16x32(ap, bw);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 b = *reinterpret_cast<const uint4*>(ap + q * 8);
-              const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                v[q * 8 + e * 2] *= dgelu_erf(bf16_lo(bw[e]));
-                v[q * 8 + e * 2 + 1] *= dgelu_erf(bf16_hi(bw[e]));
-              }
+            for (int e = 0; e < 16; ++e) {
+              v[e * 2] *= dgelu_erf(bf16_lo(bw[e]));
+              v[e * 2 + 1] *= dgelu_erf(bf16_hi(bw[e]));
             }
           } else {
             for (int j = 0; j < 32; ++j)
@@ -415,15 +404,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         __nv_bfloat16* o =
             reinterpret_cast<__nv_bfloat16*>(p.out) + z * p.bs_out + static_cast<long long>(row) * p.ldo + nc;
         if (vec) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 u;
-            u.x = pack_bf16(v[q * 8], v[q * 8 + 1]);
-            u.y = pack_bf16(v[q * 8 + 2], v[q * 8 + 3]);
-            u.z = pack_bf16(v[q * 8 + 4], v[q * 8 + 5]);
-            u.w = pack_bf16(v[q * 8 + 6], v[q * 8 + 7]);
-            reinterpret_cast<uint4*>(o)[q] = u;
-          }
+          store_bf16x32(o, v);
         } else {
           for (int j = 0; j < 32; ++j)
             if (nc + j < p.N) o[j] = __float2bfloat16(v[j]);
@@ -434,15 +415,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = gelu_erf(__bfloat162float(__float2bfloat16(v[j])));
           if (full && (p.ldo2 % 8 == 0)) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 u;
-              u.x = pack_bf16(v[q * 8], v[q * 8 + 1]);
-              u.y = pack_bf16(v[q * 8 + 2], v[q * 8 + 3]);
-              u.z = pack_bf16(v[q * 8 + 4], v[q * 8 + 5]);
-              u.w = pack_bf16(v[q * 8 + 6], v[q * 8 + 7]);
-              reinterpret_cast<uint4*>(o2)[q] = u;
-            }
+            store_bf16x32(o2, v);
           } else {
             for (int j = 0; j < 32; ++j)
               if (nc + j < p.N) o2[j] = __float2bfloat16(v[j]);

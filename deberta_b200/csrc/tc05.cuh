@@ -215,4 +215,45 @@ __device__ __forceinline__ uint32_t swz128(uint32_t row, uint32_t c16) {
   return row * 128u + ((c16 ^ (row & 7u)) << 4);
 }
 
+
+// 32 bf16 values (64 contiguous bytes) of one row: two 256-bit accesses when the address allows it, so that
+// every access covers a whole 32-byte sector (lanes of a warp sit on different rows in the TMEM-row layout,
+// and 16-byte pieces would reach L2 as half-written sectors), else four 128-bit ones.
+__device__ __forceinline__ void st_global_32B(void* ptr, const uint32_t* w) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+               "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
+__device__ __forceinline__ void ld_global_32B(const void* ptr, uint32_t* w) {
+  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+               : "l"(ptr));
+}
+__device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float* v) {
+  uint32_t w[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) w[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+  if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+    st_global_32B(dst, w);
+    st_global_32B(dst + 16, w + 8);
+  } else {
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      reinterpret_cast<uint4*>(dst)[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+  }
+}
+// 32 bf16 values of one row as packed pairs (16 words); the address must be 16-byte aligned.
+__device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* src, uint32_t* w) {
+  if ((reinterpret_cast<uintptr_t>(src) & 31) == 0) {
+    ld_global_32B(src, w);
+    ld_global_32B(src + 16, w + 8);
+  } else {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint4 u = reinterpret_cast<const uint4*>(src)[q];
+      w[4 * q] = u.x; w[4 * q + 1] = u.y; w[4 * q + 2] = u.z; w[4 * q + 3] = u.w;
+    }
+  }
+}
+
 }  // namespace tc05
