@@ -123,6 +123,10 @@ int db200_posbias_build(const void* c2p, const void* p2c, const void* lut_c2p, c
                         int S, int ldb, int heads, int span2, void* stream);
 int db200_posbias_scatter(const void* dbias, const void* lut, void* dtab, int rows_are_keys, int B, int S, int ldb,
                           int heads, int span2, void* stream);
+// The same reduction for bucket maps in which every bucket collects one contiguous run of offsets q-k
+// (ranges: int[2*span2] = lo[], hi[]; lo > hi for unused buckets): prefix sums instead of atomics.
+int db200_posbias_scatter_ranges(const void* dbias, const void* ranges, void* dtab, int rows_are_keys, int B, int S,
+                                 int ldb, int heads, int span2, void* stream);
 
 int db200_attn_fwd(const AttnArgs* args, void* stream);
 int db200_attn_bwd(const AttnArgs* args, void* stream);

@@ -59,6 +59,69 @@ posbias_build_kernel(const __nv_bfloat16* __restrict__ c2p, const __nv_bfloat16*
   }
 }
 
+
+// Interior tiles (all 64 x 64 entries valid), the common case: same data flow as the kernel above with
+// the offset -> bucket map of the tile (127 offsets) staged in shared memory and 32-bit index arithmetic.
+// grid (S/64, S/64, B*heads), 256 threads; needs S % 64 == 0.
+template <bool HAS_C, bool HAS_P>
+__global__ void __launch_bounds__(256)
+posbias_build_full_kernel(const __nv_bfloat16* __restrict__ c2p, const __nv_bfloat16* __restrict__ p2c,
+                          const unsigned short* __restrict__ lut_c2p, const unsigned short* __restrict__ lut_p2c,
+                          __nv_bfloat16* __restrict__ bias, int S, int ldb, int heads, int span2) {
+  __shared__ float tile[kT][kT + 1];
+  __shared__ unsigned short slc[128], slp[128];
+  const int tid = threadIdx.x;
+  const int k0 = blockIdx.x * kT, q0 = blockIdx.y * kT;
+  const int b = blockIdx.z / heads, h = blockIdx.z % heads;
+  const int row_stride = heads * span2;
+  const long long base = static_cast<long long>(b) * S * row_stride + static_cast<long long>(h) * span2;
+  if (tid < 127) {  // offsets q-k of this tile: q0-k0-63 .. q0-k0+63
+    const int d = q0 - k0 - 63 + tid + S - 1;
+    if (HAS_C) slc[tid] = lut_c2p[d];
+    if (HAS_P) slp[tid] = lut_p2c[d];
+  }
+  __syncthreads();
+  const int lane64 = tid & 63, grp = tid >> 6;
+  // all 16 bucket indices, then all 16 table reads, then the shared-memory updates: the reads of one
+  // thread are independent and stay in flight together
+  if (HAS_C) {  // lanes along k: consecutive keys read consecutive table entries of one query row
+    const unsigned short* src = reinterpret_cast<const unsigned short*>(c2p + base) + (q0 + grp) * row_stride;
+    const unsigned short* l = slc + (grp - lane64 + 63);
+    int idx[16];
+    unsigned short raw[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) idx[i] = i * 4 * row_stride + l[4 * i];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) raw[i] = __ldg(src + idx[i]);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) tile[grp + 4 * i][lane64] = __uint_as_float(static_cast<unsigned int>(raw[i]) << 16);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) tile[grp + 4 * i][lane64] = 0.f;
+  }
+  __syncthreads();
+  if (HAS_P) {  // lanes along q: consecutive queries read consecutive table entries of one key row
+    const unsigned short* src = reinterpret_cast<const unsigned short*>(p2c + base) + (k0 + grp) * row_stride;
+    const unsigned short* l = slp + (lane64 - grp + 63);
+    int idx[16];
+    unsigned short raw[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) idx[i] = i * 4 * row_stride + l[-4 * i];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) raw[i] = __ldg(src + idx[i]);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) tile[lane64][grp + 4 * i] += __uint_as_float(static_cast<unsigned int>(raw[i]) << 16);
+    __syncthreads();
+  }
+  __nv_bfloat16* out = bias + (static_cast<long long>(blockIdx.z) * S + q0) * ldb + k0;
+  const int c2 = (tid & 31) * 2, r0 = tid >> 5;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = r0 + 8 * i;
+    *reinterpret_cast<__nv_bfloat162*>(out + r * ldb + c2) = __floats2bfloat162_rn(tile[r][c2], tile[r][c2 + 1]);
+  }
+}
+
 constexpr int kRows = 32;    // scatter: table rows (queries or keys) owned by one block
 constexpr int kOther = 128;  // scatter: extent of the other axis processed per iteration
 
@@ -122,17 +185,189 @@ posbias_scatter_kernel(const __nv_bfloat16* __restrict__ dbias, const unsigned s
   }
 }
 
+
+// ---- scatter by prefix sums -----------------------------------------------------------------
+// When every bucket j collects one contiguous run of offsets  lo[j] <= q-k <= hi[j]  (true for the
+// log-bucket maps, which are monotone in q-k), the scatter is a difference of prefix sums along the
+// row (keys) or the column (queries) of dbias: no atomics, every element read once.
+//
+// ranges: int[2 * span2] = lo[0..span2), hi[0..span2) ; lo > hi marks an unused bucket.
+
+__device__ __forceinline__ float warp_inclusive_scan(float x, int lane) {
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  return x;
+}
+
+// rows of dbias are queries: one warp per query row. grid (ceil(S/8), heads, B), 256 threads.
+__global__ void __launch_bounds__(256)
+posbias_rowscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __restrict__ ranges,
+                       __nv_bfloat16* __restrict__ dtab, int S, int ldb, int heads, int span2) {
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stride = (S + 1) + ((S + 1) >> 3) + 1;
+  // P[i] = sum of the first i keys, kept at word i + i/8: the lanes of the scan write 8 words apart
+  float* P = sm + warp * stride;
+  int* rng = reinterpret_cast<int*>(sm + 8 * stride);  // lo[], hi[]
+  for (int i = threadIdx.x; i < 2 * span2; i += 256) rng[i] = ranges[i];
+  __syncthreads();
+  const int q = blockIdx.x * 8 + warp, h = blockIdx.y, b = blockIdx.z;
+  if (q >= S) return;
+  const __nv_bfloat16* src = dbias + ((static_cast<long long>(b) * heads + h) * S + q) * ldb;
+  float carry = 0.f;
+  if (lane == 0) P[0] = 0.f;
+  for (int base = 0; base < S; base += 256) {
+    const int k = base + lane * 8;
+    float v[8];
+    if (k < S) {
+      const uint4 u = *reinterpret_cast<const uint4*>(src + k);
+      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&u);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = (k + j < S) ? __bfloat162float(e[j]) : 0.f;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    }
+#pragma unroll
+    for (int j = 1; j < 8; ++j) v[j] += v[j - 1];
+    const float incl = warp_inclusive_scan(v[7], lane);
+    const float off = carry + incl - v[7];
+    if (k < S) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (k + j < S) P[(k + j + 1) + ((k + j + 1) >> 3)] = off + v[j];
+    }
+    carry += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  __syncwarp();
+  __nv_bfloat16* dst = dtab + (static_cast<long long>(b) * S + q) * (static_cast<long long>(heads) * span2) + h * span2;
+  for (int j = lane * 2; j < span2; j += 64) {
+    float out[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      const int lo = rng[j + t], hi = rng[span2 + j + t];
+      const int a = max(0, q - hi), z = min(S - 1, q - lo);  // keys k with lo <= q-k <= hi
+      out[t] = (lo <= hi && a <= z) ? P[(z + 1) + ((z + 1) >> 3)] - P[a + (a >> 3)] : 0.f;
+    }
+    *reinterpret_cast<__nv_bfloat162*>(dst + j) = __floats2bfloat162_rn(out[0], out[1]);
+  }
+}
+
+// table rows are keys: a block owns 32 key columns of dbias and scans them along the queries.
+// grid (ceil(S/32), heads, B), 256 threads; shared: T[32][stride]. Prefix i of a key sits at word
+// i + (i >> sh) with 2^sh >= ceil(S/32): each lane scans a contiguous run of `per` queries, and the skew
+// keeps the 32 lanes on different banks.
+template <int PER>  // PER > 0: ceil(S/32) known at compile time (the run of a lane lives in registers); 0: any S
+__global__ void __launch_bounds__(256)
+posbias_colscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __restrict__ ranges,
+                       __nv_bfloat16* __restrict__ dtab, int S, int ldb, int heads, int span2, int stride, int per, int sh) {
+  extern __shared__ float sm[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int* rng = reinterpret_cast<int*>(sm + 32 * stride);
+  for (int i = tid; i < 2 * span2; i += 256) rng[i] = ranges[i];
+  const int k0 = blockIdx.x * 32, h = blockIdx.y, b = blockIdx.z;
+  const __nv_bfloat16* src = dbias + (static_cast<long long>(b) * heads + h) * S * ldb + k0;
+  const int cg = tid & 3;  // 8-key group of this thread
+  for (int qb = tid >> 2; qb < S; qb += 256) {  // four independent 16-byte loads in flight per thread
+    uint4 u[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int q = qb + 64 * t;
+      u[t] = q < S ? *reinterpret_cast<const uint4*>(src + static_cast<long long>(q) * ldb + cg * 8) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int q = qb + 64 * t;
+      if (q < S) {
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&u[t]);
+        const int w = (q + 1) + ((q + 1) >> sh);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sm[(cg * 8 + j) * stride + w] = __bfloat162float(e[j]);
+      }
+    }
+  }
+  if (tid < 32) sm[tid * stride] = 0.f;
+  __syncthreads();
+  const long long row_stride = static_cast<long long>(heads) * span2;
+  for (int kk = warp * 4; kk < warp * 4 + 4; ++kk) {
+    const int k = k0 + kk;
+    if (k >= S) break;  // warp-uniform
+    float* T = sm + kk * stride;  // T[phys(i)] = sum of the first i queries
+    // lane owns prefixes i = lane*per + 1 .. lane*per + per
+    const int first = lane * per + 1;
+    if (PER > 0) {
+      float x[PER > 0 ? PER : 1];
+#pragma unroll
+      for (int o = 0; o < PER; ++o) {
+        const int i = first + o;
+        x[o] = (i <= S) ? T[i + (i >> sh)] : 0.f;
+      }
+#pragma unroll
+      for (int o = 1; o < PER; ++o) x[o] += x[o - 1];
+      const float run = x[PER > 0 ? PER - 1 : 0];
+      const float off = warp_inclusive_scan(run, lane) - run;
+#pragma unroll
+      for (int o = 0; o < PER; ++o) {
+        const int i = first + o;
+        if (i <= S) T[i + (i >> sh)] = x[o] + off;
+      }
+    } else {
+      float run = 0.f;
+      for (int o = 0; o < per; ++o) {
+        const int i = first + o;
+        if (i <= S) {
+          run += T[i + (i >> sh)];
+          T[i + (i >> sh)] = run;
+        }
+      }
+      const float off = warp_inclusive_scan(run, lane) - run;
+      for (int o = 0; o < per; ++o) {
+        const int i = first + o;
+        if (i <= S) T[i + (i >> sh)] += off;
+      }
+    }
+    __syncwarp();
+    __nv_bfloat16* dst = dtab + (static_cast<long long>(b) * S + k) * row_stride + h * span2;
+    for (int j = lane * 2; j < span2; j += 64) {
+      float out[2];
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const int lo = rng[j + t], hi = rng[span2 + j + t];
+        const int a = max(0, k + lo), z = min(S - 1, k + hi) + 1;  // queries q with lo <= q-k <= hi
+        out[t] = (lo <= hi && a < z) ? T[z + (z >> sh)] - T[a + (a >> sh)] : 0.f;
+      }
+      *reinterpret_cast<__nv_bfloat162*>(dst + j) = __floats2bfloat162_rn(out[0], out[1]);
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" int db200_posbias_build(const void* c2p, const void* p2c, const void* lut_c2p, const void* lut_p2c, void* bias,
                                    int B, int S, int ldb, int heads, int span2, void* stream) {
   if (B <= 0 || S <= 0) return 0;
   if (ldb % 2) return -10;
-  dim3 grid((ldb + kT - 1) / kT, (S + kT - 1) / kT, B * heads);
-  posbias_build_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(c2p), static_cast<const __nv_bfloat16*>(p2c),
-      static_cast<const unsigned short*>(lut_c2p), static_cast<const unsigned short*>(lut_p2c),
-      static_cast<__nv_bfloat16*>(bias), S, ldb, heads, span2);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  auto c = static_cast<const __nv_bfloat16*>(c2p);
+  auto pp = static_cast<const __nv_bfloat16*>(p2c);
+  auto lc = static_cast<const unsigned short*>(lut_c2p);
+  auto lp = static_cast<const unsigned short*>(lut_p2c);
+  auto o = static_cast<__nv_bfloat16*>(bias);
+  if (S % kT == 0 && ldb == S && static_cast<long long>(S) * heads * span2 < (1ll << 30)) {
+    dim3 grid(S / kT, S / kT, B * heads);
+    if (c && pp)
+      posbias_build_full_kernel<true, true><<<grid, 256, 0, st>>>(c, pp, lc, lp, o, S, ldb, heads, span2);
+    else if (c)
+      posbias_build_full_kernel<true, false><<<grid, 256, 0, st>>>(c, pp, lc, lp, o, S, ldb, heads, span2);
+    else
+      posbias_build_full_kernel<false, true><<<grid, 256, 0, st>>>(c, pp, lc, lp, o, S, ldb, heads, span2);
+  } else {
+    dim3 grid((ldb + kT - 1) / kT, (S + kT - 1) / kT, B * heads);
+    posbias_build_kernel<<<grid, 256, 0, st>>>(c, pp, lc, lp, o, S, ldb, heads, span2);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -162,6 +397,45 @@ extern "C" int db200_posbias_scatter(const void* dbias, const void* lut, void* d
       cfg = true;
     }
     posbias_scatter_kernel<false><<<grid, 256, smem, st>>>(db, lt, dt, S, ldb, heads, span2);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int db200_posbias_scatter_ranges(const void* dbias, const void* ranges, void* dtab, int rows_are_keys, int B,
+                                            int S, int ldb, int heads, int span2, void* stream) {
+  if (B <= 0 || S <= 0) return 0;
+  if ((span2 % 2) || (ldb % 8) || ldb < S) return -12;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  auto db = static_cast<const __nv_bfloat16*>(dbias);
+  auto rg = static_cast<const int*>(ranges);
+  auto dt = static_cast<__nv_bfloat16*>(dtab);
+  constexpr int kMaxSmem = 200 * 1024;
+  if (rows_are_keys) {
+    if (ldb % 32) return -12;  // 32-key column groups are read with 16-byte loads up to the padded width
+    const int per = (S + 31) / 32;
+    int sh = 0;
+    while ((1 << sh) < per) ++sh;
+    int stride = (S + 1) + ((S + 1) >> sh) + 1;
+    stride |= 1;  // odd: the 32 key rows start on different banks
+    const int smem = 32 * stride * 4 + 2 * span2 * 4;
+    if (smem > kMaxSmem) return -12;
+    auto kern = posbias_colscan_kernel<0>;
+    if (per == 16) kern = posbias_colscan_kernel<16>;
+    else if (per == 8) kern = posbias_colscan_kernel<8>;
+    else if (per == 32) kern = posbias_colscan_kernel<32>;
+    else if (per == 4) kern = posbias_colscan_kernel<4>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) != cudaSuccess) return -3;
+    kern<<<dim3((S + 31) / 32, heads, B), 256, smem, st>>>(db, rg, dt, S, ldb, heads, span2, stride, per, sh);
+  } else {
+    const int smem = 8 * ((S + 1) + ((S + 1) >> 3) + 1) * 4 + 2 * span2 * 4;
+    if (smem > kMaxSmem) return -12;
+    static bool cfg = false;
+    if (!cfg) {
+      if (cudaFuncSetAttribute(posbias_rowscan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) != cudaSuccess)
+        return -3;
+      cfg = true;
+    }
+    posbias_rowscan_kernel<<<dim3((S + 7) / 8, heads, B), 256, smem, st>>>(db, rg, dt, S, ldb, heads, span2);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

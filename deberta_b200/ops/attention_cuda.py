@@ -56,6 +56,37 @@ def _luts(S: int, bucket_size: int, max_position: int, att_span: int, device) ->
     return hit
 
 
+_RANGE_CACHE: dict[tuple, tuple] = {}
+
+
+def _bucket_ranges(lut: torch.Tensor, S: int, span2: int) -> torch.Tensor | None:
+    """Per bucket the run ``lo <= q-k <= hi`` of offsets it collects (int32 ``[lo..., hi...]`` on the LUT's device).
+
+    ``None`` when some bucket's offsets are not one contiguous run (the prefix-sum scatter then does not apply).
+    """
+    idx = lut.to(torch.int64).cpu()
+    delta = torch.arange(-(S - 1), S, dtype=torch.int64)
+    big = 1 << 20
+    lo = torch.full((span2,), big, dtype=torch.int64).scatter_reduce_(0, idx, delta, "amin")
+    hi = torch.full((span2,), -big, dtype=torch.int64).scatter_reduce_(0, idx, delta, "amax")
+    cnt = torch.bincount(idx, minlength=span2)
+    used = cnt > 0
+    if not bool(((hi - lo + 1)[used] == cnt[used]).all()):
+        return None
+    lo = torch.where(used, lo, torch.ones_like(lo))
+    hi = torch.where(used, hi, torch.zeros_like(hi))
+    return torch.cat([lo, hi]).to(torch.int32).to(lut.device)
+
+
+def _ranges(luts: tuple[torch.Tensor, torch.Tensor], S: int, span2: int) -> tuple:
+    key = (luts[0].data_ptr(), luts[1].data_ptr(), S, span2)
+    hit = _RANGE_CACHE.get(key)
+    if hit is None:
+        hit = (_bucket_ranges(luts[0], S, span2), _bucket_ranges(luts[1], S, span2))
+        _RANGE_CACHE[key] = hit
+    return hit
+
+
 def _token_major(x: torch.Tensor) -> torch.Tensor:
     """[B,S,H] with unit inner stride, 16-byte aligned rows and batch stride = S · row stride (else a copy)."""
     B, S, H = x.shape
@@ -176,8 +207,13 @@ class _FlashAttention(torch.autograd.Function):
                 if tab is None:
                     continue
                 gt = torch.empty((T, heads, span2), dtype=torch.bfloat16, device=dev)
-                _lib.call("db200_posbias_scatter", _lib.ptr(dbias), _lib.ptr(luts[which]), _lib.ptr(gt), c_int(which),
-                          c_int(B), c_int(S), c_int(bias.shape[-1]), c_int(heads), c_int(span2), _lib.stream_ptr())
+                rng = _ranges(luts, S, span2)[which]
+                if rng is not None:  # monotone bucket map: differences of prefix sums
+                    _lib.call("db200_posbias_scatter_ranges", _lib.ptr(dbias), _lib.ptr(rng), _lib.ptr(gt), c_int(which),
+                              c_int(B), c_int(S), c_int(bias.shape[-1]), c_int(heads), c_int(span2), _lib.stream_ptr())
+                else:
+                    _lib.call("db200_posbias_scatter", _lib.ptr(dbias), _lib.ptr(luts[which]), _lib.ptr(gt), c_int(which),
+                              c_int(B), c_int(S), c_int(bias.shape[-1]), c_int(heads), c_int(span2), _lib.stream_ptr())
                 if which == 0:
                     g_c2p = gt
                 else:
