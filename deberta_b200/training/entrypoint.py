@@ -174,9 +174,17 @@ def run_pretraining(*, model_cfg: ModelConfig, data_cfg: DataConfig, train_cfg: 
         save_training_state(directory, engine=engine, trainer=trainer, ctx=ctx)
 
     save_kw = dict(save_total_limit=int(ck.save_total_limit), optimizer_param_digest=digest, gradient_accumulation_steps=ga)
+    watchdog = None
+    deadline = float(os.environ.get("DEBERTA_STEP_DEADLINE_S", "0") or 0)
+    if deadline > 0:  # host-side liveness report when no optimizer step completes in time (off by default)
+        from .watchdog import StepWatchdog
+
+        watchdog = StepWatchdog(deadline, report_dir=out_dir / "watchdog").start()
     try:
         while trainer.global_step < max_steps:
             stats = trainer.train_window([next(batches) for _ in range(ga)])
+            if watchdog is not None:
+                watchdog.beat(trainer.global_step)
             pending.append(stats)
             tokens_seen += stats.input_tokens
             step = trainer.global_step
@@ -206,6 +214,8 @@ def run_pretraining(*, model_cfg: ModelConfig, data_cfg: DataConfig, train_cfg: 
                                                     "error": f"{type(exc).__name__}: {exc}"})
         raise
     finally:
+        if watchdog is not None:
+            watchdog.stop()
         flush_loggers()
         # a crash checkpoint is only safe without peers (a collective save could deadlock on a dead rank)
         if (not crashed or ctx.world_size == 1) and trainer.global_step > 0 and last_saved != trainer.global_step:

@@ -26,6 +26,7 @@ import torch
 from deberta_b200.models.mask_utils import AttnMask
 from deberta_b200.parallel.dist import DistContext
 from deberta_b200.parallel.engine import TrainEngine, param_order_digest
+from deberta_b200.utils.trace import nvtx_range
 
 from .loop_utils import (apply_nonfinite_recovery, count_input_tokens_for_batch, count_rtd_tokens_for_batch,
                          micro_loss_scale, recover_lr_mult)
@@ -190,29 +191,35 @@ class Trainer:
             for b, (g_i, d_i) in zip(batches, counts):
                 b = self._to_device(b)
                 mask = self._mask_of(b)
-                out = model(input_ids=b["input_ids"], attention_mask=mask, labels=b["labels"],
-                            token_type_ids=b.get("token_type_ids"), sampling_temperature=self.temperature,
-                            phase="generator")
+                with nvtx_range("generator fwd"):
+                    out = model(input_ids=b["input_ids"], attention_mask=mask, labels=b["labels"],
+                                token_type_ids=b.get("token_type_ids"), sampling_temperature=self.temperature,
+                                phase="generator")
                 w = (g_i / gen_den) if self.token_weighted else 1.0
-                (out.gen_loss_raw * (self.gen_w * scale) * w).backward()
+                with nvtx_range("generator bwd"):
+                    (out.gen_loss_raw * (self.gen_w * scale) * w).backward()
                 guard = guard + out.gen_loss_raw.detach().float()
                 stats.gen_loss_tokens += out.gen_loss_raw.detach().float() * g_i
                 cached.append((b, mask, out.corrupted_input_ids, out.disc_labels, g_i, d_i))
-            norms["generator"] = self._finish_optimizer("generator", guard)
+            with nvtx_range("generator optimizer"):
+                norms["generator"] = self._finish_optimizer("generator", guard)
             model.sync_discriminator_embeddings_from_generator()
             eng.zero_grad("generator")
             guard = zero()
             for b, mask, corrupted, labels, g_i, d_i in cached:
-                out = model(input_ids=b["input_ids"], corrupted_input_ids=corrupted, disc_labels=labels,
-                            attention_mask=mask, token_type_ids=b.get("token_type_ids"), phase="discriminator")
+                with nvtx_range("discriminator fwd"):
+                    out = model(input_ids=b["input_ids"], corrupted_input_ids=corrupted, disc_labels=labels,
+                                attention_mask=mask, token_type_ids=b.get("token_type_ids"), phase="discriminator")
                 w = (d_i / disc_den) if self.token_weighted else 1.0
                 w = w * (1.0 if g_i > 0 else 0.0) * has_targets  # micro-batches / windows without masked tokens carry no RTD signal
-                (out.disc_loss_raw * (self.disc_w * scale) * w).backward()
+                with nvtx_range("discriminator bwd"):
+                    (out.disc_loss_raw * (self.disc_w * scale) * w).backward()
                 guard = guard + out.disc_loss_raw.detach().float()
                 stats.disc_loss_tokens += out.disc_loss_raw.detach().float() * d_i
                 stats.disc_acc_tokens += out.disc_accuracy.float() * d_i
                 stats.disc_pos += out.disc_positive_count.float()
-            norms["discriminator"] = self._finish_optimizer("discriminator", guard)
+            with nvtx_range("discriminator optimizer"):
+                norms["discriminator"] = self._finish_optimizer("discriminator", guard)
             eng.zero_grad("discriminator")
         else:
             guard = zero()
