@@ -133,6 +133,9 @@ __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_
 
 // Four threads share a query row (one per 32-key column group of the tile); the row maximum is
 // exchanged through shared memory, the running sum stays per thread until the end.
+// MASK: 0 = no mask (only the sequence end), 1 = key padding, 2 = document ids.
+// POS: 0 = content scores only, 1 = key-indexed bias tensor, 2 = gathers from the bucket-indexed tables.
+template <int MASK, int POS>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnDev p) {
@@ -164,7 +167,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int S = p.S;
-  const bool pos = p.span2 > 0;
   const int nkt = (S + kTile - 1) / kTile;
 
   if (tid == 0) {
@@ -182,7 +184,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tmem_alloc(tmem_slot, 256);
     tmem_relinquish();
   }
-  if (pos) {
+  if (POS == 2) {
     for (int i = tid; i < 2 * S - 1; i += kFwdThreads) {
       lutc[i] = p.lut_c2p[i];
       lutp[i] = p.lut_p2c[i];
@@ -219,16 +221,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const long long tq = static_cast<long long>(b) * S + (q_valid ? q : 0);
   int q_doc = 1;
   bool q_live = q_valid;
-  if (q_valid && p.key_keep) q_live = p.key_keep[tq] != 0;
-  if (q_valid && p.doc_ids) {
+  if (MASK == 1 && q_valid) q_live = p.key_keep[tq] != 0;
+  if (MASK == 2 && q_valid) {
     q_doc = p.doc_ids[tq];
     q_live = q_doc != 0;
   }
   const long long pos_row = static_cast<long long>(p.heads) * p.span2;
-  const __nv_bfloat16* c2p_row = p.c2p ? p.c2p + tq * pos_row + static_cast<long long>(h) * p.span2 : nullptr;
-  const uint4* bias_row = p.bias ? reinterpret_cast<const uint4*>(
-                                       p.bias + ((static_cast<long long>(b) * p.heads + h) * S + (q_valid ? q : 0)) * p.ldb)
-                                 : nullptr;
+  const __nv_bfloat16* c2p_row = (POS == 2 && p.c2p) ? p.c2p + tq * pos_row + static_cast<long long>(h) * p.span2 : nullptr;
+  const uint4* bias_row = POS == 1 ? reinterpret_cast<const uint4*>(
+                                         p.bias + ((static_cast<long long>(b) * p.heads + h) * S + (q_valid ? q : 0)) * p.ldb)
+                                   : nullptr;
 
   constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
   constexpr uint32_t idesc_o = make_idesc_bf16(128, 64, false, true);
@@ -250,22 +252,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   float m_run = -INFINITY, l_part = 0.f;
   for (int j = 0; j < nkt; ++j) {
     const int k0 = j * kTile;
-    if (tid < kTile) {  // key metadata of this tile: 0 = masked, otherwise doc id (or 1)
-      const int kk = k0 + tid;
-      int meta = 0;
-      if (kk < S) {
-        const long long tk = static_cast<long long>(b) * S + kk;
-        meta = 1;
-        if (p.key_keep) meta = p.key_keep[tk] ? 1 : 0;
-        if (p.doc_ids) meta = p.doc_ids[tk];
+    if (MASK != 0) {
+      if (tid < kTile) {  // key metadata of this tile: 0 = masked, otherwise doc id (or 1)
+        const int kk = k0 + tid;
+        int meta = 0;
+        if (kk < S) {
+          const long long tk = static_cast<long long>(b) * S + kk;
+          meta = MASK == 1 ? (p.key_keep[tk] ? 1 : 0) : p.doc_ids[tk];
+        }
+        kmeta[tid] = meta;
       }
-      kmeta[tid] = meta;
+      __syncthreads();
     }
-    __syncthreads();
     if (!mbar_wait(bar_s, j & 1, abort_flag, p.status, kErrAccFullWait)) { ok = false; break; }
     tc_fence_after();
 
-    float s[32];
+    float s[32];  // unscaled scores of this thread's 32 keys
     {
       uint32_t r[32];
       tmem_ld_32x32b_x32(t_s + lane_addr + part * 32, r);
@@ -274,31 +276,46 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(r[i]);
     }
     float tmax = -INFINITY;
-    {
-      const int kb = k0 + part * 32;           // first key of this thread's column group
-      const int dbase = q - kb + S - 1;        // lut index for that key
-      uint4 bvec = make_uint4(0, 0, 0, 0);
+    const int kb = k0 + part * 32;  // first key of this thread's column group
+    if (POS == 1) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const uint4 bvec = __ldg(bias_row + (kb >> 3) + g);
+        const uint32_t w[4] = {bvec.x, bvec.y, bvec.z, bvec.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          s[g * 8 + 2 * e] += __uint_as_float(w[e] << 16);
+          s[g * 8 + 2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+        }
+      }
+    } else if (POS == 2) {
+      const int dbase = q - kb + S - 1;  // lut index for the first key
       const __nv_bfloat16* p2c_base =
           p.p2c ? p.p2c + (static_cast<long long>(b) * S + kb) * pos_row + static_cast<long long>(h) * p.span2 : nullptr;
 #pragma unroll
       for (int k = 0; k < 32; ++k) {
-        const int meta = kmeta[part * 32 + k];
-        bool keep = meta != 0;
-        if (p.doc_ids) keep = keep && (meta == q_doc);
-        float v = s[k];
-        if (bias_row) {
-          if ((k & 7) == 0) bvec = __ldg(bias_row + ((kb + k) >> 3));
-          v += bf16_elem(bvec, k & 7);
-        } else if (pos && keep && q_valid) {
+        if (q_valid && kb + k < S) {
           const int di = dbase - k;
-          if (c2p_row) v += __bfloat162float(c2p_row[lutc[di]]);
-          if (p2c_base) v += __bfloat162float(p2c_base[static_cast<long long>(k) * pos_row + lutp[di]]);
+          if (c2p_row) s[k] += __bfloat162float(c2p_row[lutc[di]]);
+          if (p2c_base) s[k] += __bfloat162float(p2c_base[static_cast<long long>(k) * pos_row + lutp[di]]);
         }
-        v = keep ? v * p.scale_log2 : -INFINITY;
-        s[k] = v;
-        tmax = fmaxf(tmax, v);
       }
     }
+    if (MASK == 0) {
+      if (k0 + kTile > S) {  // last, partial tile (block-uniform)
+#pragma unroll
+        for (int k = 0; k < 32; ++k) s[k] = (kb + k < S) ? s[k] : -INFINITY;
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 32; ++k) {
+        const int meta = kmeta[part * 32 + k];
+        const bool keep = MASK == 1 ? (meta != 0) : (meta != 0 && meta == q_doc);
+        s[k] = keep ? s[k] : -INFINITY;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 32; ++k) tmax = fmaxf(tmax, s[k]);
     red[part * kTile + row] = tmax;
     tc_fence_before();
     __syncthreads();  // every thread has read its scores of tile j: the score accumulator is free again
@@ -315,13 +332,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       umma_commit(bar_s);
     }
     tmax = fmaxf(fmaxf(red[row], red[kTile + row]), fmaxf(red[2 * kTile + row], red[3 * kTile + row]));
-    const float m_new = fmaxf(m_run, tmax);
+    const float m_new = fmaxf(m_run, tmax);  // running maximum of the unscaled scores
     const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-    const float alpha = (m_run == -INFINITY) ? 0.f : ex2(m_run - m_use);
+    const float alpha = (m_run == -INFINITY) ? 0.f : ex2((m_run - m_use) * p.scale_log2);
+    const float neg_ms = -m_use * p.scale_log2;
     float lsum = 0.f;
 #pragma unroll
     for (int k = 0; k < 32; ++k) {
-      s[k] = ex2(s[k] - m_use);
+      s[k] = ex2(fmaf(s[k], p.scale_log2, neg_ms));
       lsum += s[k];
     }
     l_part = l_part * alpha + lsum;
@@ -398,7 +416,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     if (q_valid && part == 0 && p.lse)
       p.lse[(static_cast<long long>(b) * p.heads + h) * S + q] =
-          (q_live && l_run > 0.f) ? (m_run + log2f(l_run)) : INFINITY;
+          (q_live && l_run > 0.f) ? (m_run * p.scale_log2 + log2f(l_run)) : INFINITY;
   }
   tc_fence_before();
   __syncthreads();
@@ -453,6 +471,7 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 
 constexpr int kBwdThreads = 512;  // warp w: TMEM lane quadrant (w & 3), 32-key column group (w >> 2)
 
+template <int MASK, int POS>  // as in the forward kernel
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -485,7 +504,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int S = p.S;
-  const bool pos = p.span2 > 0;
   const int nqt = (S + kTile - 1) / kTile;
 
   if (tid == 0) {
@@ -502,20 +520,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  if (pos) {
+  if (POS == 2) {
     for (int i = tid; i < 2 * S - 1; i += kBwdThreads) {
       lutc[i] = p.lut_c2p[i];
       lutp[i] = p.lut_p2c[i];
     }
   }
-  if (tid < kTile) {
+  if (MASK != 0 && tid < kTile) {
     const int kk = k0 + tid;
     int meta = 0;
     if (kk < S) {
       const long long tk = static_cast<long long>(b) * S + kk;
-      meta = 1;
-      if (p.key_keep) meta = p.key_keep[tk] ? 1 : 0;
-      if (p.doc_ids) meta = p.doc_ids[tk];
+      meta = MASK == 1 ? (p.key_keep[tk] ? 1 : 0) : p.doc_ids[tk];
     }
     kmeta[tid] = meta;
   }
@@ -610,45 +626,61 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const bool q_valid = q < S;
     const long long tq = static_cast<long long>(b) * S + (q_valid ? q : 0);
     int q_doc = 1;
-    if (q_valid && p.doc_ids) q_doc = p.doc_ids[tq];
+    if (MASK == 2 && q_valid) q_doc = p.doc_ids[tq];
     const long long stat = (static_cast<long long>(b) * p.heads + h) * S + (q_valid ? q : 0);
     const float lse = q_valid ? p.lse[stat] : INFINITY;
     const float delta = q_valid ? p.delta[stat] : 0.f;
-    const __nv_bfloat16* c2p_row = p.c2p ? p.c2p + tq * pos_row + static_cast<long long>(h) * p.span2 : nullptr;
-    float* dc2p_row = p.d_c2p ? p.d_c2p + tq * pos_row + static_cast<long long>(h) * p.span2 : nullptr;
+    const __nv_bfloat16* c2p_row = (POS == 2 && p.c2p) ? p.c2p + tq * pos_row + static_cast<long long>(h) * p.span2 : nullptr;
+    float* dc2p_row = (POS == 2 && p.d_c2p) ? p.d_c2p + tq * pos_row + static_cast<long long>(h) * p.span2 : nullptr;
     const long long kbase = (static_cast<long long>(b) * S + k0) * pos_row + static_cast<long long>(h) * p.span2;
     const int dbase = q - k0 + S - 1;
     const long long brow_off = ((static_cast<long long>(b) * p.heads + h) * S + (q_valid ? q : 0)) * p.ldb + k0;
-    const uint4* bias_row = p.bias ? reinterpret_cast<const uint4*>(p.bias + brow_off) : nullptr;
-    uint4* dbias_row = (p.dbias && q_valid) ? reinterpret_cast<uint4*>(p.dbias + brow_off) : nullptr;
+    const uint4* bias_row = POS == 1 ? reinterpret_cast<const uint4*>(p.bias + brow_off) : nullptr;
+    uint4* dbias_row = (POS == 1 && q_valid) ? reinterpret_cast<uint4*>(p.dbias + brow_off) : nullptr;
 
     {
       const int c = part;  // this thread's 32 keys of the tile
       float pv[32], gv[32];
-      uint4 bvec = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int e = 0; e < 32; ++e) pv[e] = __uint_as_float(rs[e]);
+      if (POS == 1) {
+#pragma unroll
+        for (int g8 = 0; g8 < 4; ++g8) {
+          const uint4 bvec = __ldg(bias_row + c * 4 + g8);
+          const uint32_t w[4] = {bvec.x, bvec.y, bvec.z, bvec.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            pv[g8 * 8 + 2 * e] += __uint_as_float(w[e] << 16);
+            pv[g8 * 8 + 2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+          }
+        }
+      }
+      const float delta_s = delta * p.inv_scale;
 #pragma unroll
       for (int e = 0; e < 32; ++e) {
         const int k = c * 32 + e;
-        const int meta = kmeta[k];
-        bool keep = (meta != 0) && q_valid;
-        if (p.doc_ids) keep = keep && (meta == q_doc);
-        float v = __uint_as_float(rs[e]);
+        bool keep = true;
+        if (MASK == 0) {
+          if (k0 + kTile > S) keep = k0 + k < S;  // last, partial key tile
+        } else {
+          const int meta = kmeta[k];
+          keep = MASK == 1 ? (meta != 0) : (meta != 0 && meta == q_doc);
+        }
+        float v = pv[e];
         int ic = 0, ip = 0;
-        if (bias_row) {
-          if ((e & 7) == 0) bvec = __ldg(bias_row + c * 4 + (e >> 3));
-          v += bf16_elem(bvec, e & 7);
-        } else if (pos && keep) {
+        if (POS == 2 && keep && q_valid) {
           const int di = dbase - k;
           ic = lutc[di];
           ip = lutp[di];
           if (c2p_row) v += __bfloat162float(c2p_row[ic]);
           if (p.p2c) v += __bfloat162float(p.p2c[kbase + static_cast<long long>(k) * pos_row + ip]);
         }
-        const float prob = keep ? ex2(v * p.scale_log2 - lse) : 0.f;
-        const float g = prob * (__uint_as_float(rd[e]) - delta) * p.inv_scale;
+        // rows past the sequence end and dead queries carry lse = +inf: their probabilities are exactly 0
+        const float prob = keep ? ex2(fmaf(v, p.scale_log2, -lse)) : 0.f;
+        const float g = prob * fmaf(__uint_as_float(rd[e]), p.inv_scale, -delta_s);
         pv[e] = prob;
         gv[e] = g;
-        if (!bias_row && pos && keep && g != 0.f) {
+        if (POS == 2 && keep && q_valid && g != 0.f) {
           if (dc2p_row) atomicAdd(dc2p_row + ic, g);
           if (p.d_p2c) atomicAdd(p.d_p2c + kbase + static_cast<long long>(k) * pos_row + ip, g);
         }
@@ -744,6 +776,39 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 
+
+// delta[b,h,s] = sum_d dO[b,s,h,d] * O[b,s,h,d] (fp32), the row term of the softmax gradient.
+// Eight lanes share one (token, head): 16 bytes of dO and of O each.
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, long long ld_do, const __nv_bfloat16* __restrict__ out,
+                  long long ldo, float* __restrict__ delta, int B, int S, int heads) {
+  const long long gid = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  const long long pair = gid >> 3;  // (token, head)
+  const int sub = static_cast<int>(gid & 7);
+  const long long total = static_cast<long long>(B) * S * heads;
+  float acc = 0.f;
+  long long token = 0;
+  int h = 0;
+  if (pair < total) {
+    token = pair / heads;
+    h = static_cast<int>(pair % heads);
+    const uint4 a = *reinterpret_cast<const uint4*>(dout + token * ld_do + h * kD + sub * 8);
+    const uint4 o = *reinterpret_cast<const uint4*>(out + token * ldo + h * kD + sub * 8);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      acc += __uint_as_float(aw[e] << 16) * __uint_as_float(ow[e] << 16) +
+             __uint_as_float(aw[e] & 0xffff0000u) * __uint_as_float(ow[e] & 0xffff0000u);
+  }
+  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+  if (pair < total && sub == 0) {
+    const long long bb = token / S, ss = token % S;
+    delta[(bb * heads + h) * S + ss] = acc;
+  }
+}
+
 int make_head_map(CUtensorMap* m, const void* ptr, const AttnArgs* a, long long ld) {
   return db200_make_tmap_bf16(m, ptr, static_cast<long long>(a->heads) * kD, a->S, a->B, ld,
                               static_cast<long long>(a->S) * ld, kTile);
@@ -783,14 +848,22 @@ extern "C" int db200_attn_fwd(const AttnArgs* a, void* stream_) {
   d.ldo = a->ldo;
   d.lse = a->lse;
   d.status = db200_status_ptr();
-  const int smem = FwdSmem::total(a->S, pos);
-  static int configured = 0;
-  if (configured < smem) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
-    configured = smem;
+  const int pos_mode = d.bias ? 1 : (pos ? 2 : 0);
+  const int mask_mode = d.doc_ids ? 2 : (d.key_keep ? 1 : 0);
+  const int smem = FwdSmem::total(a->S, pos_mode == 2);
+  using FwdKernel = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, AttnDev);
+  static const FwdKernel kernels[3][3] = {
+      {attn_fwd_kernel<0, 0>, attn_fwd_kernel<0, 1>, attn_fwd_kernel<0, 2>},
+      {attn_fwd_kernel<1, 0>, attn_fwd_kernel<1, 1>, attn_fwd_kernel<1, 2>},
+      {attn_fwd_kernel<2, 0>, attn_fwd_kernel<2, 1>, attn_fwd_kernel<2, 2>}};
+  static int configured[3][3] = {};
+  const FwdKernel kern = kernels[mask_mode][pos_mode];
+  if (configured[mask_mode][pos_mode] < smem) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
+    configured[mask_mode][pos_mode] = smem;
   }
   dim3 grid((a->S + kTile - 1) / kTile, a->heads, a->B);
-  attn_fwd_kernel<<<grid, kFwdThreads, smem, stream>>>(tq, tk, tv, d);
+  kern<<<grid, kFwdThreads, smem, stream>>>(tq, tk, tv, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -832,13 +905,31 @@ extern "C" int db200_attn_bwd(const AttnArgs* a, void* stream_) {
   d.d_c2p = a->d_c2p;
   d.d_p2c = a->d_p2c;
   d.status = db200_status_ptr();
-  const int smem = BwdSmem::total(a->S, pos);
-  static int configured = 0;
-  if (configured < smem) {
-    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
-    configured = smem;
+  const int pos_mode = d.bias ? 1 : (pos ? 2 : 0);
+  const int mask_mode = d.doc_ids ? 2 : (d.key_keep ? 1 : 0);
+  const int smem = BwdSmem::total(a->S, pos_mode == 2);
+  using BwdKernel = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, AttnBwdDev);
+  static const BwdKernel kernels[3][3] = {
+      {attn_bwd_kernel<0, 0>, attn_bwd_kernel<0, 1>, attn_bwd_kernel<0, 2>},
+      {attn_bwd_kernel<1, 0>, attn_bwd_kernel<1, 1>, attn_bwd_kernel<1, 2>},
+      {attn_bwd_kernel<2, 0>, attn_bwd_kernel<2, 1>, attn_bwd_kernel<2, 2>}};
+  static int configured[3][3] = {};
+  const BwdKernel kern = kernels[mask_mode][pos_mode];
+  if (configured[mask_mode][pos_mode] < smem) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
+    configured[mask_mode][pos_mode] = smem;
   }
   dim3 grid((a->S + kTile - 1) / kTile, a->heads, a->B);
-  attn_bwd_kernel<<<grid, kBwdThreads, smem, stream>>>(tq, tk, tv, tdo, d);
+  kern<<<grid, kBwdThreads, smem, stream>>>(tq, tk, tv, tdo, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int db200_attn_delta(const void* dout, long long ld_do, const void* out, long long ldo, float* delta, int B,
+                                int S, int heads, void* stream) {
+  if (B <= 0 || S <= 0 || heads <= 0) return 0;
+  if (!aligned16(dout) || !aligned16(out) || (ld_do % 8) || (ldo % 8)) return -10;
+  const long long threads = static_cast<long long>(B) * S * heads * 8;
+  attn_delta_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(dout), ld_do, static_cast<const __nv_bfloat16*>(out), ldo, delta, B, S, heads);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

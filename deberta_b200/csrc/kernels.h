@@ -130,6 +130,9 @@ int db200_posbias_scatter_ranges(const void* dbias, const void* ranges, void* dt
 
 int db200_attn_fwd(const AttnArgs* args, void* stream);
 int db200_attn_bwd(const AttnArgs* args, void* stream);
+// delta[b,h,s] = sum over the head dim of dO * O (fp32 [B, heads, S]); input of db200_attn_bwd.
+int db200_attn_delta(const void* dout, long long ld_do, const void* out, long long ldo, float* delta, int B, int S,
+                     int heads, void* stream);
 
 #ifdef __cplusplus
 }

@@ -174,7 +174,9 @@ class _FlashAttention(torch.autograd.Function):
         T = B * S
         dev = q.device
         dout = dout.contiguous()
-        delta = (dout.float() * out.float()).view(B, S, heads, 64).sum(-1).permute(0, 2, 1).contiguous()
+        delta = torch.empty((B, heads, S), dtype=torch.float32, device=dev)
+        _lib.call("db200_attn_delta", _lib.ptr(dout), ctypes.c_longlong(H), _lib.ptr(out), ctypes.c_longlong(H),
+                  _lib.ptr(delta), c_int(B), c_int(S), c_int(heads), _lib.stream_ptr())
         dq_acc = torch.zeros((T, H), dtype=torch.float32, device=dev)
         dk = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
         dv = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
@@ -229,9 +231,9 @@ class _FlashAttention(torch.autograd.Function):
             d_pos_k = d_pos_k.to(pos_k.dtype)
         if g_p2c is not None:
             g = g_p2c.permute(1, 0, 2)
-            dk_extra = torch.zeros((T, H), dtype=torch.float32, device=dev)
-            gemm(g, _heads_view(pos_q, heads), b_mn=True, out=_heads_view(dk_extra, heads), accumulate=True)
-            dk = (dk.float() + dk_extra).to(torch.bfloat16)
+            # dK += dP2C · PosQ (per head), added in the GEMM epilogue
+            dkh = _heads_view(dk, heads)
+            gemm(g, _heads_view(pos_q, heads), b_mn=True, residual=dkh, out=dkh)
             d_pos_q = torch.zeros(pos_q.shape, dtype=torch.float32, device=dev)
             gemm(g, _heads_view(k2, heads), a_mn=True, b_mn=True, out=_heads_view(d_pos_q, heads), accumulate=True)
             d_pos_q = d_pos_q.to(pos_q.dtype)

@@ -81,7 +81,8 @@ def check_forbidden_apis() -> CheckResult:
     """No travelling source may name the batched-memcpy driver calls or a cluster-multicast bulk/TMA load."""
     names = ["cuda" + "Memcpy" + "BatchAsync", "cuda" + "Memcpy3D" + "BatchAsync", "cu" + "Memcpy" + "BatchAsync",
              "cu" + "Memcpy3D" + "BatchAsync"]
-    bulk_mc = re.compile(r"cp\.async\.bulk[\w\.:]*\.multicast::cluster")
+    # (the qualifier is spelled in two pieces so that this checker does not itself contain the pattern)
+    bulk_mc = re.compile(r"cp\.async\.bulk[\w\.:]*\.multi" + "cast::cluster")
     hits = []
     for path in list(REPO.rglob("*.py")) + list(REPO.rglob("*.cu")) + list(REPO.rglob("*.cuh")) + list(REPO.rglob("*.h")):
         rel = path.relative_to(REPO)
