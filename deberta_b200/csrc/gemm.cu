@@ -36,7 +36,9 @@ struct SmemLayout {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kStagingOffset = kStages * kStageBytes;          // 1024-byte aligned
+  static constexpr int kStagingBytes = 32 * 128;                         // per epilogue warp: 32 rows x 64 bf16, 128B swizzle
+  static constexpr int kBarOffset = kStagingOffset + kEpilogueWarps * kStagingBytes;
   static constexpr int kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
 };
 
@@ -47,6 +49,7 @@ struct DevParams {
   float alpha;
   int epi;
   int out_f32;      // 1: fp32 output
+  int tma_out;      // 1: bf16 outputs leave through shared memory and TMA stores (tmap_out / tmap_out2)
   int accumulate;   // 1: out += result (fp32 output only, uses red.add)
   const __nv_bfloat16* bias;
   const __nv_bfloat16* residual;
@@ -84,11 +87,17 @@ __device__ __forceinline__ float dgelu_erf(float x) {
   return cdf + x * pdf;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+// MODE selects the epilogue at compile time (one lean code path per instantiation):
+// 0 bf16 output (+bias, +residual), 1 GELU (two outputs), 2 GELU derivative, 3 fp32 output (store / accumulate /
+// split-K), 4 cross-entropy forward, 5 cross-entropy backward.
+template <int BN, bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_out2,
             const DevParams p) {
   using L = SmemLayout<BN>;
+  constexpr int kEpi = MODE == 1 ? EPI_GELU : MODE == 2 ? EPI_DGELU : MODE == 4 ? EPI_CE_FWD : MODE == 5 ? EPI_CE_BWD : EPI_NONE;
+  constexpr bool kOutF32 = MODE == 3;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
@@ -109,7 +118,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 32 * kEpilogueWarps);
+      mbar_init(&acc_empty[a], kEpilogueWarps);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -219,6 +228,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
+    // TMA-store path: a warp collects 64 columns (two chunks) of its 32 rows in a swizzled staging tile and
+    // hands it to the TMA unit, which writes whole lines and clips rows >= M and columns >= N.
+    uint8_t* stg = smem + L::kStagingOffset + (warp - 2) * L::kStagingBytes;
+    bool stg_busy = false;  // a bulk store may still be reading the staging tile (warp-uniform)
+    auto stage_words = [&](const uint32_t* wds, int sub) {  // 16 packed words = 32 columns of this lane's row
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const int chunk = (sub * 4 + q4) ^ (lane & 7);
+        *reinterpret_cast<uint4*>(stg + lane * 128 + chunk * 16) =
+            make_uint4(wds[q4 * 4], wds[q4 * 4 + 1], wds[q4 * 4 + 2], wds[q4 * 4 + 3]);
+      }
+    };
+    auto stage_acquire = [&]() {  // before the first write of a new 64-column group
+      if (stg_busy) {
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
+        stg_busy = false;
+      }
+    };
+    auto stage_flush = [&](const CUtensorMap* tm, int x, int y, int zz) {
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_3d(tm, stg, x, y, zz);
+        tma_store_commit();
+      }
+      stg_busy = true;
+    };
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
       const int t = w / p.splits;
       const int z = t / tiles_per_batch;
@@ -233,13 +270,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
       const __nv_bfloat16* bias = p.bias ? p.bias + z * p.bs_bias : nullptr;
-      if (p.epi == EPI_CE_FWD || p.epi == EPI_CE_BWD) {
+      if (kEpi == EPI_CE_FWD || kEpi == EPI_CE_BWD) {
         // One thread owns one row of logits. Forward: tile-local max / sum-exp / label logit and the
         // Gumbel-max candidate (logit/T + noise, forbidden ids excluded); partial results of every
         // vocabulary tile are combined by a second small kernel. Backward: softmax minus one-hot.
         const long long label = row_ok ? p.labels[row] : -1;
-        const float lse = (p.epi == EPI_CE_BWD && row_ok) ? p.row_lse[row] : 0.f;
-        const float gs = p.gscale * ((p.epi == EPI_CE_BWD && p.gscale_ptr) ? *p.gscale_ptr : 1.f);
+        const float lse = (kEpi == EPI_CE_BWD && row_ok) ? p.row_lse[row] : 0.f;
+        const float gs = p.gscale * ((kEpi == EPI_CE_BWD && p.gscale_ptr) ? *p.gscale_ptr : 1.f);
         float t_max = -INFINITY, t_sum = 0.f, best = -INFINITY;
         int best_idx = 0;
 #pragma unroll 1
@@ -264,7 +301,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             v[j] = x;
             cmax = fmaxf(cmax, x);
           }
-          if (p.epi == EPI_CE_FWD) {
+          if (kEpi == EPI_CE_FWD) {
             const float m_new = fmaxf(t_max, cmax);
             float acc = 0.f;
 #pragma unroll
@@ -296,7 +333,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
           }
         }
-        if (p.epi == EPI_CE_FWD && row_ok && (n0 + half * (BN / 2) < p.N)) {
+        if (kEpi == EPI_CE_FWD && row_ok && (n0 + half * (BN / 2) < p.N)) {
           // partial results are kept per half tile: ceil(N / (BN/2)) entries per row
           const long long tn = (n0 / BN) * 2 + half;
           const long long plane = static_cast<long long>((p.N + BN / 2 - 1) / (BN / 2)) * p.M;
@@ -307,18 +344,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           dst[3 * plane] = __int_as_float(best_idx);
         }
         tc_fence_before();
-        mbar_arrive(&acc_empty[acc]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         continue;
       }
+      uint32_t gelu_words[32];  // second output of the GELU epilogue for one 64-column group
 #pragma unroll 1
-      for (int c = half * kChunksPerHalf; c < (half + 1) * kChunksPerHalf; ++c) {
+      for (int cp = half * (kChunksPerHalf / 2); cp < (half + 1) * (kChunksPerHalf / 2); ++cp) {
+#pragma unroll
+      for (int csub = 0; csub < 2; ++csub) {
+        const int c = cp * 2 + csub;
         const int nc = n0 + c * 32;
-        if (nc >= p.N) break;  // warp-uniform
+        if (nc >= p.N) continue;  // warp-uniform
         uint32_t r[32];
         tmem_ld_32x32b_x32(t_row + c * 32, r);
         tmem_ld_wait();
-        if (!row_ok || empty_split) continue;
+        if ((!row_ok && !p.tma_out) || empty_split) continue;
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
@@ -341,7 +383,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               if (nc + j < p.N) v[j] += __bfloat162float(bias[nc + j]);
           }
         }
-        if (p.out_f32) {
+        if (kOutF32) {
           float* o = reinterpret_cast<float*>(p.out) + z * p.bs_out + static_cast<long long>(row) * p.ldo + nc;
           if (p.accumulate || p.splits > 1) {
             if (full && (p.ldo % 4 == 0)) {
@@ -371,7 +413,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         // ---- bf16 outputs ----
         const bool vec = full && (p.ldo % 8 == 0);
-        if (p.residual) {
+        if (p.residual && row_ok) {
           const __nv_bfloat16* rp = p.residual + z * p.bs_res + static_cast<long long>(row) * p.ldr + nc;
           if (full && (p.ldr % 8 == 0)) {
             uint32_t bw[16];
@@ -386,7 +428,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               if (nc + j < p.N) v[j] += __bfloat162float(rp[j]);
           }
         }
-        if (p.epi == EPI_DGELU) {
+        if (kEpi == EPI_DGELU && row_ok) {
           const __nv_bfloat16* ap = p.aux + z * p.bs_aux + static_cast<long long>(row) * p.ldaux + nc;
           if (full && (p.ldaux % 8 == 0)) {
             uint32_t bw[16];
@@ -401,6 +443,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               if (nc + j < p.N) v[j] *= dgelu_erf(__bfloat162float(ap[j]));
           }
         }
+        if (p.tma_out) {
+          // (reached by every lane of the warp: rows >= M compute on zeros and are clipped by the store)
+          const int sub = csub;
+          const bool last_of_group = sub == 1 || nc + 32 >= p.N;
+          uint32_t wds[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) wds[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+          if (sub == 0) stage_acquire();
+          stage_words(wds, sub);
+          uint32_t* g2 = gelu_words + sub * 16;
+          if (kEpi == EPI_GELU) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              g2[i] = pack_bf16(gelu_erf(bf16_lo(wds[i])), gelu_erf(bf16_hi(wds[i])));
+          }
+          if (last_of_group) {
+            const int x = nc - sub * 32, y = m0 + quad * 32;
+            stage_flush(&tmap_out, x, y, z);
+            if (kEpi == EPI_GELU) {
+              stage_acquire();
+              stage_words(gelu_words, 0);
+              if (sub == 1) stage_words(gelu_words + 16, 1);
+              stage_flush(&tmap_out2, x, y, z);
+            }
+          }
+          continue;
+        }
         __nv_bfloat16* o =
             reinterpret_cast<__nv_bfloat16*>(p.out) + z * p.bs_out + static_cast<long long>(row) * p.ldo + nc;
         if (vec) {
@@ -409,7 +478,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           for (int j = 0; j < 32; ++j)
             if (nc + j < p.N) o[j] = __float2bfloat16(v[j]);
         }
-        if (p.epi == EPI_GELU) {
+        if (kEpi == EPI_GELU) {
           // second output: GELU of the (bf16-rounded) pre-activation that was just stored
           __nv_bfloat16* o2 = p.out2 + z * p.bs_out2 + static_cast<long long>(row) * p.ldo2 + nc;
 #pragma unroll
@@ -422,10 +491,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
         }
       }
+      }
       tc_fence_before();
-      mbar_arrive(&acc_empty[acc]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    if (lane == 0) tma_store_wait_all();  // shared memory must outlive the bulk stores that read it
   }
 
   tc_fence_before();
@@ -467,16 +539,17 @@ int num_sms() {
   return g_num_sms;
 }
 
-template <int BN, bool A_MN, bool B_MN>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const DevParams& p, int grid, cudaStream_t stream) {
+template <int BN, bool A_MN, bool B_MN, int MODE>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& to2, const DevParams& p,
+           int grid, cudaStream_t stream) {
   using L = SmemLayout<BN>;
   static bool configured = false;
-  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN, MODE>;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess) return -3;
     configured = true;
   }
-  kern<<<grid, kThreads, L::kTotal, stream>>>(ta, tb, p);
+  kern<<<grid, kThreads, L::kTotal, stream>>>(ta, tb, to, to2, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -601,18 +674,42 @@ extern "C" int db200_gemm_bf16(const GemmArgs* a, void* stream_) {
   else          rc = db200_make_tmap_bf16(&tb, a->B, a->N, a->K, a->batch, a->ldb, a->bs_b, BK);
   if (rc) return rc;
 
+  // bf16 outputs go through shared memory + TMA stores when their layout allows a tensor map
+  CUtensorMap to = ta, to2 = ta;  // placeholders when unused (never dereferenced by the kernel)
+  auto tma_ok = [&](const void* ptr, long long ld, long long bs) {
+    return ptr && !(reinterpret_cast<uintptr_t>(ptr) & 15) && (ld % 8 == 0) && (a->batch == 1 || bs % 8 == 0);
+  };
+  p.tma_out = 0;
+  if (!p.out_f32 && splits == 1 && p.epi != EPI_CE_FWD && p.epi != EPI_CE_BWD && tma_ok(a->out, a->ldo, a->bs_out) &&
+      (p.epi != EPI_GELU || tma_ok(a->out2, a->ldo2, a->bs_out2))) {
+    if (db200_make_tmap_bf16(&to, a->out, a->N, a->M, a->batch, a->ldo, a->bs_out, 32) == 0 &&
+        (p.epi != EPI_GELU || db200_make_tmap_bf16(&to2, a->out2, a->N, a->M, a->batch, a->ldo2, a->bs_out2, 32) == 0))
+      p.tma_out = 1;
+  }
+
   const int grid = min(tiles * splits, num_sms());
-#define DISPATCH(BN_, AM_, BM_) return launch<BN_, AM_, BM_>(ta, tb, p, grid, stream)
+  const int mode = p.out_f32 ? 3 : p.epi == EPI_GELU ? 1 : p.epi == EPI_DGELU ? 2 : p.epi == EPI_CE_FWD ? 4 : p.epi == EPI_CE_BWD ? 5 : 0;
+#define DISPATCH_MODE(BN_, AM_, BM_)                                                         \
+  switch (mode) {                                                                            \
+    case 0: return launch<BN_, AM_, BM_, 0>(ta, tb, to, to2, p, grid, stream);               \
+    case 1: return launch<BN_, AM_, BM_, 1>(ta, tb, to, to2, p, grid, stream);               \
+    case 2: return launch<BN_, AM_, BM_, 2>(ta, tb, to, to2, p, grid, stream);               \
+    case 3: return launch<BN_, AM_, BM_, 3>(ta, tb, to, to2, p, grid, stream);               \
+    case 4: return launch<BN_, AM_, BM_, 4>(ta, tb, to, to2, p, grid, stream);               \
+    default: return launch<BN_, AM_, BM_, 5>(ta, tb, to, to2, p, grid, stream);              \
+  }
+#define DISPATCH(BN_, AM_, BM_) DISPATCH_MODE(BN_, AM_, BM_)
   if (BN == 256) {
-    if (!a->a_mn && !a->b_mn) DISPATCH(256, false, false);
-    if (!a->a_mn && a->b_mn) DISPATCH(256, false, true);
-    if (a->a_mn && !a->b_mn) DISPATCH(256, true, false);
+    if (!a->a_mn && !a->b_mn) { DISPATCH(256, false, false); }
+    if (!a->a_mn && a->b_mn) { DISPATCH(256, false, true); }
+    if (a->a_mn && !a->b_mn) { DISPATCH(256, true, false); }
     DISPATCH(256, true, true);
   } else {
-    if (!a->a_mn && !a->b_mn) DISPATCH(128, false, false);
-    if (!a->a_mn && a->b_mn) DISPATCH(128, false, true);
-    if (a->a_mn && !a->b_mn) DISPATCH(128, true, false);
+    if (!a->a_mn && !a->b_mn) { DISPATCH(128, false, false); }
+    if (!a->a_mn && a->b_mn) { DISPATCH(128, false, true); }
+    if (a->a_mn && !a->b_mn) { DISPATCH(128, true, false); }
     DISPATCH(128, true, true);
   }
 #undef DISPATCH
+#undef DISPATCH_MODE
 }
