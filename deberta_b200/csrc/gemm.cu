@@ -80,11 +80,32 @@ __device__ __forceinline__ float hash_uniform(unsigned long long seed, unsigned 
   return (static_cast<float>(x >> 40) + 0.5f) * (1.0f / 16777216.0f);
 }
 
-__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+// Normal CDF and density through one exponential: erf by Abramowitz-Stegun 7.1.26 (|error| < 1.5e-7, far below
+// bf16 resolution) shares exp(-x^2/2) with the density, so GELU and its derivative cost one ex2 and one
+// reciprocal per element instead of an erff plus an expf.
+__device__ __forceinline__ void normal_cdf_pdf(float x, float& cdf, float& pdf) {
+  const float ax = fabsf(x) * 0.70710678118654752f;
+  float t;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, ax, 1.0f)));
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * x * -0.72134752044448170f));  // exp(-x^2/2)
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float half_erfc = 0.5f * poly * t * e;  // 0.5 * erfc(|x|/sqrt 2)
+  cdf = x >= 0.f ? 1.0f - half_erfc : half_erfc;
+  pdf = 0.3989422804014327f * e;
+}
+__device__ __forceinline__ float gelu_erf(float x) {
+  float cdf, pdf;
+  normal_cdf_pdf(x, cdf, pdf);
+  return x * cdf;
+}
 __device__ __forceinline__ float dgelu_erf(float x) {
-  const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752f));
-  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
-  return cdf + x * pdf;
+  float cdf, pdf;
+  normal_cdf_pdf(x, cdf, pdf);
+  return fmaf(x, pdf, cdf);
 }
 
 // MODE selects the epilogue at compile time (one lean code path per instantiation):
@@ -349,9 +370,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         continue;
       }
-      uint32_t gelu_words[32];  // second output of the GELU epilogue for one 64-column group
 #pragma unroll 1
       for (int cp = half * (kChunksPerHalf / 2); cp < (half + 1) * (kChunksPerHalf / 2); ++cp) {
+      // GELU-derivative operand of both chunks of the group: one round trip instead of two
+      uint32_t auxp[2][16];
+      bool auxv[2] = {false, false};
+      if (kEpi == EPI_DGELU) {
+#pragma unroll
+        for (int csub = 0; csub < 2; ++csub) {
+          const int nc = n0 + (cp * 2 + csub) * 32;
+          auxv[csub] = row_ok && (nc + 32 <= p.N) && (p.ldaux % 8 == 0);
+          if (auxv[csub]) load_bf16x32(p.aux + z * p.bs_aux + static_cast<long long>(row) * p.ldaux + nc, auxp[csub]);
+        }
+      }
 #pragma unroll
       for (int csub = 0; csub < 2; ++csub) {
         const int c = cp * 2 + csub;
@@ -359,12 +390,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (nc >= p.N) continue;  // warp-uniform
         uint32_t r[32];
         tmem_ld_32x32b_x32(t_row + c * 32, r);
+        const bool full = (nc + 32 <= p.N);
+        // row-indexed epilogue operands are requested before the accumulator wait so that both latencies overlap
+        uint32_t resw[16];
+        const uint32_t* auxw = auxp[csub];
+        const bool res_vec = !kOutF32 && p.residual && row_ok && full && (p.ldr % 8 == 0);
+        const bool aux_vec = auxv[csub];
+        if (res_vec) load_bf16x32(p.residual + z * p.bs_res + static_cast<long long>(row) * p.ldr + nc, resw);
         tmem_ld_wait();
         if ((!row_ok && !p.tma_out) || empty_split) continue;
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-        const bool full = (nc + 32 <= p.N);
         if (bias && split == 0) {
           if (full) {
             const uint4* bp = reinterpret_cast<const uint4*>(bias + nc);
@@ -414,31 +451,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         // ---- bf16 outputs ----
         const bool vec = full && (p.ldo % 8 == 0);
         if (p.residual && row_ok) {
-          const __nv_bfloat16* rp = p.residual + z * p.bs_res + static_cast<long long>(row) * p.ldr + nc;
-          if (full && (p.ldr % 8 == 0)) {
-            uint32_t bw[16];
-            load_bf16x32(rp, bw);
+          if (res_vec) {
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
-              v[e * 2] += bf16_lo(bw[e]);
-              v[e * 2 + 1] += bf16_hi(bw[e]);
+              v[e * 2] += bf16_lo(resw[e]);
+              v[e * 2 + 1] += bf16_hi(resw[e]);
             }
           } else {
+            const __nv_bfloat16* rp = p.residual + z * p.bs_res + static_cast<long long>(row) * p.ldr + nc;
             for (int j = 0; j < 32; ++j)
               if (nc + j < p.N) v[j] += __bfloat162float(rp[j]);
           }
         }
         if (kEpi == EPI_DGELU && row_ok) {
-          const __nv_bfloat16* ap = p.aux + z * p.bs_aux + static_cast<long long>(row) * p.ldaux + nc;
-          if (full && (p.ldaux % 8 == 0)) {
-            uint32_t bw[16];
-            load_bf16x32(ap, bw);
+          if (aux_vec) {
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
-              v[e * 2] *= dgelu_erf(bf16_lo(bw[e]));
-              v[e * 2 + 1] *= dgelu_erf(bf16_hi(bw[e]));
+              v[e * 2] *= dgelu_erf(bf16_lo(auxw[e]));
+              v[e * 2 + 1] *= dgelu_erf(bf16_hi(auxw[e]));
             }
           } else {
+            const __nv_bfloat16* ap = p.aux + z * p.bs_aux + static_cast<long long>(row) * p.ldaux + nc;
             for (int j = 0; j < 32; ++j)
               if (nc + j < p.N) v[j] *= dgelu_erf(__bfloat162float(ap[j]));
           }
@@ -450,24 +483,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           uint32_t wds[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) wds[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
+          if (kEpi == EPI_GELU) {
+            // two outputs, one staging tile: the pre-activation leaves with direct 32-byte row stores, gelu(z) through
+            // the staging tile (waiting for a bulk store to release the tile twice per group would stall the warp)
+            if (row_ok && full) {
+              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + z * p.bs_out + static_cast<long long>(row) * p.ldo + nc;
+              store_words16(o, wds);
+            } else if (row_ok) {
+              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + z * p.bs_out + static_cast<long long>(row) * p.ldo + nc;
+              for (int j = 0; j < 32; ++j)
+                if (nc + j < p.N) o[j] = __float2bfloat16(v[j]);
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) wds[i] = pack_bf16(gelu_erf(bf16_lo(wds[i])), gelu_erf(bf16_hi(wds[i])));
+          }
           if (sub == 0) stage_acquire();
           stage_words(wds, sub);
-          uint32_t* g2 = gelu_words + sub * 16;
-          if (kEpi == EPI_GELU) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              g2[i] = pack_bf16(gelu_erf(bf16_lo(wds[i])), gelu_erf(bf16_hi(wds[i])));
-          }
-          if (last_of_group) {
-            const int x = nc - sub * 32, y = m0 + quad * 32;
-            stage_flush(&tmap_out, x, y, z);
-            if (kEpi == EPI_GELU) {
-              stage_acquire();
-              stage_words(gelu_words, 0);
-              if (sub == 1) stage_words(gelu_words + 16, 1);
-              stage_flush(&tmap_out2, x, y, z);
-            }
-          }
+          if (last_of_group) stage_flush(kEpi == EPI_GELU ? &tmap_out2 : &tmap_out, nc - sub * 32, m0 + quad * 32, z);
           continue;
         }
         __nv_bfloat16* o =

@@ -248,6 +248,17 @@ __device__ __forceinline__ void store_bf16x32(__nv_bfloat16* dst, const float* v
       reinterpret_cast<uint4*>(dst)[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
   }
 }
+// The same for 16 already packed words; the address must be 16-byte aligned.
+__device__ __forceinline__ void store_words16(__nv_bfloat16* dst, const uint32_t* w) {
+  if ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+    st_global_32B(dst, w);
+    st_global_32B(dst + 16, w + 8);
+  } else {
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      reinterpret_cast<uint4*>(dst)[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+  }
+}
 // 32 bf16 values of one row as packed pairs (16 words); the address must be 16-byte aligned.
 __device__ __forceinline__ void load_bf16x32(const __nv_bfloat16* src, uint32_t* w) {
   if ((reinterpret_cast<uintptr_t>(src) & 31) == 0) {
