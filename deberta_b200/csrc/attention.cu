@@ -252,7 +252,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   float m_run = -INFINITY, l_part = 0.f;
   for (int j = 0; j < nkt; ++j) {
     const int k0 = j * kTile;
+    bool tile_all_keep = false;
     if (MASK != 0) {
+      int tile_meta = 1;
       if (tid < kTile) {  // key metadata of this tile: 0 = masked, otherwise doc id (or 1)
         const int kk = k0 + tid;
         int meta = 0;
@@ -261,8 +263,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           meta = MASK == 1 ? (p.key_keep[tk] ? 1 : 0) : p.doc_ids[tk];
         }
         kmeta[tid] = meta;
+        tile_meta = meta;
       }
-      __syncthreads();
+      // padding masks are all-ones for most tiles: those skip the per-element selects
+      tile_all_keep = __syncthreads_and(MASK == 1 && tile_meta != 0) != 0;
     }
     if (!mbar_wait(bar_s, j & 1, abort_flag, p.status, kErrAccFullWait)) { ok = false; break; }
     tc_fence_after();
@@ -306,7 +310,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int k = 0; k < 32; ++k) s[k] = (kb + k < S) ? s[k] : -INFINITY;
       }
-    } else {
+    } else if (!tile_all_keep) {
 #pragma unroll
       for (int k = 0; k < 32; ++k) {
         const int meta = kmeta[part * 32 + k];
@@ -526,6 +530,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       lutp[i] = p.lut_p2c[i];
     }
   }
+  int cta_meta = 1;
   if (MASK != 0 && tid < kTile) {
     const int kk = k0 + tid;
     int meta = 0;
@@ -534,9 +539,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       meta = MASK == 1 ? (p.key_keep[tk] ? 1 : 0) : p.doc_ids[tk];
     }
     kmeta[tid] = meta;
+    cta_meta = meta;
   }
   tc_fence_before();
-  __syncthreads();
+  const bool tile_all_keep = __syncthreads_and(MASK == 1 && cta_meta != 0) != 0;  // all 128 keys of this CTA are kept
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 320,
@@ -662,7 +668,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         bool keep = true;
         if (MASK == 0) {
           if (k0 + kTile > S) keep = k0 + k < S;  // last, partial key tile
-        } else {
+        } else if (!tile_all_keep) {
           const int meta = kmeta[k];
           keep = MASK == 1 ? (meta != 0) : (meta != 0 && meta == q_doc);
         }

@@ -71,13 +71,14 @@ struct DevParams {
   const float* gscale_ptr;          // optional device scalar multiplied into gscale
 };
 
-// Counter-based uniform in (0,1): two rounds of a 64-bit mix of (seed, row, column).
+// Counter-based uniform in (0,1) from (seed, row, column): 32-bit multiply-xorshift mixing (two rounds), the seed's
+// halves entering before and between the rounds. One value per logit, so it has to be cheap: ~10 integer operations.
 __device__ __forceinline__ float hash_uniform(unsigned long long seed, unsigned int row, unsigned int col) {
-  unsigned long long x = seed ^ (static_cast<unsigned long long>(row) << 32 | col);
-  x ^= x >> 33; x *= 0xff51afd7ed558ccdULL;
-  x ^= x >> 33; x *= 0xc4ceb9fe1a85ec53ULL;
-  x ^= x >> 33;
-  return (static_cast<float>(x >> 40) + 0.5f) * (1.0f / 16777216.0f);
+  unsigned int x = (col * 0x9E3779B1u) ^ (row * 0x85EBCA77u) ^ static_cast<unsigned int>(seed);
+  x ^= x >> 16; x *= 0x7FEB352Du;
+  x ^= x >> 15; x ^= static_cast<unsigned int>(seed >> 32);
+  x *= 0x846CA68Bu; x ^= x >> 16;
+  return (static_cast<float>(x >> 9) + 0.5f) * (1.0f / 8388608.0f);  // 23 bits + 1/2: exact in fp32, inside (0,1)
 }
 
 // Normal CDF and density through one exponential: erf by Abramowitz-Stegun 7.1.26 (|error| < 1.5e-7, far below
@@ -325,16 +326,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if (kEpi == EPI_CE_FWD) {
             const float m_new = fmaxf(t_max, cmax);
             float acc = 0.f;
+            // forbidden-id flags of the chunk as one bit mask (two 16-byte loads when the chunk is complete)
+            unsigned int ban_mask = 0;
+            if (p.forbidden) {
+              if (nc + 32 <= p.N && ((reinterpret_cast<uintptr_t>(p.forbidden) + nc) & 15) == 0) {
+                const uint4 f0 = __ldg(reinterpret_cast<const uint4*>(p.forbidden + nc));
+                const uint4 f1 = __ldg(reinterpret_cast<const uint4*>(p.forbidden + nc) + 1);
+                const unsigned int fw[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  ban_mask |= ((fw[j >> 2] >> ((j & 3) * 8)) & 0xffu) ? (1u << j) : 0u;
+              } else {
+                for (int j = 0; j < 32; ++j)
+                  if (nc + j < p.N && p.forbidden[nc + j]) ban_mask |= 1u << j;
+              }
+            }
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const int n = nc + j;
               acc += __expf(v[j] - m_new);
               if (n == label) p.label_logit[row] = v[j];
               if (n < p.N) {
-                const bool banned = p.forbidden && p.forbidden[n];
-                float u = hash_uniform(p.seed, static_cast<unsigned int>(row), static_cast<unsigned int>(n));
-                u = fminf(fmaxf(u, 1e-6f), 1.f - 1e-6f);
-                const float cand = (banned ? -1e9f : v[j] * p.inv_temp) - __logf(-__logf(u));
+                const bool banned = (ban_mask >> j) & 1u;
+                // u is an odd multiple of 2^-24: never 0 or 1, so both logarithms are finite
+                const float u = hash_uniform(p.seed, static_cast<unsigned int>(row), static_cast<unsigned int>(n));
+                const float cand = (banned ? -1e9f : v[j] * p.inv_temp) - 0.69314718f * __log2f(-0.69314718f * __log2f(u));
                 if (cand > best) { best = cand; best_idx = n; }
               }
             }

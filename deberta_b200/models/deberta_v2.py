@@ -19,7 +19,7 @@ from transformers import DebertaV2Config, PreTrainedModel
 from transformers.modeling_outputs import BaseModelOutput
 
 from deberta_b200.ops.attention import disentangled_attention
-from deberta_b200.ops.linear import ffn_gelu, linear
+from deberta_b200.ops.linear import ffn_gelu, linear, linear_qkv
 from deberta_b200.ops.norm import layer_norm
 
 from .activations import get_act_fn
@@ -115,10 +115,13 @@ class DisentangledSelfAttention(nn.Module):
         relative_pos: torch.Tensor | None = None,
         rel_embeddings: torch.Tensor | None = None,
     ) -> torch.Tensor:
-        xq = hidden_states if query_states is None else query_states
-        q = linear(xq, self.query_proj.weight, self.query_proj.bias)
-        k = linear(hidden_states, self.key_proj.weight, self.key_proj.bias)
-        v = linear(hidden_states, self.value_proj.weight, self.value_proj.bias)
+        if query_states is None:
+            q, k, v = linear_qkv(hidden_states, self.query_proj.weight, self.query_proj.bias, self.key_proj.weight,
+                                 self.key_proj.bias, self.value_proj.weight, self.value_proj.bias)
+        else:
+            q = linear(query_states, self.query_proj.weight, self.query_proj.bias)
+            k = linear(hidden_states, self.key_proj.weight, self.key_proj.bias)
+            v = linear(hidden_states, self.value_proj.weight, self.value_proj.bias)
         pos_k = pos_q = None
         if self.relative_attention and rel_embeddings is not None:
             rel = _drop(rel_embeddings, self.pos_dropout_p, self.training)

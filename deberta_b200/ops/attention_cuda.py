@@ -178,8 +178,9 @@ class _FlashAttention(torch.autograd.Function):
         _lib.call("db200_attn_delta", _lib.ptr(dout), ctypes.c_longlong(H), _lib.ptr(out), ctypes.c_longlong(H),
                   _lib.ptr(delta), c_int(B), c_int(S), c_int(heads), _lib.stream_ptr())
         dq_acc = torch.zeros((T, H), dtype=torch.float32, device=dev)
-        dk = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
-        dv = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        # dQ | dK | dV side by side in one [T, 3H] buffer: a fused QKV projection takes it as is
+        dqkv = torch.empty((T, 3 * H), dtype=torch.bfloat16, device=dev)
+        dk, dv = dqkv[:, H : 2 * H], dqkv[:, 2 * H :]
         d_c2p = torch.zeros((T, heads, span2), dtype=torch.float32, device=dev) if c2p is not None else None
         d_p2c = torch.zeros((T, heads, span2), dtype=torch.float32, device=dev) if p2c is not None else None
         dbias = torch.empty_like(bias) if bias is not None else None
@@ -197,7 +198,7 @@ class _FlashAttention(torch.autograd.Function):
         a.key_keep = None if kk is None else kk.data_ptr()
         a.doc_ids = None if dd is None else dd.data_ptr()
         a.dout, a.ld_do, a.delta = dout.data_ptr(), H, delta.data_ptr()
-        a.dq_acc, a.dk, a.dv, a.ld_dk, a.ld_dv = dq_acc.data_ptr(), dk.data_ptr(), dv.data_ptr(), H, H
+        a.dq_acc, a.dk, a.dv, a.ld_dk, a.ld_dv = dq_acc.data_ptr(), dk.data_ptr(), dv.data_ptr(), 3 * H, 3 * H
         a.d_c2p = None if d_c2p is None else d_c2p.data_ptr()
         a.d_p2c = None if d_p2c is None else d_p2c.data_ptr()
         _lib.call("db200_attn_bwd", ctypes.byref(a), _lib.stream_ptr())
@@ -237,8 +238,9 @@ class _FlashAttention(torch.autograd.Function):
             d_pos_q = torch.zeros(pos_q.shape, dtype=torch.float32, device=dev)
             gemm(g, _heads_view(k2, heads), a_mn=True, b_mn=True, out=_heads_view(d_pos_q, heads), accumulate=True)
             d_pos_q = d_pos_q.to(pos_q.dtype)
-        dq = dq_acc.to(torch.bfloat16).view(B, S, H)
-        return dq, dk.view(B, S, H), dv.view(B, S, H), d_pos_k, d_pos_q, None, None, None, None, None
+        dq = dqkv[:, :H]
+        dq.copy_(dq_acc)
+        return dq.view(B, S, H), dk.view(B, S, H), dv.view(B, S, H), d_pos_k, d_pos_q, None, None, None, None, None
 
 
 def disentangled_attention_cuda(q, k, v, pos_k, pos_q, *, heads, scale_factor, bucket_size, max_position, att_span,

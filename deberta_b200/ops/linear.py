@@ -15,7 +15,7 @@ import torch.nn.functional as F
 
 from .gemm import EPI_DGELU, EPI_GELU, gemm
 
-__all__ = ["linear", "ffn_gelu", "use_kernels"]
+__all__ = ["linear", "linear_qkv", "ffn_gelu", "use_kernels"]
 
 
 def use_kernels(x: torch.Tensor) -> bool:
@@ -133,3 +133,100 @@ def ffn_gelu(x, w1, b1, w2, b2, residual=None):
     r2 = None if residual is None else residual.reshape(-1, w2.shape[0]).contiguous()
     out = _FFNGelu.apply(x2, w1, b1, w2, b2, r2)
     return out.view(*lead, w2.shape[0])
+
+
+# ---- fused query / key / value projection ------------------------------------------------------------
+
+def _follows(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """``b`` starts where ``a`` ends in memory (both dense)."""
+    return a.is_contiguous() and b.is_contiguous() and b.data_ptr() == a.data_ptr() + a.numel() * a.element_size()
+
+
+def _span3(t: torch.Tensor, shape: tuple[int, ...]) -> torch.Tensor:
+    """View over ``t`` and the two tensors that follow it in memory."""
+    strides = (shape[1], 1) if len(shape) == 2 else (1,)
+    return t.detach().as_strided(shape, strides, t.storage_offset())
+
+
+def _qkv_fusable(x, wq, bq, wk, bk, wv, bv) -> bool:
+    if not (use_kernels(x) and wq.dtype == torch.bfloat16 and wq.shape == wk.shape == wv.shape):
+        return False
+    if wq.shape[0] % 8 or wq.shape[1] % 8 or not (_follows(wq, wk) and _follows(wk, wv)):
+        return False
+    if (bq is None) != (bk is None) or (bq is None) != (bv is None):
+        return False
+    if bq is not None and not (_follows(bq, bk) and _follows(bk, bv)):
+        return False
+    grads = [getattr(t, "main_grad", None) for t in (wq, wk, wv)]
+    if any(g is None for g in grads) or not (_follows(grads[0], grads[1]) and _follows(grads[1], grads[2])):
+        return False
+    if bq is not None:
+        bg = [getattr(t, "main_grad", None) for t in (bq, bk, bv)]
+        if any(g is None for g in bg) or not (_follows(bg[0], bg[1]) and _follows(bg[1], bg[2])):
+            return False
+    return all(t.requires_grad for t in (wq, wk, wv))
+
+
+class _LinearQKV(torch.autograd.Function):
+    """``x @ [Wq; Wk; Wv]ᵀ + [bq; bk; bv]`` as one GEMM when the three parameter sets are adjacent in memory."""
+
+    @staticmethod
+    def forward(ctx, x, wq, bq):
+        n, k = wq.shape
+        w_all = _span3(wq, (3 * n, k))
+        b_all = None if bq is None else _span3(bq, (3 * n,))
+        ctx.save_for_backward(x, wq)
+        ctx.bq = bq
+        return gemm(x, w_all, bias=b_all)
+
+    @staticmethod
+    def backward(ctx, dqkv):
+        x, wq = ctx.saved_tensors
+        n, k = wq.shape
+        if dqkv.stride(1) != 1 or dqkv.stride(0) % 8 or dqkv.data_ptr() % 16:
+            dqkv = dqkv.contiguous()
+        dx = gemm(dqkv, _span3(wq, (3 * n, k)), b_mn=True) if ctx.needs_input_grad[0] else None
+        gemm(dqkv, x, a_mn=True, b_mn=True, out=_span3(wq.main_grad, (3 * n, k)), accumulate=True)
+        if ctx.bq is not None and ctx.bq.requires_grad:
+            colsum_into(dqkv, _span3(ctx.bq.main_grad, (3 * n,)))
+        return dx, None, None
+
+
+class _SplitQKV(torch.autograd.Function):
+    """[T, 3N] → three [T, N] column views; the backward hands back one [T, 3N] tensor without a copy when the
+    three gradients already sit side by side in one buffer (the attention backward writes them that way)."""
+
+    @staticmethod
+    def forward(ctx, qkv):
+        n = qkv.shape[-1] // 3
+        return qkv[:, :n], qkv[:, n : 2 * n], qkv[:, 2 * n :]
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        n = dq.shape[-1]
+        es = dq.element_size()
+        side_by_side = (
+            dq.stride() == dk.stride() == dv.stride() == (3 * n, 1)
+            and dk.data_ptr() == dq.data_ptr() + n * es and dv.data_ptr() == dk.data_ptr() + n * es
+        )
+        if side_by_side:
+            return dq.as_strided((dq.shape[0], 3 * n), (3 * n, 1), dq.storage_offset())
+        return torch.cat([dq, dk, dv], dim=-1)
+
+
+def linear_qkv(x, wq, bq, wk, bk, wv, bv):
+    """Query, key and value projections of the same input: ``(q, k, v)`` with ``x``'s leading shape.
+
+    One GEMM with a three times wider output when the engine laid the three weights (and biases, and their fp32
+    gradient buffers) out back to back, three GEMMs otherwise.
+    """
+    if not _qkv_fusable(x, wq, bq, wk, bk, wv, bv):
+        return linear(x, wq, bq), linear(x, wk, bk), linear(x, wv, bv)
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 or x2.stride(0) % 8:
+        x2 = x2.contiguous()
+    q, k, v = _SplitQKV.apply(_LinearQKV.apply(x2, wq, bq))
+    if len(lead) == 1:
+        return q, k, v
+    return tuple(t.unflatten(0, lead) for t in (q, k, v))

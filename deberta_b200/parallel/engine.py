@@ -155,7 +155,19 @@ class TrainEngine:
         self.comm = None
         if compute_dtype == torch.bfloat16 and fused_comm_wanted(world, dev):
             # gradient and parameter buffers live in memory every rank of the node can address
-            self.comm = PeerComm(total, rank=ctx.rank, world_size=world, device=dev)
+            try:
+                self.comm = PeerComm(total, rank=ctx.rank, world_size=world, device=dev)
+            except Exception as e:  # no peer access / symmetric allocator unavailable: NCCL collectives instead
+                import logging
+
+                logging.getLogger(__name__).warning("Fused peer-memory collectives unavailable (%s); using NCCL.", e)
+                self.comm = None
+            # every rank must take the same path
+            flag = torch.tensor([1 if self.comm is not None else 0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag) == 0:
+                self.comm = None
+        if self.comm is not None:
             self.grads, self.compute = self.comm.grads, self.comm.params
             ctx.fast_vector_sum = self.comm.vector_sum
         else:

@@ -85,9 +85,10 @@ class PeerComm:
         hg, hp = self._handles[0], self._handles[1]
         hw = self._handles[2] if want_params else None
         if use_multicast is None:
-            # through-the-switch reduction pays off from 4 ranks on; at 2 ranks plain peer access measured faster
-            env = os.environ.get("DEBERTA_COMM_MULTICAST", "").strip().lower()
-            use_multicast = (world_size >= 4) if env == "" else env not in ("0", "false", "no", "off")
+            # plain peer loads/stores unless asked: at 2 ranks they measured faster than the switch reduction, and the
+            # multimem path has only been timed there
+            env = os.environ.get("DEBERTA_COMM_MULTICAST", "0").strip().lower()
+            use_multicast = env in ("1", "true", "yes", "on")
         mc_g = int(getattr(hg, "multicast_ptr", 0) or 0) if use_multicast else 0
         mc_w = int(getattr(hw, "multicast_ptr", 0) or 0) if (use_multicast and hw is not None) else 0
         self.multicast = bool(mc_g)

@@ -93,3 +93,41 @@ def test_gemm_speed_report():
         ms = s.elapsed_time(e) / 10
         print(f"\n[gemm {M}x{N}x{K}] {name}: {ms * 1e3:.1f} us, {2 * M * N * K / ms / 1e9:.1f} TFLOP/s")
     _lib.check_status()
+
+
+def test_fused_qkv_projection_matches_three_linears():
+    """Weights laid out back to back (as the engine does) take the one-GEMM path; results and gradients must agree."""
+    from deberta_b200.ops.linear import _qkv_fusable, linear_qkv
+
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    n, k, t = 128, 64, 300
+    flat_w = (torch.randn(3 * n * k, device=dev) * 0.1).to(torch.bfloat16)
+    flat_b = (torch.randn(3 * n, device=dev) * 0.1).to(torch.bfloat16)
+    gw = torch.zeros(3 * n * k, device=dev)
+    gb = torch.zeros(3 * n, device=dev)
+    ws, bs = [], []
+    for i in range(3):
+        w = torch.nn.Parameter(flat_w[i * n * k:(i + 1) * n * k].view(n, k))
+        b = torch.nn.Parameter(flat_b[i * n:(i + 1) * n])
+        w.main_grad = gw[i * n * k:(i + 1) * n * k].view(n, k)
+        b.main_grad = gb[i * n:(i + 1) * n]
+        ws.append(w)
+        bs.append(b)
+    x = (torch.randn(2, t // 2, k, device=dev) * 0.5).to(torch.bfloat16).requires_grad_(True)
+    assert _qkv_fusable(x, ws[0], bs[0], ws[1], bs[1], ws[2], bs[2])
+    q, kk, v = linear_qkv(x, ws[0], bs[0], ws[1], bs[1], ws[2], bs[2])
+    gq, gk, gv = (torch.randn_like(q) for _ in range(3))
+    (q * gq + kk * gk + v * gv).sum().backward()
+    xr = x.detach().float().requires_grad_(True)
+    outs = [torch.nn.functional.linear(xr, w.detach().float(), b.detach().float()) for w, b in zip(ws, bs)]
+    sum((o * g.float()).sum() for o, g in zip(outs, (gq, gk, gv))).backward()
+    for got, want in zip((q, kk, v), outs):
+        assert (got.float() - want).abs().max() <= 2e-2 * want.abs().max()
+    assert (x.grad.float() - xr.grad).abs().max() <= 3e-2 * xr.grad.abs().max()
+    x2 = x.detach().float().reshape(-1, k)
+    for i, g in enumerate((gq, gk, gv)):
+        want_w = g.float().reshape(-1, n).t() @ x2
+        assert (ws[i].main_grad - want_w).abs().max() <= 3e-2 * want_w.abs().max()
+        want_b = g.float().reshape(-1, n).sum(0)
+        assert (bs[i].main_grad - want_b).abs().max() <= 3e-2 * want_b.abs().max()
