@@ -104,7 +104,7 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
 }
 
 template <int V, bool RMS>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, (V <= 3) ? 2 : 1)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                 const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
                 const float* __restrict__ rstd_in, const unsigned char* __restrict__ row_keep,
@@ -211,6 +211,8 @@ int launch_bwd(const void* dy, const void* x, const void* g, const float* mean, 
   auto K = static_cast<const unsigned char*>(keep);
   auto DX = static_cast<__nv_bfloat16*>(dx);
   if (H <= 256) norm_bwd_kernel<1, RMS><<<blocks, kWarpsPerBlock * 32, 0, st>>>(DY, X, G, mean, rstd, K, DX, dgamma, dbeta, rows, H);
+  else if (H <= 512) norm_bwd_kernel<2, RMS><<<blocks, kWarpsPerBlock * 32, 0, st>>>(DY, X, G, mean, rstd, K, DX, dgamma, dbeta, rows, H);
+  else if (H <= 768) norm_bwd_kernel<3, RMS><<<blocks, kWarpsPerBlock * 32, 0, st>>>(DY, X, G, mean, rstd, K, DX, dgamma, dbeta, rows, H);
   else if (H <= 1024) norm_bwd_kernel<4, RMS><<<blocks, kWarpsPerBlock * 32, 0, st>>>(DY, X, G, mean, rstd, K, DX, dgamma, dbeta, rows, H);
   else if (H <= 2048) norm_bwd_kernel<8, RMS><<<blocks, kWarpsPerBlock * 32, 0, st>>>(DY, X, G, mean, rstd, K, DX, dgamma, dbeta, rows, H);
   else return -12;

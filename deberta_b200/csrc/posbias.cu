@@ -256,31 +256,34 @@ posbias_rowscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __res
   }
 }
 
-// table rows are keys: a block owns 32 key columns of dbias and scans them along the queries.
-// grid (ceil(S/32), heads, B), 256 threads; shared: T[32][stride]. Prefix i of a key sits at word
+// table rows are keys: a block owns kColKeys key columns of dbias and scans them along the queries.
+// grid (ceil(S/kColKeys), heads, B), 256 threads; shared: T[kColKeys][stride] (16 keys keep six blocks per SM resident). Prefix i of a key sits at word
 // i + (i >> sh) with 2^sh >= ceil(S/32): each lane scans a contiguous run of `per` queries, and the skew
 // keeps the 32 lanes on different banks.
+constexpr int kColKeys = 16;
+
 template <int PER>  // PER > 0: ceil(S/32) known at compile time (the run of a lane lives in registers); 0: any S
 __global__ void __launch_bounds__(256)
 posbias_colscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __restrict__ ranges,
                        __nv_bfloat16* __restrict__ dtab, int S, int ldb, int heads, int span2, int stride, int per, int sh) {
   extern __shared__ float sm[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  int* rng = reinterpret_cast<int*>(sm + 32 * stride);
+  int* rng = reinterpret_cast<int*>(sm + kColKeys * stride);
   for (int i = tid; i < 2 * span2; i += 256) rng[i] = ranges[i];
-  const int k0 = blockIdx.x * 32, h = blockIdx.y, b = blockIdx.z;
+  const int k0 = blockIdx.x * kColKeys, h = blockIdx.y, b = blockIdx.z;
   const __nv_bfloat16* src = dbias + (static_cast<long long>(b) * heads + h) * S * ldb + k0;
-  const int cg = tid & 3;  // 8-key group of this thread
-  for (int qb = tid >> 2; qb < S; qb += 256) {  // four independent 16-byte loads in flight per thread
+  constexpr int kGroups = kColKeys / 8, kRowsPerPass = 256 / kGroups;
+  const int cg = tid % kGroups;  // 8-key group of this thread
+  for (int qb = tid / kGroups; qb < S; qb += 4 * kRowsPerPass) {  // four independent 16-byte loads in flight per thread
     uint4 u[4];
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
-      const int q = qb + 64 * t;
+      const int q = qb + kRowsPerPass * t;
       u[t] = q < S ? *reinterpret_cast<const uint4*>(src + static_cast<long long>(q) * ldb + cg * 8) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
-      const int q = qb + 64 * t;
+      const int q = qb + kRowsPerPass * t;
       if (q < S) {
         const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&u[t]);
         const int w = (q + 1) + ((q + 1) >> sh);
@@ -289,10 +292,10 @@ posbias_colscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __res
       }
     }
   }
-  if (tid < 32) sm[tid * stride] = 0.f;
+  if (tid < kColKeys) sm[tid * stride] = 0.f;
   __syncthreads();
   const long long row_stride = static_cast<long long>(heads) * span2;
-  for (int kk = warp * 4; kk < warp * 4 + 4; ++kk) {
+  for (int kk = warp * (kColKeys / 8); kk < (warp + 1) * (kColKeys / 8); ++kk) {
     const int k = k0 + kk;
     if (k >= S) break;  // warp-uniform
     float* T = sm + kk * stride;  // T[phys(i)] = sum of the first i queries
@@ -411,13 +414,13 @@ extern "C" int db200_posbias_scatter_ranges(const void* dbias, const void* range
   auto dt = static_cast<__nv_bfloat16*>(dtab);
   constexpr int kMaxSmem = 200 * 1024;
   if (rows_are_keys) {
-    if (ldb % 32) return -12;  // 32-key column groups are read with 16-byte loads up to the padded width
+    if (ldb % kColKeys) return -12;  // key groups are read with 16-byte loads up to the padded width
     const int per = (S + 31) / 32;
     int sh = 0;
     while ((1 << sh) < per) ++sh;
     int stride = (S + 1) + ((S + 1) >> sh) + 1;
     stride |= 1;  // odd: the 32 key rows start on different banks
-    const int smem = 32 * stride * 4 + 2 * span2 * 4;
+    const int smem = kColKeys * stride * 4 + 2 * span2 * 4;
     if (smem > kMaxSmem) return -12;
     auto kern = posbias_colscan_kernel<0>;
     if (per == 16) kern = posbias_colscan_kernel<16>;
@@ -425,7 +428,7 @@ extern "C" int db200_posbias_scatter_ranges(const void* dbias, const void* range
     else if (per == 32) kern = posbias_colscan_kernel<32>;
     else if (per == 4) kern = posbias_colscan_kernel<4>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) != cudaSuccess) return -3;
-    kern<<<dim3((S + 31) / 32, heads, B), 256, smem, st>>>(db, rg, dt, S, ldb, heads, span2, stride, per, sh);
+    kern<<<dim3((S + kColKeys - 1) / kColKeys, heads, B), 256, smem, st>>>(db, rg, dt, S, ldb, heads, span2, stride, per, sh);
   } else {
     const int smem = 8 * ((S + 1) + ((S + 1) >> 3) + 1) * 4 + 2 * span2 * 4;
     if (smem > kMaxSmem) return -12;

@@ -15,6 +15,7 @@ colsum_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, int N, f
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   if (col < N) {
     const bool vec = (col + 8 <= N);
+#pragma unroll 4
     for (int r = blockIdx.y * 8 + ty; r < M; r += gridDim.y * 8) {
       const __nv_bfloat16* src = x + static_cast<long long>(r) * ld + col;
       if (vec) {
@@ -43,8 +44,12 @@ colsum_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int M, int N, f
 extern "C" int db200_colsum_bf16(const void* x, long long ld, int M, int N, float* out_accum, void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if ((ld % 8) || (reinterpret_cast<uintptr_t>(x) & 15)) return -10;
-  int splits = (M + 255) / 256;
-  if (splits > 64) splits = 64;
+  // enough blocks to keep every SM's memory pipeline full: about 64 rows per block, at most ~1200 blocks
+  int splits = (M + 63) / 64;
+  const int col_blocks = (N + 255) / 256;
+  const int max_splits = (1184 + col_blocks - 1) / col_blocks;
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
   dim3 grid((N + 255) / 256, splits), block(32, 8);
   colsum_kernel<<<grid, block, 0, reinterpret_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(x), ld, M, N,
                                                                           out_accum);
