@@ -70,8 +70,11 @@ def run_reference(args) -> dict:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
     torch.manual_seed(1234)
-    model_cfg = ModelConfig(profile="deberta_v3_parity", backbone_type="hf_deberta_v2", embedding_sharing="gdes",
-                            hf={"model_size": args.model_size})
+    if getattr(args, "backbone", "hf_deberta_v2") == "rope":
+        model_cfg = ModelConfig(backbone_type="rope", embedding_sharing="gdes")
+    else:
+        model_cfg = ModelConfig(profile="deberta_v3_parity", backbone_type="hf_deberta_v2", embedding_sharing="gdes",
+                                hf={"model_size": args.model_size})
     train_cfg = TrainConfig(per_device_train_batch_size=args.micro_batch, gradient_accumulation_steps=args.ga,
                             mixed_precision="bf16", max_steps=10_000)
     for k, v in dict(learning_rate=2e-4, generator_learning_rate=-1.0, discriminator_learning_rate=-1.0, weight_decay=0.01,
@@ -176,7 +179,9 @@ def run_reference(args) -> dict:
     tokens = args.ga * args.micro_batch * args.seq_len * world * args.steps
     h2d = sum(v.numel() * v.element_size() for b in host for v in b.values())
     result = {
-        "metric": "RTD pretrain tokens/s, DeBERTa-v3-base seq512, max over ranks", "value": tokens / (ms / 1e3),
+        "metric": ("RTD pretrain tokens/s, DeBERTa-v3-base seq512, max over ranks"
+                   if getattr(args, "backbone", "hf_deberta_v2") == "hf_deberta_v2"
+                   else f"RTD pretrain tokens/s, rope backbone seq{args.seq_len}, max over ranks"), "value": tokens / (ms / 1e3),
         "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic packed Zipf(1.1) token streams, random-init weights", "impl": "reference",

@@ -50,6 +50,8 @@ def parse_args() -> argparse.Namespace:
     p.add_argument("--micro-batch", type=int, default=MICRO_BATCH)
     p.add_argument("--seq-len", type=int, default=SEQ_LEN)
     p.add_argument("--model-size", default="base")
+    p.add_argument("--backbone", choices=("hf_deberta_v2", "rope"), default="hf_deberta_v2",
+                   help="rope: the RoPE/RMSNorm/SwiGLU family at its config defaults (secondary benchmark)")
     p.add_argument("--parallelism", choices=("ddp", "zero"), default="zero")
     return p.parse_args()
 
@@ -125,8 +127,10 @@ def build_config(args: argparse.Namespace):
     from deberta_b200.config import Config, DataConfig, ModelConfig, OptimConfig, TrainConfig, validate_config
 
     cfg = Config(
-        model=ModelConfig(profile="deberta_v3_parity", backbone_type="hf_deberta_v2", embedding_sharing="gdes",
-                          hf={"model_size": args.model_size}, tokenizer={"name_or_path": f"synthetic:{VOCAB}"}),
+        model=(ModelConfig(profile="deberta_v3_parity", backbone_type="hf_deberta_v2", embedding_sharing="gdes",
+                           hf={"model_size": args.model_size}, tokenizer={"name_or_path": f"synthetic:{VOCAB}"})
+               if args.backbone == "hf_deberta_v2" else
+               ModelConfig(backbone_type="rope", embedding_sharing="gdes", tokenizer={"name_or_path": f"synthetic:{VOCAB}"})),
         data=DataConfig(dataset_name="synthetic", dataset_config_name=f"zipf1.1-mean60-vocab{VOCAB}",
                         max_seq_length=args.seq_len),
         train=TrainConfig(per_device_train_batch_size=args.micro_batch, gradient_accumulation_steps=args.ga,
@@ -198,11 +202,13 @@ def run_ours(args: argparse.Namespace) -> dict:
     gen_loss = float(stats.gen_loss_tokens) / max(stats.gen_tokens, 1.0)
     value = tokens_per_step * ctx.world_size * args.steps / (ms / 1e3)
     result = {
-        "metric": "RTD pretrain tokens/s, DeBERTa-v3-base seq512, max over ranks", "value": value, "unit": "tokens/s",
+        "metric": ("RTD pretrain tokens/s, DeBERTa-v3-base seq512, max over ranks" if args.backbone == "hf_deberta_v2"
+                   else f"RTD pretrain tokens/s, rope backbone seq{args.seq_len}, max over ranks"), "value": value, "unit": "tokens/s",
         "n_gpus": ctx.world_size, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic packed Zipf(1.1) token streams, random-init weights", "impl": "ours",
-        "config": {"model": f"deberta-v3-{args.model_size} RTD (12L disc + 6L gen, GDES, EMD)",
+        "config": {"model": (f"deberta-v3-{args.model_size} RTD (12L disc + 6L gen, GDES, EMD)" if args.backbone == "hf_deberta_v2"
+                             else "rope RTD (config defaults, GDES)"),
                    "global_batch": args.micro_batch * args.ga * ctx.world_size, "micro_batch": args.micro_batch,
                    "grad_accum": args.ga, "seq_len": args.seq_len,
                    "parallelism": f"dp{ctx.world_size}" + ("-zero1" if args.parallelism == "zero" else "-replicated"),

@@ -1,0 +1,151 @@
+// Fused elementwise kernels of the RoPE backbone.
+//   db200_rotary_bf16 : interleaved-pair rotary embedding on the first `rotary_dim` features of every head of q and k
+//                       in one pass (forward, or the inverse rotation for the backward pass); may run in place
+//   db200_swiglu_fwd  : out = silu(gate) * up           with [gate | up] the two halves of one row
+//   db200_swiglu_bwd  : d[gate | up] from d(out)         (silu'(g) = s * (1 + g * (1 - s)), s = sigmoid(g))
+#include "kernels.h"
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace {
+
+__device__ __forceinline__ float lo_f(unsigned int w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float hi_f(unsigned int w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ unsigned int pack2(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<unsigned int*>(&v);
+}
+
+// One thread rotates 4 pairs (8 features, 16 bytes). cos/sin: fp32 [S, rotary_dim] with every frequency stored twice
+// (entries 2i and 2i+1 equal), as the rotary cache of the model keeps them.
+__global__ void __launch_bounds__(256)
+rotary_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long long ldx, long long ldy,
+              const float* __restrict__ cos_t, const float* __restrict__ sin_t, long long tokens, int S, int heads,
+              int head_dim, int rotary_dim, float sign) {
+  const int vec_per_head = head_dim / 8;
+  const long long vecs = tokens * heads * vec_per_head;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < vecs;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int v = static_cast<int>(i % vec_per_head);
+    const long long th = i / vec_per_head;
+    const int h = static_cast<int>(th % heads);
+    const long long t = th / heads;
+    const int s = static_cast<int>(t % S);
+    const int f0 = v * 8;
+    uint4 u = *reinterpret_cast<const uint4*>(x + t * ldx + h * head_dim + f0);
+    if (f0 < rotary_dim) {
+      unsigned int w[4] = {u.x, u.y, u.z, u.w};
+      const float* c = cos_t + static_cast<long long>(s) * rotary_dim + f0;
+      const float* sn = sin_t + static_cast<long long>(s) * rotary_dim + f0;
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        if (f0 + 2 * p < rotary_dim) {
+          const float a = lo_f(w[p]), b = hi_f(w[p]);
+          const float cc = c[2 * p], ss = sn[2 * p] * sign;
+          w[p] = pack2(a * cc - b * ss, b * cc + a * ss);
+        }
+      }
+      u = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    *reinterpret_cast<uint4*>(y + t * ldy + h * head_dim + f0) = u;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_in, __nv_bfloat16* __restrict__ out, long long ld_out,
+                  long long rows, int F) {
+  const int vec_per_row = F / 8;
+  const long long vecs = rows * vec_per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < vecs;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int c = static_cast<int>(i % vec_per_row) * 8;
+    const uint4 g = *reinterpret_cast<const uint4*>(gu + r * ld_in + c);
+    const uint4 u = *reinterpret_cast<const uint4*>(gu + r * ld_in + F + c);
+    const unsigned int gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    unsigned int o[4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const float g0 = lo_f(gw[p]), g1 = hi_f(gw[p]);
+      const float s0 = g0 / (1.f + __expf(-g0)), s1 = g1 / (1.f + __expf(-g1));
+      // the product is formed from the bf16-rounded silu, as the unfused composition does
+      o[p] = pack2(__bfloat162float(__float2bfloat16(s0)) * lo_f(uw[p]), __bfloat162float(__float2bfloat16(s1)) * hi_f(uw[p]));
+    }
+    *reinterpret_cast<uint4*>(out + r * ld_out + c) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_in, const __nv_bfloat16* __restrict__ dout,
+                  long long ld_do, __nv_bfloat16* __restrict__ dgu, long long ld_dg, long long rows, int F) {
+  const int vec_per_row = F / 8;
+  const long long vecs = rows * vec_per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < vecs;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int c = static_cast<int>(i % vec_per_row) * 8;
+    const uint4 g = *reinterpret_cast<const uint4*>(gu + r * ld_in + c);
+    const uint4 u = *reinterpret_cast<const uint4*>(gu + r * ld_in + F + c);
+    const uint4 d = *reinterpret_cast<const uint4*>(dout + r * ld_do + c);
+    const unsigned int gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w}, dw[4] = {d.x, d.y, d.z, d.w};
+    unsigned int og[4], ou[4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      float gv[2] = {lo_f(gw[p]), hi_f(gw[p])}, uv[2] = {lo_f(uw[p]), hi_f(uw[p])}, dv[2] = {lo_f(dw[p]), hi_f(dw[p])};
+      float dg[2], du[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float sig = 1.f / (1.f + __expf(-gv[e]));
+        const float silu = gv[e] * sig;
+        du[e] = dv[e] * silu;
+        dg[e] = dv[e] * uv[e] * sig * (1.f + gv[e] * (1.f - sig));
+      }
+      og[p] = pack2(dg[0], dg[1]);
+      ou[p] = pack2(du[0], du[1]);
+    }
+    *reinterpret_cast<uint4*>(dgu + r * ld_dg + c) = make_uint4(og[0], og[1], og[2], og[3]);
+    *reinterpret_cast<uint4*>(dgu + r * ld_dg + F + c) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+  }
+}
+
+int ew_grid(long long vecs) {
+  long long blocks = (vecs + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return static_cast<int>(blocks < 1 ? 1 : blocks);
+}
+bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+extern "C" int db200_rotary_bf16(const void* x, void* y, long long ldx, long long ldy, const float* cos_t,
+                                 const float* sin_t, long long tokens, int S, int heads, int head_dim, int rotary_dim,
+                                 int inverse, void* stream) {
+  if (tokens <= 0) return 0;
+  if (!al16(x) || !al16(y) || (ldx % 8) || (ldy % 8) || (head_dim % 8) || (rotary_dim % 2) || rotary_dim > head_dim || S <= 0)
+    return -10;
+  const long long vecs = tokens * heads * (head_dim / 8);
+  rotary_kernel<<<ew_grid(vecs), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), ldx, ldy, cos_t, sin_t, tokens, S, heads,
+      head_dim, rotary_dim, inverse ? -1.f : 1.f);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int db200_swiglu_fwd(const void* gate_up, long long ld_in, void* out, long long ld_out, long long rows, int F,
+                                void* stream) {
+  if (rows <= 0) return 0;
+  if (!al16(gate_up) || !al16(out) || (ld_in % 8) || (ld_out % 8) || (F % 8)) return -10;
+  swiglu_fwd_kernel<<<ew_grid(rows * (F / 8)), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate_up), ld_in, static_cast<__nv_bfloat16*>(out), ld_out, rows, F);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int db200_swiglu_bwd(const void* gate_up, long long ld_in, const void* dout, long long ld_do, void* d_gate_up,
+                                long long ld_dg, long long rows, int F, void* stream) {
+  if (rows <= 0) return 0;
+  if (!al16(gate_up) || !al16(dout) || !al16(d_gate_up) || (ld_in % 8) || (ld_do % 8) || (ld_dg % 8) || (F % 8)) return -10;
+  swiglu_bwd_kernel<<<ew_grid(rows * (F / 8)), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate_up), ld_in, static_cast<const __nv_bfloat16*>(dout), ld_do,
+      static_cast<__nv_bfloat16*>(d_gate_up), ld_dg, rows, F);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

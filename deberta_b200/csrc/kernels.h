@@ -63,6 +63,17 @@ int db200_adamw(float* p, const float* g, float* m, float* v, void* shadow_bf16,
                 float b1, float b2, float eps, float inv_bc1, float inv_sqrt_bc2, const float* norm_sq,
                 float max_norm, float grad_scale, void* stream);
 
+// ----- elementwise kernels of the RoPE backbone (see elementwise.cu) ---------------------------
+// Interleaved-pair rotary embedding of the first rotary_dim features of every head: y = rot(x) (inverse != 0: the
+// transposed rotation, i.e. the backward pass). x, y: bf16 [tokens, ld*] with heads*head_dim features; cos/sin: fp32
+// [S, rotary_dim] with each frequency stored twice; token t sits at position t % S. x == y is allowed.
+int db200_rotary_bf16(const void* x, void* y, long long ldx, long long ldy, const float* cos_t, const float* sin_t,
+                      long long tokens, int S, int heads, int head_dim, int rotary_dim, int inverse, void* stream);
+// out[r, c] = silu(gate_up[r, c]) * gate_up[r, F + c]  and its backward (d_gate_up has the layout of gate_up).
+int db200_swiglu_fwd(const void* gate_up, long long ld_in, void* out, long long ld_out, long long rows, int F, void* stream);
+int db200_swiglu_bwd(const void* gate_up, long long ld_in, const void* dout, long long ld_do, void* d_gate_up,
+                     long long ld_dg, long long rows, int F, void* stream);
+
 // ----- fused gradient collectives over NVLink peer memory (see comm.cu) -----------------------
 #define DB200_COMM_MAX_WORLD 8
 #define DB200_COMM_VEC_MAX 128      // longest vector db200_comm_vector_sum takes

@@ -17,6 +17,7 @@ from transformers import PretrainedConfig, PreTrainedModel
 from transformers.modeling_outputs import BaseModelOutput
 
 from deberta_b200.ops.attention import rope_attention
+from deberta_b200.ops.elementwise import swiglu
 from deberta_b200.ops.linear import ffn_gelu, linear
 
 from .activations import get_act_fn
@@ -155,8 +156,7 @@ class DebertaRoPEMLP(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.ffn_type == "swiglu":
-            gate, up = linear(x, self.w12.weight, self.w12.bias).chunk(2, dim=-1)
-            return linear(F.silu(gate) * up, self.w3.weight, self.w3.bias)
+            return linear(swiglu(linear(x, self.w12.weight, self.w12.bias)), self.w3.weight, self.w3.bias)
         if self.act_name == "gelu":
             return ffn_gelu(x, self.dense_in.weight, self.dense_in.bias, self.dense_out.weight, self.dense_out.bias)
         return linear(self.act(linear(x, self.dense_in.weight, self.dense_in.bias)),

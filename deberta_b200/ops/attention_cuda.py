@@ -260,9 +260,8 @@ def rope_attention_cuda(q, k, v, cos, sin, *, heads, rotary_dim, key_keep=None, 
     B, S, H = q.shape
     d = H // heads
     if rotary_dim > 0:
-        from .attention import rotate_interleaved
+        from .elementwise import rotary_tokens
 
-        c, s = cos.to(q.dtype)[None, :, None, :], sin.to(q.dtype)[None, :, None, :]
-        q = rotate_interleaved(q.reshape(B, S, heads, d), c, s, rotary_dim).reshape(B, S, H)
-        k = rotate_interleaved(k.reshape(B, S, heads, d), c, s, rotary_dim).reshape(B, S, H)
+        q = rotary_tokens(q, cos, sin, heads=heads, rotary_dim=rotary_dim)
+        k = rotary_tokens(k, cos, sin, heads=heads, rotary_dim=rotary_dim)
     return _FlashAttention.apply(q, k, v, None, None, heads, math.sqrt(float(d)), None, key_keep, doc_ids)

@@ -109,3 +109,36 @@ def test_attention_speed_report():
         torch.cuda.synchronize()
         print(f"\n[disentangled attention B={B} S={S} h={heads}] {label}: {s.elapsed_time(e) / 5 * 1e3:.0f} us")
     _lib.check_status()
+
+
+def test_rotary_and_swiglu_kernels_match_pytorch():
+    from deberta_b200.ops.attention import rotate_interleaved
+    from deberta_b200.ops.elementwise import rotary_tokens, swiglu
+
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    B, S, heads, d, rot = 2, 100, 4, 64, 32
+    x = (torch.randn(B, S, heads * d, device=dev) * 0.5).to(torch.bfloat16).requires_grad_(True)
+    inv = 1.0 / (10000 ** (torch.arange(0, rot, 2, device=dev).float() / d))
+    ang = torch.arange(S, device=dev).float()[:, None] * inv[None]
+    emb = torch.repeat_interleave(ang, 2, dim=-1)
+    cos, sin = emb.cos(), emb.sin()
+    y = rotary_tokens(x, cos, sin, heads=heads, rotary_dim=rot)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_(True)
+    yr = rotate_interleaved(xr.reshape(B, S, heads, d), cos[None, :, None, :], sin[None, :, None, :], rot).reshape(B, S, -1)
+    yr.backward(g.float())
+    assert (y.float() - yr).abs().max() < 2e-2
+    assert (x.grad.float() - xr.grad).abs().max() < 3e-2
+    # SwiGLU
+    gu = (torch.randn(300, 2 * 256, device=dev)).to(torch.bfloat16).requires_grad_(True)
+    out = swiglu(gu)
+    go = torch.randn_like(out)
+    out.backward(go)
+    gr = gu.detach().float().requires_grad_(True)
+    a, b = gr.chunk(2, dim=-1)
+    ref = torch.nn.functional.silu(a) * b
+    ref.backward(go.float())
+    assert (out.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
+    assert (gu.grad.float() - gr.grad).abs().max() <= 2e-2 * gr.grad.abs().max()
