@@ -149,3 +149,79 @@ extern "C" int db200_swiglu_bwd(const void* gate_up, long long ld_in, const void
       static_cast<__nv_bfloat16*>(d_gate_up), ld_dg, rows, F);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// ---- embedding lookup (+ optional second table) and its gradient ----------------------------------------------------
+//   db200_embed_fwd : out[t, :] = table[id[t], :] (+ delta[id[t], :])         one warp per token, 16-byte accesses
+//   db200_embed_bwd : grad[id[t], :] += dout[t, :] (fp32, red.add.v4), tokens whose id equals padding_idx are skipped.
+//                     Rows that many tokens share are summed in an order that varies from run to run.
+namespace {
+
+__global__ void __launch_bounds__(256)
+embed_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                 const __nv_bfloat16* __restrict__ delta, __nv_bfloat16* __restrict__ out, long long tokens, int H,
+                 long long vocab) {
+  const int lane = threadIdx.x & 31;
+  const int vecs = H / 8;
+  for (long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; t < tokens;
+       t += (static_cast<long long>(gridDim.x) * blockDim.x) >> 5) {
+    long long id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // out-of-range ids are clamped, never dereferenced as given
+    const uint4* src = reinterpret_cast<const uint4*>(table + id * H);
+    const uint4* dsrc = delta ? reinterpret_cast<const uint4*>(delta + id * H) : nullptr;
+    uint4* dst = reinterpret_cast<uint4*>(out + t * H);
+    for (int v = lane; v < vecs; v += 32) {
+      uint4 a = __ldg(src + v);
+      if (dsrc) {
+        const uint4 b = __ldg(dsrc + v);
+        a.x = pack2(lo_f(a.x) + lo_f(b.x), hi_f(a.x) + hi_f(b.x));
+        a.y = pack2(lo_f(a.y) + lo_f(b.y), hi_f(a.y) + hi_f(b.y));
+        a.z = pack2(lo_f(a.z) + lo_f(b.z), hi_f(a.z) + hi_f(b.z));
+        a.w = pack2(lo_f(a.w) + lo_f(b.w), hi_f(a.w) + hi_f(b.w));
+      }
+      dst[v] = a;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+embed_bwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ dout, long long ld_do,
+                 float* __restrict__ grad, long long tokens, int H, long long vocab, long long padding_idx) {
+  const int lane = threadIdx.x & 31;
+  const int vecs = H / 8;
+  for (long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; t < tokens;
+       t += (static_cast<long long>(gridDim.x) * blockDim.x) >> 5) {
+    const long long id = ids[t];
+    if (id < 0 || id >= vocab || id == padding_idx) continue;  // warp-uniform
+    const uint4* src = reinterpret_cast<const uint4*>(dout + t * ld_do);
+    float* dst = grad + id * H;
+    for (int v = lane; v < vecs; v += 32) {
+      const uint4 a = src[v];
+      float* d = dst + v * 8;
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d), "f"(lo_f(a.x)), "f"(hi_f(a.x)),
+                   "f"(lo_f(a.y)), "f"(hi_f(a.y)) : "memory");
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(d + 4), "f"(lo_f(a.z)), "f"(hi_f(a.z)),
+                   "f"(lo_f(a.w)), "f"(hi_f(a.w)) : "memory");
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" int db200_embed_fwd(const long long* ids, const void* table, const void* delta, void* out, long long tokens,
+                               int H, long long vocab, void* stream) {
+  if (tokens <= 0) return 0;
+  if (!al16(table) || !al16(out) || (delta && !al16(delta)) || (H % 8) || vocab <= 0) return -10;
+  embed_fwd_kernel<<<ew_grid(tokens * 32), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      ids, static_cast<const __nv_bfloat16*>(table), static_cast<const __nv_bfloat16*>(delta),
+      static_cast<__nv_bfloat16*>(out), tokens, H, vocab);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int db200_embed_bwd(const long long* ids, const void* dout, long long ld_do, float* grad, long long tokens,
+                               int H, long long vocab, long long padding_idx, void* stream) {
+  if (tokens <= 0) return 0;
+  if (!al16(dout) || !al16(grad) || (H % 8) || (ld_do % 8) || vocab <= 0) return -10;
+  embed_bwd_kernel<<<ew_grid(tokens * 32), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      ids, static_cast<const __nv_bfloat16*>(dout), ld_do, grad, tokens, H, vocab, padding_idx);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

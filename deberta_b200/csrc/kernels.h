@@ -74,6 +74,13 @@ int db200_swiglu_fwd(const void* gate_up, long long ld_in, void* out, long long 
 int db200_swiglu_bwd(const void* gate_up, long long ld_in, const void* dout, long long ld_do, void* d_gate_up,
                      long long ld_dg, long long rows, int F, void* stream);
 
+// Embedding lookup out[t] = table[ids[t]] (+ delta[ids[t]]) over bf16 tables [vocab, H], and the fp32 gradient
+// scatter grad[ids[t]] += dout[t] (tokens with ids[t] == padding_idx skipped; pass -1 for none).
+int db200_embed_fwd(const long long* ids, const void* table, const void* delta, void* out, long long tokens, int H,
+                    long long vocab, void* stream);
+int db200_embed_bwd(const long long* ids, const void* dout, long long ld_do, float* grad, long long tokens, int H,
+                    long long vocab, long long padding_idx, void* stream);
+
 // ----- fused gradient collectives over NVLink peer memory (see comm.cu) -----------------------
 #define DB200_COMM_MAX_WORLD 8
 #define DB200_COMM_VEC_MAX 128      // longest vector db200_comm_vector_sum takes

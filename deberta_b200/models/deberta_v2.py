@@ -53,6 +53,15 @@ def _drop(x: torch.Tensor, p: float, training: bool) -> torch.Tensor:
     return F.dropout(x, p, True) if (training and p > 0.0) else x
 
 
+
+def _embed(module: nn.Module, input_ids: torch.Tensor) -> torch.Tensor:
+    """Word-embedding lookup: plain ``nn.Embedding`` tables go through the gather kernel, wrapped ones keep their forward."""
+    if type(module) is nn.Embedding and module.max_norm is None and not module.sparse:
+        from deberta_b200.ops.embedding import embedding_lookup
+
+        return embedding_lookup(input_ids, module.weight, None, module.padding_idx)
+    return module(input_ids)
+
 class DisentangledSelfAttention(nn.Module):
     """Content/position attention of DeBERTa (``deberta_v2_native.py:168-652``).
 
@@ -318,7 +327,7 @@ class DebertaV2Embeddings(nn.Module):
         shape = input_ids.shape if input_ids is not None else inputs_embeds.shape[:-1]
         device = input_ids.device if input_ids is not None else inputs_embeds.device
         seq_len = int(shape[1])
-        x = self.word_embeddings(input_ids) if inputs_embeds is None else inputs_embeds
+        x = _embed(self.word_embeddings, input_ids) if inputs_embeds is None else inputs_embeds
         if self.position_biased_input:
             pos = self.position_ids[:, :seq_len].to(device) if position_ids is None else position_ids.to(device)
             x = x + self.position_embeddings(pos.long())

@@ -28,6 +28,15 @@ from .rope import RotaryEmbedding
 __all__ = ["DebertaRoPEConfig", "DebertaRoPEModel", "DebertaRoPELayer", "DebertaRoPEEncoder"]
 
 
+
+def _embed(module: nn.Module, input_ids: torch.Tensor) -> torch.Tensor:
+    """Word-embedding lookup: plain ``nn.Embedding`` tables go through the gather kernel, wrapped ones keep their forward."""
+    if type(module) is nn.Embedding and module.max_norm is None and not module.sparse:
+        from deberta_b200.ops.embedding import embedding_lookup
+
+        return embedding_lookup(input_ids, module.weight, None, module.padding_idx)
+    return module(input_ids)
+
 class DebertaRoPEConfig(PretrainedConfig):
     model_type = "deberta-rope"
 
@@ -90,7 +99,7 @@ class DebertaRoPEEmbeddings(nn.Module):
 
     def forward(self, input_ids: torch.Tensor, token_type_ids: torch.Tensor | None = None) -> torch.Tensor:
         bsz, seq_len = input_ids.shape
-        x = self.word_embeddings(input_ids)
+        x = _embed(self.word_embeddings, input_ids)
         if self.token_type_embeddings is not None:
             if token_type_ids is None:
                 token_type_ids = torch.zeros((bsz, seq_len), dtype=torch.long, device=input_ids.device)

@@ -95,10 +95,9 @@ class _SyncedBufferEmbedding(nn.Module):
         return self.base_weight if self.bias is None else self.base_weight + self.bias
 
     def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
-        out = F.embedding(input_ids, self.base_weight, padding_idx=self.padding_idx)
-        if self.bias is not None:
-            out = out + F.embedding(input_ids, self.bias, padding_idx=self.padding_idx)
-        return out
+        from deberta_b200.ops.embedding import embedding_lookup
+
+        return embedding_lookup(input_ids, self.base_weight, self.bias, self.padding_idx)
 
 
 class MLMTransform(nn.Module):

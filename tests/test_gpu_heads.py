@@ -51,3 +51,32 @@ def test_sampling_follows_softmax():
     _, s2 = mlm_loss_and_sample(x, w, b, labels, None, 1.0)
     assert not torch.equal(s, s2)
     _lib.check_status()
+
+
+def test_embedding_lookup_kernel_matches_pytorch():
+    import torch
+    from deberta_b200.ops.embedding import embedding_lookup
+
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    vocab, hidden = 1000, 256
+    base = torch.nn.Parameter((torch.randn(vocab, hidden, device=dev) * 0.1).to(torch.bfloat16), requires_grad=False)
+    delta = torch.nn.Parameter((torch.randn(vocab, hidden, device=dev) * 0.1).to(torch.bfloat16))
+    delta.main_grad = torch.zeros(vocab, hidden, device=dev)
+    ids = torch.randint(0, vocab, (4, 77), device=dev)
+    ids[0, :20] = 5  # a hot row
+    ids[1, :5] = 0   # padding
+    out = embedding_lookup(ids, base, delta, padding_idx=0)
+    ref = (base.float()[ids] + delta.float()[ids])
+    assert (out.float() - ref).abs().max() <= 1e-2
+    g = torch.randn_like(out)
+    out.backward(g)
+    want = torch.zeros(vocab, hidden, device=dev)
+    keep = ids.reshape(-1) != 0
+    want.index_add_(0, ids.reshape(-1)[keep], g.float().reshape(-1, hidden)[keep])
+    assert (delta.main_grad - want).abs().max() <= 1e-3 * want.abs().max() + 1e-4
+    assert float(delta.main_grad[0].abs().max()) == 0.0
+    # single table, no autograd
+    with torch.no_grad():
+        out2 = embedding_lookup(ids, base)
+    assert torch.equal(out2, base[ids])
