@@ -250,6 +250,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
 
   float m_run = -INFINITY, l_part = 0.f;
+  // bias of this thread's 32 keys, fetched one tile ahead so that the L2 round trip overlaps the previous tile's math
+  uint4 bias_pf[4] = {};
+  if (POS == 1) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) bias_pf[g] = __ldg(bias_row + ((part * 32) >> 3) + g);
+  }
   for (int j = 0; j < nkt; ++j) {
     const int k0 = j * kTile;
     bool tile_all_keep = false;
@@ -284,13 +290,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (POS == 1) {
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
-        const uint4 bvec = __ldg(bias_row + (kb >> 3) + g);
+        const uint4 bvec = bias_pf[g];
         const uint32_t w[4] = {bvec.x, bvec.y, bvec.z, bvec.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           s[g * 8 + 2 * e] += __uint_as_float(w[e] << 16);
           s[g * 8 + 2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
         }
+      }
+      if (j + 1 < nkt) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) bias_pf[g] = __ldg(bias_row + ((kb + kTile) >> 3) + g);
       }
     } else if (POS == 2) {
       const int dbase = q - kb + S - 1;  // lut index for the first key
@@ -610,6 +620,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   for (int i = 0; i < nqt; ++i) {
     const int buf = i % 3;
     const int q0 = i * kTile;
+    // per-row inputs that do not depend on the scores are requested before the wait: their latency hides behind the MMAs
+    const int q = q0 + row;
+    const bool q_valid = q < S;
+    const long long stat = (static_cast<long long>(b) * p.heads + h) * S + (q_valid ? q : 0);
+    const float lse = q_valid ? p.lse[stat] : INFINITY;
+    const float delta = q_valid ? p.delta[stat] : 0.f;
+    const long long brow_off = ((static_cast<long long>(b) * p.heads + h) * S + (q_valid ? q : 0)) * p.ldb + k0;
+    const uint4* bias_row = POS == 1 ? reinterpret_cast<const uint4*>(p.bias + brow_off) : nullptr;
+    uint4 bias_cur[4] = {};
+    if (POS == 1) {
+#pragma unroll
+      for (int g8 = 0; g8 < 4; ++g8) bias_cur[g8] = __ldg(bias_row + part * 4 + g8);
+    }
     if (!mbar_wait(bar_s, i & 1, abort_flag, p.status, kErrAccFullWait)) { ok = false; break; }
     tc_fence_after();
     uint32_t rs[32], rd[32];  // this thread's 32 scores and 32 dP values of tile i
@@ -628,20 +651,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
 
-    const int q = q0 + row;
-    const bool q_valid = q < S;
     const long long tq = static_cast<long long>(b) * S + (q_valid ? q : 0);
     int q_doc = 1;
     if (MASK == 2 && q_valid) q_doc = p.doc_ids[tq];
-    const long long stat = (static_cast<long long>(b) * p.heads + h) * S + (q_valid ? q : 0);
-    const float lse = q_valid ? p.lse[stat] : INFINITY;
-    const float delta = q_valid ? p.delta[stat] : 0.f;
     const __nv_bfloat16* c2p_row = (POS == 2 && p.c2p) ? p.c2p + tq * pos_row + static_cast<long long>(h) * p.span2 : nullptr;
     float* dc2p_row = (POS == 2 && p.d_c2p) ? p.d_c2p + tq * pos_row + static_cast<long long>(h) * p.span2 : nullptr;
     const long long kbase = (static_cast<long long>(b) * S + k0) * pos_row + static_cast<long long>(h) * p.span2;
     const int dbase = q - k0 + S - 1;
-    const long long brow_off = ((static_cast<long long>(b) * p.heads + h) * S + (q_valid ? q : 0)) * p.ldb + k0;
-    const uint4* bias_row = POS == 1 ? reinterpret_cast<const uint4*>(p.bias + brow_off) : nullptr;
     uint4* dbias_row = (POS == 1 && q_valid) ? reinterpret_cast<uint4*>(p.dbias + brow_off) : nullptr;
 
     {
@@ -652,7 +668,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (POS == 1) {
 #pragma unroll
         for (int g8 = 0; g8 < 4; ++g8) {
-          const uint4 bvec = __ldg(bias_row + c * 4 + g8);
+          const uint4 bvec = bias_cur[g8];
           const uint32_t w[4] = {bvec.x, bvec.y, bvec.z, bvec.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
