@@ -45,17 +45,6 @@ struct AttnDev {
   int* status;
 };
 
-__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
-      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
-      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -74,27 +63,6 @@ __device__ __forceinline__ void store_bf16x16(__nv_bfloat16* dst, const uint32_t
   }
 }
 
-__device__ __forceinline__ float bf16_elem(const uint4& u, int j) {
-  const uint32_t w = (j >> 1) == 0 ? u.x : (j >> 1) == 1 ? u.y : (j >> 1) == 2 ? u.z : u.w;
-  return (j & 1) ? bf16_hi(w) : bf16_lo(w);
-}
-
-// Write one row of a 128x128 bf16 tile (two 64-column, 128B-swizzled blocks) from fp32 values.
-__device__ __forceinline__ void store_row_bf16_sw128(uint8_t* tile, int row, const float* v) {
-#pragma unroll
-  for (int blk = 0; blk < 2; ++blk) {
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      const float* s = v + blk * 64 + c * 8;
-      uint4 u;
-      u.x = pack_bf16(s[0], s[1]);
-      u.y = pack_bf16(s[2], s[3]);
-      u.z = pack_bf16(s[4], s[5]);
-      u.w = pack_bf16(s[6], s[7]);
-      *reinterpret_cast<uint4*>(tile + blk * kTileBytes + swz128(row, c)) = u;
-    }
-  }
-}
 
 // --------------------------------------------------------------------------------------------
 // forward

@@ -292,7 +292,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
       const __nv_bfloat16* bias = p.bias ? p.bias + z * p.bs_bias : nullptr;
-      if (kEpi == EPI_CE_FWD || kEpi == EPI_CE_BWD) {
+      if constexpr (kEpi == EPI_CE_FWD || kEpi == EPI_CE_BWD) {
         // One thread owns one row of logits. Forward: tile-local max / sum-exp / label logit and the
         // Gumbel-max candidate (logit/T + noise, forbidden ids excluded); partial results of every
         // vocabulary tile are combined by a second small kernel. Backward: softmax minus one-hot.
@@ -384,8 +384,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[acc]);
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
-        continue;
-      }
+      } else {
 #pragma unroll 1
       for (int cp = half * (kChunksPerHalf / 2); cp < (half + 1) * (kChunksPerHalf / 2); ++cp) {
       // GELU-derivative operand of both chunks of the group: one round trip instead of two
@@ -544,6 +543,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }  // regular (non-CE) epilogue
     }
     if (lane == 0) tma_store_wait_all();  // shared memory must outlive the bulk stores that read it
   }
