@@ -73,6 +73,16 @@ struct DevParams {
 
 // Counter-based uniform in (0,1) from (seed, row, column): 32-bit multiply-xorshift mixing (two rounds), the seed's
 // halves entering before and between the rounds. One value per logit, so it has to be cheap: ~10 integer operations.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float lg2_approx(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float hash_uniform(unsigned long long seed, unsigned int row, unsigned int col) {
   unsigned int x = (col * 0x9E3779B1u) ^ (row * 0x85EBCA77u) ^ static_cast<unsigned int>(seed);
   x ^= x >> 16; x *= 0x7FEB352Du;
@@ -311,17 +321,37 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if (!row_ok) continue;
           float v[32];
           float cmax = -INFINITY;
+          const bool full_chunk = nc + 32 <= p.N;  // warp-uniform
+          if (full_chunk && (bias == nullptr || ((reinterpret_cast<uintptr_t>(bias + nc) & 15) == 0))) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int n = nc + j;
-            float x = __uint_as_float(r[j]);
-            if (n < p.N) {
-              if (bias) x += __bfloat162float(bias[n]);
-            } else {
-              x = -INFINITY;
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            if (bias) {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                const uint4 b = __ldg(reinterpret_cast<const uint4*>(bias + nc) + q4);
+                const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  v[q4 * 8 + 2 * e] += bf16_lo(bw[e]);
+                  v[q4 * 8 + 2 * e + 1] += bf16_hi(bw[e]);
+                }
+              }
             }
-            v[j] = x;
-            cmax = fmaxf(cmax, x);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) cmax = fmaxf(cmax, v[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int n = nc + j;
+              float x = __uint_as_float(r[j]);
+              if (n < p.N) {
+                if (bias) x += __bfloat162float(bias[n]);
+              } else {
+                x = -INFINITY;
+              }
+              v[j] = x;
+              cmax = fmaxf(cmax, x);
+            }
           }
           if (kEpi == EPI_CE_FWD) {
             const float m_new = fmaxf(t_max, cmax);
@@ -341,16 +371,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                   if (nc + j < p.N && p.forbidden[nc + j]) ban_mask |= 1u << j;
               }
             }
+            const long long label_off = label - nc;  // position of the label inside this chunk, if it falls there
+            const float m_l2 = m_new * 1.4426950408889634f;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const int n = nc + j;
-              acc += __expf(v[j] - m_new);
-              if (n == label) p.label_logit[row] = v[j];
-              if (n < p.N) {
+              acc += ex2_approx(fmaf(v[j], 1.4426950408889634f, -m_l2));
+              if (label_off == j) p.label_logit[row] = v[j];
+              if (full_chunk || n < p.N) {
                 const bool banned = (ban_mask >> j) & 1u;
-                // u is an odd multiple of 2^-24: never 0 or 1, so both logarithms are finite
+                // u is an odd multiple of 2^-24: never 0 or 1, so both logarithms are finite.
+                // Gumbel noise -ln(-ln u) = -ln2 * lg2(-ln2 * lg2 u), one MUFU per logarithm
                 const float u = hash_uniform(p.seed, static_cast<unsigned int>(row), static_cast<unsigned int>(n));
-                const float cand = (banned ? -1e9f : v[j] * p.inv_temp) - 0.69314718f * __log2f(-0.69314718f * __log2f(u));
+                const float cand = (banned ? -1e9f : v[j] * p.inv_temp) - 0.69314718f * lg2_approx(-0.69314718f * lg2_approx(u));
                 if (cand > best) { best = cand; best_idx = n; }
               }
             }
@@ -625,33 +658,52 @@ extern "C" int db200_gemm_tile_n(int N) { return (N > 128) ? 128 : 64; }
 
 // Combine the per-vocabulary-tile partials of EPI_CE_FWD: per row log-sum-exp (natural log),
 // cross-entropy against the label logit, and the arg-max of the noisy logits (the sample).
-__global__ void ce_combine_kernel(const float* __restrict__ part, const float* __restrict__ label_logit, int tiles_n,
-                                  int M, float* __restrict__ lse_out, float* __restrict__ loss_rows,
-                                  long long* __restrict__ sampled) {
-  const int row = blockIdx.x * blockDim.x + threadIdx.x;
-  if (row >= M) return;
+// block (32 rows, 16 tile slices): every thread folds the tiles t = slice, slice + 16, ... of its row, the slices are
+// then combined through shared memory (online log-sum-exp, arg-max of the noisy logits).
+__global__ void __launch_bounds__(512)
+ce_combine_kernel(const float* __restrict__ part, const float* __restrict__ label_logit, int tiles_n, int M,
+                  float* __restrict__ lse_out, float* __restrict__ loss_rows, long long* __restrict__ sampled) {
+  constexpr int kSlices = 16;
+  __shared__ float s_m[kSlices][33], s_s[kSlices][33], s_b[kSlices][33];
+  __shared__ int s_i[kSlices][33];
+  const int rl = threadIdx.x, slice = threadIdx.y;
+  const int row = blockIdx.x * 32 + rl;
   const long long plane = static_cast<long long>(tiles_n) * M;
-  float m = -INFINITY;
-  for (int t = 0; t < tiles_n; ++t) m = fmaxf(m, part[static_cast<long long>(t) * M + row]);
-  float s = 0.f, best = -INFINITY;
+  float m = -INFINITY, sum = 0.f, best = -INFINITY;
   int idx = 0;
-  for (int t = 0; t < tiles_n; ++t) {
-    const long long o = static_cast<long long>(t) * M + row;
-    s += part[plane + o] * __expf(part[o] - m);
-    const float b = part[2 * plane + o];
-    if (b > best) { best = b; idx = __float_as_int(part[3 * plane + o]); }
+  if (row < M) {
+    for (int t = slice; t < tiles_n; t += kSlices) {
+      const long long o = static_cast<long long>(t) * M + row;
+      const float tm = part[o], ts = part[plane + o], tb = part[2 * plane + o];
+      const float nm = fmaxf(m, tm);
+      if (nm > -INFINITY) sum = sum * __expf(m - nm) + ts * __expf(tm - nm);
+      m = nm;
+      if (tb > best) { best = tb; idx = __float_as_int(part[3 * plane + o]); }
+    }
   }
-  const float lse = m + logf(s);
-  lse_out[row] = lse;
-  loss_rows[row] = lse - label_logit[row];
-  sampled[row] = idx;
+  s_m[slice][rl] = m; s_s[slice][rl] = sum; s_b[slice][rl] = best; s_i[slice][rl] = idx;
+  __syncthreads();
+  if (slice == 0 && row < M) {
+    // slices are folded in a fixed order; ties of the noisy maximum go to the lowest tile index seen first
+    for (int k = 1; k < kSlices; ++k) {
+      const float tm = s_m[k][rl], ts = s_s[k][rl];
+      const float nm = fmaxf(m, tm);
+      if (nm > -INFINITY) sum = sum * __expf(m - nm) + ts * __expf(tm - nm);
+      m = nm;
+      if (s_b[k][rl] > best) { best = s_b[k][rl]; idx = s_i[k][rl]; }
+    }
+    const float lse = m + logf(sum);
+    lse_out[row] = lse;
+    loss_rows[row] = lse - label_logit[row];
+    sampled[row] = idx;
+  }
 }
 
 extern "C" int db200_ce_combine(const float* part, const float* label_logit, int tiles_n, int M, float* lse,
                                 float* loss_rows, long long* sampled, void* stream) {
   if (M <= 0) return 0;
-  ce_combine_kernel<<<(M + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(part, label_logit, tiles_n, M, lse,
-                                                                                     loss_rows, sampled);
+  ce_combine_kernel<<<(M + 31) / 32, dim3(32, 16), 0, reinterpret_cast<cudaStream_t>(stream)>>>(part, label_logit, tiles_n, M,
+                                                                                            lse, loss_rows, sampled);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
