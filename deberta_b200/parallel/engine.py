@@ -167,6 +167,11 @@ class TrainEngine:
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)
             if int(flag) == 0:
                 self.comm = None
+            elif not self.comm.self_check():
+                import logging
+
+                logging.getLogger(__name__).warning("Fused peer-memory collectives failed their self-check; using NCCL.")
+                self.comm = None
         if self.comm is not None:
             self.grads, self.compute = self.comm.grads, self.comm.params
             ctx.fast_vector_sum = self.comm.vector_sum

@@ -105,6 +105,43 @@ class PeerComm:
         self.epoch = 0
         dist.barrier()  # every pad is zeroed and mapped before the first flag is written
 
+    def self_check(self) -> bool:
+        """Run the three launches on a few KiB and compare with ``torch.distributed``; True when all ranks agree.
+
+        Called once by the engine before the buffers carry data: a fabric on which peer access misbehaves is found
+        here (and the engine falls back to NCCL collectives) instead of in the middle of a run.
+        """
+        ok = True
+        try:
+            world, rank, dev = self.world, self.rank, self.device
+            per = 256
+            n = per * world
+            probe = (torch.arange(n, device=dev, dtype=torch.float32) % 7) + float(rank)
+            want = probe.clone()
+            dist.all_reduce(want)
+            self.grads[:n].copy_(probe)
+            dist.barrier()
+            norm = torch.zeros(1, device=dev)
+            self.reduce(rank * per, per, scale=1.0, to_all=True, extra_share=None, norm_sq_out=norm)
+            vec = torch.arange(5, device=dev, dtype=torch.float32) * (rank + 1)
+            got_vec = self.vector_sum(vec)
+            want_vec = vec.clone()
+            dist.all_reduce(want_vec)
+            torch.cuda.synchronize(dev)
+            ok = bool(torch.allclose(self.grads[:n], want, rtol=1e-5, atol=1e-5)) and \
+                bool(torch.allclose(got_vec, want_vec, rtol=1e-6, atol=1e-6)) and \
+                abs(float(norm) - float(want.double().pow(2).sum())) <= 1e-3 * float(want.double().pow(2).sum()) + 1e-3
+            code = int(_lib.lib().db200_status_read_and_clear())
+            ok = ok and code == 0
+        except Exception:  # noqa: BLE001
+            ok = False
+        flag = torch.tensor([1 if ok else 0], device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        self.grads[: 256 * self.world].zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier()
+        return bool(int(flag))
+
     # ---- launches -------------------------------------------------------------------------------
     def _next_epoch(self) -> ctypes.c_uint:
         self.epoch += 1
