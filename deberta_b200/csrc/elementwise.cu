@@ -225,3 +225,199 @@ extern "C" int db200_embed_bwd(const long long* ids, const void* dout, long long
       ids, static_cast<const __nv_bfloat16*>(dout), ld_do, grad, tokens, H, vocab, padding_idx);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// ---- replaced-token-detection head: classifier dot product + masked BCE-with-logits + counts ----------------------------
+//   db200_rtd_tail_fwd : logit[t] = a[t,:] . w + b ;  stats += {sum of BCE over active tokens, correct, active, positive}
+//   db200_rtd_tail_bwd : dz[t] = (sigmoid(logit) - y) * active * gscale ;  d_pre[t,:] = dz * w * gelu'(pre[t,:]) (or dz * w
+//                        when pre is null) ;  dw += sum_t dz * a[t,:] ;  db += sum_t dz        (gscale = *grad / max(count,1))
+// One warp per token row; H <= 1024 (multiple of 8).
+namespace {
+
+constexpr int kTailVec = 4;  // 16-byte vectors per lane: H <= 1024
+
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float dgelu_exact(float x) {
+  const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752f));
+  return cdf + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+}
+
+__global__ void __launch_bounds__(256)
+rtd_tail_fwd_kernel(const __nv_bfloat16* __restrict__ a, long long lda, const __nv_bfloat16* __restrict__ w,
+                    const __nv_bfloat16* __restrict__ bias, const long long* __restrict__ labels,
+                    const unsigned char* __restrict__ active, float* __restrict__ logits, float* __restrict__ stats,
+                    long long tokens, int H) {
+  __shared__ float part[8][4];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int vecs = H / 8;
+  float wv[kTailVec][8];
+#pragma unroll
+  for (int i = 0; i < kTailVec; ++i) {
+    const int v = lane + 32 * i;
+    uint4 u = make_uint4(0, 0, 0, 0);
+    if (v < vecs) u = __ldg(reinterpret_cast<const uint4*>(w) + v);
+    const unsigned int uw[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { wv[i][2 * e] = lo_f(uw[e]); wv[i][2 * e + 1] = hi_f(uw[e]); }
+  }
+  const float b = bias ? __bfloat162float(bias[0]) : 0.f;
+  float s_loss = 0.f, s_correct = 0.f, s_count = 0.f, s_pos = 0.f;
+  for (long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; t < tokens;
+       t += (static_cast<long long>(gridDim.x) * blockDim.x) >> 5) {
+    const uint4* row = reinterpret_cast<const uint4*>(a + t * lda);
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < kTailVec; ++i) {
+      const int v = lane + 32 * i;
+      if (v < vecs) {
+        const uint4 u = row[v];
+        const unsigned int uw[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc += lo_f(uw[e]) * wv[i][2 * e] + hi_f(uw[e]) * wv[i][2 * e + 1];
+      }
+    }
+    // the reference rounds the logit to the activation dtype before the loss
+    const float z = __bfloat162float(__float2bfloat16(warp_sum_f(acc) + b));
+    if (lane == 0) {
+      logits[t] = z;
+      if (active[t]) {
+        const float y = labels[t] > 0 ? 1.f : 0.f;
+        s_loss += fmaxf(z, 0.f) - z * y + log1pf(__expf(-fabsf(z)));
+        s_correct += ((z > 0.f) == (y > 0.5f)) ? 1.f : 0.f;
+        s_count += 1.f;
+        s_pos += y;
+      }
+    }
+  }
+  if (lane == 0) { part[warp][0] = s_loss; part[warp][1] = s_correct; part[warp][2] = s_count; part[warp][3] = s_pos; }
+  __syncthreads();
+  if (threadIdx.x < 4) {
+    float s = 0.f;
+    for (int k = 0; k < 8; ++k) s += part[k][threadIdx.x];
+    if (s != 0.f) atomicAdd(stats + threadIdx.x, s);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+rtd_tail_bwd_kernel(const __nv_bfloat16* __restrict__ a, long long lda, const __nv_bfloat16* __restrict__ pre,
+                    long long ldp, const __nv_bfloat16* __restrict__ w, const float* __restrict__ logits,
+                    const long long* __restrict__ labels, const unsigned char* __restrict__ active,
+                    const float* __restrict__ grad, const float* __restrict__ stats, __nv_bfloat16* __restrict__ d_pre,
+                    long long ldd, float* __restrict__ dw, float* __restrict__ db, long long tokens, int H) {
+  __shared__ float red[8][33];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int vecs = H / 8;
+  const float gscale = grad[0] / fmaxf(stats[2], 1.f);
+  float wv[kTailVec][8], dwv[kTailVec][8];
+#pragma unroll
+  for (int i = 0; i < kTailVec; ++i) {
+    const int v = lane + 32 * i;
+    uint4 u = make_uint4(0, 0, 0, 0);
+    if (v < vecs) u = __ldg(reinterpret_cast<const uint4*>(w) + v);
+    const unsigned int uw[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { wv[i][2 * e] = lo_f(uw[e]); wv[i][2 * e + 1] = hi_f(uw[e]); }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dwv[i][e] = 0.f;
+  }
+  float dbv = 0.f;
+  for (long long t = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; t < tokens;
+       t += (static_cast<long long>(gridDim.x) * blockDim.x) >> 5) {
+    float dz = 0.f;
+    if (active[t]) {
+      const float z = logits[t];
+      const float y = labels[t] > 0 ? 1.f : 0.f;
+      dz = (1.f / (1.f + __expf(-z)) - y) * gscale;
+    }
+    dz = __bfloat162float(__float2bfloat16(dz));  // the logit gradient reaches the classifier in the activation dtype
+    dbv += dz;
+    const uint4* arow = reinterpret_cast<const uint4*>(a + t * lda);
+    const uint4* prow = pre ? reinterpret_cast<const uint4*>(pre + t * ldp) : nullptr;
+    uint4* drow = reinterpret_cast<uint4*>(d_pre + t * ldd);
+#pragma unroll
+    for (int i = 0; i < kTailVec; ++i) {
+      const int v = lane + 32 * i;
+      if (v < vecs) {
+        const uint4 ua = arow[v];
+        const unsigned int aw[4] = {ua.x, ua.y, ua.z, ua.w};
+        float g[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          dwv[i][2 * e] += dz * lo_f(aw[e]);
+          dwv[i][2 * e + 1] += dz * hi_f(aw[e]);
+          g[2 * e] = dz * wv[i][2 * e];
+          g[2 * e + 1] = dz * wv[i][2 * e + 1];
+        }
+        if (prow) {
+          const uint4 up = prow[v];
+          const unsigned int pw[4] = {up.x, up.y, up.z, up.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            g[2 * e] *= dgelu_exact(lo_f(pw[e]));
+            g[2 * e + 1] *= dgelu_exact(hi_f(pw[e]));
+          }
+        }
+        drow[v] = make_uint4(pack2(g[0], g[1]), pack2(g[2], g[3]), pack2(g[4], g[5]), pack2(g[6], g[7]));
+      }
+    }
+  }
+  // block reduction of the classifier gradient: one 8-feature vector slot at a time
+#pragma unroll
+  for (int i = 0; i < kTailVec; ++i) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      red[warp][lane] = dwv[i][e];
+      __syncthreads();
+      if (warp == 0) {
+        float s = 0.f;
+        for (int k = 0; k < 8; ++k) s += red[k][lane];
+        const int v = lane + 32 * i;
+        if (v < vecs && s != 0.f) atomicAdd(dw + v * 8 + e, s);
+      }
+      __syncthreads();
+    }
+  }
+  dbv = (lane == 0) ? dbv : 0.f;  // every lane of a warp carries the same dz
+  red[warp][lane] = dbv;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.f;
+    for (int k = 0; k < 8; ++k) s += red[k][0];
+    if (s != 0.f) atomicAdd(db, s);
+  }
+}
+
+}  // namespace
+
+extern "C" int db200_rtd_tail_fwd(const void* a, long long lda, const void* w, const void* bias, const long long* labels,
+                                  const unsigned char* active, float* logits, float* stats, long long tokens, int H,
+                                  void* stream) {
+  if (tokens <= 0) return 0;
+  if (!al16(a) || !al16(w) || (lda % 8) || (H % 8) || H > 1024) return -10;
+  int blocks = static_cast<int>((tokens + 7) / 8);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  rtd_tail_fwd_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(a), lda, static_cast<const __nv_bfloat16*>(w),
+      static_cast<const __nv_bfloat16*>(bias), labels, active, logits, stats, tokens, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int db200_rtd_tail_bwd(const void* a, long long lda, const void* pre, long long ldp, const void* w,
+                                  const float* logits, const long long* labels, const unsigned char* active,
+                                  const float* grad, const float* stats, void* d_pre, long long ldd, float* dw, float* db,
+                                  long long tokens, int H, void* stream) {
+  if (tokens <= 0) return 0;
+  if (!al16(a) || !al16(w) || !al16(d_pre) || (pre && !al16(pre)) || (lda % 8) || (ldp % 8) || (ldd % 8) || (H % 8) || H > 1024)
+    return -10;
+  int blocks = static_cast<int>((tokens + 7) / 8);
+  if (blocks > 148 * 2) blocks = 148 * 2;  // few blocks: each ends with a reduction of the classifier gradient
+  rtd_tail_bwd_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(a), lda, static_cast<const __nv_bfloat16*>(pre), ldp,
+      static_cast<const __nv_bfloat16*>(w), logits, labels, active, grad, stats, static_cast<__nv_bfloat16*>(d_pre), ldd, dw,
+      db, tokens, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -81,6 +81,16 @@ int db200_embed_fwd(const long long* ids, const void* table, const void* delta, 
 int db200_embed_bwd(const long long* ids, const void* dout, long long ld_do, float* grad, long long tokens, int H,
                     long long vocab, long long padding_idx, void* stream);
 
+// Tail of the replaced-token-detection head. Forward: logit[t] = a[t,:].w + bias (rounded to bf16), and
+// stats[0..3] += {BCE-with-logits summed over active tokens, correct predictions, active tokens, positive labels}.
+// Backward: d_pre[t,:] = dz[t] * w * gelu'(pre[t,:]) (pre null: no activation derivative), dw += sum dz * a[t,:],
+// db += sum dz, with dz = (sigmoid(logit) - label) * active * grad[0] / max(stats[2], 1). H <= 1024, H % 8 == 0.
+int db200_rtd_tail_fwd(const void* a, long long lda, const void* w, const void* bias, const long long* labels,
+                       const unsigned char* active, float* logits, float* stats, long long tokens, int H, void* stream);
+int db200_rtd_tail_bwd(const void* a, long long lda, const void* pre, long long ldp, const void* w, const float* logits,
+                       const long long* labels, const unsigned char* active, const float* grad, const float* stats,
+                       void* d_pre, long long ldd, float* dw, float* db, long long tokens, int H, void* stream);
+
 // ----- fused gradient collectives over NVLink peer memory (see comm.cu) -----------------------
 #define DB200_COMM_MAX_WORLD 8
 #define DB200_COMM_VEC_MAX 128      // longest vector db200_comm_vector_sum takes

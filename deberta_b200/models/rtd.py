@@ -249,6 +249,22 @@ class RTDHead(nn.Module):
         x = self.act(linear(_norm(self.norm, x), self.dense.weight, self.dense.bias))
         return F.linear(x, self.classifier.weight.to(x.dtype), self.classifier.bias.to(x.dtype)).squeeze(-1)
 
+    def loss_stats(self, hidden_states: torch.Tensor, attention_mask, labels: torch.Tensor, active: torch.Tensor):
+        """Head + masked BCE in one go: ``RTDStats`` of ``rtd_loss(self(hidden_states), labels, active)``.
+
+        On bf16 CUDA tensors with a GELU head the dense layer runs with the GELU epilogue and the classifier, the
+        loss and the counts come from one kernel; otherwise this is the composition above.
+        """
+        from deberta_b200.ops.heads import RTDStats
+        from deberta_b200.ops.heads_cuda import rtd_head_loss_cuda, rtd_head_supported
+
+        if not rtd_head_supported(hidden_states, self.dense.weight, self.classifier.weight, self.act_name):
+            return rtd_loss(self(hidden_states, attention_mask=attention_mask), labels, active)
+        x = hidden_states + hidden_states[:, 0:1, :] if self._use_global_cls_context(attention_mask) else hidden_states
+        loss, acc, count, positive = rtd_head_loss_cuda(_norm(self.norm, x), self.dense.weight, self.dense.bias,
+                                                        self.classifier.weight, self.classifier.bias, labels, active)
+        return RTDStats(loss=loss, accuracy=acc, token_count=count, positive_count=positive)
+
 
 @dataclass
 class RTDOutput:
@@ -451,11 +467,10 @@ class DebertaV3RTDPretrainer(nn.Module):
         """Discriminator pass over the corrupted ids + masked-mean BCE over active tokens (``:1095-1152``)."""
         out = self.discriminator(input_ids=corrupted_input_ids, attention_mask=attention_mask,
                                  token_type_ids=token_type_ids, return_dict=True)
-        logits = self.discriminator_head(out.last_hidden_state, attention_mask=attention_mask)
         pad = getattr(self.disc_config, "pad_token_id", None)
         active = attention_mask_to_active_tokens(input_ids=input_ids, attention_mask=attention_mask,
                                                  pad_token_id=int(pad) if pad is not None else None)
-        st = rtd_loss(logits, disc_labels, active)
+        st = self.discriminator_head.loss_stats(out.last_hidden_state, attention_mask, disc_labels, active)
         return RTDDiscriminatorPhaseOutput(disc_loss_raw=st.loss, disc_accuracy=st.accuracy,
                                            disc_token_count=st.token_count, disc_positive_count=st.positive_count)
 

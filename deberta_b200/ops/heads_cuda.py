@@ -101,3 +101,69 @@ def mlm_loss_and_sample_cuda(x, weight, bias, labels, forbidden_mask, temperatur
         raise ValueError("sampling_temperature must be > 0")
     loss, sampled = _VocabCE.apply(x, weight, bias, labels, forbidden_mask, float(temperature))
     return loss, sampled
+
+
+# ---- replaced-token-detection head ---------------------------------------------------------------------------------
+
+class _RTDHead(torch.autograd.Function):
+    """dense + GELU (GEMM epilogue) → classifier dot + masked BCE + counts (one kernel); see ``csrc/elementwise.cu``."""
+
+    @staticmethod
+    def forward(ctx, x, dense_w, dense_b, cls_w, cls_b, labels, active):
+        from .gemm import EPI_GELU
+
+        pre, act = gemm(x, dense_w, bias=dense_b, epi=EPI_GELU)
+        T, H = act.shape
+        logits = torch.empty(T, dtype=torch.float32, device=x.device)
+        stats = torch.zeros(4, dtype=torch.float32, device=x.device)
+        _lib.call("db200_rtd_tail_fwd", _lib.ptr(act), ctypes.c_longlong(act.stride(0)), _lib.ptr(cls_w), _lib.ptr(cls_b),
+                  _lib.ptr(labels), _lib.ptr(active), _lib.ptr(logits), _lib.ptr(stats), ctypes.c_longlong(T),
+                  ctypes.c_int(H), _lib.stream_ptr())
+        denom = stats[2].clamp(min=1.0)
+        ctx.save_for_backward(x, dense_w, pre, act, logits, labels, active, stats)
+        ctx.refs = (dense_b, cls_w, cls_b)
+        out = (stats[0] / denom, stats[1] / denom, stats[2].clone(), stats[3].clone())
+        ctx.mark_non_differentiable(*out[1:])
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_loss, *_unused):
+        from .linear import _bias_grad, _weight_grad
+
+        x, dense_w, pre, act, logits, labels, active, stats = ctx.saved_tensors
+        dense_b, cls_w, cls_b = ctx.refs
+        T, H = act.shape
+        dev = x.device
+        g = grad_loss.detach().float().reshape(1).contiguous()
+        d_pre = torch.empty_like(pre)
+        dw_main, db_main = getattr(cls_w, "main_grad", None), getattr(cls_b, "main_grad", None) if cls_b is not None else None
+        dw = dw_main if dw_main is not None else torch.zeros(H, dtype=torch.float32, device=dev)
+        db = db_main if db_main is not None else torch.zeros(1, dtype=torch.float32, device=dev)
+        _lib.call("db200_rtd_tail_bwd", _lib.ptr(act), ctypes.c_longlong(act.stride(0)), _lib.ptr(pre),
+                  ctypes.c_longlong(pre.stride(0)), _lib.ptr(cls_w), _lib.ptr(logits), _lib.ptr(labels), _lib.ptr(active),
+                  _lib.ptr(g), _lib.ptr(stats), _lib.ptr(d_pre), ctypes.c_longlong(d_pre.stride(0)), _lib.ptr(dw), _lib.ptr(db),
+                  ctypes.c_longlong(T), ctypes.c_int(H), _lib.stream_ptr())
+        dx = gemm(d_pre, dense_w, b_mn=True) if ctx.needs_input_grad[0] else None
+        d_dense_w = _weight_grad(d_pre, x, dense_w) if dense_w.requires_grad else None
+        d_dense_b = _bias_grad(d_pre, dense_b) if (dense_b is not None and dense_b.requires_grad) else None
+        d_cls_w = None if dw_main is not None else dw.view(1, H).to(cls_w.dtype)
+        d_cls_b = None if (cls_b is None or db_main is not None) else db.to(cls_b.dtype)
+        return dx, d_dense_w, d_dense_b, d_cls_w, d_cls_b, None, None
+
+
+def rtd_head_supported(x: torch.Tensor, dense_w: torch.Tensor, cls_w: torch.Tensor, act_name: str) -> bool:
+    h = x.shape[-1]
+    return (x.is_cuda and x.dtype == torch.bfloat16 and dense_w.dtype == torch.bfloat16 and cls_w.dtype == torch.bfloat16
+            and act_name == "gelu" and h % 8 == 0 and h <= 1024 and tuple(dense_w.shape) == (h, h)
+            and tuple(cls_w.shape) == (1, h) and cls_w.is_contiguous())
+
+
+def rtd_head_loss_cuda(x, dense_w, dense_b, cls_w, cls_b, labels, active):
+    """(loss, accuracy, active-token count, positive count) of the RTD head on normalised hidden states ``x`` [..., H]."""
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 or x2.stride(0) % 8 or x2.data_ptr() % 16:
+        x2 = x2.contiguous()
+    lab = labels.reshape(-1).gt(0.5).to(torch.int64).contiguous() if labels.is_floating_point() else \
+        labels.reshape(-1).to(torch.int64).contiguous()
+    act = active.reshape(-1).to(torch.uint8).contiguous()
+    return _RTDHead.apply(x2, dense_w, dense_b, cls_w, cls_b, lab, act)

@@ -80,3 +80,36 @@ def test_embedding_lookup_kernel_matches_pytorch():
     with torch.no_grad():
         out2 = embedding_lookup(ids, base)
     assert torch.equal(out2, base[ids])
+
+
+def test_rtd_head_kernel_matches_composition():
+    import torch
+    from deberta_b200.ops.heads import rtd_loss
+    from deberta_b200.ops.heads_cuda import rtd_head_loss_cuda, rtd_head_supported
+
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    B, S, H = 3, 50, 256
+    x = (torch.randn(B, S, H, device=dev) * 0.7).to(torch.bfloat16).requires_grad_(True)
+    dense_w = torch.nn.Parameter((torch.randn(H, H, device=dev) * 0.06).to(torch.bfloat16))
+    dense_b = torch.nn.Parameter((torch.randn(H, device=dev) * 0.1).to(torch.bfloat16))
+    cls_w = torch.nn.Parameter((torch.randn(1, H, device=dev) * 0.1).to(torch.bfloat16))
+    cls_b = torch.nn.Parameter(torch.tensor([0.05], device=dev).to(torch.bfloat16))
+    labels = (torch.rand(B, S, device=dev) < 0.2).float()
+    active = torch.rand(B, S, device=dev) < 0.9
+    assert rtd_head_supported(x, dense_w, cls_w, "gelu")
+    loss, acc, count, pos = rtd_head_loss_cuda(x, dense_w, dense_b, cls_w, cls_b, labels, active)
+    (loss * 3.0).backward()
+    got = [x.grad.float(), dense_w.grad.float(), dense_b.grad.float(), cls_w.grad.float(), cls_b.grad.float()]
+    xr = x.detach().float().requires_grad_(True)
+    ps = [p.detach().float().requires_grad_(True) for p in (dense_w, dense_b, cls_w, cls_b)]
+    h = torch.nn.functional.gelu(torch.nn.functional.linear(xr, ps[0], ps[1]))
+    logits = torch.nn.functional.linear(h, ps[2], ps[3]).squeeze(-1)
+    ref = rtd_loss(logits, labels, active)
+    (ref.loss * 3.0).backward()
+    assert abs(float(loss) - float(ref.loss)) < 2e-2 * float(ref.loss)
+    assert abs(float(acc) - float(ref.accuracy)) < 0.02
+    assert float(count) == float(ref.token_count) and float(pos) == float(ref.positive_count)
+    want = [xr.grad] + [p.grad for p in ps]
+    for g, w in zip(got, want):
+        assert (g - w).abs().max() <= 6e-2 * w.abs().max() + 1e-5, (float((g - w).abs().max()), float(w.abs().max()))
