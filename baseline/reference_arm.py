@@ -179,7 +179,7 @@ def run_reference(args) -> dict:
     tokens = args.ga * args.micro_batch * args.seq_len * world * args.steps
     h2d = sum(v.numel() * v.element_size() for b in host for v in b.values())
     result = {
-        "metric": ("RTD pretrain tokens/s, DeBERTa-v3-base seq512, max over ranks"
+        "metric": (f"RTD pretrain tokens/s, DeBERTa-v3-{args.model_size} seq{args.seq_len}, max over ranks"
                    if getattr(args, "backbone", "hf_deberta_v2") == "hf_deberta_v2"
                    else f"RTD pretrain tokens/s, rope backbone seq{args.seq_len}, max over ranks"), "value": tokens / (ms / 1e3),
         "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,

@@ -202,7 +202,7 @@ def run_ours(args: argparse.Namespace) -> dict:
     gen_loss = float(stats.gen_loss_tokens) / max(stats.gen_tokens, 1.0)
     value = tokens_per_step * ctx.world_size * args.steps / (ms / 1e3)
     result = {
-        "metric": ("RTD pretrain tokens/s, DeBERTa-v3-base seq512, max over ranks" if args.backbone == "hf_deberta_v2"
+        "metric": (f"RTD pretrain tokens/s, DeBERTa-v3-{args.model_size} seq{args.seq_len}, max over ranks" if args.backbone == "hf_deberta_v2"
                    else f"RTD pretrain tokens/s, rope backbone seq{args.seq_len}, max over ranks"), "value": value, "unit": "tokens/s",
         "n_gpus": ctx.world_size, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
