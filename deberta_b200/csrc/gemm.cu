@@ -750,10 +750,17 @@ extern "C" int db200_gemm_bf16(const GemmArgs* a, void* stream_) {
   const int tiles = p.tiles_m * p.tiles_n * p.batch;
   int splits = 1;
   if (a->out_f32 && a->allow_split_k && a->residual == nullptr) {
-    // Fill the machine when the output grid is small (weight gradients: K = tokens).
+    // Fill the machine when the output grid is small (weight gradients: K = tokens). Cost of a split count s in
+    // k-block units: waves of work items x (k-blocks per item + a fixed epilogue share, an fp32 tile of reductions).
     const int sms = num_sms();
-    while (tiles * splits * 2 <= sms && p.kb_total / (splits * 2) >= 4) splits *= 2;
-    if (tiles * splits < sms && p.kb_total / (splits * 2) >= 8) splits *= 2;
+    constexpr int kEpilogueCost = 6;
+    long long best_cost = -1;
+    for (int s = 1; s <= 16; s *= 2) {
+      if (s > 1 && p.kb_total / s < 4) break;
+      const long long waves = (static_cast<long long>(tiles) * s + sms - 1) / sms;
+      const long long cost = waves * ((p.kb_total + s - 1) / s + kEpilogueCost);
+      if (best_cost < 0 || cost < best_cost) { best_cost = cost; splits = s; }
+    }
   }
   p.splits = splits;
   if (splits > 1 && !p.accumulate) {
