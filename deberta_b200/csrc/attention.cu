@@ -9,7 +9,9 @@
 // products of queries / keys with the projected relative-position table, computed once per
 // layer by the GEMM kernel; they are read through L1/L2 with the bucket lookup tables held in
 // shared memory. Masking: optional key-padding flags or packed-document ids; inactive queries
-// produce zero rows. The position terms are optional, which gives plain (rotary) attention.
+// produce zero rows. With document ids and a per-tile table of the ids' range, a CTA only visits the
+// tiles whose range meets its own (block-diagonal skipping for packed sequences).
+// The position terms are optional, which gives plain (rotary) attention.
 //
 // Forward : grid (q-tiles, heads, batch), 512 threads: four threads share a query row so that
 //           16 warps hide the latency of the softmax arithmetic.
@@ -37,6 +39,7 @@ struct AttnDev {
   const unsigned short* lut_p2c;
   const unsigned char* key_keep;  // [B*S] or null
   const int* doc_ids;             // [B*S] or null
+  const int* doc_tiles;           // [B, tiles, 2]: smallest / largest non-zero id of each 128-token tile, or null
   const __nv_bfloat16* bias;      // [B, heads, S, ldb] pre-gathered position bias (unscaled) or null
   long long ldb;
   __nv_bfloat16* out;   // [B*S, ldo]
@@ -51,6 +54,31 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// Tiles whose document-id range [lo, hi] meets that of tile `self`: first such tile and the length of the
+// run up to the last one (tiles inside the run that do not meet it are still visited and fully masked).
+// A tile without live tokens has lo > hi and meets nothing; a CTA always visits at least one tile.
+// Called by whole warps; without a table, or with more than 32 tiles, every tile is visited.
+__device__ __forceinline__ void doc_tile_run(const int* tiles, int b, int ntiles, int self, int lane, int& first,
+                                             int& count) {
+  first = 0;
+  count = ntiles;
+  if (tiles == nullptr || ntiles > 32) return;
+  const int* t = tiles + static_cast<long long>(b) * ntiles * 2;
+  const int slo = t[2 * self], shi = t[2 * self + 1];
+  bool hit = false;
+  if (lane < ntiles) {
+    const int lo = t[2 * lane], hi = t[2 * lane + 1];
+    hit = lo <= hi && slo <= shi && lo <= shi && hi >= slo;
+  }
+  const unsigned m = __ballot_sync(0xffffffffu, hit);
+  if (m == 0) {
+    count = 1;
+  } else {
+    first = __ffs(m) - 1;
+    count = 32 - __clz(m) - first;
+  }
 }
 
 // 16 packed bf16 (32 contiguous bytes) of one row: one 256-bit store when aligned, else two 128-bit ones.
@@ -135,7 +163,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int S = p.S;
-  const int nkt = (S + kTile - 1) / kTile;
+  int jb = 0, nkt = (S + kTile - 1) / kTile;  // first key tile and number of key tiles this CTA visits
+  if (MASK == 2) doc_tile_run(p.doc_tiles, b, nkt, blockIdx.x, lane, jb, nkt);
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
@@ -173,14 +202,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_expect_tx(bar_q, kTileBytes);
     tma_load_3d(sQ, &tm_q, bar_q, h * kD, q0, b);
     mbar_expect_tx(&bar_k[0], kTileBytes);
-    tma_load_3d(sK, &tm_k, &bar_k[0], h * kD, 0, b);
+    tma_load_3d(sK, &tm_k, &bar_k[0], h * kD, jb * kTile, b);
     mbar_expect_tx(&bar_v[0], kTileBytes);
-    tma_load_3d(sV, &tm_v, &bar_v[0], h * kD, 0, b);
+    tma_load_3d(sV, &tm_v, &bar_v[0], h * kD, jb * kTile, b);
     if (nkt > 1) {  // second tile of K and V straight away: both buffers start empty
       mbar_expect_tx(&bar_k[1], kTileBytes);
-      tma_load_3d(sK + kTileBytes, &tm_k, &bar_k[1], h * kD, kTile, b);
+      tma_load_3d(sK + kTileBytes, &tm_k, &bar_k[1], h * kD, (jb + 1) * kTile, b);
       mbar_expect_tx(&bar_v[1], kTileBytes);
-      tma_load_3d(sV + kTileBytes, &tm_v, &bar_v[1], h * kD, kTile, b);
+      tma_load_3d(sV + kTileBytes, &tm_v, &bar_v[1], h * kD, (jb + 1) * kTile, b);
     }
   }
 
@@ -222,10 +251,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint4 bias_pf[4] = {};
   if (POS == 1) {
 #pragma unroll
-    for (int g = 0; g < 4; ++g) bias_pf[g] = __ldg(bias_row + ((part * 32) >> 3) + g);
+    for (int g = 0; g < 4; ++g) bias_pf[g] = __ldg(bias_row + ((jb * kTile + part * 32) >> 3) + g);
   }
-  for (int j = 0; j < nkt; ++j) {
-    const int k0 = j * kTile;
+  for (int j = 0; j < nkt; ++j) {  // j counts visited tiles (buffers and barrier phases follow it)
+    const int k0 = (jb + j) * kTile;
     bool tile_all_keep = false;
     if (MASK != 0) {
       int tile_meta = 1;
@@ -420,6 +449,7 @@ struct AttnBwdDev {
   const unsigned short* lut_p2c;
   const unsigned char* key_keep;
   const int* doc_ids;
+  const int* doc_tiles;       // as in the forward kernel
   const __nv_bfloat16* bias;  // [B, heads, S, ldb] or null
   __nv_bfloat16* dbias;       // [B, heads, S, ldb] gradient of the bias (written when bias is given)
   long long ldb;
@@ -486,7 +516,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int S = p.S;
-  const int nqt = (S + kTile - 1) / kTile;
+  int ib = 0, nqt = (S + kTile - 1) / kTile;  // first query tile and number of query tiles this CTA visits
+  if (MASK == 2) doc_tile_run(p.doc_tiles, b, nqt, blockIdx.x, lane, ib, nqt);
 
   if (tid == 0) {
     mbar_init(bar_kv, 1);
@@ -554,12 +585,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tma_load_3d(sK, &tm_k, bar_kv, h * kD, k0, b);
     tma_load_3d(sV, &tm_v, bar_kv, h * kD, k0, b);
     mbar_expect_tx(&bar_qd[0], 2 * kTileBytes);
-    tma_load_3d(sQ, &tm_q, &bar_qd[0], h * kD, 0, b);
-    tma_load_3d(sdO, &tm_do, &bar_qd[0], h * kD, 0, b);
+    tma_load_3d(sQ, &tm_q, &bar_qd[0], h * kD, ib * kTile, b);
+    tma_load_3d(sdO, &tm_do, &bar_qd[0], h * kD, ib * kTile, b);
     if (nqt > 1) {
       mbar_expect_tx(&bar_qd[1], 2 * kTileBytes);
-      tma_load_3d(sQ + kTileBytes, &tm_q, &bar_qd[1], h * kD, kTile, b);
-      tma_load_3d(sdO + kTileBytes, &tm_do, &bar_qd[1], h * kD, kTile, b);
+      tma_load_3d(sQ + kTileBytes, &tm_q, &bar_qd[1], h * kD, (ib + 1) * kTile, b);
+      tma_load_3d(sdO + kTileBytes, &tm_do, &bar_qd[1], h * kD, (ib + 1) * kTile, b);
     }
     if (mbar_wait(bar_kv, 0, abort_flag, p.status, kErrFullWait) &&
         mbar_wait(&bar_qd[0], 0, abort_flag, p.status, kErrFullWait)) {
@@ -585,9 +616,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   };
 
   bool ok = true;
-  for (int i = 0; i < nqt; ++i) {
+  for (int i = 0; i < nqt; ++i) {  // i counts visited tiles (buffers and barrier phases follow it)
     const int buf = i % 3;
-    const int q0 = i * kTile;
+    const int q0 = (ib + i) * kTile;
     // per-row inputs that do not depend on the scores are requested before the wait: their latency hides behind the MMAs
     const int q = q0 + row;
     const bool q_valid = q < S;
@@ -685,11 +716,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tma_load_3d(sQ + nb * kTileBytes, &tm_q, &bar_qd[nb], h * kD, q0 + 2 * kTile, b);
           tma_load_3d(sdO + nb * kTileBytes, &tm_do, &bar_qd[nb], h * kD, q0 + 2 * kTile, b);
         }
-        flush_dq(i - 1);
+        flush_dq(ib + i - 1);
       } else if (tid == 0 && nqt > 2) {
         mbar_expect_tx(&bar_qd[2], 2 * kTileBytes);
-        tma_load_3d(sQ + 2 * kTileBytes, &tm_q, &bar_qd[2], h * kD, 2 * kTile, b);
-        tma_load_3d(sdO + 2 * kTileBytes, &tm_do, &bar_qd[2], h * kD, 2 * kTile, b);
+        tma_load_3d(sQ + 2 * kTileBytes, &tm_q, &bar_qd[2], h * kD, (ib + 2) * kTile, b);
+        tma_load_3d(sdO + 2 * kTileBytes, &tm_do, &bar_qd[2], h * kD, (ib + 2) * kTile, b);
       }
       // rows of P and dS for these 32 keys: 4 chunks of 8 bf16 inside 64-key block (c >> 1)
       uint32_t dsw[16];
@@ -740,7 +771,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   if (ok && mbar_wait(bar_g, (nqt - 1) & 1, abort_flag, p.status, kErrAccFullWait)) {
     tc_fence_after();
-    flush_dq(nqt - 1);
+    flush_dq(ib + nqt - 1);
     const int kk = k0 + row;
     const long long tk = static_cast<long long>(b) * S + kk;
 #pragma unroll
@@ -799,6 +830,32 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, long long ld_do, const
   }
 }
 
+// tiles[b, t] = (smallest, largest) non-zero document id among tokens [128 t, 128 t + 128) of row b;
+// (INT_MAX, -1) when the tile holds padding only. One block of 128 threads per tile.
+__global__ void __launch_bounds__(kTile)
+attn_doc_tiles_kernel(const int* __restrict__ doc_ids, int* __restrict__ tiles, int S) {
+  __shared__ int s_lo[4], s_hi[4];
+  const int t = blockIdx.x, b = blockIdx.y;
+  const int pos = t * kTile + threadIdx.x;
+  const int id = pos < S ? doc_ids[static_cast<long long>(b) * S + pos] : 0;
+  int lo = id != 0 ? id : 2147483647, hi = id != 0 ? id : -1;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+    hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    s_lo[threadIdx.x >> 5] = lo;
+    s_hi[threadIdx.x >> 5] = hi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* dst = tiles + (static_cast<long long>(b) * gridDim.x + t) * 2;
+    dst[0] = min(min(s_lo[0], s_lo[1]), min(s_lo[2], s_lo[3]));
+    dst[1] = max(max(s_hi[0], s_hi[1]), max(s_hi[2], s_hi[3]));
+  }
+}
+
 int make_head_map(CUtensorMap* m, const void* ptr, const AttnArgs* a, long long ld) {
   return db200_make_tmap_bf16(m, ptr, static_cast<long long>(a->heads) * kD, a->S, a->B, ld,
                               static_cast<long long>(a->S) * ld, kTile);
@@ -831,6 +888,7 @@ extern "C" int db200_attn_fwd(const AttnArgs* a, void* stream_) {
   d.lut_p2c = static_cast<const unsigned short*>(a->lut_p2c);
   d.key_keep = static_cast<const unsigned char*>(a->key_keep);
   d.doc_ids = static_cast<const int*>(a->doc_ids);
+  d.doc_tiles = d.doc_ids ? static_cast<const int*>(a->doc_tiles) : nullptr;
   d.bias = static_cast<const __nv_bfloat16*>(a->bias);
   d.ldb = a->ldb;
   if (d.bias && ((a->ldb % 128) || !aligned16(a->bias))) return -10;
@@ -882,6 +940,7 @@ extern "C" int db200_attn_bwd(const AttnArgs* a, void* stream_) {
   d.lut_p2c = static_cast<const unsigned short*>(a->lut_p2c);
   d.key_keep = static_cast<const unsigned char*>(a->key_keep);
   d.doc_ids = static_cast<const int*>(a->doc_ids);
+  d.doc_tiles = d.doc_ids ? static_cast<const int*>(a->doc_tiles) : nullptr;
   d.bias = static_cast<const __nv_bfloat16*>(a->bias);
   d.dbias = static_cast<__nv_bfloat16*>(a->dbias);
   d.ldb = a->ldb;
@@ -921,5 +980,14 @@ extern "C" int db200_attn_delta(const void* dout, long long ld_do, const void* o
   const long long threads = static_cast<long long>(B) * S * heads * 8;
   attn_delta_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(dout), ld_do, static_cast<const __nv_bfloat16*>(out), ldo, delta, B, S, heads);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int db200_attn_doc_tiles(const void* doc_ids, void* tiles, int B, int S, void* stream) {
+  if (B <= 0 || S <= 0) return 0;
+  if (!doc_ids || !tiles) return -10;
+  dim3 grid((S + kTile - 1) / kTile, B);
+  attn_doc_tiles_kernel<<<grid, kTile, 0, reinterpret_cast<cudaStream_t>(stream)>>>(static_cast<const int*>(doc_ids),
+                                                                                   static_cast<int*>(tiles), S);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -144,6 +144,8 @@ typedef struct AttnArgs {
   const void* bias;               // bf16 [B, heads, S, ldb] pre-gathered position bias (then span2 = 0), or null
   void* dbias;                    // bf16 [B, heads, S, ldb] its gradient (backward)
   long long ldb;                  // multiple of 128
+  const void* doc_tiles;          // int32 [B, ceil(S/128), 2] from db200_attn_doc_tiles, or null: with it the kernels
+                                  // skip the tiles no document of theirs reaches (bias gradient must then be zeroed)
 } AttnArgs;
 
 // key-indexed position bias: build from / scatter back to the bucket-indexed score tables (posbias.cu)
@@ -161,6 +163,8 @@ int db200_attn_bwd(const AttnArgs* args, void* stream);
 // delta[b,h,s] = sum over the head dim of dO * O (fp32 [B, heads, S]); input of db200_attn_bwd.
 int db200_attn_delta(const void* dout, long long ld_do, const void* out, long long ldo, float* delta, int B, int S,
                      int heads, void* stream);
+// tiles[b, t] = (smallest, largest) non-zero document id of tokens [128 t, 128 t + 128) of row b (int32 [B, tiles, 2]).
+int db200_attn_doc_tiles(const void* doc_ids, void* tiles, int B, int S, void* stream);
 
 #ifdef __cplusplus
 }

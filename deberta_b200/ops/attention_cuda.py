@@ -33,6 +33,7 @@ class AttnArgs(ctypes.Structure):
         ("dk", c_void_p), ("dv", c_void_p), ("ld_dk", c_ll), ("ld_dv", c_ll),
         ("d_c2p", c_void_p), ("d_p2c", c_void_p),
         ("bias", c_void_p), ("dbias", c_void_p), ("ldb", c_ll),
+        ("doc_tiles", c_void_p),
     ]
 
 # Up to this sequence length the position terms are pre-gathered into a key-indexed
@@ -141,6 +142,10 @@ class _FlashAttention(torch.autograd.Function):
             gemm(_heads_view(k2, heads), _heads_view(pos_q, heads), out=p2c.permute(1, 0, 2))
         kk = None if key_keep is None else key_keep.to(torch.uint8).contiguous()
         dd = None if doc_ids is None else doc_ids.to(torch.int32).contiguous()
+        tiles = None
+        if dd is not None:  # id range of every 128-token tile: the kernels visit only tiles that share a document
+            tiles = torch.empty((B, (S + 127) // 128, 2), dtype=torch.int32, device=q.device)
+            _lib.call("db200_attn_doc_tiles", _lib.ptr(dd), _lib.ptr(tiles), c_int(B), c_int(S), _lib.stream_ptr())
         bias = None
         ldb = (S + 127) // 128 * 128
         if span2 and S <= BIAS_MODE_MAX_SEQ:
@@ -161,14 +166,15 @@ class _FlashAttention(torch.autograd.Function):
             a.lut_c2p, a.lut_p2c = luts[0].data_ptr(), luts[1].data_ptr()
         a.key_keep = None if kk is None else kk.data_ptr()
         a.doc_ids = None if dd is None else dd.data_ptr()
+        a.doc_tiles = None if tiles is None else tiles.data_ptr()
         _lib.call("db200_attn_fwd", ctypes.byref(a), _lib.stream_ptr())
-        ctx.save_for_backward(q, k, v, out, lse, c2p, p2c, pos_k, pos_q, kk, dd, bias)
+        ctx.save_for_backward(q, k, v, out, lse, c2p, p2c, pos_k, pos_q, kk, dd, bias, tiles)
         ctx.meta = (heads, scale, luts, span2)
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        q, k, v, out, lse, c2p, p2c, pos_k, pos_q, kk, dd, bias = ctx.saved_tensors
+        q, k, v, out, lse, c2p, p2c, pos_k, pos_q, kk, dd, bias, tiles = ctx.saved_tensors
         heads, scale, luts, span2 = ctx.meta
         B, S, H = q.shape
         T = B * S
@@ -183,7 +189,8 @@ class _FlashAttention(torch.autograd.Function):
         dk, dv = dqkv[:, H : 2 * H], dqkv[:, 2 * H :]
         d_c2p = torch.zeros((T, heads, span2), dtype=torch.float32, device=dev) if c2p is not None else None
         d_p2c = torch.zeros((T, heads, span2), dtype=torch.float32, device=dev) if p2c is not None else None
-        dbias = torch.empty_like(bias) if bias is not None else None
+        # skipped tiles are never written: with document ids the bias gradient starts from zero
+        dbias = (torch.zeros_like(bias) if tiles is not None else torch.empty_like(bias)) if bias is not None else None
         a = AttnArgs()
         a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
         a.ldq, a.ldk, a.ldv = q.stride(1), k.stride(1), v.stride(1)
@@ -197,6 +204,7 @@ class _FlashAttention(torch.autograd.Function):
             a.lut_c2p, a.lut_p2c = luts[0].data_ptr(), luts[1].data_ptr()
         a.key_keep = None if kk is None else kk.data_ptr()
         a.doc_ids = None if dd is None else dd.data_ptr()
+        a.doc_tiles = None if tiles is None else tiles.data_ptr()
         a.dout, a.ld_do, a.delta = dout.data_ptr(), H, delta.data_ptr()
         a.dq_acc, a.dk, a.dv, a.ld_dk, a.ld_dv = dq_acc.data_ptr(), dk.data_ptr(), dv.data_ptr(), 3 * H, 3 * H
         a.d_c2p = None if d_c2p is None else d_c2p.data_ptr()

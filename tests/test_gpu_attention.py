@@ -90,6 +90,113 @@ def test_rope_forward_backward(S, mask):
         assert _rel_err(a.grad, b.grad) < 4e-2, name
 
 
+def _packed_doc_ids(B, S, mean_len, seed, tail_pad=0, shuffle_ids=False):
+    g = torch.Generator().manual_seed(seed)
+    doc = torch.zeros(B, S, dtype=torch.long)
+    for b in range(B):
+        pos, d = 0, 1
+        while pos < S - tail_pad:
+            n = int(torch.randint(max(1, mean_len // 2), mean_len * 2, (1,), generator=g))
+            doc[b, pos:min(S - tail_pad, pos + n)] = d
+            pos, d = pos + n, d + 1
+        if shuffle_ids:  # ids need not grow along the row: relabel the documents at random
+            perm = torch.randperm(d, generator=g) + 1
+            live = doc[b] > 0
+            doc[b, live] = perm[doc[b, live] - 1]
+    return doc.cuda()
+
+
+@pytest.mark.parametrize("S,mean_len,tail_pad,shuffle", [(1024, 60, 0, False), (1024, 200, 300, False), (768, 90, 140, True),
+                                                         (2048, 150, 0, False)])
+def test_rope_packed_documents_skip_tiles(S, mean_len, tail_pad, shuffle):
+    """Many short documents per row: most tile pairs share no document and are skipped; results must not change."""
+    B, heads = 2, 2
+    q, k, v, _, _ = _inputs(B, S, heads, 8, seed=5)
+    inv = 1.0 / (10000 ** (torch.arange(0, 64, 2, device="cuda").float() / 64))
+    ang = torch.repeat_interleave(torch.outer(torch.arange(S, device="cuda").float(), inv), 2, dim=-1)
+    cos, sin = ang.cos(), ang.sin()
+    doc = _packed_doc_ids(B, S, mean_len, seed=S + mean_len, tail_pad=tail_pad, shuffle_ids=shuffle)
+    out = rope_attention(q, k, v, cos, sin, heads=heads, rotary_dim=64, doc_ids=doc)
+    ref_in = [t.detach().float().requires_grad_(True) for t in (q, k, v)]
+    ref = rope_attention_reference(*ref_in, cos, sin, heads=heads, rotary_dim=64, doc_ids=doc)
+    _lib.check_status()
+    assert _rel_err(out, ref) < 2e-2
+    if tail_pad:
+        assert float(out[:, S - tail_pad:].abs().max()) == 0.0  # padding queries give zero rows
+    w = torch.randn_like(ref)
+    (out.float() * w).sum().backward()
+    (ref * w).sum().backward()
+    _lib.check_status()
+    for name, a, b in zip("qkv", (q, k, v), ref_in):
+        assert _rel_err(a.grad, b.grad) < 4e-2, name
+
+
+@pytest.mark.parametrize("mode,S", [("bias", 640), ("gather", 640)])
+def test_disentangled_packed_documents_skip_tiles(mode, S, monkeypatch):
+    from deberta_b200.ops import attention_cuda
+
+    monkeypatch.setattr(attention_cuda, "BIAS_MODE_MAX_SEQ", 1024 if mode == "bias" else 0)
+    B, heads, span, buckets, maxpos = 2, 2, 256, 256, 512
+    q, k, v, pk, pq = _inputs(B, S, heads, span, seed=7)
+    doc = _packed_doc_ids(B, S, 70, seed=11, tail_pad=150)
+    out = disentangled_attention(q, k, v, pk, pq, heads=heads, scale_factor=3, bucket_size=buckets, max_position=maxpos,
+                                 att_span=span, doc_ids=doc)
+    ref_in = [t.detach().float().requires_grad_(True) for t in (q, k, v, pk, pq)]
+    ref = disentangled_attention_reference(*ref_in, heads=heads, scale_factor=3,
+                                           rel_pos=relative_positions(S, S, buckets, maxpos, device="cuda"),
+                                           att_span=span, doc_ids=doc)
+    _lib.check_status()
+    assert _rel_err(out, ref) < 2e-2
+    w = torch.randn_like(ref)
+    (out.float() * w).sum().backward()
+    (ref * w).sum().backward()
+    _lib.check_status()
+    for name, a, b in zip("q k v pos_k pos_q".split(), (q, k, v, pk, pq), ref_in):
+        assert _rel_err(a.grad, b.grad) < 4e-2, name
+
+
+def test_document_tile_table_matches_pytorch():
+    import ctypes
+
+    B, S = 3, 1000
+    doc = _packed_doc_ids(B, S, 50, seed=2, tail_pad=260, shuffle_ids=True).to(torch.int32)
+    nt = (S + 127) // 128
+    tiles = torch.empty(B, nt, 2, dtype=torch.int32, device="cuda")
+    _lib.call("db200_attn_doc_tiles", _lib.ptr(doc), _lib.ptr(tiles), ctypes.c_int(B), ctypes.c_int(S), _lib.stream_ptr())
+    padded = torch.zeros(B, nt * 128, dtype=torch.int32, device="cuda")
+    padded[:, :S] = doc
+    padded = padded.view(B, nt, 128)
+    lo = torch.where(padded > 0, padded, torch.full_like(padded, 2**31 - 1)).amin(-1)
+    hi = torch.where(padded > 0, padded, torch.full_like(padded, -1)).amax(-1)
+    assert torch.equal(tiles[..., 0], lo) and torch.equal(tiles[..., 1], hi)
+    assert int(tiles[0, -1, 1]) == -1  # the last tile of every row is padding only
+
+
+def test_rope_packed_documents_speed_report():
+    B, S, heads = 4, 4096, 12
+    q, k, v, _, _ = _inputs(B, S, heads, 8, seed=9, scale=0.3)
+    inv = 1.0 / (10000 ** (torch.arange(0, 64, 2, device="cuda").float() / 64))
+    ang = torch.repeat_interleave(torch.outer(torch.arange(S, device="cuda").float(), inv), 2, dim=-1)
+    cos, sin = ang.cos(), ang.sin()
+    one = torch.ones(B, S, dtype=torch.long, device="cuda")
+    packed = _packed_doc_ids(B, S, 300, seed=4)
+    for label, doc in (("one document per row", one), ("packed, ~300-token documents", packed)):
+        fn = lambda: rope_attention(q, k, v, cos, sin, heads=heads, rotary_dim=64, doc_ids=doc)  # noqa: E731,B023
+        g = torch.randn_like(fn())
+        for name, f in (("fwd", fn), ("fwd+bwd", lambda: fn().backward(g))):  # noqa: B023
+            for _ in range(2):
+                f()
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(5):
+                f()
+            e.record()
+            torch.cuda.synchronize()
+            print(f"\n[rope attention B={B} S={S} h={heads}, {label}] {name}: {s.elapsed_time(e) / 5 * 1e3:.0f} us")
+    _lib.check_status()
+
+
 def test_attention_speed_report():
     B, S, heads, span = 32, 512, 12, 256
     q, k, v, pk, pq = _inputs(B, S, heads, span, scale=0.3)
