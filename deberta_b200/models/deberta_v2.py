@@ -436,6 +436,9 @@ class DebertaV2PreTrainedModel(PreTrainedModel):
             init_embedding_(module, std)
         elif isinstance(module, nn.LayerNorm):
             init_norm_(module.weight, module.bias)
+        elif isinstance(module, DebertaV2Embeddings):
+            # non-persistent buffer: absent from checkpoints, so it is rewritten after a load from the meta device
+            module.position_ids.data.copy_(torch.arange(module.position_ids.shape[-1]).unsqueeze(0))
 
     def _set_gradient_checkpointing(self, module: nn.Module = None, value: bool = False, **_: Any) -> None:
         for m in self.modules():

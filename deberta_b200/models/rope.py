@@ -22,11 +22,22 @@ class RotaryEmbedding(nn.Module):
         if self.dim % 2:
             raise ValueError(f"Rotary dim must be even, got {self.dim}")
         self.base = float(base)
-        denom = float(full_dim if full_dim is not None else self.dim)
-        inv_freq = 1.0 / (self.base ** (torch.arange(0, self.dim, 2).float() / denom))
-        self.register_buffer("inv_freq", inv_freq, persistent=False)
+        self.denom = float(full_dim if full_dim is not None else self.dim)
+        self.register_buffer("inv_freq", self._inv_freq(), persistent=False)
         self._cache: tuple[torch.Tensor, torch.Tensor] | None = None
         self._key: tuple | None = None
+
+    def _inv_freq(self) -> torch.Tensor:
+        return 1.0 / (self.base ** (torch.arange(0, self.dim, 2).float() / self.denom))
+
+    def reset_buffers(self) -> None:
+        """Recompute the frequency table in place and drop the cos/sin cache.
+
+        The table is a non-persistent buffer: no checkpoint stores it, so a model that was
+        materialised from the meta device (``from_pretrained``) has to write it again.
+        """
+        self.inv_freq.data.copy_(self._inv_freq().to(self.inv_freq.device))
+        self._cache, self._key = None, None
 
     def _build(self, seq_len: int, device, dtype):
         t = torch.arange(seq_len, device=device, dtype=self.inv_freq.dtype)

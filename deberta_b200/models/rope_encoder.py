@@ -175,6 +175,7 @@ class DebertaRoPEMLP(nn.Module):
 class _KEELAlpha(nn.Module):
     def __init__(self, init: float, learnable: bool) -> None:
         super().__init__()
+        self.init_value = float(init)
         if learnable:
             self.alpha = nn.Parameter(torch.tensor(float(init), dtype=torch.float32))
         else:
@@ -249,6 +250,13 @@ class DebertaRoPEPreTrainedModel(PreTrainedModel):
             init_embedding_(module, std)
         elif isinstance(module, RMSNorm):
             init_norm_(module.weight)
+        elif isinstance(module, RotaryEmbedding):
+            module.reset_buffers()
+        elif isinstance(module, _KEELAlpha):
+            # a fixed alpha is a non-persistent buffer: no checkpoint carries it, and a model materialised from the
+            # meta device holds arbitrary memory there until it is written again
+            if not module.learnable or not getattr(module.alpha, "_is_hf_initialized", False):
+                module.alpha.data.fill_(module.init_value)
 
     def _set_gradient_checkpointing(self, module: nn.Module = None, value: bool = False, **_: Any) -> None:
         for m in self.modules():
