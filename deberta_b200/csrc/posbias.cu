@@ -11,6 +11,7 @@
 // bias columns.
 #include "kernels.h"
 
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -262,17 +263,17 @@ posbias_rowscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __res
 // keeps the 32 lanes on different banks.
 constexpr int kColKeys = 16;
 
-template <int PER>  // PER > 0: ceil(S/32) known at compile time (the run of a lane lives in registers); 0: any S
+template <int PER, int KEYS>  // PER > 0: ceil(S/32) known at compile time (the run of a lane lives in registers); 0: any S
 __global__ void __launch_bounds__(256)
 posbias_colscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __restrict__ ranges,
                        __nv_bfloat16* __restrict__ dtab, int S, int ldb, int heads, int span2, int stride, int per, int sh) {
   extern __shared__ float sm[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  int* rng = reinterpret_cast<int*>(sm + kColKeys * stride);
+  int* rng = reinterpret_cast<int*>(sm + KEYS * stride);
   for (int i = tid; i < 2 * span2; i += 256) rng[i] = ranges[i];
-  const int k0 = blockIdx.x * kColKeys, h = blockIdx.y, b = blockIdx.z;
+  const int k0 = blockIdx.x * KEYS, h = blockIdx.y, b = blockIdx.z;
   const __nv_bfloat16* src = dbias + (static_cast<long long>(b) * heads + h) * S * ldb + k0;
-  constexpr int kGroups = kColKeys / 8, kRowsPerPass = 256 / kGroups;
+  constexpr int kGroups = KEYS / 8, kRowsPerPass = 256 / kGroups;
   const int cg = tid % kGroups;  // 8-key group of this thread
   for (int qb = tid / kGroups; qb < S; qb += 4 * kRowsPerPass) {  // four independent 16-byte loads in flight per thread
     uint4 u[4];
@@ -292,10 +293,10 @@ posbias_colscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __res
       }
     }
   }
-  if (tid < kColKeys) sm[tid * stride] = 0.f;
+  if (tid < KEYS) sm[tid * stride] = 0.f;
   __syncthreads();
   const long long row_stride = static_cast<long long>(heads) * span2;
-  for (int kk = warp * (kColKeys / 8); kk < (warp + 1) * (kColKeys / 8); ++kk) {
+  for (int kk = warp * (KEYS / 8); kk < (warp + 1) * (KEYS / 8); ++kk) {
     const int k = k0 + kk;
     if (k >= S) break;  // warp-uniform
     float* T = sm + kk * stride;  // T[phys(i)] = sum of the first i queries
@@ -422,13 +423,19 @@ extern "C" int db200_posbias_scatter_ranges(const void* dbias, const void* range
     stride |= 1;  // odd: the 32 key rows start on different banks
     const int smem = kColKeys * stride * 4 + 2 * span2 * 4;
     if (smem > kMaxSmem) return -12;
-    auto kern = posbias_colscan_kernel<0>;
-    if (per == 16) kern = posbias_colscan_kernel<16>;
-    else if (per == 8) kern = posbias_colscan_kernel<8>;
-    else if (per == 32) kern = posbias_colscan_kernel<32>;
-    else if (per == 4) kern = posbias_colscan_kernel<4>;
+    static const int exp_keys = getenv("DB200_COLKEYS") ? atoi(getenv("DB200_COLKEYS")) : 16;
+    auto kern = posbias_colscan_kernel<0, 16>;
+    int keys = 16;
+    if (per == 16 && exp_keys == 32 && (ldb % 32) == 0) { kern = posbias_colscan_kernel<16, 32>; keys = 32; }
+    else if (per == 16 && exp_keys == 64 && (ldb % 64) == 0) { kern = posbias_colscan_kernel<16, 64>; keys = 64; }
+    else if (per == 16) kern = posbias_colscan_kernel<16, 16>;
+    else if (per == 8) kern = posbias_colscan_kernel<8, 16>;
+    else if (per == 32) kern = posbias_colscan_kernel<32, 16>;
+    else if (per == 4) kern = posbias_colscan_kernel<4, 16>;
+    const int smem_k = keys * stride * 4 + 2 * span2 * 4;
+    if (smem_k > kMaxSmem) return -12;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) != cudaSuccess) return -3;
-    kern<<<dim3((S + kColKeys - 1) / kColKeys, heads, B), 256, smem, st>>>(db, rg, dt, S, ldb, heads, span2, stride, per, sh);
+    kern<<<dim3((S + keys - 1) / keys, heads, B), 256, smem_k, st>>>(db, rg, dt, S, ldb, heads, span2, stride, per, sh);
   } else {
     const int smem = 8 * ((S + 1) + ((S + 1) >> 3) + 1) * 4 + 2 * span2 * 4;
     if (smem > kMaxSmem) return -12;
