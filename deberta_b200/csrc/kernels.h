@@ -153,8 +153,9 @@ int db200_posbias_build(const void* c2p, const void* p2c, const void* lut_c2p, c
                         int S, int ldb, int heads, int span2, void* stream);
 int db200_posbias_scatter(const void* dbias, const void* lut, void* dtab, int rows_are_keys, int B, int S, int ldb,
                           int heads, int span2, void* stream);
-// The same reduction for bucket maps in which every bucket collects one contiguous run of offsets q-k
-// (ranges: int[2*span2] = lo[], hi[]; lo > hi for unused buckets): prefix sums instead of atomics.
+// The same reduction for bucket maps that are monotone in q-k, by differences of prefix sums instead of atomics.
+// ranges: int[span2 + 2] = {sign, E_0 .. E_span2}: with sign = +1 bucket j collects E_j <= q-k < E_{j+1}, with
+// sign = -1 it collects E_{j+1} <= q-k < E_j; unused buckets have E_j = E_{j+1}. span2 must be a multiple of 8.
 int db200_posbias_scatter_ranges(const void* dbias, const void* ranges, void* dtab, int rows_are_keys, int B, int S,
                                  int ldb, int heads, int span2, void* stream);
 

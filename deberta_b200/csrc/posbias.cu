@@ -11,7 +11,6 @@
 // bias columns.
 #include "kernels.h"
 
-#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -192,7 +191,24 @@ posbias_scatter_kernel(const __nv_bfloat16* __restrict__ dbias, const unsigned s
 // log-bucket maps, which are monotone in q-k), the scatter is a difference of prefix sums along the
 // row (keys) or the column (queries) of dbias: no atomics, every element read once.
 //
-// ranges: int[2 * span2] = lo[0..span2), hi[0..span2) ; lo > hi marks an unused bucket.
+// edges: int[span2 + 2] = {sign, E_0 .. E_span2}. With sign = +1 bucket j collects the offsets E_j <= q-k < E_{j+1},
+// with sign = -1 the offsets E_{j+1} <= q-k < E_j (the bucket index falls as q-k grows); an unused bucket has
+// E_j = E_{j+1}. Every output is then the difference of the prefix sums at two neighbouring edges, so a thread that
+// writes eight consecutive buckets reads nine prefix values and stores 16 bytes.
+
+// eight outputs sign * (g[t+1] - g[t]) (or the reverse for row scans) as one 16-byte store
+__device__ __forceinline__ void store_edge_diffs(__nv_bfloat16* dst, const float (&g)[9], float sign) {
+  uint4 u;
+  __nv_bfloat162 w[4];
+#pragma unroll
+  for (int t = 0; t < 4; ++t)
+    w[t] = __floats2bfloat162_rn(sign * (g[2 * t + 1] - g[2 * t]), sign * (g[2 * t + 2] - g[2 * t + 1]));
+  u.x = *reinterpret_cast<uint32_t*>(&w[0]);
+  u.y = *reinterpret_cast<uint32_t*>(&w[1]);
+  u.z = *reinterpret_cast<uint32_t*>(&w[2]);
+  u.w = *reinterpret_cast<uint32_t*>(&w[3]);
+  *reinterpret_cast<uint4*>(dst) = u;
+}
 
 __device__ __forceinline__ float warp_inclusive_scan(float x, int lane) {
 #pragma unroll
@@ -211,9 +227,10 @@ posbias_rowscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __res
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stride = (S + 1) + ((S + 1) >> 3) + 1;
   // P[i] = sum of the first i keys, kept at word i + i/8: the lanes of the scan write 8 words apart
-  float* P = sm + warp * stride;
-  int* rng = reinterpret_cast<int*>(sm + 8 * stride);  // lo[], hi[]
-  for (int i = threadIdx.x; i < 2 * span2; i += 256) rng[i] = ranges[i];
+  int* edge = reinterpret_cast<int*>(sm);  // E_0 .. E_span2, 16-byte aligned for vector loads
+  float* P = sm + ((span2 + 4) & ~3) + warp * stride;
+  for (int i = threadIdx.x; i <= span2; i += 256) edge[i] = ranges[i + 1];
+  const float sign = ranges[0] >= 0 ? 1.f : -1.f;
   __syncthreads();
   const int q = blockIdx.x * 8 + warp, h = blockIdx.y, b = blockIdx.z;
   if (q >= S) return;
@@ -245,15 +262,17 @@ posbias_rowscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __res
   }
   __syncwarp();
   __nv_bfloat16* dst = dtab + (static_cast<long long>(b) * S + q) * (static_cast<long long>(heads) * span2) + h * span2;
-  for (int j = lane * 2; j < span2; j += 64) {
-    float out[2];
+  // keys with offset q-k >= E are the first q-E+1 keys: g = P[clamp(q - E + 1)], and bucket j is sign * (g_j - g_{j+1})
+  for (int j = lane * 8; j < span2; j += 256) {
+    const int4 e0 = *reinterpret_cast<const int4*>(edge + j), e1 = *reinterpret_cast<const int4*>(edge + j + 4);
+    const int e[9] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w, edge[j + 8]};
+    float g[9];
 #pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      const int lo = rng[j + t], hi = rng[span2 + j + t];
-      const int a = max(0, q - hi), z = min(S - 1, q - lo);  // keys k with lo <= q-k <= hi
-      out[t] = (lo <= hi && a <= z) ? P[(z + 1) + ((z + 1) >> 3)] - P[a + (a >> 3)] : 0.f;
+    for (int t = 0; t < 9; ++t) {
+      const int i = min(max(q + 1 - e[t], 0), S);
+      g[t] = P[i + (i >> 3)];
     }
-    *reinterpret_cast<__nv_bfloat162*>(dst + j) = __floats2bfloat162_rn(out[0], out[1]);
+    store_edge_diffs(dst + j, g, -sign);
   }
 }
 
@@ -269,8 +288,10 @@ posbias_colscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __res
                        __nv_bfloat16* __restrict__ dtab, int S, int ldb, int heads, int span2, int stride, int per, int sh) {
   extern __shared__ float sm[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  int* rng = reinterpret_cast<int*>(sm + KEYS * stride);
-  for (int i = tid; i < 2 * span2; i += 256) rng[i] = ranges[i];
+  int* edge = reinterpret_cast<int*>(sm);  // E_0 .. E_span2, 16-byte aligned for vector loads
+  float* tb = sm + ((span2 + 4) & ~3);     // T[KEYS][stride]
+  for (int i = tid; i <= span2; i += 256) edge[i] = ranges[i + 1];
+  const float sign = ranges[0] >= 0 ? 1.f : -1.f;
   const int k0 = blockIdx.x * KEYS, h = blockIdx.y, b = blockIdx.z;
   const __nv_bfloat16* src = dbias + (static_cast<long long>(b) * heads + h) * S * ldb + k0;
   constexpr int kGroups = KEYS / 8, kRowsPerPass = 256 / kGroups;
@@ -289,17 +310,17 @@ posbias_colscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __res
         const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&u[t]);
         const int w = (q + 1) + ((q + 1) >> sh);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) sm[(cg * 8 + j) * stride + w] = __bfloat162float(e[j]);
+        for (int j = 0; j < 8; ++j) tb[(cg * 8 + j) * stride + w] = __bfloat162float(e[j]);
       }
     }
   }
-  if (tid < KEYS) sm[tid * stride] = 0.f;
+  if (tid < KEYS) tb[tid * stride] = 0.f;
   __syncthreads();
   const long long row_stride = static_cast<long long>(heads) * span2;
   for (int kk = warp * (KEYS / 8); kk < (warp + 1) * (KEYS / 8); ++kk) {
     const int k = k0 + kk;
     if (k >= S) break;  // warp-uniform
-    float* T = sm + kk * stride;  // T[phys(i)] = sum of the first i queries
+    float* T = tb + kk * stride;  // T[phys(i)] = sum of the first i queries
     // lane owns prefixes i = lane*per + 1 .. lane*per + per
     const int first = lane * per + 1;
     if (PER > 0) {
@@ -335,15 +356,17 @@ posbias_colscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __res
     }
     __syncwarp();
     __nv_bfloat16* dst = dtab + (static_cast<long long>(b) * S + k) * row_stride + h * span2;
-    for (int j = lane * 2; j < span2; j += 64) {
-      float out[2];
+    // queries with offset q-k < E are the first k+E queries: g = T[clamp(k + E)], and bucket j is sign * (g_{j+1} - g_j)
+    for (int j = lane * 8; j < span2; j += 256) {
+      const int4 e0 = *reinterpret_cast<const int4*>(edge + j), e1 = *reinterpret_cast<const int4*>(edge + j + 4);
+      const int e[9] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w, edge[j + 8]};
+      float g[9];
 #pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        const int lo = rng[j + t], hi = rng[span2 + j + t];
-        const int a = max(0, k + lo), z = min(S - 1, k + hi) + 1;  // queries q with lo <= q-k <= hi
-        out[t] = (lo <= hi && a < z) ? T[z + (z >> sh)] - T[a + (a >> sh)] : 0.f;
+      for (int t = 0; t < 9; ++t) {
+        const int i = min(max(k + e[t], 0), S);
+        g[t] = T[i + (i >> sh)];
       }
-      *reinterpret_cast<__nv_bfloat162*>(dst + j) = __floats2bfloat162_rn(out[0], out[1]);
+      store_edge_diffs(dst + j, g, sign);
     }
   }
 }
@@ -408,7 +431,7 @@ extern "C" int db200_posbias_scatter(const void* dbias, const void* lut, void* d
 extern "C" int db200_posbias_scatter_ranges(const void* dbias, const void* ranges, void* dtab, int rows_are_keys, int B,
                                             int S, int ldb, int heads, int span2, void* stream) {
   if (B <= 0 || S <= 0) return 0;
-  if ((span2 % 2) || (ldb % 8) || ldb < S) return -12;
+  if ((span2 % 8) || (ldb % 8) || ldb < S) return -12;  // eight buckets per 16-byte store
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   auto db = static_cast<const __nv_bfloat16*>(dbias);
   auto rg = static_cast<const int*>(ranges);
@@ -423,19 +446,14 @@ extern "C" int db200_posbias_scatter_ranges(const void* dbias, const void* range
     stride |= 1;  // odd: the 32 key rows start on different banks
     const int smem = kColKeys * stride * 4 + 2 * span2 * 4;
     if (smem > kMaxSmem) return -12;
-    static const int exp_keys = getenv("DB200_COLKEYS") ? atoi(getenv("DB200_COLKEYS")) : 16;
-    auto kern = posbias_colscan_kernel<0, 16>;
-    int keys = 16;
-    if (per == 16 && exp_keys == 32 && (ldb % 32) == 0) { kern = posbias_colscan_kernel<16, 32>; keys = 32; }
-    else if (per == 16 && exp_keys == 64 && (ldb % 64) == 0) { kern = posbias_colscan_kernel<16, 64>; keys = 64; }
-    else if (per == 16) kern = posbias_colscan_kernel<16, 16>;
-    else if (per == 8) kern = posbias_colscan_kernel<8, 16>;
-    else if (per == 32) kern = posbias_colscan_kernel<32, 16>;
-    else if (per == 4) kern = posbias_colscan_kernel<4, 16>;
-    const int smem_k = keys * stride * 4 + 2 * span2 * 4;
-    if (smem_k > kMaxSmem) return -12;
+    // 16 keys per block measured fastest (228 us against 253 / 492 us for 32 / 64 keys at B=32, S=512, 12 heads)
+    auto kern = posbias_colscan_kernel<0, kColKeys>;
+    if (per == 16) kern = posbias_colscan_kernel<16, kColKeys>;
+    else if (per == 8) kern = posbias_colscan_kernel<8, kColKeys>;
+    else if (per == 32) kern = posbias_colscan_kernel<32, kColKeys>;
+    else if (per == 4) kern = posbias_colscan_kernel<4, kColKeys>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) != cudaSuccess) return -3;
-    kern<<<dim3((S + keys - 1) / keys, heads, B), 256, smem_k, st>>>(db, rg, dt, S, ldb, heads, span2, stride, per, sh);
+    kern<<<dim3((S + kColKeys - 1) / kColKeys, heads, B), 256, smem, st>>>(db, rg, dt, S, ldb, heads, span2, stride, per, sh);
   } else {
     const int smem = 8 * ((S + 1) + ((S + 1) >> 3) + 1) * 4 + 2 * span2 * 4;
     if (smem > kMaxSmem) return -12;

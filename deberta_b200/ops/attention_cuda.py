@@ -61,22 +61,37 @@ _RANGE_CACHE: dict[tuple, tuple] = {}
 
 
 def _bucket_ranges(lut: torch.Tensor, S: int, span2: int) -> torch.Tensor | None:
-    """Per bucket the run ``lo <= q-k <= hi`` of offsets it collects (int32 ``[lo..., hi...]`` on the LUT's device).
+    """Bucket edges for the prefix-sum scatter: int32 ``[sign, E_0 .. E_span2]`` on the LUT's device.
 
-    ``None`` when some bucket's offsets are not one contiguous run (the prefix-sum scatter then does not apply).
+    With ``sign = +1`` bucket ``j`` collects the offsets ``E_j <= q-k < E_{j+1}``; with ``sign = -1`` (the bucket index
+    falls as ``q-k`` grows) it collects ``E_{j+1} <= q-k < E_j``; unused buckets have ``E_j = E_{j+1}``.
+    ``None`` when the map is not monotone in ``q-k`` (the kernels then fall back to the atomic scatter).
     """
     idx = lut.to(torch.int64).cpu()
     delta = torch.arange(-(S - 1), S, dtype=torch.int64)
     big = 1 << 20
-    lo = torch.full((span2,), big, dtype=torch.int64).scatter_reduce_(0, idx, delta, "amin")
-    hi = torch.full((span2,), -big, dtype=torch.int64).scatter_reduce_(0, idx, delta, "amax")
-    cnt = torch.bincount(idx, minlength=span2)
-    used = cnt > 0
-    if not bool(((hi - lo + 1)[used] == cnt[used]).all()):
+    lo = torch.full((span2,), big, dtype=torch.int64).scatter_reduce_(0, idx, delta, "amin").tolist()
+    hi = torch.full((span2,), -big, dtype=torch.int64).scatter_reduce_(0, idx, delta, "amax").tolist()
+    cnt = torch.bincount(idx, minlength=span2).tolist()
+    used = [j for j in range(span2) if cnt[j] > 0]
+    if not used or span2 % 8 or any(hi[j] - lo[j] + 1 != cnt[j] for j in used):
         return None
-    lo = torch.where(used, lo, torch.ones_like(lo))
-    hi = torch.where(used, hi, torch.zeros_like(hi))
-    return torch.cat([lo, hi]).to(torch.int32).to(lut.device)
+    sign = 1 if (len(used) < 2 or lo[used[1]] > lo[used[0]]) else -1
+    start = (lambda j: lo[j]) if sign > 0 else (lambda j: hi[j] + 1)
+    end = (lambda j: hi[j] + 1) if sign > 0 else (lambda j: lo[j])
+    edges = [0] * (span2 + 1)
+    last = used[-1]
+    for j in range(last + 1, span2 + 1):
+        edges[j] = end(last)
+    live = set(used)
+    for j in range(last, -1, -1):
+        if j in live:
+            if end(j) != edges[j + 1]:
+                return None  # a gap or an overlap between neighbouring buckets
+            edges[j] = start(j)
+        else:
+            edges[j] = edges[j + 1]
+    return torch.tensor([sign, *edges], dtype=torch.int32).to(lut.device)
 
 
 def _ranges(luts: tuple[torch.Tensor, torch.Tensor], S: int, span2: int) -> tuple:
