@@ -121,14 +121,18 @@ __device__ __forceinline__ float dgelu_erf(float x) {
 
 // MODE selects the epilogue at compile time (one lean code path per instantiation):
 // 0 bf16 output (+bias, +residual), 1 GELU (two outputs), 2 GELU derivative, 3 fp32 output (store / accumulate /
-// split-K), 4 cross-entropy forward, 5 cross-entropy backward.
+// split-K), 4 cross-entropy forward, 5 cross-entropy backward, 6 GELU with its derivative as the first output,
+// 7 product with a stored operand (the backward partner of 6: no transcendental in the epilogue).
 template <int BN, bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_out2,
             const DevParams p) {
   using L = SmemLayout<BN>;
-  constexpr int kEpi = MODE == 1 ? EPI_GELU : MODE == 2 ? EPI_DGELU : MODE == 4 ? EPI_CE_FWD : MODE == 5 ? EPI_CE_BWD : EPI_NONE;
+  constexpr int kEpi = MODE == 1 ? EPI_GELU : MODE == 2 ? EPI_DGELU : MODE == 4 ? EPI_CE_FWD : MODE == 5 ? EPI_CE_BWD
+                       : MODE == 6 ? EPI_GELU_GRAD : MODE == 7 ? EPI_MUL : EPI_NONE;
+  constexpr bool kTwoOut = kEpi == EPI_GELU || kEpi == EPI_GELU_GRAD;  // second output: gelu of the pre-activation
+  constexpr bool kAuxMul = kEpi == EPI_DGELU || kEpi == EPI_MUL;       // accumulator times a function of `aux`
   constexpr bool kOutF32 = MODE == 3;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -423,7 +427,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       // GELU-derivative operand of both chunks of the group: one round trip instead of two
       uint32_t auxp[2][16];
       bool auxv[2] = {false, false};
-      if (kEpi == EPI_DGELU) {
+      if (kAuxMul) {
 #pragma unroll
         for (int csub = 0; csub < 2; ++csub) {
           const int nc = n0 + (cp * 2 + csub) * 32;
@@ -511,17 +515,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               if (nc + j < p.N) v[j] += __bfloat162float(rp[j]);
           }
         }
-        if (kEpi == EPI_DGELU && row_ok) {
+        if (kAuxMul && row_ok) {
           if (aux_vec) {
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
-              v[e * 2] *= dgelu_erf(bf16_lo(auxw[e]));
-              v[e * 2 + 1] *= dgelu_erf(bf16_hi(auxw[e]));
+              v[e * 2] *= kEpi == EPI_MUL ? bf16_lo(auxw[e]) : dgelu_erf(bf16_lo(auxw[e]));
+              v[e * 2 + 1] *= kEpi == EPI_MUL ? bf16_hi(auxw[e]) : dgelu_erf(bf16_hi(auxw[e]));
             }
           } else {
             const __nv_bfloat16* ap = p.aux + z * p.bs_aux + static_cast<long long>(row) * p.ldaux + nc;
             for (int j = 0; j < 32; ++j)
-              if (nc + j < p.N) v[j] *= dgelu_erf(__bfloat162float(ap[j]));
+              if (nc + j < p.N) v[j] *= kEpi == EPI_MUL ? __bfloat162float(ap[j]) : dgelu_erf(__bfloat162float(ap[j]));
           }
         }
         if (p.tma_out) {
@@ -531,9 +535,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           uint32_t wds[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) wds[i] = pack_bf16(v[2 * i], v[2 * i + 1]);
-          if (kEpi == EPI_GELU) {
-            // two outputs, one staging tile: the pre-activation leaves with direct 32-byte row stores, gelu(z) through
+          if (kTwoOut) {
+            // two outputs, one staging tile: the first leaves with direct 32-byte row stores, gelu(z) through
             // the staging tile (waiting for a bulk store to release the tile twice per group would stall the warp)
+            uint32_t act[16];
+            if (kEpi == EPI_GELU_GRAD) {
+              // first output = gelu'(z), second = gelu(z), both of the bf16-rounded pre-activation, from one cdf/pdf pair
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const float z0 = bf16_lo(wds[i]), z1 = bf16_hi(wds[i]);
+                float c0, d0, c1, d1;
+                normal_cdf_pdf(z0, c0, d0);
+                normal_cdf_pdf(z1, c1, d1);
+                act[i] = pack_bf16(z0 * c0, z1 * c1);
+                wds[i] = pack_bf16(fmaf(z0, d0, c0), fmaf(z1, d1, c1));
+                v[2 * i] = fmaf(z0, d0, c0);  // the scalar tail below stores v
+                v[2 * i + 1] = fmaf(z1, d1, c1);
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) act[i] = pack_bf16(gelu_erf(bf16_lo(wds[i])), gelu_erf(bf16_hi(wds[i])));
+            }
             if (row_ok && full) {
               __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + z * p.bs_out + static_cast<long long>(row) * p.ldo + nc;
               store_words16(o, wds);
@@ -543,26 +565,36 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 if (nc + j < p.N) o[j] = __float2bfloat16(v[j]);
             }
 #pragma unroll
-            for (int i = 0; i < 16; ++i) wds[i] = pack_bf16(gelu_erf(bf16_lo(wds[i])), gelu_erf(bf16_hi(wds[i])));
+            for (int i = 0; i < 16; ++i) wds[i] = act[i];
           }
           if (sub == 0) stage_acquire();
           stage_words(wds, sub);
-          if (last_of_group) stage_flush(kEpi == EPI_GELU ? &tmap_out2 : &tmap_out, nc - sub * 32, m0 + quad * 32, z);
+          if (last_of_group) stage_flush(kTwoOut ? &tmap_out2 : &tmap_out, nc - sub * 32, m0 + quad * 32, z);
           continue;
         }
         __nv_bfloat16* o =
             reinterpret_cast<__nv_bfloat16*>(p.out) + z * p.bs_out + static_cast<long long>(row) * p.ldo + nc;
+        float act2[kTwoOut ? 32 : 1];
+        if (kTwoOut) {  // gelu (and for EPI_GELU_GRAD the derivative, which replaces the first output) of the rounded value
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float zr = __bfloat162float(__float2bfloat16(v[j]));
+            float c, d;
+            normal_cdf_pdf(zr, c, d);
+            act2[j] = zr * c;
+            if (kEpi == EPI_GELU_GRAD) v[j] = fmaf(zr, d, c);
+          }
+        }
         if (vec) {
           store_bf16x32(o, v);
         } else {
           for (int j = 0; j < 32; ++j)
             if (nc + j < p.N) o[j] = __float2bfloat16(v[j]);
         }
-        if (kEpi == EPI_GELU) {
-          // second output: GELU of the (bf16-rounded) pre-activation that was just stored
+        if (kTwoOut) {
           __nv_bfloat16* o2 = p.out2 + z * p.bs_out2 + static_cast<long long>(row) * p.ldo2 + nc;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = gelu_erf(__bfloat162float(__float2bfloat16(v[j])));
+          for (int j = 0; j < 32; ++j) v[j] = act2[j];
           if (full && (p.ldo2 % 8 == 0)) {
             store_bf16x32(o2, v);
           } else {
@@ -744,8 +776,9 @@ extern "C" int db200_gemm_bf16(const GemmArgs* a, void* stream_) {
   p.gscale_ptr = a->gscale_ptr;
   if ((p.epi == EPI_CE_FWD) && (!p.labels || !p.ce_part || !p.label_logit || a->batch != 1)) return -11;
   if ((p.epi == EPI_CE_BWD) && (!p.labels || !p.row_lse || p.out_f32 || a->batch != 1)) return -11;
-  if (p.epi == EPI_GELU && (p.out_f32 || !p.out2)) return -11;
-  if (p.epi == EPI_DGELU && (p.out_f32 || !p.aux)) return -11;
+  const bool two_out = p.epi == EPI_GELU || p.epi == EPI_GELU_GRAD;
+  if (two_out && (p.out_f32 || !p.out2)) return -11;
+  if ((p.epi == EPI_DGELU || p.epi == EPI_MUL) && (p.out_f32 || !p.aux)) return -11;
 
   const int tiles = p.tiles_m * p.tiles_n * p.batch;
   int splits = 1;
@@ -788,14 +821,15 @@ extern "C" int db200_gemm_bf16(const GemmArgs* a, void* stream_) {
   };
   p.tma_out = 0;
   if (!p.out_f32 && splits == 1 && p.epi != EPI_CE_FWD && p.epi != EPI_CE_BWD && tma_ok(a->out, a->ldo, a->bs_out) &&
-      (p.epi != EPI_GELU || tma_ok(a->out2, a->ldo2, a->bs_out2))) {
+      (!two_out || tma_ok(a->out2, a->ldo2, a->bs_out2))) {
     if (db200_make_tmap_bf16(&to, a->out, a->N, a->M, a->batch, a->ldo, a->bs_out, 32) == 0 &&
-        (p.epi != EPI_GELU || db200_make_tmap_bf16(&to2, a->out2, a->N, a->M, a->batch, a->ldo2, a->bs_out2, 32) == 0))
+        (!two_out || db200_make_tmap_bf16(&to2, a->out2, a->N, a->M, a->batch, a->ldo2, a->bs_out2, 32) == 0))
       p.tma_out = 1;
   }
 
   const int grid = min(tiles * splits, num_sms());
-  const int mode = p.out_f32 ? 3 : p.epi == EPI_GELU ? 1 : p.epi == EPI_DGELU ? 2 : p.epi == EPI_CE_FWD ? 4 : p.epi == EPI_CE_BWD ? 5 : 0;
+  const int mode = p.out_f32 ? 3 : p.epi == EPI_GELU ? 1 : p.epi == EPI_DGELU ? 2 : p.epi == EPI_CE_FWD ? 4
+                   : p.epi == EPI_CE_BWD ? 5 : p.epi == EPI_GELU_GRAD ? 6 : p.epi == EPI_MUL ? 7 : 0;
 #define DISPATCH_MODE(BN_, AM_, BM_)                                                         \
   switch (mode) {                                                                            \
     case 0: return launch<BN_, AM_, BM_, 0>(ta, tb, to, to2, p, grid, stream);               \
@@ -803,7 +837,9 @@ extern "C" int db200_gemm_bf16(const GemmArgs* a, void* stream_) {
     case 2: return launch<BN_, AM_, BM_, 2>(ta, tb, to, to2, p, grid, stream);               \
     case 3: return launch<BN_, AM_, BM_, 3>(ta, tb, to, to2, p, grid, stream);               \
     case 4: return launch<BN_, AM_, BM_, 4>(ta, tb, to, to2, p, grid, stream);               \
-    default: return launch<BN_, AM_, BM_, 5>(ta, tb, to, to2, p, grid, stream);              \
+    case 5: return launch<BN_, AM_, BM_, 5>(ta, tb, to, to2, p, grid, stream);               \
+    case 6: return launch<BN_, AM_, BM_, 6>(ta, tb, to, to2, p, grid, stream);               \
+    default: return launch<BN_, AM_, BM_, 7>(ta, tb, to, to2, p, grid, stream);              \
   }
 #define DISPATCH(BN_, AM_, BM_) DISPATCH_MODE(BN_, AM_, BM_)
   if (BN == 256) {

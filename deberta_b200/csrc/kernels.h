@@ -13,16 +13,18 @@ int* db200_status_ptr(void);          // device address of the status word (lazi
 int db200_status_read_and_clear(void);  // synchronises the device; 0 = no error recorded
 
 // ----- GEMM ---------------------------------------------------------------------------
-enum { EPI_NONE = 0, EPI_GELU = 1, EPI_DGELU = 2, EPI_CE_FWD = 3, EPI_CE_BWD = 4 };
+enum { EPI_NONE = 0, EPI_GELU = 1, EPI_DGELU = 2, EPI_CE_FWD = 3, EPI_CE_BWD = 4,
+       EPI_GELU_GRAD = 5,  // out = gelu'(z), out2 = gelu(z): the backward pass then needs no transcendental
+       EPI_MUL = 6 };      // out = acc * aux (aux = the gelu'(z) written by EPI_GELU_GRAD)
 
 typedef struct GemmArgs {
   const void* A;     // bf16
   const void* B;     // bf16
   void* out;         // bf16 or fp32 (out_f32)
-  void* out2;        // bf16, EPI_GELU: gelu(out)
+  void* out2;        // bf16, EPI_GELU / EPI_GELU_GRAD: gelu of the pre-activation
   const void* bias;  // bf16 [N] or null
   const void* residual;  // bf16 [M, N] or null (added before the activation derivative)
-  const void* aux;       // bf16 [M, N] pre-activation for EPI_DGELU
+  const void* aux;       // bf16 [M, N]: pre-activation for EPI_DGELU, factor for EPI_MUL
   int M, N, K, batch;
   int a_mn, b_mn;    // operand majors, see gemm.cu
   int epi, out_f32, accumulate, allow_split_k;

@@ -15,9 +15,9 @@ import ctypes
 import torch
 
 from . import _lib
-from ._lib import EPI_DGELU, EPI_GELU, EPI_NONE
+from ._lib import EPI_DGELU, EPI_GELU, EPI_GELU_GRAD, EPI_MUL, EPI_NONE
 
-__all__ = ["gemm", "gemm_reference", "EPI_NONE", "EPI_GELU", "EPI_DGELU"]
+__all__ = ["gemm", "gemm_reference", "EPI_NONE", "EPI_GELU", "EPI_DGELU", "EPI_GELU_GRAD", "EPI_MUL"]
 
 
 def _gelu(x: torch.Tensor) -> torch.Tensor:
@@ -55,9 +55,15 @@ def gemm_reference(
     if epi == EPI_DGELU:
         assert aux is not None
         acc = acc * _dgelu(aux.float())
+    if epi == EPI_MUL:
+        assert aux is not None
+        acc = acc * aux.float()
     if epi == EPI_GELU:
         z = acc.to(out_dtype)
         return z, _gelu(z.float()).to(out_dtype)
+    if epi == EPI_GELU_GRAD:  # (gelu'(z), gelu(z)) of the rounded pre-activation
+        z = acc.to(out_dtype).float()
+        return _dgelu(z).to(out_dtype), _gelu(z).to(out_dtype)
     return acc.to(out_dtype)
 
 
@@ -89,7 +95,8 @@ def gemm(
     accumulate: bool = False,
     split_k: bool = True,
 ):
-    """``out = epilogue(alpha * A·Bᵀ)``; returns ``out`` or ``(out, gelu(out))`` for ``EPI_GELU``.
+    """``out = epilogue(alpha * A·Bᵀ)``; returns ``out``, ``(z, gelu(z))`` for ``EPI_GELU`` or ``(gelu'(z), gelu(z))``
+    for ``EPI_GELU_GRAD`` (``EPI_MUL`` with that first output as ``aux`` is then the whole GELU backward).
 
     ``a``: [M,K] (``a_mn=False``) or [K,M] (``a_mn=True``); ``b``: [N,K] or [K,N]
     likewise; optional leading batch dim on both. ``accumulate`` adds into an fp32
@@ -102,7 +109,7 @@ def gemm(
             out_dtype=out_dtype or (out.dtype if out is not None else None),
         )
         if out is not None:
-            if epi == EPI_GELU:
+            if epi in (EPI_GELU, EPI_GELU_GRAD):
                 out.copy_(res[0])
                 if out2 is not None:
                     out2.copy_(res[1])
@@ -131,7 +138,7 @@ def gemm(
             out.zero_()
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise ValueError("GEMM output must be bf16 or fp32")
-    if epi == EPI_GELU and out2 is None:
+    if epi in (EPI_GELU, EPI_GELU_GRAD) and out2 is None:
         out2 = torch.empty_like(out)
 
     args = GemmArgsCache.get()
@@ -160,7 +167,7 @@ def gemm(
         if t is not None and t.data_ptr() % 16:
             raise ValueError("GEMM epilogue tensors must be 16-byte aligned")
     _lib.call("db200_gemm_bf16", ctypes.byref(args), _lib.stream_ptr())
-    if epi == EPI_GELU:
+    if epi in (EPI_GELU, EPI_GELU_GRAD):
         return out, out2
     return out
 

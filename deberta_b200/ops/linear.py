@@ -13,7 +13,7 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
-from .gemm import EPI_DGELU, EPI_GELU, gemm
+from .gemm import EPI_DGELU, EPI_GELU, EPI_GELU_GRAD, EPI_MUL, gemm
 
 __all__ = ["linear", "linear_qkv", "ffn_gelu", "use_kernels"]
 
@@ -97,23 +97,27 @@ def linear(
 
 
 class _FFNGelu(torch.autograd.Function):
-    """y = W2·gelu(W1·x + b1) + b2 + residual, with dGELU fused into the W2 data-gradient GEMM."""
+    """y = W2·gelu(W1·x + b1) + b2 + residual.
+
+    The first GEMM writes gelu(z) and gelu'(z) (both from one cdf/pdf evaluation) instead of z, so the W2
+    data-gradient GEMM only multiplies by a stored factor in its epilogue.
+    """
 
     @staticmethod
     def forward(ctx, x, w1, b1, w2, b2, residual):
-        z, a = gemm(x, w1, bias=b1, epi=EPI_GELU)
+        g, a = gemm(x, w1, bias=b1, epi=EPI_GELU_GRAD)
         y = gemm(a, w2, bias=b2, residual=residual)
-        ctx.save_for_backward(x, w1, w2, z, a)
+        ctx.save_for_backward(x, w1, w2, g, a)
         ctx.params = (b1, b2)
         ctx.has_res = residual is not None
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, w1, w2, z, a = ctx.saved_tensors
+        x, w1, w2, g, a = ctx.saved_tensors
         b1, b2 = ctx.params
         dy = dy.contiguous()
-        dz = gemm(dy, w2, b_mn=True, epi=EPI_DGELU, aux=z)
+        dz = gemm(dy, w2, b_mn=True, epi=EPI_MUL, aux=g)
         dw2 = _weight_grad(dy, a, w2) if w2.requires_grad else None
         db2 = _bias_grad(dy, b2) if (b2 is not None and b2.requires_grad) else None
         dx = gemm(dz, w1, b_mn=True) if ctx.needs_input_grad[0] else None

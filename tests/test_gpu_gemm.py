@@ -6,7 +6,7 @@ import pytest
 import torch
 
 from deberta_b200.ops import _lib
-from deberta_b200.ops.gemm import EPI_DGELU, EPI_GELU, gemm, gemm_reference
+from deberta_b200.ops.gemm import EPI_DGELU, EPI_GELU, EPI_GELU_GRAD, EPI_MUL, gemm, gemm_reference
 
 pytestmark = pytest.mark.gpu
 
@@ -48,6 +48,48 @@ def test_gemm_bias_residual_gelu():
     _close(act, ar)
     dz = gemm(a, w, epi=EPI_DGELU, aux=z)
     _close(dz, gemm_reference(a, w, epi=EPI_DGELU, aux=z, out_dtype=torch.float32))
+    _lib.check_status()
+
+
+@pytest.mark.parametrize("M,N", [(520, 3072), (300, 200)])  # TMA-store path and the ragged scalar path
+def test_gemm_gelu_with_stored_derivative(M, N):
+    """EPI_GELU_GRAD writes (gelu'(z), gelu(z)); EPI_MUL with that factor equals the EPI_DGELU backward."""
+    torch.manual_seed(4)
+    K = 768
+    a, w, bias = _rand(M, K), _rand(N, K, scale=0.05), _rand(N)
+    g, act = gemm(a, w, bias=bias, epi=EPI_GELU_GRAD)
+    gr, ar = gemm_reference(a, w, bias=bias, epi=EPI_GELU_GRAD)
+    _close(g, gr)
+    _close(act, ar)
+    z, act_z = gemm(a, w, bias=bias, epi=EPI_GELU)
+    assert torch.equal(act, act_z)  # the activation is the same in both forms
+    dy, w2 = _rand(M, 256), _rand(256, N, scale=0.05)
+    via_mul = gemm(dy, w2, b_mn=True, epi=EPI_MUL, aux=g)
+    via_dgelu = gemm(dy, w2, b_mn=True, epi=EPI_DGELU, aux=z)
+    _close(via_mul, gemm_reference(dy, w2, b_mn=True, epi=EPI_MUL, aux=g, out_dtype=torch.float32))
+    _close(via_mul, via_dgelu.float(), tol=1e-2)  # the stored factor is rounded to bf16 once more
+    _lib.check_status()
+
+
+def test_ffn_gelu_block_matches_pytorch():
+    from deberta_b200.ops.linear import ffn_gelu
+
+    torch.manual_seed(5)
+    T, H, I = 384, 768, 3072
+    x = _rand(T, H).requires_grad_(True)
+    w1, b1 = _rand(I, H, scale=0.03).requires_grad_(True), _rand(I, scale=0.1).requires_grad_(True)
+    w2, b2 = _rand(H, I, scale=0.03).requires_grad_(True), _rand(H, scale=0.1).requires_grad_(True)
+    res = _rand(T, H)
+    y = ffn_gelu(x, w1, b1, w2, b2, residual=res)
+    ref_in = [t.detach().float().requires_grad_(True) for t in (x, w1, b1, w2, b2)]
+    xr, w1r, b1r, w2r, b2r = ref_in
+    yr = torch.nn.functional.gelu(xr @ w1r.t() + b1r) @ w2r.t() + b2r + res.float()
+    _close(y, yr)
+    dy = torch.randn_like(yr)
+    (y.float() * dy).sum().backward()
+    (yr * dy).sum().backward()
+    for name, a, b in zip("x w1 b1 w2 b2".split(), (x, w1, b1, w2, b2), ref_in):
+        _close(a.grad, b.grad, tol=3e-2)
     _lib.check_status()
 
 
