@@ -109,6 +109,22 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_in, const _
   }
 }
 
+// y[r, c] = bf16(x[r, c]) for a dense fp32 matrix and a row-strided bf16 destination: 8 values per thread
+// (two 16-byte loads, one 16-byte store), grid-stride over rows * cols / 8 vectors.
+__global__ void __launch_bounds__(256)
+cast_rows_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, long long ld_y, long long rows, int cols) {
+  const int vpr = cols / 8;
+  const long long total = rows * vpr;
+  for (long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * 256) {
+    const long long r = i / vpr;
+    const int c = static_cast<int>(i % vpr) * 8;
+    const float4 a = *reinterpret_cast<const float4*>(x + r * cols + c);
+    const float4 b = *reinterpret_cast<const float4*>(x + r * cols + c + 4);
+    *reinterpret_cast<uint4*>(y + r * ld_y + c) = make_uint4(pack2(a.x, a.y), pack2(a.z, a.w), pack2(b.x, b.y), pack2(b.z, b.w));
+  }
+}
+
 int ew_grid(long long vecs) {
   long long blocks = (vecs + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
@@ -128,6 +144,14 @@ extern "C" int db200_rotary_bf16(const void* x, void* y, long long ldx, long lon
   rotary_kernel<<<ew_grid(vecs), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), ldx, ldy, cos_t, sin_t, tokens, S, heads,
       head_dim, rotary_dim, inverse ? -1.f : 1.f);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int db200_cast_f32_bf16(const float* x, void* y, long long ld_y, long long rows, int cols, void* stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (!al16(x) || !al16(y) || (ld_y % 8) || (cols % 8) || ld_y < cols) return -10;
+  cast_rows_kernel<<<ew_grid(rows * (cols / 8)), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      x, static_cast<__nv_bfloat16*>(y), ld_y, rows, cols);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -72,6 +72,8 @@ int db200_adamw(float* p, const float* g, float* m, float* v, void* shadow_bf16,
 int db200_rotary_bf16(const void* x, void* y, long long ldx, long long ldy, const float* cos_t, const float* sin_t,
                       long long tokens, int S, int heads, int head_dim, int rotary_dim, int inverse, void* stream);
 // out[r, c] = silu(gate_up[r, c]) * gate_up[r, F + c]  and its backward (d_gate_up has the layout of gate_up).
+// y[r, 0:cols] = bf16(x[r, 0:cols]); x dense fp32 [rows, cols], y bf16 with row stride ld_y (cols, ld_y multiples of 8).
+int db200_cast_f32_bf16(const float* x, void* y, long long ld_y, long long rows, int cols, void* stream);
 int db200_swiglu_fwd(const void* gate_up, long long ld_in, void* out, long long ld_out, long long rows, int F, void* stream);
 int db200_swiglu_bwd(const void* gate_up, long long ld_in, const void* dout, long long ld_do, void* d_gate_up,
                      long long ld_dg, long long rows, int F, void* stream);

@@ -262,7 +262,8 @@ class _FlashAttention(torch.autograd.Function):
             gemm(g, _heads_view(k2, heads), a_mn=True, b_mn=True, out=_heads_view(d_pos_q, heads), accumulate=True)
             d_pos_q = d_pos_q.to(pos_q.dtype)
         dq = dqkv[:, :H]
-        dq.copy_(dq_acc)
+        _lib.call("db200_cast_f32_bf16", _lib.ptr(dq_acc), _lib.ptr(dq), ctypes.c_longlong(3 * H), ctypes.c_longlong(T),
+                  c_int(H), _lib.stream_ptr())
         return dq.view(B, S, H), dk.view(B, S, H), dv.view(B, S, H), d_pos_k, d_pos_q, None, None, None, None, None
 
 
