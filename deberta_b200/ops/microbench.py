@@ -41,6 +41,23 @@ def bench_gemm(a) -> None:
         print(f"gemm {M}x{N}x{K}: tcgen05 {us:.1f} us ({2 * M * N * K / us / 1e6:.0f} TFLOP/s) | cuBLAS {ref:.1f} us")
 
 
+def bench_ffn(a) -> None:
+    """The four GELU-epilogue forms of the FFN GEMMs (M = batch*seq, 768 -> 3072 -> 768)."""
+    from deberta_b200.ops.gemm import EPI_DGELU, EPI_GELU, EPI_GELU_GRAD, EPI_MUL, gemm
+
+    M, H, I = a.batch * a.seq, 768, 3072
+    x, w1, b1 = _rand(M, H), _rand(I, H, scale=0.03), _rand(I)
+    dy, w2 = _rand(M, H), _rand(H, I, scale=0.03)
+    z, _ = gemm(x, w1, bias=b1, epi=EPI_GELU)
+    g, _ = gemm(x, w1, bias=b1, epi=EPI_GELU_GRAD)
+    for name, fn in (("forward, outputs z and gelu(z)", lambda: gemm(x, w1, bias=b1, epi=EPI_GELU)),
+                     ("forward, outputs gelu'(z) and gelu(z)", lambda: gemm(x, w1, bias=b1, epi=EPI_GELU_GRAD)),
+                     ("backward, dy.W2 * gelu'(z) computed from z", lambda: gemm(dy, w2, b_mn=True, epi=EPI_DGELU, aux=z)),
+                     ("backward, dy.W2 * stored gelu'(z)", lambda: gemm(dy, w2, b_mn=True, epi=EPI_MUL, aux=g)),
+                     ("backward, dy.W2 alone", lambda: gemm(dy, w2, b_mn=True))):
+        print(f"ffn {M}x{I}x{H} {name}: {_time(fn, a.iters):.1f} us")
+
+
 def bench_attention(a) -> None:
     from deberta_b200.ops.attention import disentangled_attention
 
@@ -91,13 +108,13 @@ def bench_layer(a) -> None:
 
 def main() -> None:
     p = argparse.ArgumentParser()
-    p.add_argument("op", choices=("gemm", "attention", "vocab_ce", "layer"))
+    p.add_argument("op", choices=("gemm", "ffn", "attention", "vocab_ce", "layer"))
     p.add_argument("--batch", type=int, default=32)
     p.add_argument("--seq", type=int, default=512)
     p.add_argument("--heads", type=int, default=12)
     p.add_argument("--iters", type=int, default=5)
     a = p.parse_args()
-    {"gemm": bench_gemm, "attention": bench_attention, "vocab_ce": bench_vocab_ce, "layer": bench_layer}[a.op](a)
+    {"gemm": bench_gemm, "ffn": bench_ffn, "attention": bench_attention, "vocab_ce": bench_vocab_ce, "layer": bench_layer}[a.op](a)
 
 
 if __name__ == "__main__":
