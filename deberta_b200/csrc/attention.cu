@@ -59,25 +59,33 @@ __device__ __forceinline__ float ex2(float x) {
 // Tiles whose document-id range [lo, hi] meets that of tile `self`: first such tile and the length of the
 // run up to the last one (tiles inside the run that do not meet it are still visited and fully masked).
 // A tile without live tokens has lo > hi and meets nothing; a CTA always visits at least one tile.
-// Called by whole warps; without a table, or with more than 32 tiles, every tile is visited.
+// Called by whole warps (32 tiles per ballot); without a table every tile is visited.
 __device__ __forceinline__ void doc_tile_run(const int* tiles, int b, int ntiles, int self, int lane, int& first,
                                              int& count) {
   first = 0;
   count = ntiles;
-  if (tiles == nullptr || ntiles > 32) return;
+  if (tiles == nullptr) return;
   const int* t = tiles + static_cast<long long>(b) * ntiles * 2;
   const int slo = t[2 * self], shi = t[2 * self + 1];
-  bool hit = false;
-  if (lane < ntiles) {
-    const int lo = t[2 * lane], hi = t[2 * lane + 1];
-    hit = lo <= hi && slo <= shi && lo <= shi && hi >= slo;
+  int lo_tile = -1, hi_tile = -1;
+  for (int base = 0; base < ntiles; base += 32) {
+    const int i = base + lane;
+    bool hit = false;
+    if (i < ntiles) {
+      const int lo = t[2 * i], hi = t[2 * i + 1];
+      hit = lo <= hi && slo <= shi && lo <= shi && hi >= slo;
+    }
+    const unsigned m = __ballot_sync(0xffffffffu, hit);
+    if (m != 0) {
+      if (lo_tile < 0) lo_tile = base + __ffs(m) - 1;
+      hi_tile = base + 31 - __clz(m);
+    }
   }
-  const unsigned m = __ballot_sync(0xffffffffu, hit);
-  if (m == 0) {
+  if (lo_tile < 0) {
     count = 1;
   } else {
-    first = __ffs(m) - 1;
-    count = 32 - __clz(m) - first;
+    first = lo_tile;
+    count = hi_tile - lo_tile + 1;
   }
 }
 

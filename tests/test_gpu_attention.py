@@ -107,7 +107,7 @@ def _packed_doc_ids(B, S, mean_len, seed, tail_pad=0, shuffle_ids=False):
 
 
 @pytest.mark.parametrize("S,mean_len,tail_pad,shuffle", [(1024, 60, 0, False), (1024, 200, 300, False), (768, 90, 140, True),
-                                                         (2048, 150, 0, False)])
+                                                         (2048, 150, 0, False), (4300, 500, 200, False)])  # 34 tiles: two ballots
 def test_rope_packed_documents_skip_tiles(S, mean_len, tail_pad, shuffle):
     """Many short documents per row: most tile pairs share no document and are skipped; results must not change."""
     B, heads = 2, 2
