@@ -94,7 +94,14 @@ def run_reference(args) -> dict:
         wrapped = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], find_unused_parameters=True)
     model.sync_discriminator_embeddings_from_generator()
     model.train()
-    host = bench.synthetic_batches(args.ga, args.micro_batch, args.seq_len, seed=100 + rank, pin=True)
+    block_docs = bool(getattr(args, "block_docs", False))
+    host = bench.synthetic_batches(args.ga, args.micro_batch, args.seq_len, seed=100 + rank, pin=True, block_docs=block_docs)
+    from deberta.training.compile import _build_doc_block_mask  # the reference loop turns document ids into [B,S,S] masks
+
+    def mask_of(b):
+        doc = b.get("doc_ids")
+        return _build_doc_block_mask(doc) if doc is not None else b.get("attention_mask")
+
     dev = [{k: v.to(device) for k, v in b.items()} for b in host]
     gen_w, disc_w, ga = 1.0, 50.0, args.ga
 
@@ -111,7 +118,8 @@ def run_reference(args) -> dict:
             ctx = contextlib.nullcontext() if sync else wrapped.no_sync()
             with ctx:
                 with torch.autocast("cuda", dtype=torch.bfloat16):
-                    out = wrapped(input_ids=b["input_ids"], attention_mask=b.get("attention_mask"), labels=b["labels"],
+                    b["_mask"] = mask_of(b)  # built once per micro-batch, as in the reference loop (entrypoint.py:1119-1121)
+                    out = wrapped(input_ids=b["input_ids"], attention_mask=b["_mask"], labels=b["labels"],
                                   phase="generator")
                 obj = out.gen_loss_raw * (g_i / gen_tot)
                 loss = _scale_loss_for_backward(loss=gen_w * obj, ga_steps=ga, token_weighted_ga=True) / ga
@@ -129,7 +137,7 @@ def run_reference(args) -> dict:
             with ctx:
                 with torch.autocast("cuda", dtype=torch.bfloat16):
                     out = wrapped(input_ids=b["input_ids"], corrupted_input_ids=corrupted, disc_labels=labels,
-                                  attention_mask=b.get("attention_mask"), phase="discriminator")
+                                  attention_mask=b["_mask"], phase="discriminator")
                 obj = out.disc_loss_raw * (d_i / disc_tot)
                 loss = _scale_loss_for_backward(loss=disc_w * obj, ga_steps=ga, token_weighted_ga=True) / ga
                 loss.backward()
@@ -187,7 +195,8 @@ def run_reference(args) -> dict:
         "data": "synthetic packed Zipf(1.1) token streams, random-init weights", "impl": "reference",
         "config": {"model": f"deberta-v3-{args.model_size} RTD (reference modules, eager, bf16 autocast)",
                    "global_batch": args.micro_batch * args.ga * world, "micro_batch": args.micro_batch,
-                   "grad_accum": args.ga, "seq_len": args.seq_len, "parallelism": f"ddp{world}",
+                   "grad_accum": args.ga, "seq_len": args.seq_len, "block_cross_document_attention": block_docs,
+                   "parallelism": f"ddp{world}",
                    "driver": "reference building blocks driven as in its decoupled loop; `accelerate` is not installed"},
         "clocks": clocks,
         "e2e": {"value": tokens / e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 8},

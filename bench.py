@@ -53,6 +53,9 @@ def parse_args() -> argparse.Namespace:
     p.add_argument("--backbone", choices=("hf_deberta_v2", "rope"), default="hf_deberta_v2",
                    help="rope: the RoPE/RMSNorm/SwiGLU family at its config defaults (secondary benchmark)")
     p.add_argument("--parallelism", choices=("ddp", "zero"), default="zero")
+    p.add_argument("--block-docs", action="store_true",
+                   help="rope backbone only: packed documents do not attend to each other (data.packing."
+                        "block_cross_document_attention); the collator then emits document ids")
     return p.parse_args()
 
 
@@ -101,7 +104,8 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def synthetic_batches(n: int, micro_batch: int, seq_len: int, seed: int, pin: bool) -> list[dict[str, torch.Tensor]]:
+def synthetic_batches(n: int, micro_batch: int, seq_len: int, seed: int, pin: bool,
+                      block_docs: bool = False) -> list[dict[str, torch.Tensor]]:
     """``n`` collated micro-batches from the synthetic corpus through the real packer + collator."""
     from deberta_b200.data import DebertaV3ElectraCollator, MLMConfig, PackedStreamingConfig, PackedStreamingDataset
     from deberta_b200.data.synthetic import SyntheticTextDataset, SyntheticTokenizer
@@ -111,7 +115,7 @@ def synthetic_batches(n: int, micro_batch: int, seq_len: int, seed: int, pin: bo
                                 tokenizer=tok, cfg=PackedStreamingConfig(max_seq_length=seq_len, seed=seed))
     col = DebertaV3ElectraCollator(tokenizer=tok, cfg=MLMConfig(mlm_probability=0.15, mask_token_prob=1.0,
                                                                 random_token_prob=0.0), packed_sequences=True,
-                                   block_cross_document_attention=False)
+                                   block_cross_document_attention=bool(block_docs))
     it = iter(ds)
     out = []
     torch.manual_seed(seed)
@@ -160,7 +164,8 @@ def run_ours(args: argparse.Namespace) -> dict:
     engine = build_engine(model=model, ctx=ctx, train_cfg=cfg.train, optim_cfg=cfg.optim, parallelism=args.parallelism)
     trainer = Trainer(model=model, engine=engine, ctx=ctx, train_cfg=cfg.train, optim_cfg=cfg.optim,
                       pad_token_id=tok.pad_token_id)
-    host = synthetic_batches(args.ga, args.micro_batch, args.seq_len, seed=100 + ctx.rank, pin=True)
+    host = synthetic_batches(args.ga, args.micro_batch, args.seq_len, seed=100 + ctx.rank, pin=True,
+                             block_docs=getattr(args, "block_docs", False))
     dev = [{k: v.to(ctx.device) for k, v in b.items()} for b in host]
     tokens_per_step = args.ga * args.micro_batch * args.seq_len
     h2d = sum(v.numel() * v.element_size() for b in host for v in b.values())
@@ -210,7 +215,7 @@ def run_ours(args: argparse.Namespace) -> dict:
         "config": {"model": (f"deberta-v3-{args.model_size} RTD (12L disc + 6L gen, GDES, EMD)" if args.backbone == "hf_deberta_v2"
                              else "rope RTD (config defaults, GDES)"),
                    "global_batch": args.micro_batch * args.ga * ctx.world_size, "micro_batch": args.micro_batch,
-                   "grad_accum": args.ga, "seq_len": args.seq_len,
+                   "grad_accum": args.ga, "seq_len": args.seq_len, "block_cross_document_attention": bool(args.block_docs),
                    "parallelism": f"dp{ctx.world_size}" + ("-zero1" if args.parallelism == "zero" else "-replicated"),
                    "collectives": ("none (1 GPU)" if ctx.world_size == 1 else
                                    ("fused peer-memory kernels" + (" (multimem)" if engine.comm.multicast else "")
