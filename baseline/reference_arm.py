@@ -103,7 +103,8 @@ def run_reference(args) -> dict:
         return _build_doc_block_mask(doc) if doc is not None else b.get("attention_mask")
 
     dev = [{k: v.to(device) for k, v in b.items()} for b in host]
-    gen_w, disc_w, ga = 1.0, 50.0, args.ga
+    # loss weights as the reference's profile defaults resolve them: 10 for the DeBERTa-v2 backbone, 50 otherwise
+    gen_w, disc_w, ga = 1.0, (10.0 if getattr(args, "backbone", "hf_deberta_v2") == "hf_deberta_v2" else 50.0), args.ga
 
     def window(batches, counts):
         gen_tot = max(sum(c[0] for c in counts), 1.0)
