@@ -43,6 +43,8 @@ _CHOICES: dict[str, set[str]] = {
     "train.compile.scope": {"auto", "backbones", "encoder", "gen_encoder", "disc_encoder", "ffn", "gen_ffn", "disc_ffn"},
     "train.compile.backend": {"inductor", "aot_eager"},
     "train.checkpoint.resume_data_strategy": {"auto", "replay", "restart_epoch"},
+    "train.distributed.parallelism": {"ddp", "zero", "fsdp"},
+    "train.distributed.multicast": {"auto", "on", "off"},
     "optim.scheduler.type": {"linear", "cosine", "cosine_with_restarts", "polynomial", "constant", "constant_with_warmup"},
     "logging.backend": {"none", "tensorboard"},
     "logging.wandb.watch": {"none", "gradients", "parameters", "all"},
@@ -58,6 +60,9 @@ _ALIASES: dict[str, dict[str, str]] = {
                             "generator_encoder": "gen_encoder", "discriminator_encoder": "disc_encoder",
                             "ffns": "ffn", "generator_ffn": "gen_ffn", "discriminator_ffn": "disc_ffn"},
     "train.compile.backend": {"aot-eager": "aot_eager"},
+    "train.distributed.parallelism": {"replicated": "ddp", "zero1": "zero", "sharded_optimizer": "zero",
+                                      "full_shard": "fsdp", "fsdp2": "fsdp", "zero3": "fsdp"},
+    "train.distributed.multicast": {"true": "on", "1": "on", "yes": "on", "false": "off", "0": "off", "no": "off"},
     "logging.wandb.watch": {"off": "none", "disabled": "none", "false": "none", "0": "none", "grad": "gradients",
                             "gradient": "gradients", "weights": "parameters", "params": "parameters",
                             "param": "parameters"},
@@ -413,6 +418,20 @@ class TrainCheckpointConfig(Section):
 
 
 @_cfg
+class TrainDistributedConfig(Section):
+    """How the ranks of one node share the work (this package's engine; the reference delegates this to its
+    Accelerate launch files ``configs/accelerate/fsdp2_*.yaml``)."""
+
+    parallelism: str = "zero"       # ddp: replicated optimizer | zero: sharded optimizer state | fsdp: parameters sharded too
+    fused_collectives: bool = True  # peer-memory kernels instead of NCCL for gradients / parameters (one node, 2..8 GPUs)
+    multicast: str = "auto"         # NVSwitch multimem path of those kernels: auto = from 4 ranks on
+    overlap_backward: bool = True   # reduce gradient buckets on a side stream while backward still runs
+    comm_timeout_s: float = 20.0    # longest device-side wait for a peer before the step fails
+    step_deadline_s: float = 0.0    # host watchdog: report when no optimizer step completes in this time (0 = off)
+    heartbeat_s: float = 0.0        # rank heartbeats through the process-group store (0 = off)
+
+
+@_cfg
 class TrainConfig(Section):
     seed: int = 42
     max_steps: int = 10_000
@@ -427,6 +446,7 @@ class TrainConfig(Section):
     compile: TrainCompileConfig = field(default_factory=TrainCompileConfig)
     objective: TrainObjectiveConfig = field(default_factory=TrainObjectiveConfig)
     checkpoint: TrainCheckpointConfig = field(default_factory=TrainCheckpointConfig)
+    distributed: TrainDistributedConfig = field(default_factory=TrainDistributedConfig)
 
     _LEGACY: ClassVar[dict[str, str]] = {
         "dataloader_num_workers": "dataloader.num_workers",
@@ -503,6 +523,7 @@ class LoggingWandbConfig(Section):
 @_cfg
 class LoggingDebugConfig(Section):
     metrics: bool = False
+    nvtx: bool = False  # NVTX ranges around the phases of a step
 
 
 @_cfg
@@ -734,6 +755,14 @@ def validate_train_config(cfg: TrainConfig) -> None:
         _set(cfg.compile, name, normalize_choice(f"train.compile.{name}", getattr(cfg.compile, name)))
     ck = cfg.checkpoint
     _set(ck, "resume_data_strategy", normalize_choice("train.checkpoint.resume_data_strategy", ck.resume_data_strategy))
+    di = cfg.distributed
+    _set(di, "parallelism", normalize_choice("train.distributed.parallelism", di.parallelism))
+    _set(di, "multicast", normalize_choice("train.distributed.multicast", di.multicast))
+    for name in ("comm_timeout_s", "step_deadline_s", "heartbeat_s"):
+        if float(getattr(di, name)) < 0.0:
+            raise ValueError(f"train.distributed.{name} must be >= 0.")
+    if float(di.comm_timeout_s) == 0.0:
+        raise ValueError("train.distributed.comm_timeout_s must be > 0: device-side waits are always bounded.")
     if ck.output_dir is not None and not str(ck.output_dir).strip():
         _set(ck, "output_dir", None)
     if ck.resume_from_checkpoint is not None:

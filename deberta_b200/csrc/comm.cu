@@ -23,9 +23,11 @@
 //
 // Ordering between ranks uses per-source flags in the pads that carry a call counter ("epoch")
 // supplied by the host; the host passes the same strictly increasing epochs on every rank. A wait
-// gives up after `timeout_ns` of the global timer, records kErrPeerWait in the status word and the
-// kernel then runs to completion on whatever data is there (all addresses stay valid), so that a
-// missing peer surfaces as a host-side error instead of a hang.
+// gives up after `timeout_ns` of the global timer and records kErrPeerWait in the status word. The
+// kernel then runs to completion (all addresses stay valid) but fails safe: a reduction whose peers
+// did not show up publishes an infinite squared-norm share, so that no rank applies an update to
+// partially reduced gradients; the update kernel treats a missing share the same way; a vector sum
+// returns NaN. The host reads the status word with the step's outcome and raises.
 //
 // These kernels spin on flags written by other GPUs: ranks must be on different GPUs.
 #include "kernels.h"
@@ -153,9 +155,9 @@ comm_reduce_kernel(const CommDev c, long long off, long long n, float scale, uin
   uint32_t* pad = c.pads[c.rank];
   __threadfence_system();
   signal_peers(c, kChStart, epoch);
-  wait_peers(c, kChStart, epoch, &wait_flag);
+  const bool peers_here = wait_peers(c, kChStart, epoch, &wait_flag);
 
-  float ss = 0.f;
+  float ss = peers_here ? 0.f : INFINITY;  // a peer never arrived: its gradients may be missing from the sum
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * 4;
   for (long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < n; i += stride) {
     float4 a;
@@ -194,9 +196,9 @@ comm_reduce_kernel(const CommDev c, long long off, long long n, float scale, uin
   signal_peers(c, kChNorm, epoch);
   if (kToAll) {
     // every peer's slab has landed here once its flag is up; then the norm is complete too
-    wait_peers(c, kChNorm, epoch, &wait_flag);
+    const bool all_in = wait_peers(c, kChNorm, epoch, &wait_flag);
     if (threadIdx.x == 0 && norm_sq_out) {
-      float t = 0.f;
+      float t = all_in ? 0.f : INFINITY;
       for (int r = 0; r < c.world; ++r) t += __uint_as_float(ld_acquire_sys(pad + kPadNorm + r));
       *norm_sq_out = t;
     }
@@ -215,15 +217,17 @@ struct AdamDev {
 
 __global__ void __launch_bounds__(256)
 comm_adamw_kernel(const CommDev c, long long off, float* __restrict__ master, float* __restrict__ m,
-                  float* __restrict__ v, const AdamDev a, uint32_t epoch, float* norm_sq_out) {
+                  float* __restrict__ v, const AdamDev a, uint32_t epoch, float* norm_sq_out,
+                  const float* __restrict__ gate) {
   __shared__ int wait_flag;
   uint32_t* pad = c.pads[c.rank];
-  wait_peers(c, kChNorm, epoch, &wait_flag);
-  float norm_sq = 0.f;
+  const bool shares_in = wait_peers(c, kChNorm, epoch, &wait_flag);
+  float norm_sq = shares_in ? 0.f : INFINITY;  // a missing share: skip the update like a non-finite norm
   for (int r = 0; r < c.world; ++r) norm_sq += __uint_as_float(ld_acquire_sys(pad + kPadNorm + r));
   if (blockIdx.x == 0 && threadIdx.x == 0 && norm_sq_out) *norm_sq_out = norm_sq;
   const float norm = sqrtf(norm_sq);
-  const bool skip = !isfinite(norm);  // same value on every rank: all of them skip together
+  // same values on every rank: all of them skip together (the gate is a sum over ranks computed earlier)
+  const bool skip = !isfinite(norm) || (gate != nullptr && !(*gate > 0.f));
   const float coef = (a.max_norm > 0.f) ? fminf(1.f, a.max_norm / (norm + 1e-6f)) : 1.f;
   const float* g = c.grads[c.rank] + off;
 
@@ -286,9 +290,9 @@ comm_vector_sum_kernel(const CommDev c, const float* __restrict__ in, float* __r
   __threadfence_system();
   __syncthreads();
   signal_peers(c, kChVec, epoch);
-  wait_peers(c, kChVec, epoch, &wait_flag);
+  const bool all_in = wait_peers(c, kChVec, epoch, &wait_flag);
   if (t < n) {
-    float s = 0.f;
+    float s = all_in ? 0.f : NAN;
     for (int r = 0; r < c.world; ++r)
       s += __uint_as_float(ld_acquire_sys(c.pads[c.rank] + kPadVec + r * DB200_COMM_VEC_MAX + t));
     out[t] = s;
@@ -345,7 +349,7 @@ extern "C" int db200_comm_reduce(const Db200CommCtx* ctx, long long offset, long
 extern "C" int db200_comm_adamw(const Db200CommCtx* ctx, long long offset, long long count, float* master, float* exp_avg,
                                 float* exp_avg_sq, const Db200AdamSegment* segs, int nseg, float b1, float b2, float eps,
                                 float inv_bc1, float inv_sqrt_bc2, float max_norm, unsigned epoch, float* norm_sq_out,
-                                void* stream) {
+                                const float* gate, void* stream) {
   CommDev d;
   if (int rc = make_dev(ctx, &d)) return rc;
   if (count <= 0 || (count % 8) || (offset % 8) || nseg < 0 || nseg > 4) return -10;
@@ -361,7 +365,7 @@ extern "C" int db200_comm_adamw(const Db200CommCtx* ctx, long long offset, long 
   }
   a.b1 = b1; a.b2 = b2; a.eps = eps; a.inv_bc1 = inv_bc1; a.inv_sqrt_bc2 = inv_sqrt_bc2; a.max_norm = max_norm;
   comm_adamw_kernel<<<comm_grid(count, 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      d, offset, master, exp_avg, exp_avg_sq, a, epoch, norm_sq_out);
+      d, offset, master, exp_avg, exp_avg_sq, a, epoch, norm_sq_out, gate);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

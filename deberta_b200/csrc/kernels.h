@@ -11,6 +11,7 @@ extern "C" {
 // ----- status word written by kernels whose bounded waits ran out -------------------
 int* db200_status_ptr(void);          // device address of the status word (lazily allocated)
 int db200_status_read_and_clear(void);  // synchronises the device; 0 = no error recorded
+int db200_status_snapshot(int* dst, void* stream);  // stream-ordered copy of the word into device / pinned memory
 
 // ----- GEMM ---------------------------------------------------------------------------
 enum { EPI_NONE = 0, EPI_GELU = 1, EPI_DGELU = 2, EPI_CE_FWD = 3, EPI_CE_BWD = 4,
@@ -61,9 +62,10 @@ int db200_colsum_bf16(const void* x, long long ld, int M, int N, float* out_accu
 
 // ----- optimizer (flat fp32 ranges) ---------------------------------------------------------
 int db200_sumsq(const float* g, long long n, float* out_accum, void* stream);
+// gate (may be null): device float; the update is skipped when it is not > 0 (decided without a host round trip).
 int db200_adamw(float* p, const float* g, float* m, float* v, void* shadow_bf16, long long n, float lr, float wd,
                 float b1, float b2, float eps, float inv_bc1, float inv_sqrt_bc2, const float* norm_sq,
-                float max_norm, float grad_scale, void* stream);
+                float max_norm, float grad_scale, const float* gate, void* stream);
 
 // ----- elementwise kernels of the RoPE backbone (see elementwise.cu) ---------------------------
 // Interleaved-pair rotary embedding of the first rotary_dim features of every head: y = rot(x) (inverse != 0: the
@@ -121,7 +123,8 @@ int db200_comm_reduce(const Db200CommCtx* ctx, long long offset, long long count
 // AdamW on this rank's slab after db200_comm_reduce(to_all = 0) with the same epoch; bf16 parameters go to all ranks.
 int db200_comm_adamw(const Db200CommCtx* ctx, long long offset, long long count, float* master, float* exp_avg,
                      float* exp_avg_sq, const Db200AdamSegment* segs, int nseg, float b1, float b2, float eps,
-                     float inv_bc1, float inv_sqrt_bc2, float max_norm, unsigned epoch, float* norm_sq_out, void* stream);
+                     float inv_bc1, float inv_sqrt_bc2, float max_norm, unsigned epoch, float* norm_sq_out,
+                     const float* gate, void* stream);
 // out[i] = sum over ranks of in[i], i < n <= DB200_COMM_VEC_MAX (in/out: this rank's own device memory).
 int db200_comm_vector_sum(const Db200CommCtx* ctx, const float* in, float* out, int n, unsigned epoch, void* stream);
 
@@ -162,6 +165,28 @@ int db200_posbias_scatter(const void* dbias, const void* lut, void* dtab, int ro
 // sign = -1 it collects E_{j+1} <= q-k < E_j; unused buckets have E_j = E_{j+1}. span2 must be a multiple of 8.
 int db200_posbias_scatter_ranges(const void* dbias, const void* ranges, void* dtab, int rows_are_keys, int B, int S,
                                  int ldb, int heads, int span2, void* stream);
+
+// Position terms on the tensor cores (posbias_tc.cu): the [q, k] bias and the gradients it induces, computed from
+// Q, K and the projected position tables directly; the bucket-indexed score tables never exist in global memory.
+typedef struct PosBiasArgs {
+  const void *q, *k;                        // bf16 [B*S, ld*], a head is a 64-column slice
+  long long ldq, ldk;
+  const void *pos_k, *pos_q;                // bf16 [span2, ld_pos] projected position tables (either may be null)
+  long long ld_pos;
+  const void *lut_c2p, *lut_p2c;            // device uint16 [2S-1]: table row of offset q-k (index q-k+S-1)
+  const void *lut_c2p_host, *lut_p2c_host;  // the same tables in host memory (window planning)
+  int B, S, heads, span2;
+  void* bias;                               // bf16 [B, heads, S, ldb]: written by the forward
+  long long ldb;                            // multiple of 128, >= S rounded up to 128
+  const void* dbias;                        // bf16 [B, heads, S, ldb]: gradient of the bias (backward input)
+  float* dq_acc;                            // fp32 [B*S, heads*64]: the c2p part of dQ is added here
+  void* dk;                                 // bf16 [B*S, ld_dk]: the p2c part of dK is added here (read-modify-write)
+  long long ld_dk;
+  float *d_pos_k, *d_pos_q;                 // fp32 [span2, heads*64]: gradients of the tables are added here
+} PosBiasArgs;
+// -13: some tile needs more than 256 consecutive table rows (or, backward, span2 > 512): use the table path instead.
+int db200_posbias_tc_fwd(const PosBiasArgs* args, void* stream);
+int db200_posbias_tc_bwd(const PosBiasArgs* args, void* stream);
 
 int db200_attn_fwd(const AttnArgs* args, void* stream);
 int db200_attn_bwd(const AttnArgs* args, void* stream);

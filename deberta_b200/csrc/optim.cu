@@ -1,9 +1,9 @@
 // Optimizer kernels over the engine's flat fp32 buffers.
 //   db200_sumsq  : sum of squares of a gradient range, accumulated into one device float
 //   db200_adamw  : AdamW on a contiguous range; the clip coefficient is derived on the device
-//                  from the (already reduced) squared gradient norm, a non-finite norm turns
-//                  the launch into a no-op, and the bf16 compute copy of every parameter is
-//                  rewritten in the same pass.
+//                  from the (already reduced) squared gradient norm, a non-finite norm (or a
+//                  device-side gate of 0) turns the launch into a no-op, and the bf16 compute
+//                  copy of every parameter is rewritten in the same pass.
 #include "kernels.h"
 
 #include <cuda_bf16.h>
@@ -40,7 +40,9 @@ struct AdamArgs {
 
 __global__ void __launch_bounds__(256)
 adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v,
-             __nv_bfloat16* __restrict__ shadow, long long n, AdamArgs a, const float* __restrict__ norm_sq) {
+             __nv_bfloat16* __restrict__ shadow, long long n, AdamArgs a, const float* __restrict__ norm_sq,
+             const float* __restrict__ gate) {
+  if (gate != nullptr && !(*gate > 0.f)) return;  // the caller switched this update off on the device
   float coef = a.grad_scale;
   if (norm_sq != nullptr) {
     const float norm = sqrtf(*norm_sq) * a.grad_scale;
@@ -109,7 +111,7 @@ extern "C" int db200_sumsq(const float* g, long long n, float* out, void* stream
 
 extern "C" int db200_adamw(float* p, const float* g, float* m, float* v, void* shadow_bf16, long long n, float lr,
                            float wd, float b1, float b2, float eps, float inv_bc1, float inv_sqrt_bc2,
-                           const float* norm_sq, float max_norm, float grad_scale, void* stream) {
+                           const float* norm_sq, float max_norm, float grad_scale, const float* gate, void* stream) {
   if (n <= 0) return 0;
   if ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
        reinterpret_cast<uintptr_t>(v)) & 15)
@@ -117,6 +119,6 @@ extern "C" int db200_adamw(float* p, const float* g, float* m, float* v, void* s
   if (shadow_bf16 && (reinterpret_cast<uintptr_t>(shadow_bf16) & 7)) return -10;
   AdamArgs a{lr, wd, b1, b2, eps, inv_bc1, inv_sqrt_bc2, max_norm, grad_scale};
   adamw_kernel<<<grid_for(n), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      p, g, m, v, static_cast<__nv_bfloat16*>(shadow_bf16), n, a, norm_sq);
+      p, g, m, v, static_cast<__nv_bfloat16*>(shadow_bf16), n, a, norm_sq, gate);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

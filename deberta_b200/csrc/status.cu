@@ -21,6 +21,15 @@ extern "C" int* db200_status_ptr(void) {
   return g_status_addr[dev];
 }
 
+// Copy the status word into `dst` (device or pinned host int) in stream order, without a synchronisation.
+extern "C" int db200_status_snapshot(int* dst, void* stream) {
+  int* p = db200_status_ptr();
+  if (!p || !dst) return -1;
+  return cudaMemcpyAsync(dst, p, sizeof(int), cudaMemcpyDefault, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? 0
+             : -2;
+}
+
 extern "C" int db200_status_read_and_clear(void) {
   int* p = db200_status_ptr();
   if (!p) return -1;

@@ -133,3 +133,14 @@ def call(name: str, *args: Any) -> None:
     LAUNCH_COUNT += 1
     fn = getattr(lib(), name)
     check(int(fn(*args)), name)
+
+
+def call_rc(name: str, *args: Any, accept: tuple[int, ...] = ()) -> int:
+    """Like :func:`call`, but return codes listed in ``accept`` come back to the caller instead of raising."""
+    global LAUNCH_COUNT
+    rc = int(getattr(lib(), name)(*args))
+    if rc == 0:
+        LAUNCH_COUNT += 1
+    elif rc not in accept:
+        check(rc, name)
+    return rc

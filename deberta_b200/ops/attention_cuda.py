@@ -1,10 +1,12 @@
-"""Launchers and autograd glue for the sm_100a attention kernels (``csrc/attention.cu``).
+"""Launchers and autograd glue for the sm_100a attention kernels (``csrc/attention.cu``, ``csrc/posbias_tc.cu``).
 
-The position terms of disentangled attention enter the kernels as two per-head score tables
-(``C2P = Q·PosKᵀ``, ``P2C = K·PosQᵀ``, both ``[tokens, heads, 2·span]``) produced by the batched
-tcgen05 GEMM; the kernels gather from them with the log-bucket lookup tables. The backward
-kernel returns the gradients of those tables, which two more batched GEMMs turn into the
-gradients of Q/K and of the projected position embeddings.
+Position terms of disentangled attention (``deberta_v2_native.py:349-432``), up to ``BIAS_MODE_MAX_SEQ`` tokens:
+``csrc/posbias_tc.cu`` computes the ``[B, heads, S, S]`` bias ``Q·PosK[δ] + K·PosQ[δ]`` tile by tile on the
+tensor cores (window products in TMEM, bucket lookup in shared memory) and, in the backward pass, folds the bias
+gradient onto the bucket axis inside the kernel and multiplies it into dQ, dK and the table gradients; no
+``[tokens, heads, 2·span]`` score table is ever written. Longer sequences, and bucket maps whose tiles span more
+than 256 table rows, use the table path: two per-head score tables from the batched GEMM, gathered inside the
+attention kernels (or pre-gathered by ``csrc/posbias.cu``), and their gradients reduced by prefix-sum scans.
 """
 
 from __future__ import annotations
@@ -36,10 +38,26 @@ class AttnArgs(ctypes.Structure):
         ("doc_tiles", c_void_p),
     ]
 
+
+class PosBiasArgs(ctypes.Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k", c_void_p), ("ldq", c_ll), ("ldk", c_ll),
+        ("pos_k", c_void_p), ("pos_q", c_void_p), ("ld_pos", c_ll),
+        ("lut_c2p", c_void_p), ("lut_p2c", c_void_p), ("lut_c2p_host", c_void_p), ("lut_p2c_host", c_void_p),
+        ("B", c_int), ("S", c_int), ("heads", c_int), ("span2", c_int),
+        ("bias", c_void_p), ("ldb", c_ll), ("dbias", c_void_p),
+        ("dq_acc", c_void_p), ("dk", c_void_p), ("ld_dk", c_ll),
+        ("d_pos_k", c_void_p), ("d_pos_q", c_void_p),
+    ]
+
+
 # Up to this sequence length the position terms are pre-gathered into a key-indexed
 # [B, heads, S, S] bf16 bias (contiguous vector loads in the attention kernels); beyond it the
 # kernels gather from the bucket-indexed tables directly, which needs no S x S storage.
 BIAS_MODE_MAX_SEQ = 1024
+# Build the bias and reduce its gradient with the tensor-core kernels of posbias_tc.cu (False: score-table path).
+POSBIAS_TENSOR_CORE = True
+_TC_REJECTED = -13  # launcher: this bucket map / table size needs the table path
 
 
 _LUT_CACHE: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
@@ -52,9 +70,28 @@ def _luts(S: int, bucket_size: int, max_position: int, att_span: int, device) ->
         from .attention import relative_position_luts
 
         c2p, p2c = relative_position_luts(S, S, bucket_size, max_position, att_span)
-        hit = (c2p.to(torch.int16).to(device), p2c.to(torch.int16).to(device))
+        c2p, p2c = c2p.to(torch.int16).contiguous(), p2c.to(torch.int16).contiguous()
+        hit = (c2p.to(device), p2c.to(device))
         _LUT_CACHE[key] = hit
+        _LUT_HOST[(hit[0].data_ptr(), hit[1].data_ptr())] = (c2p, p2c)
     return hit
+
+
+_LUT_HOST: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _posbias_args(q, k, pos_k, pos_q, luts, heads: int, span2: int) -> PosBiasArgs:
+    B, S, _ = q.shape
+    host = _LUT_HOST[(luts[0].data_ptr(), luts[1].data_ptr())]
+    a = PosBiasArgs()
+    a.q, a.k, a.ldq, a.ldk = q.data_ptr(), k.data_ptr(), q.stride(1), k.stride(1)
+    a.pos_k = None if pos_k is None else pos_k.data_ptr()
+    a.pos_q = None if pos_q is None else pos_q.data_ptr()
+    a.ld_pos = (pos_k if pos_k is not None else pos_q).stride(0)
+    a.lut_c2p, a.lut_p2c = luts[0].data_ptr(), luts[1].data_ptr()
+    a.lut_c2p_host, a.lut_p2c_host = host[0].data_ptr(), host[1].data_ptr()
+    a.B, a.S, a.heads, a.span2 = B, S, heads, span2
+    return a
 
 
 _RANGE_CACHE: dict[tuple, tuple] = {}
@@ -136,6 +173,42 @@ def rope_supported(q, k, v, heads, rotary_dim, pair_keep, dropout_p, training) -
     return _common_ok(q, k, v, heads, pair_keep, dropout_p, training)
 
 
+def _score_tables(q, k, pos_k, pos_q, heads: int):
+    """``C2P = Q·PosKᵀ`` and ``P2C = K·PosQᵀ`` as ``[tokens, heads, 2·span]`` bf16 tables (batched GEMM per head)."""
+    B, S, H = q.shape
+    T = B * S
+    q2 = q.as_strided((T, H), (q.stride(1), 1), q.storage_offset())
+    k2 = k.as_strided((T, H), (k.stride(1), 1), k.storage_offset())
+    c2p = p2c = None
+    if pos_k is not None:
+        c2p = torch.empty((T, heads, pos_k.shape[0]), dtype=torch.bfloat16, device=q.device)
+        gemm(_heads_view(q2, heads), _heads_view(pos_k, heads), out=c2p.permute(1, 0, 2))
+    if pos_q is not None:
+        p2c = torch.empty((T, heads, pos_q.shape[0]), dtype=torch.bfloat16, device=q.device)
+        gemm(_heads_view(k2, heads), _heads_view(pos_q, heads), out=p2c.permute(1, 0, 2))
+    return c2p, p2c
+
+
+def position_bias(q, k, pos_k, pos_q, luts, heads: int, tensor_core: bool | None = None):
+    """Key-indexed position bias ``[B, heads, S, ldb]`` (unscaled, bf16) and whether the tensor-core kernel built it.
+
+    ``q``/``k``: token-major ``[B, S, heads·64]`` bf16; ``pos_k``/``pos_q``: ``[2·span, heads·64]`` or ``None``.
+    """
+    B, S, _ = q.shape
+    span2 = (pos_k if pos_k is not None else pos_q).shape[0]
+    ldb = (S + 127) // 128 * 128
+    bias = torch.empty((B, heads, S, ldb), dtype=torch.bfloat16, device=q.device)
+    if POSBIAS_TENSOR_CORE if tensor_core is None else tensor_core:
+        pa = _posbias_args(q, k, pos_k, pos_q, luts, heads, span2)
+        pa.bias, pa.ldb = bias.data_ptr(), ldb
+        if _lib.call_rc("db200_posbias_tc_fwd", ctypes.byref(pa), _lib.stream_ptr(), accept=(_TC_REJECTED,)) == 0:
+            return bias, True
+    c2p, p2c = _score_tables(q, k, pos_k, pos_q, heads)
+    _lib.call("db200_posbias_build", _lib.ptr(c2p), _lib.ptr(p2c), _lib.ptr(luts[0]), _lib.ptr(luts[1]),
+              _lib.ptr(bias), c_int(B), c_int(S), c_int(ldb), c_int(heads), c_int(span2), _lib.stream_ptr())
+    return bias, False
+
+
 class _FlashAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, pos_k, pos_q, heads, scale, luts, key_keep, doc_ids):
@@ -144,30 +217,21 @@ class _FlashAttention(torch.autograd.Function):
         T = B * S
         out = torch.empty((B, S, H), dtype=torch.bfloat16, device=q.device)
         lse = torch.empty((B, heads, S), dtype=torch.float32, device=q.device)
-        q2, k2 = q.as_strided((T, H), (q.stride(1), 1), q.storage_offset()), k.as_strided((T, H), (k.stride(1), 1), k.storage_offset())
         c2p = p2c = None
-        span2 = 0
-        if pos_k is not None:
-            span2 = pos_k.shape[0]
-            c2p = torch.empty((T, heads, span2), dtype=torch.bfloat16, device=q.device)
-            gemm(_heads_view(q2, heads), _heads_view(pos_k, heads), out=c2p.permute(1, 0, 2))
-        if pos_q is not None:
-            span2 = pos_q.shape[0]
-            p2c = torch.empty((T, heads, span2), dtype=torch.bfloat16, device=q.device)
-            gemm(_heads_view(k2, heads), _heads_view(pos_q, heads), out=p2c.permute(1, 0, 2))
+        span2 = 0 if pos_k is None and pos_q is None else (pos_k if pos_k is not None else pos_q).shape[0]
+        ldb = (S + 127) // 128 * 128
+        bias = None
+        tc_bias = False
+        if span2 and S <= BIAS_MODE_MAX_SEQ:
+            bias, tc_bias = position_bias(q, k, pos_k, pos_q, luts, heads)
+        elif span2:
+            c2p, p2c = _score_tables(q, k, pos_k, pos_q, heads)
         kk = None if key_keep is None else key_keep.to(torch.uint8).contiguous()
         dd = None if doc_ids is None else doc_ids.to(torch.int32).contiguous()
         tiles = None
         if dd is not None:  # id range of every 128-token tile: the kernels visit only tiles that share a document
             tiles = torch.empty((B, (S + 127) // 128, 2), dtype=torch.int32, device=q.device)
             _lib.call("db200_attn_doc_tiles", _lib.ptr(dd), _lib.ptr(tiles), c_int(B), c_int(S), _lib.stream_ptr())
-        bias = None
-        ldb = (S + 127) // 128 * 128
-        if span2 and S <= BIAS_MODE_MAX_SEQ:
-            bias = torch.empty((B, heads, S, ldb), dtype=torch.bfloat16, device=q.device)
-            _lib.call("db200_posbias_build", _lib.ptr(c2p), _lib.ptr(p2c), _lib.ptr(luts[0]), _lib.ptr(luts[1]),
-                      _lib.ptr(bias), c_int(B), c_int(S), c_int(ldb), c_int(heads), c_int(span2), _lib.stream_ptr())
-            c2p = p2c = None  # only the key-indexed form is needed from here on
         a = AttnArgs()
         a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
         a.ldq, a.ldk, a.ldv = q.stride(1), k.stride(1), v.stride(1)
@@ -184,13 +248,13 @@ class _FlashAttention(torch.autograd.Function):
         a.doc_tiles = None if tiles is None else tiles.data_ptr()
         _lib.call("db200_attn_fwd", ctypes.byref(a), _lib.stream_ptr())
         ctx.save_for_backward(q, k, v, out, lse, c2p, p2c, pos_k, pos_q, kk, dd, bias, tiles)
-        ctx.meta = (heads, scale, luts, span2)
+        ctx.meta = (heads, scale, luts, span2, tc_bias)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse, c2p, p2c, pos_k, pos_q, kk, dd, bias, tiles = ctx.saved_tensors
-        heads, scale, luts, span2 = ctx.meta
+        heads, scale, luts, span2, tc_bias = ctx.meta
         B, S, H = q.shape
         T = B * S
         dev = q.device
@@ -228,7 +292,21 @@ class _FlashAttention(torch.autograd.Function):
         d_pos_k = d_pos_q = None
         g_c2p = None if d_c2p is None else d_c2p.to(torch.bfloat16)
         g_p2c = None if d_p2c is None else d_p2c.to(torch.bfloat16)
-        if bias is not None:  # reduce the key-indexed bias gradient back onto the bucket-indexed tables
+        tc_done = False
+        if bias is not None and tc_bias and POSBIAS_TENSOR_CORE:
+            # fold the bias gradient onto the bucket axis and multiply it into dQ, dK and the table gradients in one kernel
+            pa = _posbias_args(q, k, pos_k, pos_q, luts, heads, span2)
+            pa.dbias, pa.ldb = dbias.data_ptr(), bias.shape[-1]
+            pa.dq_acc, pa.dk, pa.ld_dk = dq_acc.data_ptr(), dk.data_ptr(), 3 * H
+            gk = None if pos_k is None else torch.zeros(pos_k.shape, dtype=torch.float32, device=dev)
+            gq = None if pos_q is None else torch.zeros(pos_q.shape, dtype=torch.float32, device=dev)
+            pa.d_pos_k = None if gk is None else gk.data_ptr()
+            pa.d_pos_q = None if gq is None else gq.data_ptr()
+            if _lib.call_rc("db200_posbias_tc_bwd", ctypes.byref(pa), _lib.stream_ptr(), accept=(_TC_REJECTED,)) == 0:
+                tc_done = True
+                d_pos_k = None if gk is None else gk.to(pos_k.dtype)
+                d_pos_q = None if gq is None else gq.to(pos_q.dtype)
+        if bias is not None and not tc_done:  # reduce the key-indexed bias gradient back onto the bucket-indexed tables
             for which, tab in ((0, pos_k), (1, pos_q)):
                 if tab is None:
                     continue

@@ -76,6 +76,35 @@ def bench_attention(a) -> None:
               f"fwd+bwd {both:.0f} us")
 
 
+def bench_posbias(a) -> None:
+    """Position-bias kernels in isolation: tensor-core tile kernels against the score-table path."""
+    import ctypes
+
+    from deberta_b200.ops import _lib, attention_cuda as ac
+
+    h, span = a.heads, 256
+    H = h * 64
+    q, k = _rand(a.batch, a.seq, H), _rand(a.batch, a.seq, H)
+    pk, pq = _rand(2 * span, H), _rand(2 * span, H)
+    luts = ac._luts(a.seq, 256, 512, span, q.device)
+    for name, tc in (("tensor cores", True), ("score tables + gather", False)):
+        us = _time(lambda: ac.position_bias(q, k, pk, pq, luts, h, tensor_core=tc), a.iters)
+        print(f"position bias fwd [{name}] B={a.batch} S={a.seq} h={h}: {us:.0f} us")
+    bias, _ = ac.position_bias(q, k, pk, pq, luts, h, tensor_core=True)
+    dbias = _rand(*bias.shape, scale=0.1)
+    T = a.batch * a.seq
+    dq_acc = torch.zeros(T, H, dtype=torch.float32, device="cuda")
+    dk = torch.zeros(T, 3 * H, dtype=torch.bfloat16, device="cuda")[:, H:2 * H]
+    gk, gq = (torch.zeros(2 * span, H, dtype=torch.float32, device="cuda") for _ in range(2))
+    pa = ac._posbias_args(q, k, pk, pq, luts, h, 2 * span)
+    pa.dbias, pa.ldb = dbias.data_ptr(), bias.shape[-1]
+    pa.dq_acc, pa.dk, pa.ld_dk = dq_acc.data_ptr(), dk.data_ptr(), 3 * H
+    pa.d_pos_k, pa.d_pos_q = gk.data_ptr(), gq.data_ptr()
+    us = _time(lambda: _lib.call("db200_posbias_tc_bwd", ctypes.byref(pa), _lib.stream_ptr()), a.iters)
+    print(f"position bias bwd [tensor cores] B={a.batch} S={a.seq} h={h}: {us:.0f} us")
+    _lib.check_status()
+
+
 def bench_vocab_ce(a) -> None:
     from deberta_b200.ops.heads import mlm_loss_and_sample, mlm_loss_and_sample_reference
 
@@ -108,13 +137,13 @@ def bench_layer(a) -> None:
 
 def main() -> None:
     p = argparse.ArgumentParser()
-    p.add_argument("op", choices=("gemm", "ffn", "attention", "vocab_ce", "layer"))
+    p.add_argument("op", choices=("gemm", "ffn", "attention", "posbias", "vocab_ce", "layer"))
     p.add_argument("--batch", type=int, default=32)
     p.add_argument("--seq", type=int, default=512)
     p.add_argument("--heads", type=int, default=12)
     p.add_argument("--iters", type=int, default=5)
     a = p.parse_args()
-    {"gemm": bench_gemm, "ffn": bench_ffn, "attention": bench_attention, "vocab_ce": bench_vocab_ce, "layer": bench_layer}[a.op](a)
+    {"gemm": bench_gemm, "ffn": bench_ffn, "attention": bench_attention, "posbias": bench_posbias, "vocab_ce": bench_vocab_ce, "layer": bench_layer}[a.op](a)
 
 
 if __name__ == "__main__":

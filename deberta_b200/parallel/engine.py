@@ -120,7 +120,8 @@ class TrainEngine:
     def __init__(self, model: nn.Module, ctx: DistContext, *, compute_dtype: torch.dtype = torch.float32,
                  parallelism: str = "ddp", decoupled: bool = True, lr_generator: float = 5e-4,
                  lr_discriminator: float = 5e-4, weight_decay: float = 0.01, betas: tuple[float, float] = (0.9, 0.999),
-                 eps: float = 1e-8) -> None:
+                 eps: float = 1e-8, fused_collectives: bool = True, multicast: str = "auto",
+                 comm_timeout_s: float = 20.0) -> None:
         if parallelism not in ("ddp", "zero"):
             raise ValueError("parallelism must be 'ddp' or 'zero'")
         self.model, self.ctx, self.parallelism = model, ctx, parallelism
@@ -153,10 +154,12 @@ class TrainEngine:
         dev = self.device
         self.master = torch.zeros(total, dtype=torch.float32, device=dev)
         self.comm = None
-        if compute_dtype == torch.bfloat16 and fused_comm_wanted(world, dev):
+        if compute_dtype == torch.bfloat16 and fused_comm_wanted(world, dev, fused_collectives):
             # gradient and parameter buffers live in memory every rank of the node can address
             try:
-                self.comm = PeerComm(total, rank=ctx.rank, world_size=world, device=dev)
+                self.comm = PeerComm(total, rank=ctx.rank, world_size=world, device=dev,
+                                     use_multicast={"on": True, "off": False}.get(str(multicast), None),
+                                     timeout_s=float(comm_timeout_s))
             except Exception as e:  # no peer access / symmetric allocator unavailable: NCCL collectives instead
                 import logging
 
@@ -294,8 +297,13 @@ class TrainEngine:
         return self.optimizers[opt_name].norm_sq.sqrt().squeeze(0)
 
     # ---- update ---------------------------------------------------------------------------------
-    def step(self, opt_name: str, *, lr_scale: float = 1.0, max_grad_norm: float = 0.0) -> None:
-        """AdamW over the optimizer's (local shard of the) range, clip + finite guard on the device."""
+    def step(self, opt_name: str, *, lr_scale: float = 1.0, max_grad_norm: float = 0.0,
+             gate: torch.Tensor | None = None) -> None:
+        """AdamW over the optimizer's (local shard of the) range, clip + finite guard on the device.
+
+        ``gate`` (one float, the same on every rank): the update is skipped when it is not positive. On a GPU the
+        decision is taken inside the kernel and the caller corrects ``step`` later; on the CPU it is taken here.
+        """
         o = self.optimizers[opt_name]
         o.step += 1
         b1, b2 = o.betas
@@ -308,11 +316,14 @@ class TrainEngine:
                     for sg in o.segments if max(sg.start, s0) < min(sg.end, s1)]
             self.comm.adamw(s0, s1 - s0, master=self.master[s0:s1], exp_avg=o.exp_avg, exp_avg_sq=o.exp_avg_sq,
                             segments=segs, betas=o.betas, eps=o.eps, inv_bc1=inv_bc1, inv_sqrt_bc2=inv_sqrt_bc2,
-                            max_norm=max_grad_norm, epoch=o.epoch, norm_sq_out=o.norm_sq)
+                            max_norm=max_grad_norm, epoch=o.epoch, norm_sq_out=o.norm_sq,
+                            gate=None if gate is None else gate.to(torch.float32).reshape(1))
             return
+        if gate is not None:
+            gate = gate.to(device=self.device, dtype=torch.float32).reshape(1)
         if not self.use_kernels:
             norm = float(o.norm_sq.sqrt())
-            if not math.isfinite(norm):
+            if not math.isfinite(norm) or (gate is not None and not float(gate) > 0.0):
                 skipped = True
             coef = min(1.0, max_grad_norm / (norm + 1e-6)) if (max_grad_norm > 0 and not skipped) else 1.0
         for seg in o.segments:
@@ -328,7 +339,7 @@ class TrainEngine:
                 _lib.call("db200_adamw", _lib.ptr(p), _lib.ptr(g), _lib.ptr(m), _lib.ptr(v), _lib.ptr(shadow),
                           ctypes.c_longlong(b - a), c_f(lr), c_f(seg.weight_decay), c_f(b1), c_f(b2), c_f(o.eps),
                           c_f(inv_bc1), c_f(inv_sqrt_bc2), _lib.ptr(o.norm_sq), c_f(max_grad_norm), c_f(1.0),
-                          _lib.stream_ptr())
+                          _lib.ptr(gate), _lib.stream_ptr())
             elif not skipped:
                 gg = g * coef if coef != 1.0 else g
                 p.mul_(1.0 - lr * seg.weight_decay)

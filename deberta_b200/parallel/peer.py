@@ -54,11 +54,9 @@ class AdamSegment(ctypes.Structure):
                 ("weight_decay", ctypes.c_float)]
 
 
-def fused_comm_wanted(world_size: int, device: torch.device) -> bool:
-    """Fused collectives are the default on 2..8 GPUs of one node; ``DEBERTA_FUSED_COMM=0`` keeps NCCL."""
-    if device.type != "cuda" or not (2 <= world_size <= MAX_WORLD):
-        return False
-    if os.environ.get("DEBERTA_FUSED_COMM", "1").strip().lower() in ("0", "false", "no", "off"):
+def fused_comm_wanted(world_size: int, device: torch.device, enabled: bool = True) -> bool:
+    """Fused collectives serve 2..8 GPUs of one node (``train.distributed.fused_collectives``); otherwise NCCL."""
+    if not enabled or device.type != "cuda" or not (2 <= world_size <= MAX_WORLD):
         return False
     local_world = int(os.environ.get("LOCAL_WORLD_SIZE", str(world_size)))
     return local_world == world_size  # peer mappings need all ranks on one node
@@ -87,8 +85,7 @@ class PeerComm:
         if use_multicast is None:
             # measured: at 2 ranks plain peer loads/stores are faster (1.11 vs 1.64 ms); at 8 ranks the switch reduction
             # is as fast for the sharded step and faster for the all-reduce (1.43 vs 1.93 ms)
-            env = os.environ.get("DEBERTA_COMM_MULTICAST", "").strip().lower()
-            use_multicast = (world_size >= 4) if env == "" else env in ("1", "true", "yes", "on")
+            use_multicast = world_size >= 4
         mc_g = int(getattr(hg, "multicast_ptr", 0) or 0) if use_multicast else 0
         mc_w = int(getattr(hw, "multicast_ptr", 0) or 0) if (use_multicast and hw is not None) else 0
         self.multicast = bool(mc_g)
@@ -158,8 +155,12 @@ class PeerComm:
 
     def adamw(self, offset: int, count: int, *, master: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor,
               segments: Sequence[tuple[int, int, float, float]], betas: tuple[float, float], eps: float, inv_bc1: float,
-              inv_sqrt_bc2: float, max_norm: float, epoch: int, norm_sq_out: torch.Tensor | None) -> None:
-        """AdamW on the slab reduced under ``epoch``; ``segments`` = (begin, end, lr, weight_decay) inside the slab."""
+              inv_sqrt_bc2: float, max_norm: float, epoch: int, norm_sq_out: torch.Tensor | None,
+              gate: torch.Tensor | None = None) -> None:
+        """AdamW on the slab reduced under ``epoch``; ``segments`` = (begin, end, lr, weight_decay) inside the slab.
+
+        ``gate``: optional device float, identical on all ranks; the update is skipped when it is not positive.
+        """
         if self.params is None:
             raise RuntimeError("PeerComm was built without a parameter buffer")
         arr = (AdamSegment * max(1, len(segments)))()
@@ -169,7 +170,7 @@ class PeerComm:
         _lib.call("db200_comm_adamw", ctypes.byref(self.ctx), ctypes.c_longlong(offset), ctypes.c_longlong(count),
                   _lib.ptr(master), _lib.ptr(exp_avg), _lib.ptr(exp_avg_sq), arr, ctypes.c_int(len(segments)),
                   cf(betas[0]), cf(betas[1]), cf(eps), cf(inv_bc1), cf(inv_sqrt_bc2), cf(max_norm),
-                  ctypes.c_uint(epoch & 0xFFFFFFFF), _lib.ptr(norm_sq_out), _lib.stream_ptr())
+                  ctypes.c_uint(epoch & 0xFFFFFFFF), _lib.ptr(norm_sq_out), _lib.ptr(gate), _lib.stream_ptr())
 
     def vector_sum(self, values: torch.Tensor) -> torch.Tensor:
         """Sum a float vector of at most ``VEC_MAX`` entries over all ranks (result on the device)."""

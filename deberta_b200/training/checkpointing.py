@@ -40,10 +40,15 @@ def normalize_resume_consumed_micro_batches(*, consumed_micro_batches: int, glob
     return boundary
 
 
+def checkpoint_is_due(*, global_step: int, save_steps: int, last_saved_step: int) -> bool:
+    """True when ``global_step`` is a multiple of ``save_steps`` that has not been saved yet."""
+    return bool(save_steps) and int(save_steps) > 0 and global_step % int(save_steps) == 0 and last_saved_step != global_step
+
+
 def save_periodic_checkpoint_if_due(*, ctx: Any, save_state, output_dir: Path, global_step: int, save_steps: int,
                                     last_saved_step: int, **kw: Any) -> int:
     """Save ``checkpoint-<step>`` when ``global_step`` hits a multiple of ``save_steps``; returns the last saved step."""
-    if not save_steps or int(save_steps) <= 0 or global_step % int(save_steps) != 0 or last_saved_step == global_step:
+    if not checkpoint_is_due(global_step=global_step, save_steps=save_steps, last_saved_step=last_saved_step):
         return last_saved_step
     save_training_checkpoint(ctx=ctx, save_state=save_state, checkpoint_dir=Path(output_dir) / f"checkpoint-{global_step}",
                              output_dir=Path(output_dir), log_label="periodic", global_step=global_step, **kw)

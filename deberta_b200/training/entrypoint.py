@@ -9,40 +9,36 @@ logging/checkpoints → final checkpoint → HF export. Distribution is this pac
 
 from __future__ import annotations
 
+import contextlib
 import logging
-import os
 import time
 from pathlib import Path
 from typing import Any
 
 import torch
 
-from deberta_b200.config import (DataConfig, LoggingConfig, ModelConfig, OptimConfig, TrainConfig,
-                                 _sync_legacy_train_aliases, asdict_without_private, validate_config, Config)
+from deberta_b200.config import (Config, DataConfig, LoggingConfig, ModelConfig, OptimConfig, TrainConfig,
+                                 _sync_legacy_train_aliases, validate_config)
 from deberta_b200.parallel.dist import DistContext, init_distributed
 from deberta_b200.run_layout import FINAL_HF_DIR
 from deberta_b200.utils.checkpoint import load_training_state, save_training_state
 from deberta_b200.utils.log import setup_process_logging
+from deberta_b200.utils.trace import set_nvtx
 
-from .checkpointing import (normalize_resume_consumed_micro_batches, resolve_data_resume_policy,
+from .checkpointing import (checkpoint_is_due, normalize_resume_consumed_micro_batches, resolve_data_resume_policy,
                             save_periodic_checkpoint_if_due)
 from .export_helpers import export_discriminator_hf_subprocess
-from .metrics import append_metrics_jsonl_row, flush_loggers, write_nonfinite_debug_artifact
-from .run_config import persist_or_validate_run_configs
+from .metrics import (append_metrics_jsonl_row, build_runtime_resolved_config, flush_loggers,
+                      write_nonfinite_debug_artifact)
+from .run_config import persist_or_validate_run_configs, write_runtime_resolved_config
 from .run_management import (load_checkpoint_progress_metadata, prepare_output_dir, resolve_output_dir_for_ranks,
                              resolve_resume_checkpoint_for_ranks, save_training_checkpoint)
 from .runtime import (build_dataloader, build_engine, build_model, build_tokenizer, build_training_dataset_and_collator,
                       cycle_dataloader)
-from .tracker_utils import init_trackers, setup_wandb_watch
+from .tracker_utils import init_trackers, setup_wandb_watch, upload_wandb_config_files
 from .trainer import Trainer
 
 logger = logging.getLogger(__name__)
-
-
-def _parallelism_from_env() -> str:
-    """``DEBERTA_PARALLELISM=ddp|zero`` selects replicated or sharded optimizer state (default ``zero``)."""
-    value = os.environ.get("DEBERTA_PARALLELISM", "zero").strip().lower()
-    return value if value in {"ddp", "zero"} else "zero"
 
 
 def _resolve_dirs(ctx: DistContext, train_cfg: TrainConfig, logging_cfg: LoggingConfig, config_path) -> tuple[Path, Path]:
@@ -117,24 +113,37 @@ def run_pretraining(*, model_cfg: ModelConfig, data_cfg: DataConfig, train_cfg: 
                                                             process_index=ctx.rank, num_processes=ctx.world_size,
                                                             hf_dataset=hf_dataset)
     loader = build_dataloader(dataset=dataset, collator=collator, train_cfg=train_cfg)
-    model, _, _ = build_model(model_cfg=model_cfg, tokenizer=tok, max_seq_length=int(data_cfg.packing.max_seq_length),
-                              load_pretrained_weights=resume is None)
-    engine = build_engine(model=model, ctx=ctx, train_cfg=train_cfg, optim_cfg=optim_cfg,
-                          parallelism=_parallelism_from_env())
+    model, disc_cfg, gen_cfg = build_model(model_cfg=model_cfg, tokenizer=tok,
+                                           max_seq_length=int(data_cfg.packing.max_seq_length),
+                                           load_pretrained_weights=resume is None)
+    set_nvtx(bool(logging_cfg.debug.nvtx))
+    engine = build_engine(model=model, ctx=ctx, train_cfg=train_cfg, optim_cfg=optim_cfg)
     trainer = Trainer(model=model, engine=engine, ctx=ctx, train_cfg=train_cfg, optim_cfg=optim_cfg,
                       pad_token_id=getattr(tok, "pad_token_id", None))
     model.sync_discriminator_embeddings_from_generator()
+    # what the run really uses (derived generator shape, vocabulary size, collective path) goes to config_resolved.yaml
+    # and to the tracker instead of the raw sections (``entrypoint.py:619-633`` of the reference)
+    resolved = build_runtime_resolved_config(
+        sections=sections, disc_config=disc_cfg, gen_config=gen_cfg, tokenizer=tok,
+        runtime={"world_size": ctx.world_size, "device": str(engine.device), "parallelism": engine.parallelism,
+                 "compute_dtype": str(engine.compute_dtype).replace("torch.", ""),
+                 "collectives": ("peer-memory kernels" + (" (multimem)" if engine.comm.multicast else ""))
+                 if engine.comm is not None else ("nccl" if ctx.backend == "nccl" else (ctx.backend or "none"))})
+    if ctx.is_main_process:
+        write_runtime_resolved_config(logging_dir=log_dir, payload=resolved)
     trackers = init_trackers(logging_cfg=logging_cfg, logging_dir=log_dir, run_name=logging_cfg.run_name,
-                             config_payload={k: asdict_without_private(v) for k, v in sections.items()},
-                             is_main_process=ctx.is_main_process)
+                             config_payload=resolved, is_main_process=ctx.is_main_process)
     setup_wandb_watch(tracker=trackers, model=model, watch_mode=logging_cfg.wandb.watch,
                       log_freq=logging_cfg.wandb.watch_log_freq)
+    if ctx.is_main_process and logging_cfg.wandb.enabled:
+        upload_wandb_config_files(tracker=trackers, logging_dir=log_dir, config_source_path=config_path,
+                                  run_name=logging_cfg.run_name)
     metrics_path = log_dir / "metrics.jsonl.gz"
     debug_dir = log_dir / "debug"
-    if logging_cfg.debug.metrics or True:
-        trainer.on_nonfinite = lambda step, norms: ctx.is_main_process and write_nonfinite_debug_artifact(
-            debug_dir=debug_dir, step=step, what="grad_norm", losses={}, lrs=trainer.current_lrs(),
-            lr_mult=trainer.lr_mult, extra={"grad_norms": {k: repr(v) for k, v in norms.items()}})
+    # a skipped (non-finite) window always leaves a debug record, as in the reference (``training/metrics.py:195-272``)
+    trainer.on_nonfinite = lambda step, norms: ctx.is_main_process and write_nonfinite_debug_artifact(
+        debug_dir=debug_dir, step=step, what="grad_norm", losses={}, lrs=trainer.current_lrs(),
+        lr_mult=trainer.lr_mult, extra={"grad_norms": {k: repr(v) for k, v in norms.items()}})
 
     # ---- resume --------------------------------------------------------------------------------------
     start_epoch = 0
@@ -174,44 +183,75 @@ def run_pretraining(*, model_cfg: ModelConfig, data_cfg: DataConfig, train_cfg: 
         save_training_state(directory, engine=engine, trainer=trainer, ctx=ctx)
 
     save_kw = dict(save_total_limit=int(ck.save_total_limit), optimizer_param_digest=digest, gradient_accumulation_steps=ga)
-    watchdog = None
-    deadline = float(os.environ.get("DEBERTA_STEP_DEADLINE_S", "0") or 0)
-    if deadline > 0:  # host-side liveness report when no optimizer step completes in time (off by default)
+    watchdog = heartbeat = None
+    di = train_cfg.distributed
+    if float(di.step_deadline_s) > 0:  # host-side liveness report when no optimizer step completes in time
         from .watchdog import StepWatchdog
 
-        watchdog = StepWatchdog(deadline, report_dir=out_dir / "watchdog").start()
+        watchdog = StepWatchdog(float(di.step_deadline_s), report_dir=out_dir / "watchdog").start()
+    if float(di.heartbeat_s) > 0 and ctx.distributed:
+        # every rank reports (step, time) through the process-group store; a rank whose report is older than the
+        # limit is named in an error before the next window is queued, instead of a collective waiting for it
+        import torch.distributed as dist
+
+        from .watchdog import RankHeartbeat
+
+        heartbeat = RankHeartbeat(dist.distributed_c10d._get_default_store(), ctx.rank, ctx.world_size)
+        heartbeat.beat(trainer.global_step)
+        ctx.wait_for_everyone()
+    weights = (float(train_cfg.objective.gen_loss_weight), float(train_cfg.objective.disc_loss_weight))
+    tokens_seen_global = 0.0
     try:
         while trainer.global_step < max_steps:
+            if heartbeat is not None:
+                stale = heartbeat.stale_ranks(float(di.heartbeat_s))
+                if stale:
+                    raise RuntimeError(f"rank(s) {stale} sent no heartbeat for {float(di.heartbeat_s):.0f} s "
+                                       f"(last completed step {trainer.global_step}); stopping before the next collective.")
             stats = trainer.train_window([next(batches) for _ in range(ga)])
             if watchdog is not None:
                 watchdog.beat(trainer.global_step)
+            if heartbeat is not None:
+                heartbeat.beat(trainer.global_step)
             pending.append(stats)
             tokens_seen += stats.input_tokens
             step = trainer.global_step
             if log_every > 0 and (step % log_every == 0 or step == max_steps):
-                row = _reduce_window_stats(ctx, pending, engine.device)
+                row = _reduce_window_stats(ctx, pending, engine.device, loss_weights=weights)
                 now = time.perf_counter()
                 global_tokens = float(ctx.reduce(torch.tensor([tokens_seen - tok_last], dtype=torch.float64), "sum")[0])
-                row.update(step=step, lr=trainer.current_lrs(), lr_mult=trainer.lr_mult,
+                tokens_seen_global += global_tokens
+                lrs = trainer.current_lrs()
+                # `lr` is the discriminator's (the schedule the reference reports, ``entrypoint.py:1493-1501``)
+                row.update(step=step, lr=float(lrs.get("discriminator", next(iter(lrs.values())))), lr_mult=trainer.lr_mult,
                            input_tokens_per_sec=global_tokens / max(now - t_last, 1e-9),
-                           input_tokens_seen=tokens_seen, skipped_steps=trainer.skipped_steps)
+                           input_tokens_seen=tokens_seen_global, skipped_steps=trainer.skipped_steps,
+                           **{f"lr_{name}": float(v) for name, v in lrs.items()})
                 t_last, tok_last, pending = now, tokens_seen, []
                 if ctx.is_main_process:
-                    logger.info("step %d | loss %.4f | gen %.4f | disc %.4f | acc %.4f | %.0f tok/s", step, row["loss"],
-                                row["gen_loss"], row["disc_loss"], row["disc_acc"], row["input_tokens_per_sec"])
+                    logger.info("step %d | loss %.4f | gen %.4f | disc %.4f | acc %.4f | lr %.3e | %.0f tok/s", step,
+                                row["loss"], row["gen_loss"], row["disc_loss"], row["disc_acc"], row["lr"],
+                                row["input_tokens_per_sec"])
                     trackers.log({k: v for k, v in row.items() if isinstance(v, (int, float))}, step)
                     if logging_cfg.debug.metrics:
                         append_metrics_jsonl_row(metrics_path, row)
                 summary.update(row)
-            last_saved = save_periodic_checkpoint_if_due(
-                ctx=ctx, save_state=save_state, output_dir=out_dir, global_step=step, save_steps=int(ck.save_steps),
-                last_saved_step=last_saved, consumed_micro_batches=trainer.consumed_micro_batches,
-                lr_mult=trainer.lr_mult, **save_kw)
+            if checkpoint_is_due(global_step=step, save_steps=int(ck.save_steps), last_saved_step=last_saved):
+                trainer.resolve_pending()  # on every rank, before anything of the optimizer or the LR multiplier is read
+                last_saved = save_periodic_checkpoint_if_due(
+                    ctx=ctx, save_state=save_state, output_dir=out_dir, global_step=step, save_steps=int(ck.save_steps),
+                    last_saved_step=last_saved, consumed_micro_batches=trainer.consumed_micro_batches,
+                    lr_mult=trainer.lr_mult, **save_kw)
+        trainer.resolve_pending()  # the last window's outcome (kernel status, skipped update) before the run ends
     except BaseException as exc:
         crashed = True
         if ctx.is_main_process:
-            append_metrics_jsonl_row(metrics_path, {"event": "crash", "step": trainer.global_step,
-                                                    "error": f"{type(exc).__name__}: {exc}"})
+            crash_row = {"event": "crash", "step": trainer.global_step, "crash": 1,
+                         "error": f"{type(exc).__name__}: {exc}"}
+            append_metrics_jsonl_row(metrics_path, crash_row)
+            with contextlib.suppress(Exception):  # the tracker gets the row too (``entrypoint.py:1886-2005``)
+                trackers.log({"crash": 1, "crash_step": trainer.global_step}, trainer.global_step)
+                trackers.set_summary({"crashed": True, "crash_type": type(exc).__name__, "crash_step": trainer.global_step})
         raise
     finally:
         if watchdog is not None:
@@ -220,6 +260,8 @@ def run_pretraining(*, model_cfg: ModelConfig, data_cfg: DataConfig, train_cfg: 
         # a crash checkpoint is only safe without peers (a collective save could deadlock on a dead rank)
         if (not crashed or ctx.world_size == 1) and trainer.global_step > 0 and last_saved != trainer.global_step:
             try:
+                with contextlib.suppress(Exception):
+                    trainer.resolve_pending()
                 save_training_checkpoint(ctx=ctx, save_state=save_state,
                                          checkpoint_dir=out_dir / f"checkpoint-{trainer.global_step}", output_dir=out_dir,
                                          consumed_micro_batches=trainer.consumed_micro_batches, log_label="final",
@@ -237,8 +279,12 @@ def run_pretraining(*, model_cfg: ModelConfig, data_cfg: DataConfig, train_cfg: 
     return summary
 
 
-def _reduce_window_stats(ctx: DistContext, windows: list[Any], device: torch.device) -> dict[str, float]:
-    """Globally token-weighted means over the windows since the last log line (one small all-reduce)."""
+def _reduce_window_stats(ctx: DistContext, windows: list[Any], device: torch.device,
+                         loss_weights: tuple[float, float] = (1.0, 1.0)) -> dict[str, float]:
+    """Globally token-weighted means over the windows since the last log line (one small all-reduce).
+
+    ``loss`` is the combined objective ``w_g·gen + w_d·disc`` (``rtd.py:1241-1244`` of the reference).
+    """
     acc = torch.zeros(6, dtype=torch.float32, device=device)
     zero_gen = zero_disc = 0
     for w in windows:
@@ -249,5 +295,6 @@ def _reduce_window_stats(ctx: DistContext, windows: list[Any], device: torch.dev
     acc = ctx.reduce(acc, "sum").cpu()
     g_tok, d_tok = max(float(acc[4]), 1.0), max(float(acc[5]), 1.0)
     gen, disc = float(acc[0]) / g_tok, float(acc[1]) / d_tok
-    return {"gen_loss": gen, "disc_loss": disc, "loss": gen, "disc_acc": float(acc[2]) / d_tok,
+    return {"gen_loss": gen, "disc_loss": disc, "loss": loss_weights[0] * gen + loss_weights[1] * disc,
+            "disc_acc": float(acc[2]) / d_tok,
             "disc_pos_frac": float(acc[3]) / d_tok, "zero_gen_windows": zero_gen, "zero_disc_windows": zero_disc}

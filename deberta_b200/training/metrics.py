@@ -50,3 +50,63 @@ def write_nonfinite_debug_artifact(*, debug_dir: Path, step: int, what: str, los
                "lr_mult": float(lr_mult), "rng": _rng_heads(), **(extra or {})}
     dump_json(payload, path)
     return path
+
+
+def _config_mapping(obj: Any) -> dict[str, Any]:
+    """Plain mapping of a backbone config object (``to_dict`` of HF configs, ``__dict__`` otherwise)."""
+    if obj is None:
+        return {}
+    if isinstance(obj, dict):
+        return dict(obj)
+    to_dict = getattr(obj, "to_dict", None)
+    if callable(to_dict):
+        try:
+            return dict(to_dict())
+        except Exception:  # noqa: BLE001
+            pass
+    return {k: v for k, v in vars(obj).items() if not k.startswith("_")}
+
+
+def build_runtime_resolved_config(*, sections: dict[str, Any], disc_config: Any = None, gen_config: Any = None,
+                                  tokenizer: Any = None, runtime: dict[str, Any] | None = None) -> dict[str, Any]:
+    """The configuration as the run really uses it, for ``config_resolved.yaml`` and the tracker.
+
+    Starts from the five config sections and fills what only exists once the model is built
+    (``training/metrics.py:82-161`` of the reference): the derived generator shape, dropout probabilities, the
+    rope position limit and the tokenizer's vocabulary size; blank pretrained paths become absent; ``None`` leaves are
+    pruned. ``runtime`` adds facts of this process group (world size, collective path, device).
+    """
+    from deberta_b200.utils.serialize import asdict_without_private, drop_none_recursive
+
+    payload: dict[str, Any] = {name: asdict_without_private(cfg) for name, cfg in sections.items()}
+    model = payload.setdefault("model", {})
+    disc, gen = _config_mapping(disc_config), _config_mapping(gen_config)
+    gen_out = dict(model.get("generator") or {})
+    for key in ("num_hidden_layers", "hidden_size", "intermediate_size", "num_attention_heads"):
+        if gen_out.get(key) is None and gen.get(key) is not None:
+            gen_out[key] = int(gen[key])
+    model["generator"] = gen_out
+    drop = dict(model.get("dropout") or {})
+    for ours, theirs in (("hidden_prob", "hidden_dropout_prob"), ("attention_probs_prob", "attention_probs_dropout_prob")):
+        if drop.get(ours) is None and disc.get(theirs) is not None:
+            drop[ours] = float(disc[theirs])
+    model["dropout"] = drop
+    rope = dict(model.get("rope") or {})
+    if rope.get("max_position_embeddings") is None and disc.get("max_position_embeddings") is not None:
+        rope["max_position_embeddings"] = int(disc["max_position_embeddings"])
+    model["rope"] = rope
+    tok = dict(model.get("tokenizer") or {})
+    if tok.get("vocab_target") is None and tokenizer is not None:
+        try:
+            tok["vocab_target"] = int(len(tokenizer))
+        except Exception:  # noqa: BLE001
+            pass
+    model["tokenizer"] = tok
+    pre = dict(model.get("pretrained") or {})
+    for key in ("discriminator_path", "generator_path"):
+        if not str(pre.get(key) or "").strip():
+            pre[key] = None
+    model["pretrained"] = pre
+    if runtime:
+        payload["runtime"] = dict(runtime)
+    return drop_none_recursive(payload)

@@ -31,7 +31,8 @@ _INERT_FIELDS = {
               "checkpoint.save_total_limit", "checkpoint.resume_from_checkpoint", "checkpoint.resume_data_strategy",
               "checkpoint.resume_replay_max_micro_batches", "checkpoint.export_hf_final", "dataloader.num_workers",
               "dataloader.pin_memory", "compile.enabled", "compile.mode", "compile.scope", "compile.backend", "tf32",
-              "sdpa_kernel"},
+              "sdpa_kernel", "distributed.fused_collectives", "distributed.multicast", "distributed.overlap_backward",
+              "distributed.comm_timeout_s", "distributed.step_deadline_s", "distributed.heartbeat_s"},
     "model": {"gradient_checkpointing", "hf.attention_kernel", "rope.attention_implementation"},
     "data": {"source.shuffle_buffer_size"},
     "optim": set(),
@@ -66,6 +67,13 @@ def write_config_yaml_snapshots(*, logging_dir: Path, config_path: Path | None, 
     else:
         _dump_yaml(resolved, logging_dir / CONFIG_ORIGINAL_FILE)
     _dump_yaml(resolved, logging_dir / CONFIG_RESOLVED_FILE)
+
+
+def write_runtime_resolved_config(*, logging_dir: Path, payload: dict[str, Any]) -> Path:
+    """Replace ``config_resolved.yaml`` by the runtime-resolved payload (values only known once the model exists)."""
+    path = Path(logging_dir) / CONFIG_RESOLVED_FILE
+    _dump_yaml(payload, path)
+    return path
 
 
 def compare_resume_config(*, section: str, stored: dict[str, Any], current: dict[str, Any]) -> list[str]:

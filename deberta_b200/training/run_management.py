@@ -281,6 +281,9 @@ def save_training_checkpoint(*, ctx: Any, save_state, checkpoint_dir: Path, outp
     save_state(str(staging))
     ctx.wait_for_everyone()
     if not ctx.is_main_process:
+        # rank 0 validates, commits and rotates alone; the others wait for it so that no rank runs ahead into
+        # device-side waits (bounded in seconds) while rank 0 is still deleting old checkpoints
+        ctx.wait_for_everyone()
         return
     try:
         save_checkpoint_data_progress(checkpoint_dir=staging, consumed_micro_batches=consumed_micro_batches, lr_mult=lr_mult,
@@ -298,3 +301,5 @@ def save_training_checkpoint(*, ctx: Any, save_state, checkpoint_dir: Path, outp
     except Exception:
         shutil.rmtree(staging, ignore_errors=True)
         raise
+    finally:
+        ctx.wait_for_everyone()

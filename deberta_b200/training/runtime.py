@@ -96,8 +96,13 @@ def resolve_learning_rates(optim_cfg: OptimConfig) -> tuple[float, float]:
 
 
 def build_engine(*, model: torch.nn.Module, ctx: DistContext, train_cfg: TrainConfig, optim_cfg: OptimConfig,
-                 parallelism: str = "ddp") -> TrainEngine:
-    """Engine with the optimizer layout of the run: two optimizers when decoupled, one otherwise."""
+                 parallelism: str | None = None) -> TrainEngine:
+    """Engine with the optimizer layout of the run: two optimizers when decoupled, one otherwise.
+
+    ``train.distributed`` chooses the parallelism and the collective path (``parallelism`` overrides the former).
+    """
+    di = train_cfg.distributed
+    parallelism = str(di.parallelism) if parallelism is None else parallelism
     bf16 = str(train_cfg.mixed_precision) == "bf16" and ctx.device.type == "cuda"
     if str(train_cfg.mixed_precision) == "bf16" and not bf16:
         logger.warning("train.mixed_precision=bf16 needs a CUDA device; running this process in fp32.")
@@ -108,4 +113,6 @@ def build_engine(*, model: torch.nn.Module, ctx: DistContext, train_cfg: TrainCo
     return TrainEngine(model, ctx, compute_dtype=torch.bfloat16 if bf16 else torch.float32, parallelism=parallelism,
                        decoupled=bool(train_cfg.decoupled_training), lr_generator=lr_g, lr_discriminator=lr_d,
                        weight_decay=float(optim_cfg.weight_decay),
-                       betas=(float(optim_cfg.adam.beta1), float(optim_cfg.adam.beta2)), eps=eps)
+                       betas=(float(optim_cfg.adam.beta1), float(optim_cfg.adam.beta2)), eps=eps,
+                       fused_collectives=bool(di.fused_collectives), multicast=str(di.multicast),
+                       comm_timeout_s=float(di.comm_timeout_s))

@@ -63,6 +63,10 @@ class StepSchedule:
     def step(self) -> None:
         self.last_step += 1
 
+    def step_back(self) -> None:
+        """Undo one ``step()`` (an update that turned out not to have happened)."""
+        self.last_step = max(0, self.last_step - 1)
+
     def scale(self) -> float:
         return float(self.fn(self.last_step))
 

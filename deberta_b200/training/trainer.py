@@ -13,6 +13,20 @@ What differs is *where* things happen: losses, token weights, the clip coefficie
 non-finite guard stay on the device, so the host never waits for the GPU inside a window; it
 learns the outcome of a step one window later from a pinned-memory copy. On CPU (tests, smoke
 runs) the same code resolves everything synchronously.
+
+Window-level rules of the reference that therefore run on the device:
+
+* a non-finite generator loss or gradient norm on any rank skips the *whole* window
+  (``entrypoint.py:1174-1212,1243-1257``): the generator's guard is added to the discriminator's, so
+  neither optimizer changes its parameters or moments; the discriminator's forward/backward of that
+  window still executes (its result is discarded), which the reference avoids by a host round trip;
+* a window in which no rank has a masked token does not step the discriminator
+  (``entrypoint.py:1269-1296``): with one process (or on the CPU) the phase is skipped on the host, with
+  several GPUs the update kernel is gated by the summed token count and the step counter and schedule
+  are corrected when the outcome arrives.
+
+The outcome also carries the kernels' status word: a bounded wait that ran out anywhere since the
+previous window raises ``KernelError`` here instead of letting the run continue on partial data.
 """
 
 from __future__ import annotations
@@ -52,12 +66,22 @@ class WindowStats:
 
 
 class _PendingOutcome:
-    """Squared grad norms of a finished step on their way to the host."""
+    """Squared grad norms, the discriminator gate and the kernel status word of a finished step on their way to the host."""
 
-    def __init__(self, step: int, norms: dict[str, torch.Tensor], sync: bool) -> None:
+    def __init__(self, step: int, norms: dict[str, torch.Tensor], sync: bool, gate: torch.Tensor | None = None) -> None:
         self.step = step
         self.names = list(norms)
-        stacked = torch.cat([norms[n].reshape(1) for n in self.names])
+        self.has_gate = gate is not None
+        parts = [norms[n].reshape(1).float() for n in self.names]
+        if gate is not None:
+            parts.append(gate.reshape(1).float())
+        stacked = torch.cat(parts)
+        self.status = None
+        if stacked.is_cuda:
+            from deberta_b200.ops import _lib
+
+            self.status = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+            _lib.call("db200_status_snapshot", _lib.ptr(self.status), _lib.stream_ptr())
         if stacked.is_cuda and not sync:
             self.host = torch.empty(stacked.shape, dtype=stacked.dtype, pin_memory=True)
             self.host.copy_(stacked, non_blocking=True)
@@ -67,11 +91,16 @@ class _PendingOutcome:
             self.host = stacked.detach().cpu()
             self.event = None
 
-    def resolve(self) -> dict[str, float]:
+    def resolve(self) -> tuple[dict[str, float], float | None, int]:
+        """(grad norms by optimizer, gate value or None, kernel status word)."""
         if self.event is not None:
             self.event.synchronize()
-        return {n: math.sqrt(v) if (v == v and v >= 0) else float("nan")
-                for n, v in zip(self.names, self.host.tolist())}
+        elif self.status is not None:
+            torch.cuda.current_stream().synchronize()
+        vals = self.host.tolist()
+        norms = {n: math.sqrt(v) if (v == v and v >= 0) else float("nan") for n, v in zip(self.names, vals)}
+        gate = vals[len(self.names)] if self.has_gate else None
+        return norms, gate, (0 if self.status is None else int(self.status[0]))
 
 
 class Trainer:
@@ -136,24 +165,41 @@ class Trainer:
         t = self.ctx.reduce(t, "mean")
         return t[0].clamp(min=1.0), t[1].clamp(min=1.0), (t[0] > 0).to(torch.float32)
 
-    def _finish_optimizer(self, name: str, loss_guard: torch.Tensor | None) -> torch.Tensor:
-        """Reduce gradients, fold a non-finite loss into the norm, update, advance the schedule."""
+    def _finish_optimizer(self, name: str, loss_guard: torch.Tensor | None, *, upstream: torch.Tensor | None = None,
+                          gate: torch.Tensor | None = None) -> torch.Tensor:
+        """Reduce gradients, fold a non-finite loss into the norm, update, advance the schedule.
+
+        ``upstream``: squared norm of an optimizer that stepped earlier in this window; when it is not finite this
+        update is skipped too (the whole window is void). ``gate``: see ``TrainEngine.step``.
+        """
         eng = self.engine
         penalty = None
         if loss_guard is not None:  # +inf when the window's loss was not finite: every rank then skips the update
             penalty = torch.where(torch.isfinite(loss_guard), 0.0, float("inf")).to(torch.float32).reshape(1)
+        if upstream is not None:
+            up = torch.where(torch.isfinite(upstream.reshape(1)), 0.0, float("inf")).to(torch.float32)
+            penalty = up if penalty is None else penalty + up
         norm_sq = eng.sync_grads(name, penalty)
-        eng.step(name, lr_scale=self.schedules[name].scale() * self.lr_mult, max_grad_norm=self.max_grad_norm)
+        eng.step(name, lr_scale=self.schedules[name].scale() * self.lr_mult, max_grad_norm=self.max_grad_norm, gate=gate)
         self.schedules[name].step()
         return norm_sq.clone()
 
-    def _resolve_pending(self) -> None:
-        """Apply the host-side consequences of the previous step (LR back-off / recovery)."""
+    def resolve_pending(self) -> None:
+        """Apply the host-side consequences of the previous step (LR back-off / recovery, gated updates, kernel errors).
+
+        Every rank must call this at the same points (``train_window`` does; so must a checkpoint save), because it
+        can change the optimizer step counters, the LR multiplier and the optimizer moments.
+        """
         if self._pending is None:
             return
-        norms = self._pending.resolve()
+        norms, gate, status = self._pending.resolve()
         step = self._pending.step
         self._pending = None
+        if status != 0:
+            from deberta_b200.ops import _lib
+
+            _lib.check_status()  # synchronises, clears the word and raises KernelError with the decoded reason
+            raise _lib.KernelError(f"device status {status} recorded during optimizer step {step}")
         self.last_outcome = norms
         if any(not math.isfinite(v) for v in norms.values()):
             self.skip_streak += 1
@@ -169,12 +215,19 @@ class Trainer:
         else:
             self.skip_streak = 0
             self.lr_mult = recover_lr_mult(self.lr_mult)
+            if gate is not None and not gate > 0.0 and "discriminator" in self.engine.optimizers:
+                # no rank had a masked token: the device gate left the discriminator untouched
+                self.engine.optimizers["discriminator"].step -= 1
+                self.schedules["discriminator"].step_back()
+
+    _resolve_pending = resolve_pending
 
     # ---- one optimizer step -------------------------------------------------------------------------
     def train_window(self, batches: list[dict[str, torch.Tensor]]) -> WindowStats:
         """Run one gradient-accumulation window (``len(batches)`` micro-batches) and step the optimizer(s)."""
-        self._resolve_pending()
+        self.resolve_pending()
         eng, model, dev = self.engine, self.model, self.engine.device
+        device_gate = None
         counts = [count_rtd_tokens_for_batch(b, pad_token_id=self.pad_token_id) for b in batches]
         input_tokens = sum(count_input_tokens_for_batch(b) for b in batches)
         gen_total, disc_total = sum(c[0] for c in counts), sum(c[1] for c in counts)
@@ -206,6 +259,18 @@ class Trainer:
             model.sync_discriminator_embeddings_from_generator()
             eng.zero_grad("generator")
             guard = zero()
+            # does any rank have a masked token in this window? known on the host unless several GPUs take part
+            device_gate = None
+            if isinstance(has_targets, torch.Tensor):
+                if has_targets.is_cuda:
+                    device_gate = has_targets
+                    run_disc = True
+                else:
+                    run_disc = bool(float(has_targets) > 0.0)
+            else:
+                run_disc = bool(has_targets)
+            if not run_disc:
+                cached = []
             for b, mask, corrupted, labels, g_i, d_i in cached:
                 with nvtx_range("discriminator fwd"):
                     out = model(input_ids=b["input_ids"], corrupted_input_ids=corrupted, disc_labels=labels,
@@ -218,9 +283,11 @@ class Trainer:
                 stats.disc_loss_tokens += out.disc_loss_raw.detach().float() * d_i
                 stats.disc_acc_tokens += out.disc_accuracy.float() * d_i
                 stats.disc_pos += out.disc_positive_count.float()
-            with nvtx_range("discriminator optimizer"):
-                norms["discriminator"] = self._finish_optimizer("discriminator", guard)
-            eng.zero_grad("discriminator")
+            if run_disc:
+                with nvtx_range("discriminator optimizer"):
+                    norms["discriminator"] = self._finish_optimizer("discriminator", guard, upstream=norms["generator"],
+                                                                    gate=device_gate)
+                eng.zero_grad("discriminator")
         else:
             guard = zero()
             for b, (g_i, d_i) in zip(batches, counts):
@@ -244,14 +311,16 @@ class Trainer:
         stats.grad_norms = {k: v.sqrt() for k, v in norms.items()}
         self.global_step += 1
         self.consumed_micro_batches += len(batches)
-        self._pending = _PendingOutcome(self.global_step, norms, self.synchronous)
+        self._pending = _PendingOutcome(self.global_step, norms, self.synchronous,
+                                        gate=device_gate if self.decoupled else None)
         if self.synchronous:
-            self._resolve_pending()
+            self.resolve_pending()
         return stats
 
     # ---- state ----------------------------------------------------------------------------------------
     def state_dict(self) -> dict[str, Any]:
-        self._resolve_pending()
+        """Host-side training state. Call ``resolve_pending()`` on every rank first (``save_training_state`` does)."""
+        self.resolve_pending()
         return {"global_step": self.global_step, "lr_mult": self.lr_mult, "skip_streak": self.skip_streak,
                 "consumed_micro_batches": self.consumed_micro_batches,
                 "schedules": {n: s.state_dict() for n, s in self.schedules.items()}}

@@ -104,6 +104,9 @@ def restore_rng_state(state: dict[str, Any]) -> None:
 def save_training_state(directory: str | Path, *, engine: Any, trainer: Any, ctx: Any) -> None:
     """Every rank's part of a checkpoint (collective: gathers fp32 masters under sharded optimizers)."""
     d = Path(directory)
+    # The outcome of the last window may still be on its way to the host; applying it can roll back an optimizer step,
+    # change the LR multiplier or clear the moments, so every rank does it before any rank reads optimizer state.
+    trainer.resolve_pending()
     model_state = engine.model_state_dict()  # collective
     sharded = engine.parallelism == "zero" and ctx.world_size > 1
     if ctx.is_main_process:

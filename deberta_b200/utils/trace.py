@@ -1,4 +1,4 @@
-"""Optional NVTX ranges around the phases of a training step (``DEBERTA_NVTX=1``).
+"""Optional NVTX ranges around the phases of a training step (``logging.debug.nvtx: true``).
 
 The reference has no tracing hooks; these ranges make the generator / discriminator / optimizer phases visible
 in a timeline profiler without touching the kernels. Disabled (the default) they cost one attribute lookup.
@@ -7,19 +7,21 @@ in a timeline profiler without touching the kernels. Disabled (the default) they
 from __future__ import annotations
 
 import contextlib
-import os
 
 import torch
 
-__all__ = ["nvtx_range", "nvtx_enabled"]
+__all__ = ["nvtx_range", "nvtx_enabled", "set_nvtx"]
 
-_ENABLED: bool | None = None
+_ENABLED = False
+
+
+def set_nvtx(enabled: bool) -> None:
+    """Switch the ranges on or off for this process (needs a CUDA build of torch to have any effect)."""
+    global _ENABLED
+    _ENABLED = bool(enabled) and torch.cuda.is_available()
 
 
 def nvtx_enabled() -> bool:
-    global _ENABLED
-    if _ENABLED is None:
-        _ENABLED = os.environ.get("DEBERTA_NVTX", "0").strip().lower() in ("1", "true", "yes", "on") and torch.cuda.is_available()
     return _ENABLED
 
 

@@ -23,13 +23,19 @@ def _inputs(B, S, heads, span, seed=0, scale=0.5):
     return mk(B, S, H), mk(B, S, H), mk(B, S, H), mk(2 * span, H), mk(2 * span, H)
 
 
-@pytest.mark.parametrize("mode", ["bias", "gather"])
-@pytest.mark.parametrize("B,S,heads,mask", [(2, 512, 2, "none"), (2, 200, 3, "pad"), (1, 384, 2, "doc"), (2, 128, 1, "none")])
-def test_disentangled_forward_backward(B, S, heads, mask, mode, monkeypatch):
+def _set_position_mode(monkeypatch, mode):
+    """"tc": bias and its gradient by the tensor-core tile kernels; "bias": bias pre-gathered from score tables,
+    gradient by prefix-sum scans; "gather": bucket tables read inside the attention kernels."""
     from deberta_b200.ops import attention_cuda
 
-    # "bias": position terms pre-gathered to [q, k] form; "gather": bucket tables read inside the kernels
-    monkeypatch.setattr(attention_cuda, "BIAS_MODE_MAX_SEQ", 1024 if mode == "bias" else 0)
+    monkeypatch.setattr(attention_cuda, "BIAS_MODE_MAX_SEQ", 0 if mode == "gather" else 1024)
+    monkeypatch.setattr(attention_cuda, "POSBIAS_TENSOR_CORE", mode == "tc")
+
+
+@pytest.mark.parametrize("mode", ["tc", "bias", "gather"])
+@pytest.mark.parametrize("B,S,heads,mask", [(2, 512, 2, "none"), (2, 200, 3, "pad"), (1, 384, 2, "doc"), (2, 128, 1, "none")])
+def test_disentangled_forward_backward(B, S, heads, mask, mode, monkeypatch):
+    _set_position_mode(monkeypatch, mode)
     span, buckets, maxpos = 256, 256, 512
     q, k, v, pk, pq = _inputs(B, S, heads, span)
     kw = {}
@@ -131,11 +137,9 @@ def test_rope_packed_documents_skip_tiles(S, mean_len, tail_pad, shuffle):
         assert _rel_err(a.grad, b.grad) < 4e-2, name
 
 
-@pytest.mark.parametrize("mode,S", [("bias", 640), ("gather", 640)])
+@pytest.mark.parametrize("mode,S", [("tc", 640), ("bias", 640), ("gather", 640)])
 def test_disentangled_packed_documents_skip_tiles(mode, S, monkeypatch):
-    from deberta_b200.ops import attention_cuda
-
-    monkeypatch.setattr(attention_cuda, "BIAS_MODE_MAX_SEQ", 1024 if mode == "bias" else 0)
+    _set_position_mode(monkeypatch, mode)
     B, heads, span, buckets, maxpos = 2, 2, 256, 256, 512
     q, k, v, pk, pq = _inputs(B, S, heads, span, seed=7)
     doc = _packed_doc_ids(B, S, 70, seed=11, tail_pad=150)
@@ -249,3 +253,72 @@ def test_rotary_and_swiglu_kernels_match_pytorch():
     ref.backward(go.float())
     assert (out.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
     assert (gu.grad.float() - gr.grad).abs().max() <= 2e-2 * gr.grad.abs().max()
+
+
+def _bias_reference(q, k, pos_k, pos_q, heads, S, buckets, maxpos, span):
+    """fp32 statement of the position bias: Q·PosK[δ(q-k)+span] + K·PosQ[span-δ(q-k)] (unscaled)."""
+    B = q.shape[0]
+    rel = relative_positions(S, S, buckets, maxpos, device=q.device).clamp(-span, span)
+    qh = q.float().view(B, S, heads, 64).permute(0, 2, 1, 3)
+    kh = k.float().view(B, S, heads, 64).permute(0, 2, 1, 3)
+    out = torch.zeros(B, heads, S, S, device=q.device)
+    if pos_k is not None:
+        pk = pos_k.float().view(2 * span, heads, 64).permute(1, 0, 2)
+        c2p = torch.einsum("bhqd,hpd->bhqp", qh, pk)
+        out = out + c2p.gather(-1, (rel + span).clamp(0, 2 * span - 1)[None, None].expand(B, heads, S, S))
+    if pos_q is not None:
+        pq = pos_q.float().view(2 * span, heads, 64).permute(1, 0, 2)
+        p2c = torch.einsum("bhkd,hpd->bhkp", kh, pq)
+        idx = (span - rel.transpose(0, 1)).clamp(0, 2 * span - 1)
+        out = out + p2c.gather(-1, idx[None, None].expand(B, heads, S, S)).transpose(-1, -2)
+    return out
+
+
+@pytest.mark.parametrize("B,S,heads,span,buckets,maxpos,which", [
+    (2, 512, 2, 256, 256, 512, "both"), (1, 200, 3, 256, 256, 512, "both"), (2, 128, 1, 256, 256, 512, "c2p"),
+    (1, 384, 2, 256, 256, 512, "p2c"), (1, 1024, 1, 256, 256, 512, "both"), (2, 300, 2, 32, 32, 64, "both")])
+def test_position_bias_on_tensor_cores_matches_fp32(B, S, heads, span, buckets, maxpos, which):
+    from deberta_b200.ops import attention_cuda
+
+    q, k, _, pk, pq = _inputs(B, S, heads, span, seed=13)
+    q, k, pk, pq = (t.detach() for t in (q, k, pk, pq))
+    if which == "c2p":
+        pq = None
+    if which == "p2c":
+        pk = None
+    luts = attention_cuda._luts(S, buckets, maxpos, span, q.device)
+    bias, used = attention_cuda.position_bias(q, k, pk, pq, luts, heads, tensor_core=True)
+    _lib.check_status()
+    assert used, "the tensor-core kernel rejected a bucket map it is meant to cover"
+    ref = _bias_reference(q, k, pk, pq, heads, S, buckets, maxpos, span)
+    assert _rel_err(bias[..., :S], ref) < 1.5e-2
+    table, used2 = attention_cuda.position_bias(q, k, pk, pq, luts, heads, tensor_core=False)
+    assert not used2 and _rel_err(table[..., :S], ref) < 1.5e-2
+
+
+@pytest.mark.parametrize("which,S,span,buckets,maxpos", [("c2p", 256, 256, 256, 512), ("p2c", 330, 256, 256, 512),
+                                                         ("both", 1000, 256, 256, 512), ("both", 300, 32, 32, 64)])
+def test_position_terms_single_sided_and_long_rows(which, S, span, buckets, maxpos, monkeypatch):
+    """One position term at a time, a 1000-token row (runs of offsets that share a log bucket cross the 32-entry
+    parts of the fold and the tiles), and a 64-row table (one window block)."""
+    _set_position_mode(monkeypatch, "tc")
+    B, heads = 1, 2
+    q, k, v, pk, pq = _inputs(B, S, heads, span, seed=21)
+    pos = {"c2p": (pk, None), "p2c": (None, pq), "both": (pk, pq)}[which]
+    out = disentangled_attention(q, k, v, *pos, heads=heads, scale_factor=1 + sum(t is not None for t in pos),
+                                 bucket_size=buckets, max_position=maxpos, att_span=span)
+    ref_in = [t.detach().float().requires_grad_(True) for t in (q, k, v, pk, pq)]
+    ref_pos = [None if t is None else r for t, r in zip(pos, ref_in[3:])]
+    ref = disentangled_attention_reference(*ref_in[:3], *ref_pos, heads=heads, scale_factor=1 + sum(t is not None for t in pos),
+                                           rel_pos=relative_positions(S, S, buckets, maxpos, device="cuda"), att_span=span)
+    _lib.check_status()
+    assert _rel_err(out, ref) < 2e-2
+    w = torch.randn_like(ref)
+    (out.float() * w).sum().backward()
+    (ref * w).sum().backward()
+    _lib.check_status()
+    for name, a, b in zip("q k v pos_k pos_q".split(), (q, k, v, pk, pq), ref_in):
+        if b.grad is None:
+            assert a.grad is None or float(a.grad.abs().max()) == 0.0, name
+            continue
+        assert _rel_err(a.grad, b.grad) < 4e-2, name

@@ -75,7 +75,7 @@ def test_emulated_ranks_reduce_adamw_match_reference():
         c = _ctx(r, grads, params, pads)
         _lib.call("db200_comm_adamw", ctypes.byref(c), ctypes.c_longlong(r * per), ctypes.c_longlong(per),
                   _lib.ptr(masters[r]), _lib.ptr(ms[r]), _lib.ptr(vs[r]), seg, ctypes.c_int(1), cf(b1), cf(b2), cf(eps),
-                  cf(1.0 / (1 - b1)), cf(1.0 / math.sqrt(1 - b2)), cf(max_norm), ctypes.c_uint(7), _lib.ptr(norm_out), stream)
+                  cf(1.0 / (1 - b1)), cf(1.0 / math.sqrt(1 - b2)), cf(max_norm), ctypes.c_uint(7), _lib.ptr(norm_out), None, stream)
     torch.cuda.synchronize()
     _lib.check_status()
     assert abs(float(norm_out) - want_norm_sq) < 1e-4 * want_norm_sq

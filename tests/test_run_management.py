@@ -248,7 +248,7 @@ def test_transactional_save_commits_atomically_and_rotates(tmp_path):
     ck = tmp_path / "checkpoint-3"
     assert rm.is_checkpoint_resumable(ck)
     assert rm.load_checkpoint_progress_metadata(ck) == (12, 0.5, "abc", 3, 4)
-    assert ctx.barriers == 9  # three barriers per save
+    assert ctx.barriers == 12  # four barriers per save: the last one holds the other ranks until rank 0 has committed
 
 
 def test_transactional_save_refuses_to_overwrite_and_cleans_up_failures(tmp_path):
@@ -279,7 +279,7 @@ def test_transactional_save_on_non_main_rank_writes_state_but_no_metadata(tmp_pa
     seen = []
     rm.save_training_checkpoint(ctx=ctx, save_state=lambda d: seen.append(d), checkpoint_dir=tmp_path / "checkpoint-1",
                                 output_dir=tmp_path, consumed_micro_batches=1, save_total_limit=1, log_label="t")
-    assert seen == [str(staging)] and ctx.barriers == 3
+    assert seen == [str(staging)] and ctx.barriers == 4
     assert not (tmp_path / "checkpoint-1").exists() and not (staging / "data_state.json").exists()
 
 

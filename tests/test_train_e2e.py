@@ -73,7 +73,7 @@ def test_two_rank_gloo_matches_layout(tmp_path, parallelism):
     out = tmp_path / f"run_{parallelism}"
     r = _train(["--train.checkpoint.output_dir", str(out), "--train.max_steps", "3", "--train.checkpoint.save_steps", "0",
                 "--train.checkpoint.export_hf_final", "false", "--train.gradient_accumulation_steps", "2",
-                "--logging.logging_steps", "1"], env={"DEBERTA_PARALLELISM": parallelism}, nproc=2,
+                "--logging.logging_steps", "1", "--train.distributed.parallelism", parallelism], nproc=2,
                port=29611 + (parallelism == "zero"))
     assert r.returncode == 0, r.stderr[-3000:]
     ck = out / "checkpoint-3"

@@ -276,11 +276,90 @@ def test_every_fourth_consecutive_skip_clears_the_optimizer_moments():
 
 def test_window_without_masked_tokens_trains_nothing_but_advances():
     model, eng, trainer = _setup(decoupled=True)
-    before = eng.master.clone()
+    trainer.train_window(_batches(2))  # moments and step counters are non-trivial from here on
+    disc = eng.optimizers["discriminator"]
+    lo, hi = disc.start, disc.end
+    before, m_before, v_before = eng.master[lo:hi].clone(), disc.exp_avg.clone(), disc.exp_avg_sq.clone()
+    sched_before = trainer.schedules["discriminator"].last_step
     stats = trainer.train_window(_batches(2, masked=False))
-    assert stats.zero_gen_window and not stats.zero_disc_window and trainer.global_step == 1
-    moved = (eng.master - before).abs().max()
-    assert float(moved) < 1e-2  # only weight decay / zero-gradient Adam noise: no RTD signal without corruption
+    assert stats.zero_gen_window and not stats.zero_disc_window and trainer.global_step == 2
+    # no rank has a generator target: the discriminator neither steps nor decays (reference entrypoint.py:1269-1296)
+    assert torch.equal(eng.master[lo:hi], before) and torch.equal(disc.exp_avg, m_before)
+    assert torch.equal(disc.exp_avg_sq, v_before) and disc.step == 1
+    assert trainer.schedules["discriminator"].last_step == sched_before
+    assert trainer.skipped_steps == 0 and trainer.lr_mult == 1.0  # not a non-finite skip
+
+
+def test_device_gate_switches_the_update_off_and_the_outcome_corrects_the_counters():
+    """The path several GPUs take: the decision sits in a tensor, the update is gated where it runs, and the step
+    counter / schedule are corrected when the outcome is read."""
+    model, eng, trainer = _setup(decoupled=True)
+    trainer.train_window(_batches(2))
+    disc = eng.optimizers["discriminator"]
+    before = eng.master[disc.start:disc.end].clone()
+    real = trainer._window_denominators
+    trainer._window_denominators = lambda g, d: (torch.tensor(max(g, 1.0)), torch.tensor(max(d, 1.0)),
+                                                 torch.tensor(1.0 if g > 0 else 0.0))
+    trainer.train_window(_batches(2, masked=False))
+    assert torch.equal(eng.master[disc.start:disc.end], before) and disc.step == 1
+    trainer.train_window(_batches(2, seed=9))
+    assert disc.step == 2 and not torch.equal(eng.master[disc.start:disc.end], before)
+    trainer._window_denominators = real
+    g = torch.tensor([0.0])
+    m0 = eng.master.clone()
+    eng.sync_grads("discriminator")
+    eng.step("discriminator", gate=g)
+    assert torch.equal(eng.master, m0) and disc.step == 2
+
+
+def test_nonfinite_generator_voids_the_whole_window():
+    """A NaN generator loss: discriminator weights and Adam moments stay bit-identical, both counters stay put."""
+    model, eng, trainer = _setup(decoupled=True)
+    trainer.train_window(_batches(2))
+    disc, gen = eng.optimizers["discriminator"], eng.optimizers["generator"]
+    w, m, v = eng.master[disc.start:disc.end].clone(), disc.exp_avg.clone(), disc.exp_avg_sq.clone()
+    with torch.no_grad():
+        model.generator_lm_head.bias.fill_(float("nan"))
+    trainer.train_window(_batches(2, seed=5))
+    assert torch.equal(eng.master[disc.start:disc.end], w) and torch.equal(disc.exp_avg, m) and torch.equal(disc.exp_avg_sq, v)
+    assert disc.step == 1 and gen.step == 1 and trainer.skipped_steps == 1 and trainer.lr_mult == 0.5
+    assert not math.isfinite(trainer.last_outcome["discriminator"])  # the generator's guard reached the discriminator
+    assert trainer.schedules["discriminator"].last_step == 2  # schedules advance on a skipped window
+
+
+def test_kernel_status_word_raises_when_the_outcome_is_read(monkeypatch):
+    from deberta_b200.ops import _lib
+    from deberta_b200.training import trainer as T
+
+    _, _, trainer = _setup()
+    trainer.train_window(_batches(2))
+
+    class Outcome:
+        step = 7
+
+        def resolve(self):
+            return {"generator": 1.0}, None, 5
+
+    monkeypatch.setattr(_lib, "check_status", lambda: (_ for _ in ()).throw(_lib.KernelError("device status 5")))
+    trainer._pending = Outcome()
+    with pytest.raises(_lib.KernelError):
+        trainer.resolve_pending()
+    assert trainer._pending is None and T.Trainer.resolve_pending is T.Trainer._resolve_pending
+
+
+def test_logged_row_matches_a_hand_computation():
+    from deberta_b200.training.entrypoint import _reduce_window_stats
+    from deberta_b200.training.trainer import WindowStats
+
+    t = lambda x: torch.tensor(float(x))  # noqa: E731
+    w1 = WindowStats(t(2.0 * 10), t(0.5 * 100), t(0.9 * 100), t(12), gen_tokens=10, disc_tokens=100, input_tokens=100)
+    w2 = WindowStats(t(4.0 * 30), t(0.25 * 300), t(0.7 * 300), t(20), gen_tokens=30, disc_tokens=300, input_tokens=300)
+    row = _reduce_window_stats(DistContext(), [w1, w2], torch.device("cpu"), loss_weights=(1.0, 50.0))
+    gen = (2.0 * 10 + 4.0 * 30) / 40
+    disc = (0.5 * 100 + 0.25 * 300) / 400
+    assert math.isclose(row["gen_loss"], gen) and math.isclose(row["disc_loss"], disc)
+    assert math.isclose(row["loss"], 1.0 * gen + 50.0 * disc, rel_tol=1e-6)
+    assert math.isclose(row["disc_acc"], (90 + 210) / 400) and math.isclose(row["disc_pos_frac"], 32 / 400)
 
 
 def test_trainer_state_round_trip_and_lr_reporting():
