@@ -5,6 +5,5 @@
 #   usage: configs/launch/single_node_sharded.sh <config.yaml> [--section.key value ...]
 set -euo pipefail
 NPROC="${NPROC:-$(nvidia-smi -L | wc -l)}"
-export DEBERTA_PARALLELISM=zero
 exec python -m torch.distributed.run --nnodes=1 --nproc-per-node "${NPROC}" --master-addr 127.0.0.1 \
-    --master-port "${MASTER_PORT:-29500}" -m deberta_b200 train "$@"
+    --master-port "${MASTER_PORT:-29500}" -m deberta_b200 train "$@" --train.distributed.parallelism "${PARALLELISM:-zero}"

@@ -61,15 +61,36 @@ def is_current() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the kernel library if it is missing or stale; return its path."""
+    """Compile the kernel library if it is missing or stale; return its path.
+
+    Safe to call from every rank of a launch at once: one process builds under an exclusive file lock (objects go to a
+    private directory, the library and its stamp are moved into place atomically), the others wait for the lock and
+    then find the library current.
+    """
     if not force and is_current():
         return LIB_PATH
+    import fcntl
+
     OUT_DIR.mkdir(parents=True, exist_ok=True)
+    with open(OUT_DIR / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and is_current():  # another process built it while this one waited
+                return LIB_PATH
+            return _build_locked(verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(verbose: bool) -> Path:
+    import tempfile
+
     nvcc = _nvcc()
     extra = ["-Xptxas", "-v"] if verbose else []
+    work = Path(tempfile.mkdtemp(prefix=".build-", dir=OUT_DIR))
 
     def compile_one(src: Path) -> Path:
-        obj = OUT_DIR / (src.stem + ".o")
+        obj = work / (src.stem + ".o")
         cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
@@ -78,13 +99,23 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             sys.stderr.write(res.stderr)
         return obj
 
-    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
-        objs = list(pool.map(compile_one, sources()))
-    link = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
-    res = subprocess.run(link, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
-    STAMP.write_text(source_hash() + "\n")
+    try:
+        digest = source_hash()
+        with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+            objs = list(pool.map(compile_one, sources()))
+        tmp_lib = work / LIB_PATH.name
+        link = [nvcc, "-shared", "-o", str(tmp_lib), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
+        res = subprocess.run(link, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+        if STAMP.exists():
+            STAMP.unlink()  # never a stamp that vouches for a library it does not describe
+        os.replace(tmp_lib, LIB_PATH)
+        tmp_stamp = work / STAMP.name
+        tmp_stamp.write_text(digest + "\n")
+        os.replace(tmp_stamp, STAMP)
+    finally:
+        shutil.rmtree(work, ignore_errors=True)
     return LIB_PATH
 
 

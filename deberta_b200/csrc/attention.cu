@@ -912,11 +912,14 @@ extern "C" int db200_attn_fwd(const AttnArgs* a, void* stream_) {
       {attn_fwd_kernel<0, 0>, attn_fwd_kernel<0, 1>, attn_fwd_kernel<0, 2>},
       {attn_fwd_kernel<1, 0>, attn_fwd_kernel<1, 1>, attn_fwd_kernel<1, 2>},
       {attn_fwd_kernel<2, 0>, attn_fwd_kernel<2, 1>, attn_fwd_kernel<2, 2>}};
-  static int configured[3][3] = {};
+  static int configured[16][3][3] = {};  // per device: the opt-in to large shared memory is a per-device attribute
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev = (dev >= 0 && dev < 16) ? dev : 0;
   const FwdKernel kern = kernels[mask_mode][pos_mode];
-  if (configured[mask_mode][pos_mode] < smem) {
+  if (configured[dev][mask_mode][pos_mode] < smem) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
-    configured[mask_mode][pos_mode] = smem;
+    configured[dev][mask_mode][pos_mode] = smem;
   }
   dim3 grid((a->S + kTile - 1) / kTile, a->heads, a->B);
   kern<<<grid, kFwdThreads, smem, stream>>>(tq, tk, tv, d);
@@ -970,11 +973,14 @@ extern "C" int db200_attn_bwd(const AttnArgs* a, void* stream_) {
       {attn_bwd_kernel<0, 0>, attn_bwd_kernel<0, 1>, attn_bwd_kernel<0, 2>},
       {attn_bwd_kernel<1, 0>, attn_bwd_kernel<1, 1>, attn_bwd_kernel<1, 2>},
       {attn_bwd_kernel<2, 0>, attn_bwd_kernel<2, 1>, attn_bwd_kernel<2, 2>}};
-  static int configured[3][3] = {};
+  static int configured[16][3][3] = {};  // per device, as in the forward launcher
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev = (dev >= 0 && dev < 16) ? dev : 0;
   const BwdKernel kern = kernels[mask_mode][pos_mode];
-  if (configured[mask_mode][pos_mode] < smem) {
+  if (configured[dev][mask_mode][pos_mode] < smem) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
-    configured[mask_mode][pos_mode] = smem;
+    configured[dev][mask_mode][pos_mode] = smem;
   }
   dim3 grid((a->S + kTile - 1) / kTile, a->heads, a->B);
   kern<<<grid, kBwdThreads, smem, stream>>>(tq, tk, tv, tdo, d);

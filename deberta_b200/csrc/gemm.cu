@@ -641,26 +641,32 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-int g_num_sms = 0;
-int num_sms() {
-  if (g_num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-    if (g_num_sms <= 0) g_num_sms = 148;
+constexpr int kMaxDevices = 16;
+int current_device() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return (dev >= 0 && dev < kMaxDevices) ? dev : 0;
+}
+int g_num_sms[kMaxDevices] = {};
+int num_sms() {  // per device: a process may drive more than one GPU
+  const int dev = current_device();
+  if (g_num_sms[dev] == 0) {
+    cudaDeviceGetAttribute(&g_num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms[dev] <= 0) g_num_sms[dev] = 148;
   }
-  return g_num_sms;
+  return g_num_sms[dev];
 }
 
 template <int BN, bool A_MN, bool B_MN, int MODE>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& to2, const DevParams& p,
            int grid, cudaStream_t stream) {
   using L = SmemLayout<BN>;
-  static bool configured = false;
+  static bool configured[kMaxDevices] = {};  // the shared-memory opt-in is a per-device attribute of the function
   auto kern = gemm_kernel<BN, A_MN, B_MN, MODE>;
-  if (!configured) {
+  const int dev = current_device();
+  if (!configured[dev]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess) return -3;
-    configured = true;
+    configured[dev] = true;
   }
   kern<<<grid, kThreads, L::kTotal, stream>>>(ta, tb, to, to2, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
@@ -669,8 +675,46 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
 }  // namespace
 
 // Build a 3-D bf16 tensor map {inner, rows, batch} with a {64, box_rows, 1} box and 128B swizzle.
+//
+// Encoding a map costs a driver call of a microsecond or two, and a training step asks for several thousand maps over
+// the same few hundred (pointer, shape, stride) combinations: parameters sit in the engine's flat buffers and the
+// caching allocator hands activations the same addresses step after step. A map is a pure function of its
+// description, so descriptions are looked up in a small direct-mapped, per-thread table first.
+namespace {
+struct TmapKey {
+  const void* ptr;
+  long long inner, rows, batch, row_stride, batch_stride;
+  int box_rows;
+  bool operator==(const TmapKey& o) const {
+    return ptr == o.ptr && inner == o.inner && rows == o.rows && batch == o.batch && row_stride == o.row_stride &&
+           batch_stride == o.batch_stride && box_rows == o.box_rows;
+  }
+};
+struct TmapSlot {
+  TmapKey key;
+  CUtensorMap map;
+  bool used;
+};
+constexpr int kTmapSlots = 4096;
+inline size_t tmap_hash(const TmapKey& k) {
+  unsigned long long h = reinterpret_cast<unsigned long long>(k.ptr) * 0x9E3779B97F4A7C15ull;
+  h ^= static_cast<unsigned long long>(k.inner) * 0xC2B2AE3D27D4EB4Full + static_cast<unsigned long long>(k.rows) * 0x165667B19E3779F9ull;
+  h ^= static_cast<unsigned long long>(k.row_stride) * 0x85EBCA77C2B2AE63ull + static_cast<unsigned long long>(k.batch) * 0x27D4EB2F165667C5ull;
+  h ^= static_cast<unsigned long long>(k.batch_stride) * 0xD6E8FEB86659FD93ull + static_cast<unsigned long long>(k.box_rows);
+  return static_cast<size_t>((h ^ (h >> 29)) % kTmapSlots);
+}
+}  // namespace
+
 int db200_make_tmap_bf16(CUtensorMap* out, const void* ptr, long long inner, long long rows, long long batch,
                          long long row_stride_elems, long long batch_stride_elems, int box_rows) {
+  static thread_local TmapSlot* table = nullptr;
+  if (!table) table = new TmapSlot[kTmapSlots]();
+  const TmapKey key{ptr, inner, rows, batch, row_stride_elems, batch_stride_elems, box_rows};
+  TmapSlot& slot = table[tmap_hash(key)];
+  if (slot.used && slot.key == key) {
+    *out = slot.map;
+    return 0;
+  }
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -1;
   cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows),
@@ -682,7 +726,11 @@ int db200_make_tmap_bf16(CUtensorMap* out, const void* ptr, long long inner, lon
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -2;
+  if (r != CUDA_SUCCESS) return -2;
+  slot.key = key;
+  slot.map = *out;
+  slot.used = true;
+  return 0;
 }
 
 // Width of the column range one partial result of EPI_CE_FWD covers (half of the GEMM tile).

@@ -29,17 +29,25 @@ constexpr int kTileBytes = kTile * kD * 2;    // 16 KB: 128 rows of one head
 constexpr int kWin = 256;                     // rows of a position-table window
 constexpr int kWinBytes = kWin * kD * 2;      // 32 KB
 constexpr int kMaxDiag = 64;                  // tile diagonals i - j the window tables can describe (S <= 4096)
-constexpr int kThreads = 512;
+// One CTA fills an SM (shared memory), so the warps of that one CTA have to hide the latencies
+// of TMEM loads, shared-memory gathers and the barriers between phases. Warp w owns TMEM lane quadrant (w & 3)
+// and "part" (w >> 2) of whatever a row is split into.
+#ifndef DB200_POS_PARTS
+#define DB200_POS_PARTS 4
+#endif
+constexpr int kParts = DB200_POS_PARTS;       // threads per tile row (4 or 8)
+constexpr int kThreads = 128 * kParts;
+constexpr int kPer = kTile / kParts;          // (q, k) entries of a row one thread handles
+constexpr int kDrain = kWin / kParts;         // window columns one thread drains
+constexpr int kAccCols = kD / kParts;         // accumulator columns one thread reads back
 
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
 }
+static_assert(kParts == 4 || kParts == 8, "a tile row is shared by 4 or 8 threads");
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
@@ -59,9 +67,10 @@ struct PosFwdDev {
   int* status;
 };
 
-// Staging rows are 256 bf16 + 8 of padding: 16-byte aligned for the vector stores of the drain, and neighbouring
-// rows start 4 banks apart.
-constexpr int kStageLd = kWin + 8;
+// Staging rows are 256 bf16 + 2 of padding = 129 words: at the gather the 32 lanes of a warp read 32 different rows
+// at (nearly) the same column, and an odd word stride puts those on different banks. The drain therefore stores
+// 32-bit words (rows are only 4-byte aligned).
+constexpr int kStageLd = kWin + 2;
 constexpr int kStageBytes = kTile * kStageLd * 2;
 
 struct FwdSmem {
@@ -75,8 +84,8 @@ struct FwdSmem {
   static int total(int nt) { return kLut + 2 * (2 * nt * kTile) * 2 + 1024; }
 };
 
-// grid (q-tiles, heads, B), 512 threads: warp w owns the TMEM lanes of quadrant (w & 3) and a quarter (w >> 2) of the
-// columns; at the gather a thread owns one query row and 32 keys of the tile.
+// grid (q-tiles, heads, B), 128·kParts threads: warp w owns the TMEM lanes of quadrant (w & 3) and share (w >> 2) of the
+// window columns; at the gather a thread owns one query row and kPer keys of the tile.
 template <bool HAS_C, bool HAS_P>
 __global__ void __launch_bounds__(kThreads, 1)
 posbias_tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -179,38 +188,32 @@ posbias_tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int qg = q0 + row;
   const uint32_t stage_row = static_cast<uint32_t>(row) * kStageLd;
 
-  auto drain = [&](uint32_t t_src) {  // this thread's 64 columns of the window product, as bf16, into its staging row
+  auto drain = [&](uint32_t t_src) {  // this thread's columns of the window product, as bf16, into its staging row
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
+    for (int c = 0; c < kDrain / 32; ++c) {
       uint32_t r[32];
-      tmem_ld_32x32b_x32(t_src + lane_addr + part * 64 + half * 32, r);
+      tmem_ld_32x32b_x32(t_src + lane_addr + part * kDrain + c * 32, r);
       tmem_ld_wait();
-      uint4* dst = reinterpret_cast<uint4*>(stage + stage_row + part * 64 + half * 32);
+      uint32_t* dst = reinterpret_cast<uint32_t*>(stage + stage_row + part * kDrain + c * 32);
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        uint4 u;
-        u.x = pack_bf16(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
-        u.y = pack_bf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
-        u.z = pack_bf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
-        u.w = pack_bf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
-        dst[g] = u;
-      }
+      for (int g = 0; g < 16; ++g) dst[g] = pack_bf16(__uint_as_float(r[2 * g]), __uint_as_float(r[2 * g + 1]));
     }
   };
 
   for (int tj = 0; tj < nt; ++tj) {
-    const bool got = mbar_wait(bar_mma, tj & 1, abort_flag, p.status, kErrAccFullWait);
-    // one decision for the whole block; the barrier also ends the previous tile's reads of the staging buffer
+    // one thread polls the barrier (a spinning CTA would burn the issue slots the working warps need); the block
+    // barrier hands its answer to everybody and also ends the previous tile's reads of the staging buffer
+    const bool got = tid != 0 || mbar_wait(bar_mma, tj & 1, abort_flag, p.status, kErrAccFullWait);
     if (!__syncthreads_and(got)) break;
     tc_fence_after();
     const bool more = tj + 1 < nt;
     if (tid == 0 && more) issue_loads(tj + 1);  // the MMAs that read these buffers have retired
     const int diag = ti - tj + nt - 1;
     const int k0 = tj * kTile;
-    const int xbase = qg - (k0 + part * 32) + nt * kTile - 1;  // lookup index of this thread's first key
-    float acc[32];
+    const int xbase = qg - (k0 + part * kPer) + nt * kTile - 1;  // lookup index of this thread's first key
+    float acc[kPer];
 #pragma unroll
-    for (int e = 0; e < 32; ++e) acc[e] = 0.f;
+    for (int e = 0; e < kPer; ++e) acc[e] = 0.f;
 
     if (HAS_C) {
       drain(t_c);
@@ -218,7 +221,7 @@ posbias_tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       const unsigned short* l = lutc + xbase;
       const __nv_bfloat16* src = stage + stage_row - p.win_c[diag] * kTile;
 #pragma unroll
-      for (int e = 0; e < 32; ++e) acc[e] = __bfloat162float(src[l[-e]]);
+      for (int e = 0; e < kPer; ++e) acc[e] = __bfloat162float(src[l[-e]]);
     }
     if (HAS_P) {
       if (HAS_C) __syncthreads();  // the gather above is done with the staging buffer
@@ -235,17 +238,17 @@ posbias_tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     }
     if (HAS_P) {
       const unsigned short* l = lutp + xbase;
-      const __nv_bfloat16* src = stage + static_cast<uint32_t>(part * 32) * kStageLd - p.win_p[diag] * kTile;
+      const __nv_bfloat16* src = stage + static_cast<uint32_t>(part * kPer) * kStageLd - p.win_p[diag] * kTile;
 #pragma unroll
-      for (int e = 0; e < 32; ++e) acc[e] += __bfloat162float(src[e * kStageLd + l[-e]]);
+      for (int e = 0; e < kPer; ++e) acc[e] += __bfloat162float(src[e * kStageLd + l[-e]]);
     }
     if (qg < S) {
-      uint32_t w[16];
+      uint32_t w[kPer / 2];
 #pragma unroll
-      for (int e = 0; e < 16; ++e) w[e] = pack_bf16(acc[2 * e], acc[2 * e + 1]);
-      __nv_bfloat16* dst = p.bias + ((static_cast<long long>(b) * p.heads + h) * S + qg) * p.ldb + k0 + part * 32;
-      st_global_32B(dst, w);
-      st_global_32B(dst + 16, w + 8);
+      for (int e = 0; e < kPer / 2; ++e) w[e] = pack_bf16(acc[2 * e], acc[2 * e + 1]);
+      __nv_bfloat16* dst = p.bias + ((static_cast<long long>(b) * p.heads + h) * S + qg) * p.ldb + k0 + part * kPer;
+#pragma unroll
+      for (int v = 0; v < kPer / 16; ++v) st_global_32B(dst + v * 16, w + v * 8);
     }
   }
 
@@ -355,8 +358,8 @@ struct BwdSmem {
 };
 
 // One CTA per (side, head, batch row). SIDE 0: rows are queries, the outer loop runs over query tiles and the
-// inner one over key tiles; SIDE 1: rows are keys, outer loop over key tiles. Thread = (row, 32 entries of the
-// other axis) during the fold, (TMEM lane, 16 columns) when accumulators are read.
+// inner one over key tiles; SIDE 1: rows are keys, outer loop over key tiles. Thread = (row, kPer entries of the
+// other axis) during the fold, (TMEM lane, kAccCols columns) when accumulators are read.
 template <int SIDE>
 __device__ __forceinline__ void posbias_bwd_body(const CUtensorMap& tm_row, const CUtensorMap& tm_tab,
                                                   const CUtensorMap& tm_g, const PosBwdDev& p, uint8_t* smem) {
@@ -419,32 +422,31 @@ __device__ __forceinline__ void posbias_bwd_body(const CUtensorMap& tm_row, cons
     mbar_expect_tx(bar_row, kTileBytes);
     tma_load_3d(sRow, &tm_row, bar_row, h * kD, outer * kTile, b);
   };
-  // gradient of the row tile `outer` out of TMEM: 16 columns per thread
+  // gradient of the row tile `outer` out of TMEM: kAccCols columns per thread
   auto flush_row = [&](int outer) {
-    uint32_t r[16];
-    tmem_ld16(t_row + lane_addr + part * 16, r);
-    tmem_ld_wait();
     const int g = outer * kTile + row;
-    if (g < S) {
-      if (SIDE == 0) {
-        float* dst = p.dq_acc + (static_cast<long long>(b) * S + g) * H + h * kD + part * 16;
 #pragma unroll
-        for (int v = 0; v < 4; ++v)
+    for (int c = 0; c < kAccCols / 8; ++c) {
+      uint32_t r[8];
+      tmem_ld8(t_row + lane_addr + part * kAccCols + c * 8, r);
+      tmem_ld_wait();
+      if (g >= S) continue;
+      if (SIDE == 0) {
+        float* dst = p.dq_acc + (static_cast<long long>(b) * S + g) * H + h * kD + part * kAccCols + c * 8;
+#pragma unroll
+        for (int v = 0; v < 2; ++v)
           red_add_v4(dst + v * 4, __uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]), __uint_as_float(r[v * 4 + 2]),
                      __uint_as_float(r[v * 4 + 3]));
       } else {
-        uint4* dst = reinterpret_cast<uint4*>(p.dk + (static_cast<long long>(b) * S + g) * p.ld_dk + h * kD + part * 16);
+        uint4* dst = reinterpret_cast<uint4*>(p.dk + (static_cast<long long>(b) * S + g) * p.ld_dk + h * kD +
+                                              part * kAccCols + c * 8);
+        const uint4 old = *dst;
+        const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+        uint32_t nw[4];
 #pragma unroll
-        for (int v = 0; v < 2; ++v) {
-          const uint4 old = dst[v];
-          const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
-          uint32_t nw[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            nw[e] = pack_bf16(bf16_lo(ow[e]) + __uint_as_float(r[v * 8 + 2 * e]),
-                              bf16_hi(ow[e]) + __uint_as_float(r[v * 8 + 2 * e + 1]));
-          dst[v] = make_uint4(nw[0], nw[1], nw[2], nw[3]);
-        }
+        for (int e = 0; e < 4; ++e)
+          nw[e] = pack_bf16(bf16_lo(ow[e]) + __uint_as_float(r[2 * e]), bf16_hi(ow[e]) + __uint_as_float(r[2 * e + 1]));
+        *dst = make_uint4(nw[0], nw[1], nw[2], nw[3]);
       }
     }
   };
@@ -473,25 +475,26 @@ __device__ __forceinline__ void posbias_bwd_body(const CUtensorMap& tm_row, cons
     const int ti = SIDE == 0 ? outer : inner, tj = SIDE == 0 ? inner : outer;
     const int wb = p.win[SIDE][ti - tj + nt - 1];          // first table block of this pair's window
     const int nwb = min(2, p.nblk - wb);                   // blocks in the window
+    // thread 0 polls: the folded tile is free and the accumulators are current (MMAs of pair n-1 retired), and this
+    // pair's tile of G has landed; the block barrier hands the answer to everybody
     bool got = true;
-    if (n > 0) {
-      // F is free and the accumulators are current; one answer per warp, since the TMEM load below is warp-wide
-      got = __all_sync(0xffffffffu, mbar_wait(bar_f, (n - 1) & 1, abort_flag, p.status, kErrAccFullWait));
-      tc_fence_after();
-      if (got && inner == 0) flush_row(outer - 1);
+    if (tid == 0) {
+      if (n > 0) got = mbar_wait(bar_f, (n - 1) & 1, abort_flag, p.status, kErrAccFullWait);
+      got = got && mbar_wait(&bar_g[n & 1], (n >> 1) & 1, abort_flag, p.status, kErrFullWait);
     }
-    // clear the folded tile (only the chunks this window uses)
-    if (got) {
-      const uint4 z = make_uint4(0, 0, 0, 0);
-      for (int i = tid; i < nwb * 2 * kTileBytes / 16; i += kThreads) reinterpret_cast<uint4*>(sF)[i] = z;
-    }
-    got = got && mbar_wait(&bar_g[n & 1], (n >> 1) & 1, abort_flag, p.status, kErrFullWait);
-    tc_fence_before();
     if (!__syncthreads_and(got)) {
       failed = true;
       fail_n = n;
       break;
     }
+    tc_fence_after();
+    if (n > 0 && inner == 0) flush_row(outer - 1);
+    {  // clear the folded tile (only the chunks this window uses)
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      for (int i = tid; i < nwb * 2 * kTileBytes / 16; i += kThreads) reinterpret_cast<uint4*>(sF)[i] = z;
+    }
+    tc_fence_before();
+    __syncthreads();  // cleared before the scattered stores of the fold; accumulator reads done before the next MMAs
     if (tid == 0) {
       if (n & 1) pend_g1 = false; else pend_g0 = false;
       if (inner == 0 && n > 0) load_row(outer);  // the MMAs that read the previous row tile have retired
@@ -500,15 +503,15 @@ __device__ __forceinline__ void posbias_bwd_body(const CUtensorMap& tm_row, cons
     // ---- fold: F[row][w - 128 wb] = sum of G over this thread's run of entries that share bucket w ----
     {
       const uint8_t* g_tile = sG + (n & 1) * 2 * kTileBytes;
-      const int o0 = part * 32;
-      float g[32];
+      const int o0 = part * kPer;
+      float g[kPer];
       int xb;
-      if (SIDE == 0) {  // row = query, entries = keys o0 .. o0+31: one 64-byte stretch of the row
+      if (SIDE == 0) {  // row = query, entries = keys o0 .. o0+kPer-1: one contiguous stretch of the row
         xb = (ti * kTile + row) - (tj * kTile + o0) + nt * kTile - 1;
-        const uint8_t* src = g_tile + (part >> 1) * kTileBytes + row * 128;
+        const uint8_t* src = g_tile + (o0 >> 6) * kTileBytes + row * 128;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const uint4 u = *reinterpret_cast<const uint4*>(src + ((((part & 1) * 4 + c) ^ (row & 7)) << 4));
+        for (int c = 0; c < kPer / 8; ++c) {
+          const uint4 u = *reinterpret_cast<const uint4*>(src + (((((o0 & 63) >> 3) + c) ^ (row & 7)) << 4));
           const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -516,12 +519,12 @@ __device__ __forceinline__ void posbias_bwd_body(const CUtensorMap& tm_row, cons
             g[c * 8 + 2 * e + 1] = bf16_hi(w[e]);
           }
         }
-      } else {          // row = key, entries = queries o0 .. o0+31: one column of the tile
+      } else {          // row = key, entries = queries o0 .. o0+kPer-1: one column of the tile
         xb = (ti * kTile + o0) - (tj * kTile + row) + nt * kTile - 1;
         const uint8_t* src = g_tile + (row >> 6) * kTileBytes + o0 * 128 + (row & 7) * 2;
         const int ck = (row & 63) >> 3;
 #pragma unroll
-        for (int e = 0; e < 32; ++e)
+        for (int e = 0; e < kPer; ++e)
           g[e] = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(src + e * 128 + ((ck ^ (e & 7)) << 4)));
       }
       constexpr int dir = SIDE == 0 ? -1 : 1;  // the lookup index falls (rises) along the entries
@@ -538,7 +541,7 @@ __device__ __forceinline__ void posbias_bwd_body(const CUtensorMap& tm_row, cons
       bool mine = part == 0;
       float run = 0.f;
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
+      for (int e = 0; e < kPer; ++e) {
         const int w = l[dir * e];
         if (w != wcur) {
           if (mine && wcur >= 0) f_store(wcur, run);
@@ -549,7 +552,7 @@ __device__ __forceinline__ void posbias_bwd_body(const CUtensorMap& tm_row, cons
         run += g[e];
       }
       if (mine) {
-        for (int o = o0 + 32; o < kTile && l[dir * (o - o0)] == wcur; ++o) {  // the run goes on in the next part
+        for (int o = o0 + kPer; o < kTile && l[dir * (o - o0)] == wcur; ++o) {  // the run goes on in the next part
           const uint8_t* src = SIDE == 0 ? g_tile + (o >> 6) * kTileBytes + row * 128 + ((((o & 63) >> 3) ^ (row & 7)) << 4) + (o & 7) * 2
                                          : g_tile + (row >> 6) * kTileBytes + o * 128 + ((((row & 63) >> 3) ^ (o & 7)) << 4) + (row & 7) * 2;
           run += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(src));
@@ -590,21 +593,22 @@ __device__ __forceinline__ void posbias_bwd_body(const CUtensorMap& tm_row, cons
   }
 
   if (!failed) {
-    const bool got = mbar_wait(bar_f, (npairs - 1) & 1, abort_flag, p.status, kErrAccFullWait);
+    const bool got = tid != 0 || mbar_wait(bar_f, (npairs - 1) & 1, abort_flag, p.status, kErrAccFullWait);
     if (__syncthreads_and(got)) {
       tc_fence_after();
       flush_row(nt - 1);
-      float* dst0 = p.d_pos[SIDE] + h * kD + part * 16;
       for (int blk = 0; blk < p.nblk; ++blk) {
         if (!((p.touched[SIDE] >> blk) & 1u)) continue;
-        uint32_t r[16];
-        tmem_ld16(t_pos + blk * 64 + lane_addr + part * 16, r);
-        tmem_ld_wait();
         const int w = blk * kTile + row;
-        if (w < p.span2) {
-          float* dst = dst0 + static_cast<long long>(w) * H;
 #pragma unroll
-          for (int v = 0; v < 4; ++v)
+        for (int c = 0; c < kAccCols / 8; ++c) {
+          uint32_t r[8];
+          tmem_ld8(t_pos + blk * 64 + lane_addr + part * kAccCols + c * 8, r);
+          tmem_ld_wait();
+          if (w >= p.span2) continue;
+          float* dst = p.d_pos[SIDE] + static_cast<long long>(w) * H + h * kD + part * kAccCols + c * 8;
+#pragma unroll
+          for (int v = 0; v < 2; ++v)
             red_add_v4(dst + v * 4, __uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]),
                        __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3]));
         }
@@ -625,7 +629,7 @@ __device__ __forceinline__ void posbias_bwd_body(const CUtensorMap& tm_row, cons
   }
 }
 
-// grid (2 sides, heads, B), 512 threads
+// grid (2 sides, heads, B), 128·kParts threads
 __global__ void __launch_bounds__(kThreads, 1)
 posbias_tc_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_pk, const __grid_constant__ CUtensorMap tm_pq,
@@ -687,11 +691,7 @@ extern "C" int db200_posbias_tc_bwd(const PosBiasArgs* a, void* stream_) {
                                  static_cast<long long>(a->S) * a->ldb, kTile)))
     return rc;
   const int smem = BwdSmem::total(nt);
-  static int configured = 0;
-  if (configured < smem) {
-    if (cudaFuncSetAttribute(posbias_tc_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
-    configured = smem;
-  }
+  if (cudaFuncSetAttribute(posbias_tc_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
   dim3 grid(2, a->heads, a->B);
   posbias_tc_bwd_kernel<<<grid, kThreads, smem, stream>>>(tq, tk, tpk, tpq, tg, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;

@@ -250,6 +250,7 @@ class DebertaV2Layer(nn.Module):
         self.attention = DebertaV2Attention(config)
         self.intermediate = DebertaV2Intermediate(config)
         self.output = DebertaV2Output(config)
+        self.call_ffn_modules = False
 
     def forward(
         self,
@@ -264,7 +265,8 @@ class DebertaV2Layer(nn.Module):
         a = self.attention(hidden_states, mask, query_states=query_states, relative_pos=relative_pos,
                            rel_embeddings=rel_embeddings)
         inter, out = self.intermediate, self.output
-        fused = inter.act_name == "gelu" and not (self.training and out.dropout_p > 0.0)
+        # (a layer whose FFN modules were compiled one by one, ``train.compile.scope: ffn``, has to call them)
+        fused = inter.act_name == "gelu" and not (self.training and out.dropout_p > 0.0) and not self.call_ffn_modules
         if fused:
             y = ffn_gelu(a, inter.dense.weight, inter.dense.bias, out.dense.weight, out.dense.bias, residual=a)
             y = _ln(out.LayerNorm, y)

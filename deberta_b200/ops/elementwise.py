@@ -29,29 +29,36 @@ def _rows_view(x: torch.Tensor) -> torch.Tensor:
     return x2
 
 
-class _Rotary(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, x, cos, sin, heads, rotary_dim):
-        B, S, H = x.shape
+def rotary_apply(x, cos, sin, heads: int, rotary_dim: int, inverse: bool):
+    """Rotate (``inverse``: rotate back, i.e. the gradient of the rotation) a token-major ``[B, S, H]`` tensor."""
+    B, S, H = x.shape
+    if _kernel_ok(x):
         x2 = _rows_view(x)
         y = torch.empty((B * S, H), dtype=x.dtype, device=x.device)
         _lib.call("db200_rotary_bf16", _lib.ptr(x2), _lib.ptr(y), ctypes.c_longlong(x2.stride(0)), ctypes.c_longlong(H),
                   _lib.ptr(cos), _lib.ptr(sin), ctypes.c_longlong(B * S), ctypes.c_int(S), ctypes.c_int(heads),
-                  ctypes.c_int(H // heads), ctypes.c_int(rotary_dim), ctypes.c_int(0), _lib.stream_ptr())
-        ctx.save_for_backward(cos, sin)
-        ctx.meta = (B, S, H, heads, rotary_dim)
+                  ctypes.c_int(H // heads), ctypes.c_int(rotary_dim), ctypes.c_int(int(inverse)), _lib.stream_ptr())
         return y.view(B, S, H)
+    from .attention import rotate_interleaved
+
+    d = H // heads
+    c = cos.to(x.dtype)[None, :, None, :]
+    s = (-sin if inverse else sin).to(x.dtype)[None, :, None, :]
+    return rotate_interleaved(x.reshape(B, S, heads, d), c, s, rotary_dim).reshape(B, S, H)
+
+
+class _Rotary(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin, heads, rotary_dim):
+        ctx.save_for_backward(cos, sin)
+        ctx.meta = (heads, rotary_dim)
+        return rotary_apply(x, cos, sin, heads, rotary_dim, False)
 
     @staticmethod
     def backward(ctx, dy):
         cos, sin = ctx.saved_tensors
-        B, S, H, heads, rotary_dim = ctx.meta
-        d2 = _rows_view(dy)
-        dx = torch.empty((B * S, H), dtype=dy.dtype, device=dy.device)
-        _lib.call("db200_rotary_bf16", _lib.ptr(d2), _lib.ptr(dx), ctypes.c_longlong(d2.stride(0)), ctypes.c_longlong(H),
-                  _lib.ptr(cos), _lib.ptr(sin), ctypes.c_longlong(B * S), ctypes.c_int(S), ctypes.c_int(heads),
-                  ctypes.c_int(H // heads), ctypes.c_int(rotary_dim), ctypes.c_int(1), _lib.stream_ptr())
-        return dx.view(B, S, H), None, None, None, None
+        heads, rotary_dim = ctx.meta
+        return rotary_apply(dy, cos, sin, heads, rotary_dim, True), None, None, None, None
 
 
 def rotary_tokens(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, *, heads: int, rotary_dim: int) -> torch.Tensor:
@@ -66,6 +73,10 @@ def rotary_tokens(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, *, head
     if _kernel_ok(x) and d % 8 == 0 and rotary_dim % 2 == 0:
         c = cos.detach().to(torch.float32).contiguous()
         s = sin.detach().to(torch.float32).contiguous()
+        if torch.compiler.is_compiling():
+            from . import library
+
+            return library.rotary(x, c, s, heads, rotary_dim, False)
         return _Rotary.apply(x, c, s, heads, rotary_dim)
     from .attention import rotate_interleaved
 
@@ -73,28 +84,42 @@ def rotary_tokens(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, *, head
     return rotate_interleaved(x.reshape(B, S, heads, d), c, s, rotary_dim).reshape(B, S, H)
 
 
-class _SwiGLU(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, gu):
-        rows, two_f = gu.shape
-        f = two_f // 2
+def swiglu_forward(gu):
+    rows, two_f = gu.shape
+    f = two_f // 2
+    if _kernel_ok(gu):
         out = torch.empty((rows, f), dtype=gu.dtype, device=gu.device)
         _lib.call("db200_swiglu_fwd", _lib.ptr(gu), ctypes.c_longlong(gu.stride(0)), _lib.ptr(out), ctypes.c_longlong(f),
                   ctypes.c_longlong(rows), ctypes.c_int(f), _lib.stream_ptr())
-        ctx.save_for_backward(gu)
         return out
+    return F.silu(gu[:, :f]) * gu[:, f:]
 
-    @staticmethod
-    def backward(ctx, dout):
-        (gu,) = ctx.saved_tensors
-        rows, two_f = gu.shape
-        f = two_f // 2
+
+def swiglu_backward(gu, dout):
+    rows, two_f = gu.shape
+    f = two_f // 2
+    if _kernel_ok(gu):
         d2 = _rows_view(dout)
         dgu = torch.empty((rows, two_f), dtype=gu.dtype, device=gu.device)
         _lib.call("db200_swiglu_bwd", _lib.ptr(gu), ctypes.c_longlong(gu.stride(0)), _lib.ptr(d2),
                   ctypes.c_longlong(d2.stride(0)), _lib.ptr(dgu), ctypes.c_longlong(two_f), ctypes.c_longlong(rows),
                   ctypes.c_int(f), _lib.stream_ptr())
         return dgu
+    gate, up = gu[:, :f].float(), gu[:, f:].float()
+    sig = torch.sigmoid(gate)
+    d = dout.float()
+    return torch.cat([d * up * sig * (1 + gate * (1 - sig)), d * gate * sig], dim=-1).to(gu.dtype)
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        ctx.save_for_backward(gu)
+        return swiglu_forward(gu)
+
+    @staticmethod
+    def backward(ctx, dout):
+        return swiglu_backward(ctx.saved_tensors[0], dout)
 
 
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
@@ -102,6 +127,10 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     f = gate_up.shape[-1] // 2
     if _kernel_ok(gate_up) and f % 8 == 0 and gate_up.shape[-1] == 2 * f:
         lead = gate_up.shape[:-1]
+        if torch.compiler.is_compiling():
+            from . import library
+
+            return library.swiglu(_rows_view(gate_up)).view(*lead, f)
         return _SwiGLU.apply(_rows_view(gate_up)).view(*lead, f)
     gate, up = gate_up.chunk(2, dim=-1)
     return F.silu(gate) * up

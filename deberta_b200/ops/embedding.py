@@ -31,30 +31,51 @@ def _grad_ready(table: torch.Tensor | None) -> bool:
     return g is not None and g.dtype == torch.float32 and g.is_contiguous()
 
 
-class _Embed(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, ids, table, delta, padding_idx):
+def embed_forward(ids, table, delta):
+    """``table[ids] (+ delta[ids])``: one kernel on bf16 CUDA tables, ``F.embedding`` otherwise."""
+    if table.is_cuda and table.dtype == torch.bfloat16:
         flat = ids.reshape(-1).to(torch.int64).contiguous()
         vocab, hidden = table.shape
         out = torch.empty((flat.numel(), hidden), dtype=table.dtype, device=table.device)
         _lib.call("db200_embed_fwd", _lib.ptr(flat), _lib.ptr(table), _lib.ptr(delta), _lib.ptr(out),
                   ctypes.c_longlong(flat.numel()), ctypes.c_int(hidden), ctypes.c_longlong(vocab), _lib.stream_ptr())
-        ctx.ids, ctx.tables, ctx.padding_idx = flat, (table, delta), padding_idx
         return out.view(*ids.shape, hidden)
+    out = F.embedding(ids, table)
+    return out if delta is None else out + F.embedding(ids, delta)
+
+
+def embed_backward(dout, ids, vocab: int, padding_idx: int, grads) -> None:
+    """Add the rows of ``dout`` to row ``ids[t]`` of every fp32 buffer in ``grads`` (``None`` entries skipped)."""
+    d2 = dout.reshape(-1, dout.shape[-1])
+    flat = ids.reshape(-1).to(torch.int64).contiguous()
+    if d2.is_cuda and d2.dtype == torch.bfloat16:
+        if d2.stride(-1) != 1 or d2.stride(0) % 8 or d2.data_ptr() % 16:
+            d2 = d2.contiguous()
+        for g in grads:
+            if g is not None:
+                _lib.call("db200_embed_bwd", _lib.ptr(flat), _lib.ptr(d2), ctypes.c_longlong(d2.stride(0)), _lib.ptr(g),
+                          ctypes.c_longlong(flat.numel()), ctypes.c_int(d2.shape[1]), ctypes.c_longlong(vocab),
+                          ctypes.c_longlong(int(padding_idx)), _lib.stream_ptr())
+        return
+    rows = d2.float()
+    if padding_idx >= 0:
+        rows = rows * flat.ne(padding_idx).unsqueeze(-1).to(rows.dtype)
+    for g in grads:
+        if g is not None:
+            g.index_add_(0, flat, rows.to(g.dtype))
+
+
+class _Embed(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, table, delta, padding_idx):
+        ctx.ids, ctx.tables, ctx.padding_idx = ids, (table, delta), padding_idx
+        return embed_forward(ids, table, delta)
 
     @staticmethod
     def backward(ctx, dout):
-        d2 = dout.reshape(-1, dout.shape[-1])
-        if d2.stride(-1) != 1 or d2.stride(0) % 8 or d2.data_ptr() % 16:
-            d2 = d2.contiguous()
         pad = -1 if ctx.padding_idx is None else int(ctx.padding_idx)
-        for table in ctx.tables:
-            if table is None or not table.requires_grad:
-                continue
-            vocab, hidden = table.shape
-            _lib.call("db200_embed_bwd", _lib.ptr(ctx.ids), _lib.ptr(d2), ctypes.c_longlong(d2.stride(0)),
-                      _lib.ptr(table.main_grad), ctypes.c_longlong(ctx.ids.numel()), ctypes.c_int(hidden),
-                      ctypes.c_longlong(vocab), ctypes.c_longlong(pad), _lib.stream_ptr())
+        grads = [t.main_grad if (t is not None and t.requires_grad) else None for t in ctx.tables]
+        embed_backward(dout, ctx.ids, ctx.tables[0].shape[0], pad, grads)
         return None, None, None, None
 
 
@@ -63,14 +84,16 @@ def embedding_lookup(ids: torch.Tensor, table: torch.Tensor, delta: torch.Tensor
     """``table[ids] (+ delta[ids])``; gradients of trainable tables go to their ``main_grad`` on the kernel path."""
     if _usable(table) and _usable(delta) and table.is_cuda and _grad_ready(table) and _grad_ready(delta) and \
             (delta is None or delta.shape == table.shape):
+        if torch.compiler.is_compiling():
+            from . import library
+
+            tg = table.main_grad if table.requires_grad else None
+            dg = delta.main_grad if (delta is not None and delta.requires_grad) else None
+            return library.embed(ids, table, delta, -1 if padding_idx is None else int(padding_idx), tg, dg)
         if torch.is_grad_enabled() and (table.requires_grad or (delta is not None and delta.requires_grad)):
             return _Embed.apply(ids, table, delta, padding_idx)
-        return _Embed.forward(_NoCtx(), ids, table, delta, padding_idx)
+        return embed_forward(ids, table, delta)
     out = F.embedding(ids, table, padding_idx=padding_idx)
     if delta is not None:
         out = out + F.embedding(ids, delta, padding_idx=padding_idx)
     return out
-
-
-class _NoCtx:
-    """Stand-in context for calling the forward outside autograd."""

@@ -22,13 +22,17 @@ def use_kernels(x: torch.Tensor) -> bool:
     return x.is_cuda and x.dtype == torch.bfloat16
 
 
-def _weight_grad(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor | None:
-    """dW[out,in] = dyᵀ·x, accumulated into ``w.main_grad`` when present."""
-    main = getattr(w, "main_grad", None)
+def weight_grad_into(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor, main: torch.Tensor | None) -> torch.Tensor | None:
+    """dW[out,in] = dyᵀ·x: added to the fp32 buffer ``main`` when given (returns ``None``), else returned in ``w``'s dtype."""
     if main is not None:
         gemm(dy, x, a_mn=True, b_mn=True, out=main, accumulate=True)
         return None
     return gemm(dy, x, a_mn=True, b_mn=True, out_dtype=torch.float32).to(w.dtype)
+
+
+def _weight_grad(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor | None:
+    """dW accumulated into ``w.main_grad`` when the engine attached one."""
+    return weight_grad_into(dy, x, w, getattr(w, "main_grad", None))
 
 
 def colsum_into(dy: torch.Tensor, out: torch.Tensor) -> None:
@@ -41,10 +45,8 @@ def colsum_into(dy: torch.Tensor, out: torch.Tensor) -> None:
               ctypes.c_int(dy.shape[1]), _lib.ptr(out), _lib.stream_ptr())
 
 
-def _bias_grad(dy: torch.Tensor, b: torch.Tensor | None) -> torch.Tensor | None:
-    if b is None:
-        return None
-    main = getattr(b, "main_grad", None)
+def bias_grad_into(dy: torch.Tensor, main: torch.Tensor | None, dtype: torch.dtype) -> torch.Tensor | None:
+    """Column sums of ``dy``: added to the fp32 buffer ``main`` when given (returns ``None``), else returned as ``dtype``."""
     kernel_ok = dy.is_cuda and dy.dtype == torch.bfloat16 and dy.stride(1) == 1 and dy.stride(0) % 8 == 0 and dy.data_ptr() % 16 == 0
     if main is not None and kernel_ok:
         colsum_into(dy, main)
@@ -57,7 +59,13 @@ def _bias_grad(dy: torch.Tensor, b: torch.Tensor | None) -> torch.Tensor | None:
     if main is not None:
         main.add_(g)
         return None
-    return g.to(b.dtype)
+    return g.to(dtype)
+
+
+def _bias_grad(dy: torch.Tensor, b: torch.Tensor | None) -> torch.Tensor | None:
+    if b is None:
+        return None
+    return bias_grad_into(dy, getattr(b, "main_grad", None), b.dtype)
 
 
 class _Linear(torch.autograd.Function):
@@ -92,7 +100,12 @@ def linear(
     if x2.stride(-1) != 1 or x2.stride(0) % 8:
         x2 = x2.contiguous()
     r2 = None if residual is None else residual.reshape(-1, w.shape[0]).contiguous()
-    out = _Linear.apply(x2, w, b, r2)
+    if torch.compiler.is_compiling():
+        from . import library
+
+        out = library.linear(x2, w, b, r2, getattr(w, "main_grad", None), None if b is None else getattr(b, "main_grad", None))
+    else:
+        out = _Linear.apply(x2, w, b, r2)
     return out.view(*lead, w.shape[0])
 
 
@@ -135,7 +148,13 @@ def ffn_gelu(x, w1, b1, w2, b2, residual=None):
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1]).contiguous()
     r2 = None if residual is None else residual.reshape(-1, w2.shape[0]).contiguous()
-    out = _FFNGelu.apply(x2, w1, b1, w2, b2, r2)
+    if torch.compiler.is_compiling():
+        from . import library
+
+        mg = lambda t: None if t is None else getattr(t, "main_grad", None)  # noqa: E731
+        out = library.ffn_gelu(x2, w1, b1, w2, b2, r2, mg(w1), mg(b1), mg(w2), mg(b2))[0]
+    else:
+        out = _FFNGelu.apply(x2, w1, b1, w2, b2, r2)
     return out.view(*lead, w2.shape[0])
 
 
@@ -224,7 +243,8 @@ def linear_qkv(x, wq, bq, wk, bk, wv, bv):
     One GEMM with a three times wider output when the engine laid the three weights (and biases, and their fp32
     gradient buffers) out back to back, three GEMMs otherwise.
     """
-    if not _qkv_fusable(x, wq, bq, wk, bk, wv, bv):
+    if torch.compiler.is_compiling() or not _qkv_fusable(x, wq, bq, wk, bk, wv, bv):
+        # (the fused form compares storage addresses of parameters, which a tracing compiler cannot see)
         return linear(x, wq, bq), linear(x, wk, bk), linear(x, wv, bv)
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])

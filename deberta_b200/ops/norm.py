@@ -37,29 +37,80 @@ def _kernel_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
     )
 
 
-def _grad_target(p: torch.Tensor | None):
-    """(buffer to accumulate into, whether it is the engine's main_grad)."""
-    if p is None:
-        return None, False
-    main = getattr(p, "main_grad", None)
-    if main is not None:
-        return main, True
-    return torch.zeros(p.shape, dtype=torch.float32, device=p.device), False
+def norm_forward(x, weight, bias, row_keep, eps: float, rms: bool):
+    """(y, mean, rstd) of ``x`` [rows, H]; ``mean`` is empty for RMSNorm. Kernel on bf16 CUDA, PyTorch otherwise."""
+    rows, H = x.shape
+    if _kernel_ok(x, weight):
+        y = torch.empty_like(x)
+        mean = torch.empty(0 if rms else rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        keep = None if row_keep is None else row_keep.to(torch.uint8).contiguous()
+        _lib.call(
+            "db200_norm_fwd", _lib.ptr(x), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(keep), _lib.ptr(y),
+            _lib.ptr(None if rms else mean), _lib.ptr(rstd), ctypes.c_int(rows), ctypes.c_int(H), ctypes.c_float(eps),
+            ctypes.c_int(int(rms)), _lib.stream_ptr(),
+        )
+        return y, mean, rstd
+    xf = x.float()
+    if rms:
+        mean = torch.empty(0, dtype=torch.float32, device=x.device)
+        rstd = torch.rsqrt(xf.pow(2).mean(dim=-1) + eps)
+        y = xf * rstd[:, None] * weight.float()
+    else:
+        mean = xf.mean(dim=-1)
+        rstd = torch.rsqrt(xf.var(dim=-1, unbiased=False) + eps)
+        y = (xf - mean[:, None]) * rstd[:, None] * weight.float()
+        if bias is not None:
+            y = y + bias.float()
+    if row_keep is not None:
+        y = y * row_keep.reshape(-1, 1).to(y.dtype)
+    return y.to(x.dtype), mean, rstd
+
+
+def norm_backward(dy, x, weight, mean, rstd, row_keep, rms: bool, has_bias: bool, w_grad, b_grad):
+    """(dx, dgamma, dbeta): a parameter gradient that was added to its fp32 buffer (``w_grad`` / ``b_grad``) is ``None``."""
+    rows, H = x.shape
+    dy = dy.contiguous()
+    if _kernel_ok(x, weight):
+        dx = torch.empty_like(x)
+        dg = w_grad if w_grad is not None else torch.zeros(H, dtype=torch.float32, device=x.device)
+        db = None
+        if has_bias:
+            db = b_grad if b_grad is not None else torch.zeros(H, dtype=torch.float32, device=x.device)
+        keep = None if row_keep is None else row_keep.to(torch.uint8).contiguous()
+        _lib.call(
+            "db200_norm_bwd", _lib.ptr(dy), _lib.ptr(x), _lib.ptr(weight), _lib.ptr(None if rms else mean), _lib.ptr(rstd),
+            _lib.ptr(keep), _lib.ptr(dx), _lib.ptr(dg), _lib.ptr(db), ctypes.c_int(rows), ctypes.c_int(H),
+            ctypes.c_int(int(rms)), _lib.stream_ptr(),
+        )
+        return (dx, None if w_grad is not None else dg.to(weight.dtype),
+                None if (db is None or b_grad is not None) else db.to(weight.dtype))
+    dyf, xf, g = dy.float(), x.float(), weight.float()
+    if row_keep is not None:
+        dyf = dyf * row_keep.reshape(-1, 1).to(dyf.dtype)
+    xhat = xf * rstd[:, None] if rms else (xf - mean[:, None]) * rstd[:, None]
+    dgamma = (dyf * xhat).sum(0)
+    dbeta = dyf.sum(0) if has_bias else None
+    dxhat = dyf * g
+    if rms:
+        dx = rstd[:, None] * (dxhat - xhat * (dxhat * xhat).mean(dim=-1, keepdim=True))
+    else:
+        dx = rstd[:, None] * (dxhat - dxhat.mean(dim=-1, keepdim=True) - xhat * (dxhat * xhat).mean(dim=-1, keepdim=True))
+    if w_grad is not None:
+        w_grad.add_(dgamma)
+        dgamma = None
+    if dbeta is not None and b_grad is not None:
+        b_grad.add_(dbeta)
+        dbeta = None
+    return (dx.to(x.dtype), None if dgamma is None else dgamma.to(weight.dtype),
+            None if dbeta is None else dbeta.to(weight.dtype))
 
 
 class _Norm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, eps, rms, row_keep):
-        rows, H = x.shape
-        y = torch.empty_like(x)
-        mean = torch.empty(rows, dtype=torch.float32, device=x.device) if not rms else None
-        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
         keep = None if row_keep is None else row_keep.to(torch.uint8).contiguous()
-        _lib.call(
-            "db200_norm_fwd", _lib.ptr(x), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(keep), _lib.ptr(y),
-            _lib.ptr(mean), _lib.ptr(rstd), ctypes.c_int(rows), ctypes.c_int(H), ctypes.c_float(eps),
-            ctypes.c_int(int(rms)), _lib.stream_ptr(),
-        )
+        y, mean, rstd = norm_forward(x, weight, bias, keep, eps, rms)
         ctx.save_for_backward(x, mean, rstd, keep)
         ctx.refs = (weight, bias)
         ctx.rms = rms
@@ -69,21 +120,20 @@ class _Norm(torch.autograd.Function):
     def backward(ctx, dy):
         x, mean, rstd, keep = ctx.saved_tensors
         weight, bias = ctx.refs
-        rows, H = x.shape
-        dy = dy.contiguous()
-        dx = torch.empty_like(x)
-        dg, g_main = _grad_target(weight if weight.requires_grad else None)
-        db, b_main = _grad_target(bias if (bias is not None and bias.requires_grad) else None)
-        if dg is None:  # kernel always needs somewhere to put the weight gradient
-            dg = torch.zeros(H, dtype=torch.float32, device=x.device)
-        _lib.call(
-            "db200_norm_bwd", _lib.ptr(dy), _lib.ptr(x), _lib.ptr(weight), _lib.ptr(mean), _lib.ptr(rstd),
-            _lib.ptr(keep), _lib.ptr(dx), _lib.ptr(dg), _lib.ptr(db), ctypes.c_int(rows), ctypes.c_int(H),
-            ctypes.c_int(int(ctx.rms)), _lib.stream_ptr(),
-        )
-        gw = None if (g_main or not weight.requires_grad) else dg.to(weight.dtype)
-        gb = None if (b_main or db is None) else db.to(bias.dtype)
-        return dx, gw, gb, None, None, None
+        has_bias = bias is not None and bias.requires_grad
+        w_grad = getattr(weight, "main_grad", None) if weight.requires_grad else None
+        b_grad = getattr(bias, "main_grad", None) if has_bias else None
+        dx, gw, gb = norm_backward(dy, x, weight, mean, rstd, keep, ctx.rms, has_bias, w_grad, b_grad)
+        return dx, (gw if weight.requires_grad else None), gb, None, None, None
+
+
+def _norm_apply(x2, weight, bias, eps: float, rms: bool, rk):
+    if torch.compiler.is_compiling():
+        from . import library
+
+        return library.norm(x2, weight, bias, rk, float(eps), rms, getattr(weight, "main_grad", None),
+                            None if bias is None else getattr(bias, "main_grad", None))[0]
+    return _Norm.apply(x2, weight, bias, float(eps), rms, rk)
 
 
 def layer_norm(x, weight, bias, eps: float, row_keep: torch.Tensor | None = None):
@@ -93,7 +143,7 @@ def layer_norm(x, weight, bias, eps: float, row_keep: torch.Tensor | None = None
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1]).contiguous()
     rk = None if row_keep is None else row_keep.reshape(-1)
-    return _Norm.apply(x2, weight, bias, float(eps), False, rk).view(*lead, x.shape[-1])
+    return _norm_apply(x2, weight, bias, eps, False, rk).view(*lead, x.shape[-1])
 
 
 def rms_norm(x, weight, eps: float, row_keep: torch.Tensor | None = None):
@@ -103,4 +153,4 @@ def rms_norm(x, weight, eps: float, row_keep: torch.Tensor | None = None):
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1]).contiguous()
     rk = None if row_keep is None else row_keep.reshape(-1)
-    return _Norm.apply(x2, weight, None, float(eps), True, rk).view(*lead, x.shape[-1])
+    return _norm_apply(x2, weight, None, eps, True, rk).view(*lead, x.shape[-1])

@@ -25,6 +25,7 @@ from deberta_b200.utils.checkpoint import load_training_state, save_training_sta
 from deberta_b200.utils.log import setup_process_logging
 from deberta_b200.utils.trace import set_nvtx
 
+from .compile import maybe_compile_model, resolve_compile_scope
 from .checkpointing import (checkpoint_is_due, normalize_resume_consumed_micro_batches, resolve_data_resume_policy,
                             save_periodic_checkpoint_if_due)
 from .export_helpers import export_discriminator_hf_subprocess
@@ -78,7 +79,10 @@ def run_pretraining_dry_run(*, model_cfg: ModelConfig, data_cfg: DataConfig, tra
     build_backbone_configs(model_cfg=model_cfg, tokenizer=tok, max_position_embeddings=int(data_cfg.packing.max_seq_length))
     return {
         "checkpoint_output_dir": str(out), "logging_output_dir": str(log_dir), "resume_checkpoint": resume,
-        "effective_compile_scope": "none (hot operators are precompiled sm_100a kernels)",
+        "effective_compile_scope": (resolve_compile_scope(
+            requested_scope=train_cfg.compile.scope, backbone_type=model_cfg.backbone_type,
+            block_cross_document_attention=bool(data_cfg.packing.block_cross_document_attention))[0]
+            if train_cfg.compile.enabled else "none (compile disabled; hot operators are precompiled sm_100a kernels)"),
         "sample_batch_shape": tuple(batch["input_ids"].shape),
         "sample_active_tokens": int(count_input_tokens_for_batch(batch)), "tokenizer_vocab_size": len(tok),
     }
@@ -121,6 +125,15 @@ def run_pretraining(*, model_cfg: ModelConfig, data_cfg: DataConfig, train_cfg: 
     trainer = Trainer(model=model, engine=engine, ctx=ctx, train_cfg=train_cfg, optim_cfg=optim_cfg,
                       pad_token_id=getattr(tok, "pad_token_id", None))
     model.sync_discriminator_embeddings_from_generator()
+    compile_scope, compile_reason, _ = maybe_compile_model(model, train_cfg=train_cfg, model_cfg=model_cfg, data_cfg=data_cfg)
+    if compile_scope is not None and ctx.is_main_process:
+        from deberta_b200.run_layout import RUN_METADATA_FILE
+        from deberta_b200.utils.io import dump_json
+
+        from .run_config import build_run_metadata
+
+        dump_json(build_run_metadata(effective_compile_scope=compile_scope, compile_scope_reason=compile_reason),
+                  out_dir / RUN_METADATA_FILE)
     # what the run really uses (derived generator shape, vocabulary size, collective path) goes to config_resolved.yaml
     # and to the tracker instead of the raw sections (``entrypoint.py:619-633`` of the reference)
     resolved = build_runtime_resolved_config(

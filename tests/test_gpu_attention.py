@@ -24,15 +24,17 @@ def _inputs(B, S, heads, span, seed=0, scale=0.5):
 
 
 def _set_position_mode(monkeypatch, mode):
-    """"tc": bias and its gradient by the tensor-core tile kernels; "bias": bias pre-gathered from score tables,
-    gradient by prefix-sum scans; "gather": bucket tables read inside the attention kernels."""
+    """"tc": bias and its gradient by the tensor-core tile kernels; "tc_fwd": bias by the tile kernel, gradient by
+    prefix-sum scans (the default); "bias": bias pre-gathered from score tables, gradient by scans; "gather": bucket
+    tables read inside the attention kernels."""
     from deberta_b200.ops import attention_cuda
 
     monkeypatch.setattr(attention_cuda, "BIAS_MODE_MAX_SEQ", 0 if mode == "gather" else 1024)
-    monkeypatch.setattr(attention_cuda, "POSBIAS_TENSOR_CORE", mode == "tc")
+    monkeypatch.setattr(attention_cuda, "POSBIAS_TENSOR_CORE", mode in ("tc", "tc_fwd"))
+    monkeypatch.setattr(attention_cuda, "POSBIAS_TENSOR_CORE_BWD", mode == "tc")
 
 
-@pytest.mark.parametrize("mode", ["tc", "bias", "gather"])
+@pytest.mark.parametrize("mode", ["tc", "tc_fwd", "bias", "gather"])
 @pytest.mark.parametrize("B,S,heads,mask", [(2, 512, 2, "none"), (2, 200, 3, "pad"), (1, 384, 2, "doc"), (2, 128, 1, "none")])
 def test_disentangled_forward_backward(B, S, heads, mask, mode, monkeypatch):
     _set_position_mode(monkeypatch, mode)
