@@ -52,7 +52,7 @@ def parse_args() -> argparse.Namespace:
     p.add_argument("--model-size", default="base")
     p.add_argument("--backbone", choices=("hf_deberta_v2", "rope"), default="hf_deberta_v2",
                    help="rope: the RoPE/RMSNorm/SwiGLU family at its config defaults (secondary benchmark)")
-    p.add_argument("--parallelism", choices=("ddp", "zero"), default="zero")
+    p.add_argument("--parallelism", choices=("ddp", "zero", "fsdp"), default="zero")
     p.add_argument("--block-docs", action="store_true",
                    help="rope backbone only: packed documents do not attend to each other (data.packing."
                         "block_cross_document_attention); the collator then emits document ids")
@@ -216,7 +216,7 @@ def run_ours(args: argparse.Namespace) -> dict:
                              else "rope RTD (config defaults, GDES)"),
                    "global_batch": args.micro_batch * args.ga * ctx.world_size, "micro_batch": args.micro_batch,
                    "grad_accum": args.ga, "seq_len": args.seq_len, "block_cross_document_attention": bool(args.block_docs),
-                   "parallelism": f"dp{ctx.world_size}" + ("-zero1" if args.parallelism == "zero" else "-replicated"),
+                   "parallelism": f"dp{ctx.world_size}" + {"zero": "-zero1", "fsdp": "-fullshard", "ddp": "-replicated"}[args.parallelism],
                    "collectives": ("none (1 GPU)" if ctx.world_size == 1 else
                                    ("fused peer-memory kernels" + (" (multimem)" if engine.comm.multicast else "")
                                     if getattr(engine, "comm", None) is not None else "NCCL")),
@@ -225,7 +225,10 @@ def run_ours(args: argparse.Namespace) -> dict:
         "e2e": {"value": tokens_per_step * ctx.world_size * args.steps / e2e_s, "unit": "tokens/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches, "final_gen_loss": gen_loss,
+        "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2**30, 2),
     }
+    if getattr(engine, "sharder", None) is not None:
+        result["config"]["param_shard_bytes"] = engine.sharder.memory_report()
     ctx.shutdown()
     return result if ctx.is_main_process else {}
 

@@ -218,7 +218,7 @@ struct AdamDev {
 __global__ void __launch_bounds__(256)
 comm_adamw_kernel(const CommDev c, long long off, float* __restrict__ master, float* __restrict__ m,
                   float* __restrict__ v, const AdamDev a, uint32_t epoch, float* norm_sq_out,
-                  const float* __restrict__ gate) {
+                  const float* __restrict__ gate, __nv_bfloat16* __restrict__ local_params) {
   __shared__ int wait_flag;
   uint32_t* pad = c.pads[c.rank];
   const bool shares_in = wait_peers(c, kChNorm, epoch, &wait_flag);
@@ -264,7 +264,9 @@ comm_adamw_kernel(const CommDev c, long long off, float* __restrict__ master, fl
         packed.y = __uint_as_float(pack_bf16(pv[2], pv[3]));
         packed.z = __uint_as_float(pack_bf16(pv[4], pv[5]));
         packed.w = __uint_as_float(pack_bf16(pv[6], pv[7]));
-        if (c.mc_params) {
+        if (local_params) {  // parameters stay sharded: only this rank keeps the slab (peers fetch it per layer)
+          *reinterpret_cast<float4*>(local_params + i) = packed;
+        } else if (c.mc_params) {
           multimem_st_v4(c.mc_params + off + i, packed);
         } else {
           for (int r = 0; r < c.world; ++r) *reinterpret_cast<float4*>(c.params[r] + off + i) = packed;
@@ -301,6 +303,31 @@ comm_vector_sum_kernel(const CommDev c, const float* __restrict__ in, float* __r
   __syncthreads();
   signal_peers(c, kChStart, epoch);
   wait_peers(c, kChStart, epoch, &wait_flag);
+}
+
+// Gather of sharded parameters: up to kMaxPieces contiguous byte ranges, each read from memory that may belong to a
+// peer GPU (plain 16-byte loads through the peer mapping) and written to this GPU's memory. One launch per layer
+// unit; ordering against the owners' optimizer kernels is the caller's (stream events after the kernels' own
+// all-rank barrier).
+constexpr int kMaxPieces = 2 * kMaxWorld;
+struct PieceList {
+  const uint4* src[kMaxPieces];
+  uint4* dst[kMaxPieces];
+  long long n16[kMaxPieces];  // 16-byte units
+  int count;
+};
+__global__ void __launch_bounds__(256) copy_pieces_kernel(const PieceList p) {
+  for (int k = 0; k < p.count; ++k) {
+    const uint4* __restrict__ s = p.src[k];
+    uint4* __restrict__ d = p.dst[k];
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.n16[k]; i += stride) {
+      uint4 v;
+      asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(s + i) : "memory");
+      d[i] = v;
+    }
+  }
 }
 
 int make_dev(const Db200CommCtx* h, CommDev* d) {
@@ -349,14 +376,15 @@ extern "C" int db200_comm_reduce(const Db200CommCtx* ctx, long long offset, long
 extern "C" int db200_comm_adamw(const Db200CommCtx* ctx, long long offset, long long count, float* master, float* exp_avg,
                                 float* exp_avg_sq, const Db200AdamSegment* segs, int nseg, float b1, float b2, float eps,
                                 float inv_bc1, float inv_sqrt_bc2, float max_norm, unsigned epoch, float* norm_sq_out,
-                                const float* gate, void* stream) {
+                                const float* gate, void* local_params, void* stream) {
   CommDev d;
   if (int rc = make_dev(ctx, &d)) return rc;
   if (count <= 0 || (count % 8) || (offset % 8) || nseg < 0 || nseg > 4) return -10;
-  if ((reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(exp_avg) | reinterpret_cast<uintptr_t>(exp_avg_sq)) & 15)
+  if ((reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(exp_avg) | reinterpret_cast<uintptr_t>(exp_avg_sq) |
+       reinterpret_cast<uintptr_t>(local_params)) & 15)
     return -10;
   for (int r = 0; r < d.world; ++r)
-    if (!d.params[r] || (reinterpret_cast<uintptr_t>(d.params[r]) & 15) || !d.grads[r]) return -10;
+    if ((!local_params && (!d.params[r] || (reinterpret_cast<uintptr_t>(d.params[r]) & 15))) || !d.grads[r]) return -10;
   AdamDev a{};
   a.nseg = nseg;
   for (int s = 0; s < nseg; ++s) {
@@ -365,7 +393,7 @@ extern "C" int db200_comm_adamw(const Db200CommCtx* ctx, long long offset, long 
   }
   a.b1 = b1; a.b2 = b2; a.eps = eps; a.inv_bc1 = inv_bc1; a.inv_sqrt_bc2 = inv_sqrt_bc2; a.max_norm = max_norm;
   comm_adamw_kernel<<<comm_grid(count, 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      d, offset, master, exp_avg, exp_avg_sq, a, epoch, norm_sq_out, gate);
+      d, offset, master, exp_avg, exp_avg_sq, a, epoch, norm_sq_out, gate, static_cast<__nv_bfloat16*>(local_params));
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -375,5 +403,28 @@ extern "C" int db200_comm_vector_sum(const Db200CommCtx* ctx, const float* in, f
   if (int rc = make_dev(ctx, &d)) return rc;
   if (n <= 0 || n > DB200_COMM_VEC_MAX) return -10;
   comm_vector_sum_kernel<<<1, DB200_COMM_VEC_MAX, 0, reinterpret_cast<cudaStream_t>(stream)>>>(d, in, out, n, epoch);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int db200_comm_copy_pieces(const void* const* src, void* const* dst, const long long* bytes, int count,
+                                      void* stream) {
+  if (count <= 0) return 0;
+  if (count > kMaxPieces) return -10;
+  PieceList p{};
+  long long total = 0;
+  for (int k = 0; k < count; ++k) {
+    if (!src[k] || !dst[k] || bytes[k] < 0 || (bytes[k] % 16) || (reinterpret_cast<uintptr_t>(src[k]) & 15) ||
+        (reinterpret_cast<uintptr_t>(dst[k]) & 15))
+      return -10;
+    p.src[k] = static_cast<const uint4*>(src[k]);
+    p.dst[k] = static_cast<uint4*>(dst[k]);
+    p.n16[k] = bytes[k] / 16;
+    total += p.n16[k];
+  }
+  p.count = count;
+  if (total == 0) return 0;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148 * 2) blocks = 148 * 2;  // a copy that shares the GPU with compute kernels: a third of the SMs' slots
+  copy_pieces_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -124,7 +124,12 @@ int db200_comm_reduce(const Db200CommCtx* ctx, long long offset, long long count
 int db200_comm_adamw(const Db200CommCtx* ctx, long long offset, long long count, float* master, float* exp_avg,
                      float* exp_avg_sq, const Db200AdamSegment* segs, int nseg, float b1, float b2, float eps,
                      float inv_bc1, float inv_sqrt_bc2, float max_norm, unsigned epoch, float* norm_sq_out,
-                     const float* gate, void* stream);
+                     const float* gate, void* local_params, void* stream);
+// local_params (may be null): bf16 buffer of `count` elements that receives the updated slab INSTEAD of the push into
+// every rank's parameter buffer (parameters stay sharded; peers fetch what they need with db200_comm_copy_pieces).
+// Copy `count` (<= 16) byte ranges, each possibly read from a peer GPU's memory, into local memory; sizes and
+// addresses are multiples of 16 bytes.
+int db200_comm_copy_pieces(const void* const* src, void* const* dst, const long long* bytes, int count, void* stream);
 // out[i] = sum over ranks of in[i], i < n <= DB200_COMM_VEC_MAX (in/out: this rank's own device memory).
 int db200_comm_vector_sum(const Db200CommCtx* ctx, const float* in, float* out, int n, unsigned epoch, void* stream);
 

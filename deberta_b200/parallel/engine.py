@@ -12,9 +12,9 @@ layout chosen for a 180 GB GPU and NVSwitch:
   discriminator-no-decay, so each optimizer (and each phase of decoupled training)
   owns one contiguous range: its gradient reduction is one collective over one range and
   its update is one fused AdamW launch per decay group.
-* ``parallelism="ddp"`` all-reduces the range; ``"zero"`` (sharded optimizer state — what
-  FSDP full-shard buys on this model size, at a third of its traffic) reduce-scatters it,
-  updates the local shard and all-gathers the bf16 compute copy.
+* ``parallelism="ddp"`` all-reduces the range; ``"zero"`` (sharded optimizer state) reduce-scatters it,
+  updates the local shard and all-gathers the bf16 compute copy; ``"fsdp"`` (full shard) also keeps the
+  compute copy sharded and gathers it layer by layer (``parallel/fsdp.py``).
 * the clip coefficient and the non-finite guard are evaluated on the device inside the
   AdamW kernel from the reduced squared norm, so a step needs no host synchronisation;
   the host reads the norm afterwards (or a step later) for logging and LR back-off.
@@ -122,9 +122,12 @@ class TrainEngine:
                  lr_discriminator: float = 5e-4, weight_decay: float = 0.01, betas: tuple[float, float] = (0.9, 0.999),
                  eps: float = 1e-8, fused_collectives: bool = True, multicast: str = "auto",
                  comm_timeout_s: float = 20.0) -> None:
-        if parallelism not in ("ddp", "zero"):
-            raise ValueError("parallelism must be 'ddp' or 'zero'")
+        if parallelism not in ("ddp", "zero", "fsdp"):
+            raise ValueError("parallelism must be 'ddp', 'zero' or 'fsdp'")
         self.model, self.ctx, self.parallelism = model, ctx, parallelism
+        self.sharded = parallelism in ("zero", "fsdp")  # optimizer state (and fp32 masters) live on one rank per slab
+        self.full_shard = parallelism == "fsdp"
+        self.sharder = None
         self.compute_dtype = compute_dtype
         self.device = ctx.device
         self.use_kernels = self.device.type == "cuda"
@@ -158,6 +161,7 @@ class TrainEngine:
             # gradient and parameter buffers live in memory every rank of the node can address
             try:
                 self.comm = PeerComm(total, rank=ctx.rank, world_size=world, device=dev,
+                                     param_elems=(total // world) if self.full_shard else None,
                                      use_multicast={"on": True, "off": False}.get(str(multicast), None),
                                      timeout_s=float(comm_timeout_s))
             except Exception as e:  # no peer access / symmetric allocator unavailable: NCCL collectives instead
@@ -176,20 +180,37 @@ class TrainEngine:
                 logging.getLogger(__name__).warning("Fused peer-memory collectives failed their self-check; using NCCL.")
                 self.comm = None
         if self.comm is not None:
-            self.grads, self.compute = self.comm.grads, self.comm.params
+            self.grads = self.comm.grads
+            self.compute = None if self.full_shard else self.comm.params
             ctx.fast_vector_sum = self.comm.vector_sum
         else:
             self.grads = torch.zeros(total, dtype=torch.float32, device=dev)
-            self.compute = torch.zeros(total, dtype=compute_dtype, device=dev) if compute_dtype != torch.float32 else None
+            self.compute = (torch.zeros(total, dtype=compute_dtype, device=dev)
+                            if (compute_dtype != torch.float32 and not self.full_shard) else None)
         self._params: dict[str, nn.Parameter] = {}
+        self._owner_bounds = bounds
+        for key in GROUP_ORDER:
+            for name, p in parts[key]:
+                off, n, _ = self.layout[name]
+                self.master[off : off + n].copy_(p.data.reshape(-1))
+        if world > 1:
+            # ranks seed their generators differently (data order, sampling noise), so their freshly initialised
+            # weights differ: every replica starts from rank 0's, as DDP / FSDP do when they wrap a module
+            dist.broadcast(self.master, src=0)
+            for p in model.parameters():
+                if not p.requires_grad and p.is_floating_point():
+                    dist.broadcast(p.data, src=0)
         for key in GROUP_ORDER:
             for name, p in parts[key]:
                 off, n, shape = self.layout[name]
-                self.master[off : off + n].copy_(p.data.reshape(-1))
                 gview = self.grads[off : off + n].view(shape)
-                if self.compute is not None:
+                if self.full_shard:  # storage comes from the sharder's slots below
+                    p.grad = None
+                    p.main_grad = gview
+                    p.register_post_accumulate_grad_hook(_fold_grad_into_main)
+                elif self.compute is not None:
                     cview = self.compute[off : off + n]
-                    cview.copy_(p.data.reshape(-1))
+                    cview.copy_(self.master[off : off + n])
                     p.data = cview.view(shape)
                     p.grad = None
                     p.main_grad = gview
@@ -198,9 +219,11 @@ class TrainEngine:
                     p.data = self.master[off : off + n].view(shape)
                     p.grad = gview
                 self._params[name] = p
-        self._alias_gdes_bases()
+        if not self.full_shard:
+            self._alias_gdes_bases()
         for p in model.parameters():  # remaining frozen parameters follow the compute dtype
-            if not p.requires_grad and p.is_floating_point() and p.dtype != compute_dtype and self.compute is not None:
+            if not p.requires_grad and p.is_floating_point() and p.dtype != compute_dtype and \
+                    (self.compute is not None or self.full_shard):
                 p.data = p.data.to(compute_dtype)
         # ---- optimizers ---------------------------------------------------------------------
         self.optimizers: dict[str, OptimizerState] = {}
@@ -212,7 +235,7 @@ class TrainEngine:
             else:
                 start, end = bounds[owner]
                 my = [s for s in segs if s.group.startswith(owner)]
-            if parallelism == "zero" and world > 1:
+            if self.sharded and world > 1:
                 per = (end - start) // world
                 shard = (start + ctx.rank * per, start + (ctx.rank + 1) * per)
             else:
@@ -224,6 +247,22 @@ class TrainEngine:
                 torch.zeros(n, dtype=torch.float32, device=dev), torch.zeros(n, dtype=torch.float32, device=dev),
                 torch.zeros(1, dtype=torch.float32, device=dev), names,
             )
+        if self.full_shard:
+            from .fsdp import ParamSharder
+
+            self.sharder = ParamSharder(self, model, self.layout, self._params, compute_dtype)
+            self.sharder.load_from_master(self.master)
+            ctx.wait_for_everyone()  # every rank's slabs are filled before anybody gathers
+            self.sharder.after_update(None)
+            self._alias_gdes_bases()
+
+    def owner_of(self, name: str) -> str:
+        """``"gen"`` or ``"disc"``: which backbone's range of the flat layout holds parameter ``name``."""
+        off = self.layout[name][0]
+        for owner, (a, b) in self._owner_bounds.items():
+            if a <= off < b:
+                return owner
+        raise KeyError(name)
 
     # ---- GDES ---------------------------------------------------------------------------------
     def _alias_gdes_bases(self) -> None:
@@ -255,7 +294,7 @@ class TrainEngine:
         world = self.ctx.world_size
         g = self.grads[o.start : o.end]
         if self.comm is not None:
-            if self.parallelism == "zero":
+            if self.sharded:
                 o.epoch = self.comm.reduce(o.shard[0], o.shard[1] - o.shard[0], scale=1.0 / world, to_all=False,
                                            extra_share=penalty, norm_sq_out=None)
             else:
@@ -265,7 +304,7 @@ class TrainEngine:
             return o.norm_sq
         if world > 1:
             avg = dist.ReduceOp.AVG if self.ctx.backend == "nccl" else dist.ReduceOp.SUM
-            if self.parallelism == "zero":
+            if self.sharded:
                 out = self.grads[o.shard[0] : o.shard[1]]
                 if self.ctx.backend == "nccl":
                     dist.reduce_scatter_tensor(out, g, op=avg)
@@ -274,7 +313,7 @@ class TrainEngine:
             else:
                 dist.all_reduce(g, op=avg)
             if avg == dist.ReduceOp.SUM:
-                (self.grads[o.shard[0] : o.shard[1]] if self.parallelism == "zero" else g).mul_(1.0 / world)
+                (self.grads[o.shard[0] : o.shard[1]] if self.sharded else g).mul_(1.0 / world)
         local = self.grads[o.shard[0] : o.shard[1]]
         o.norm_sq.zero_()
         if self.use_kernels:
@@ -282,7 +321,7 @@ class TrainEngine:
                       _lib.stream_ptr())
         else:
             o.norm_sq.add_(local.double().pow(2).sum().float())
-        if world > 1 and self.parallelism == "zero":
+        if world > 1 and self.sharded:
             if penalty is not None:
                 o.norm_sq.add_(penalty.to(o.norm_sq.dtype).reshape(1))
             dist.all_reduce(o.norm_sq, op=dist.ReduceOp.SUM)
@@ -311,13 +350,16 @@ class TrainEngine:
         inv_sqrt_bc2 = 1.0 / math.sqrt(1.0 - b2 ** o.step)
         s0, s1 = o.shard
         skipped = False
-        if self.comm is not None and self.parallelism == "zero":
+        if self.comm is not None and self.sharded:
             segs = [(max(sg.start, s0) - s0, min(sg.end, s1) - s0, sg.base_lr * lr_scale, sg.weight_decay)
                     for sg in o.segments if max(sg.start, s0) < min(sg.end, s1)]
             self.comm.adamw(s0, s1 - s0, master=self.master[s0:s1], exp_avg=o.exp_avg, exp_avg_sq=o.exp_avg_sq,
                             segments=segs, betas=o.betas, eps=o.eps, inv_bc1=inv_bc1, inv_sqrt_bc2=inv_sqrt_bc2,
                             max_norm=max_grad_norm, epoch=o.epoch, norm_sq_out=o.norm_sq,
-                            gate=None if gate is None else gate.to(torch.float32).reshape(1))
+                            gate=None if gate is None else gate.to(torch.float32).reshape(1),
+                            local_params=self.sharder.slab_view(opt_name) if self.full_shard else None)
+            if self.full_shard:
+                self.sharder.after_update(opt_name)
             return
         if gate is not None:
             gate = gate.to(device=self.device, dtype=torch.float32).reshape(1)
@@ -334,6 +376,8 @@ class TrainEngine:
             p, g = self.master[a:b], self.grads[a:b]
             m, v = o.exp_avg[a - s0 : b - s0], o.exp_avg_sq[a - s0 : b - s0]
             shadow = self.compute[a:b] if self.compute is not None else None
+            if self.full_shard:
+                shadow = self.sharder.slab_view(opt_name)[a - s0 : b - s0]
             if self.use_kernels:
                 c_f = ctypes.c_float
                 _lib.call("db200_adamw", _lib.ptr(p), _lib.ptr(g), _lib.ptr(m), _lib.ptr(v), _lib.ptr(shadow),
@@ -351,10 +395,15 @@ class TrainEngine:
                     shadow.copy_(p)
         if skipped:
             o.step -= 1
-        if self.ctx.world_size > 1 and self.parallelism == "zero":
+        if self.full_shard:
+            if self.ctx.world_size > 1:
+                self.ctx.wait_for_everyone()  # every rank's slab is written before any rank reads it
+            self.sharder.after_update(opt_name)
+        elif self.ctx.world_size > 1 and self.parallelism == "zero":
             # masters stay sharded (only the owner's slice is authoritative); the compute copy is gathered
             buf = self.compute if self.compute is not None else self.master
-            dist.all_gather_into_tensor(buf[o.start : o.end], buf[s0:s1])
+            mine = buf[s0:s1] if self.ctx.backend == "nccl" else buf[s0:s1].clone()  # only NCCL gathers in place
+            dist.all_gather_into_tensor(buf[o.start : o.end], mine)
 
     def reset_optimizer_state(self, opt_name: str | None = None) -> None:
         for name, o in self.optimizers.items():
@@ -366,7 +415,7 @@ class TrainEngine:
     # ---- state ----------------------------------------------------------------------------------
     def gather_master(self) -> None:
         """Make every rank's fp32 master buffer complete (needed before saving under sharded optimizers)."""
-        if self.ctx.world_size > 1 and self.parallelism == "zero":
+        if self.ctx.world_size > 1 and self.sharded:
             for o in self.optimizers.values():
                 dist.all_gather_into_tensor(self.master[o.start : o.end], self.master[o.shard[0] : o.shard[1]].clone())
 
@@ -413,6 +462,10 @@ class TrainEngine:
                     continue  # aliases of generator tables
                 else:
                     t.data.copy_(src.to(t.dtype))
+        if self.full_shard:
+            self.sharder.load_from_master(self.master)
+            self.ctx.wait_for_everyone()
+            self.sharder.after_update(None)
 
     def optimizer_state_dict(self) -> dict[str, Any]:
         return {name: {"step": o.step, "shard": list(o.shard), "range": [o.start, o.end], "names": list(o.names),

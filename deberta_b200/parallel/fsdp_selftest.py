@@ -1,0 +1,99 @@
+"""Multi-GPU check of the full-shard mode: ``torchrun --nproc-per-node N -m deberta_b200.parallel.fsdp_selftest``.
+
+Builds the same small DeBERTa-v3 RTD model twice, once with the sharded-optimizer engine (parameters replicated)
+and once with the full-shard engine (parameters gathered layer by layer from the peers' slabs), feeds both the same
+batches for ``--steps`` optimizer steps and compares losses and the final fp32 masters. Prints one JSON line on rank 0
+(``ok``, the largest differences, gather counts, bytes fetched from peers, step times); exit status 1 on a mismatch.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+
+import torch
+
+
+def _run(mode: str, args, ctx):
+    from deberta_b200.config import Config, DataConfig, ModelConfig, OptimConfig, TrainConfig, validate_config
+    from deberta_b200.training.runtime import build_engine, build_model, build_tokenizer
+    from deberta_b200.training.trainer import Trainer
+
+    cfg = Config(model=ModelConfig(hf={"model_size": args.model_size}, tokenizer={"name_or_path": "synthetic:8192"}),
+                 data=DataConfig(dataset_name="synthetic", max_seq_length=args.seq_len),
+                 train=TrainConfig(per_device_train_batch_size=args.micro_batch, gradient_accumulation_steps=2, max_steps=100,
+                                   dataloader_num_workers=0, distributed={"parallelism": mode}),
+                 optim=OptimConfig(warmup_steps=2))
+    import warnings
+
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        validate_config(cfg)
+    torch.manual_seed(1234)
+    tok = build_tokenizer(cfg.model)
+    model, _, _ = build_model(model_cfg=cfg.model, tokenizer=tok, max_seq_length=args.seq_len)
+    engine = build_engine(model=model, ctx=ctx, train_cfg=cfg.train, optim_cfg=cfg.optim)
+    trainer = Trainer(model=model, engine=engine, ctx=ctx, train_cfg=cfg.train, optim_cfg=cfg.optim,
+                      pad_token_id=tok.pad_token_id, synchronous=True)
+    g = torch.Generator().manual_seed(77 + ctx.rank)
+    losses, times = [], []
+    for step in range(args.steps):
+        window = []
+        for _ in range(2):
+            ids = torch.randint(5, 8192, (args.micro_batch, args.seq_len), generator=g)
+            labels = torch.full_like(ids, -100)
+            pick = torch.rand(ids.shape, generator=g) < 0.15
+            labels[pick] = ids[pick]
+            ids = ids.masked_fill(pick, tok.mask_token_id)
+            window.append({"input_ids": ids, "labels": labels})
+        torch.manual_seed(999 + step)  # same sampling noise in both modes
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        st = trainer.train_window(window)
+        torch.cuda.synchronize()
+        times.append(time.perf_counter() - t0)
+        losses.append((float(st.gen_loss_tokens) / max(st.gen_tokens, 1.0), float(st.disc_loss_tokens) / max(st.disc_tokens, 1.0)))
+    engine.gather_master()
+    from deberta_b200.ops import _lib
+
+    _lib.check_status()
+    return losses, engine.master.clone(), engine, sorted(times)[len(times) // 2]
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=6)
+    ap.add_argument("--model-size", default="xsmall")
+    ap.add_argument("--seq-len", type=int, default=256)
+    ap.add_argument("--micro-batch", type=int, default=4)
+    args = ap.parse_args()
+    from deberta_b200.parallel.dist import init_distributed
+
+    ctx = init_distributed()
+    ref_losses, ref_master, ref_eng, ref_t = _run("zero", args, ctx)
+    peak_zero = torch.cuda.max_memory_allocated()
+    del ref_eng
+    torch.cuda.empty_cache()
+    torch.cuda.reset_peak_memory_stats()
+    losses, master, eng, t = _run("fsdp", args, ctx)
+    peak_fsdp = torch.cuda.max_memory_allocated()
+    dl = max(abs(a - b) / max(abs(a), 1e-6) for ra, rb in zip(ref_losses, losses) for a, b in zip(ra, rb))
+    dm = float((master - ref_master).abs().max())
+    ok = dl < 2e-3 and dm < 2e-3
+    flag = torch.tensor([1 if ok else 0], device=ctx.device)
+    torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
+    if ctx.is_main_process:
+        sh = eng.sharder
+        print(json.dumps({"ok": bool(int(flag)), "world": ctx.world_size, "max_rel_loss_diff": dl, "max_master_diff": dm,
+                          "gathers": sh.gathers, "bytes_from_peers": sh.bytes_gathered, "units": len(sh.units),
+                          "fused_collectives": eng.comm is not None, "memory": sh.memory_report(),
+                          "step_ms": {"zero": ref_t * 1e3, "fsdp": t * 1e3},
+                          "peak_bytes": {"zero": peak_zero, "fsdp": peak_fsdp}, "losses": losses[-1]}))
+    ctx.shutdown()
+    return 0 if bool(int(flag)) else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())

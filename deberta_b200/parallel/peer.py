@@ -66,13 +66,15 @@ class PeerComm:
     """Symmetric gradient / parameter buffers of one rank plus the launches that use them."""
 
     def __init__(self, n_elems: int, *, rank: int, world_size: int, device: torch.device, want_params: bool = True,
-                 use_multicast: bool | None = None, timeout_s: float = 20.0) -> None:
+                 use_multicast: bool | None = None, timeout_s: float = 20.0, param_elems: int | None = None) -> None:
         import torch.distributed._symmetric_memory as symm
 
         self.rank, self.world, self.device = rank, world_size, device
         group = dist.group.WORLD
         self.grads = symm.empty(n_elems, dtype=torch.float32, device=device)
-        self.params = symm.empty(n_elems, dtype=torch.bfloat16, device=device) if want_params else None
+        # full-shard mode keeps only this rank's slabs here (``param_elems``); peers read them through the mapping
+        self.params = symm.empty(n_elems if param_elems is None else param_elems, dtype=torch.bfloat16,
+                                 device=device) if want_params else None
         self.pad = symm.empty(PAD_WORDS, dtype=torch.int32, device=device)
         self.grads.zero_()
         self.pad.zero_()
@@ -99,6 +101,7 @@ class PeerComm:
         ctx.mc_params = mc_w or None
         ctx.timeout_ns = int(timeout_s * 1e9)
         self.ctx = ctx
+        self.param_ptrs = [int(hw.buffer_ptrs[r]) for r in range(world_size)] if hw is not None else None
         self.epoch = 0
         dist.barrier()  # every pad is zeroed and mapped before the first flag is written
 
@@ -156,12 +159,12 @@ class PeerComm:
     def adamw(self, offset: int, count: int, *, master: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor,
               segments: Sequence[tuple[int, int, float, float]], betas: tuple[float, float], eps: float, inv_bc1: float,
               inv_sqrt_bc2: float, max_norm: float, epoch: int, norm_sq_out: torch.Tensor | None,
-              gate: torch.Tensor | None = None) -> None:
+              gate: torch.Tensor | None = None, local_params: torch.Tensor | None = None) -> None:
         """AdamW on the slab reduced under ``epoch``; ``segments`` = (begin, end, lr, weight_decay) inside the slab.
 
         ``gate``: optional device float, identical on all ranks; the update is skipped when it is not positive.
         """
-        if self.params is None:
+        if self.params is None and local_params is None:
             raise RuntimeError("PeerComm was built without a parameter buffer")
         arr = (AdamSegment * max(1, len(segments)))()
         for i, (b, en, lr, wd) in enumerate(segments):
@@ -170,7 +173,7 @@ class PeerComm:
         _lib.call("db200_comm_adamw", ctypes.byref(self.ctx), ctypes.c_longlong(offset), ctypes.c_longlong(count),
                   _lib.ptr(master), _lib.ptr(exp_avg), _lib.ptr(exp_avg_sq), arr, ctypes.c_int(len(segments)),
                   cf(betas[0]), cf(betas[1]), cf(eps), cf(inv_bc1), cf(inv_sqrt_bc2), cf(max_norm),
-                  ctypes.c_uint(epoch & 0xFFFFFFFF), _lib.ptr(norm_sq_out), _lib.ptr(gate), _lib.stream_ptr())
+                  ctypes.c_uint(epoch & 0xFFFFFFFF), _lib.ptr(norm_sq_out), _lib.ptr(gate), _lib.ptr(local_params), _lib.stream_ptr())
 
     def vector_sum(self, values: torch.Tensor) -> torch.Tensor:
         """Sum a float vector of at most ``VEC_MAX`` entries over all ranks (result on the device)."""

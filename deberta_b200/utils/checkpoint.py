@@ -108,7 +108,7 @@ def save_training_state(directory: str | Path, *, engine: Any, trainer: Any, ctx
     # change the LR multiplier or clear the moments, so every rank does it before any rank reads optimizer state.
     trainer.resolve_pending()
     model_state = engine.model_state_dict()  # collective
-    sharded = engine.parallelism == "zero" and ctx.world_size > 1
+    sharded = engine.sharded and ctx.world_size > 1
     if ctx.is_main_process:
         save_model_state_dict(model_state, d)
         tstate = trainer.state_dict()
@@ -130,7 +130,7 @@ def save_training_state(directory: str | Path, *, engine: Any, trainer: Any, ctx
 def load_training_state(directory: str | Path, *, engine: Any, trainer: Any, ctx: Any, strict: bool = True) -> None:
     d = Path(directory)
     engine.load_model_state_dict(load_model_state_dict(d), strict=strict)
-    sharded = engine.parallelism == "zero" and ctx.world_size > 1
+    sharded = engine.sharded and ctx.world_size > 1
     if sharded:
         path = d / f"optimizer_shard{ctx.rank}.bin"
         if not path.exists():

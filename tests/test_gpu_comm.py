@@ -75,7 +75,7 @@ def test_emulated_ranks_reduce_adamw_match_reference():
         c = _ctx(r, grads, params, pads)
         _lib.call("db200_comm_adamw", ctypes.byref(c), ctypes.c_longlong(r * per), ctypes.c_longlong(per),
                   _lib.ptr(masters[r]), _lib.ptr(ms[r]), _lib.ptr(vs[r]), seg, ctypes.c_int(1), cf(b1), cf(b2), cf(eps),
-                  cf(1.0 / (1 - b1)), cf(1.0 / math.sqrt(1 - b2)), cf(max_norm), ctypes.c_uint(7), _lib.ptr(norm_out), None, stream)
+                  cf(1.0 / (1 - b1)), cf(1.0 / math.sqrt(1 - b2)), cf(max_norm), ctypes.c_uint(7), _lib.ptr(norm_out), None, None, stream)
     torch.cuda.synchronize()
     _lib.check_status()
     assert abs(float(norm_out) - want_norm_sq) < 1e-4 * want_norm_sq
@@ -158,3 +158,17 @@ def test_two_gpu_selftest_matches_nccl(multicast):
            "--elems", str(1 << 20)] + ([] if multicast else ["--no-multicast"])
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_full_shard_matches_sharded_optimizer():
+    """Parameters gathered layer by layer from the peer's slabs: same losses and masters as with replicated parameters."""
+    import json
+
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29535", "-m", "deberta_b200.parallel.fsdp_selftest", "--steps", "5"]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    row = json.loads([ln for ln in res.stdout.splitlines() if ln.startswith("{")][-1])
+    assert row["ok"] and row["fused_collectives"] and row["bytes_from_peers"] > 0

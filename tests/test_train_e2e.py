@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import json
 import os
+import re
 import subprocess
 import sys
 from pathlib import Path
@@ -68,23 +69,33 @@ def test_train_resume_export(tmp_path):
     assert r.returncode != 0 and "Resume config mismatch" in r.stderr
 
 
-@pytest.mark.parametrize("parallelism", ["ddp", "zero"])
+@pytest.mark.parametrize("parallelism", ["ddp", "zero", "fsdp"])
 def test_two_rank_gloo_matches_layout(tmp_path, parallelism):
     out = tmp_path / f"run_{parallelism}"
     r = _train(["--train.checkpoint.output_dir", str(out), "--train.max_steps", "3", "--train.checkpoint.save_steps", "0",
                 "--train.checkpoint.export_hf_final", "false", "--train.gradient_accumulation_steps", "2",
                 "--logging.logging_steps", "1", "--train.distributed.parallelism", parallelism], nproc=2,
-               port=29611 + (parallelism == "zero"))
+               port=29611 + ["ddp", "zero", "fsdp"].index(parallelism))
     assert r.returncode == 0, r.stderr[-3000:]
     ck = out / "checkpoint-3"
     assert (ck / ".complete").exists() and (ck / "model.safetensors").exists()
     names = {p.name for p in ck.iterdir()}
-    if parallelism == "zero":
+    if parallelism in ("zero", "fsdp"):
         assert {"optimizer_shard0.bin", "optimizer_shard1.bin"} <= names
     else:
         assert {"optimizer.bin", "optimizer_1.bin"} <= names
     assert {"random_states_0.pkl", "random_states_1.pkl"} <= names
     assert "step 3" in r.stderr
+    losses = [float(m) for m in re.findall(r"step \d+ \| loss ([0-9.]+)", r.stderr)]
+    assert len(losses) == 3
+    _TWO_RANK_LOSSES[parallelism] = losses
+    if len(_TWO_RANK_LOSSES) > 1:  # replicated, sharded-optimizer and full-shard runs are the same computation
+        ref = next(iter(_TWO_RANK_LOSSES.values()))
+        for other in _TWO_RANK_LOSSES.values():
+            assert all(abs(a - b) < 2e-4 * max(1.0, abs(a)) for a, b in zip(ref, other)), _TWO_RANK_LOSSES
+
+
+_TWO_RANK_LOSSES: dict[str, list[float]] = {}
 
 
 def test_dry_run_reports_batch_shape(tmp_path, capsys):

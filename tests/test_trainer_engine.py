@@ -374,3 +374,39 @@ def test_trainer_state_round_trip_and_lr_reporting():
     assert other.schedules["generator"].last_step == 1
     digest = trainer.optimizer_param_digest()
     assert set(digest) == {"generator", "discriminator"} and digest == other.optimizer_param_digest()
+
+
+def test_full_shard_mode_gathers_layers_on_demand_and_matches_replicated():
+    """One process: the same windows through ``ddp`` and ``fsdp`` engines end in bit-identical masters; the sharder
+    gathered layer units into its two slots and kept the roots resident."""
+    def run(parallelism):
+        model_cfg, train_cfg, optim_cfg = _configs()
+        torch.manual_seed(0)
+        model, _, _ = build_model(model_cfg=model_cfg, tokenizer=SyntheticTokenizer(VOCAB), max_seq_length=32)
+        ctx = DistContext()
+        engine = build_engine(model=model, ctx=ctx, train_cfg=train_cfg, optim_cfg=optim_cfg, parallelism=parallelism)
+        trainer = Trainer(model=model, engine=engine, ctx=ctx, train_cfg=train_cfg, optim_cfg=optim_cfg, pad_token_id=0)
+        losses = []
+        for i in range(3):
+            torch.manual_seed(100 + i)
+            losses.append(float(trainer.train_window(_batches(2, seed=3 + i)).gen_loss_tokens))
+        return losses, engine, model
+
+    ref_losses, ref_eng, _ = run("ddp")
+    losses, eng, model = run("fsdp")
+    assert losses == ref_losses and torch.equal(eng.master, ref_eng.master)
+    sh = eng.sharder
+    names = [u.name for u in sh.units]
+    assert names == ["gen.layer0", "disc.layer0", "disc.layer1", "disc.layer2", "gen.root", "disc.root"]
+    covered = sorted(r for u in sh.units for r in u.ranges)
+    assert covered[0][0] == 0 and all(a[1] == b[0] for a, b in zip(covered, covered[1:])) and covered[-1][1] == eng.total_elems
+    assert eng.compute is None and len(sh.slots) == 2 and sh.slot_elems == max(u.size for u in sh.units if not u.is_root)
+    assert sh.gathers > 3 * 2 * 4  # every layer unit, forward and backward, every window (plus roots after each update)
+    # a layer's parameters live in a slot, a root's in its own buffer; the GDES base aliases the generator's table
+    lay = model.discriminator.encoder.layers[1]
+    p0 = next(lay.parameters())
+    assert sh.slots[1].data_ptr() <= p0.data_ptr() < sh.slots[1].data_ptr() + sh.slots[1].numel() * 4
+    emb = model.discriminator.embeddings.word_embeddings
+    assert emb.base_weight.data_ptr() == model.generator.embeddings.word_embeddings.weight.data_ptr()
+    rep = sh.memory_report()
+    assert rep["shard_bytes"] == eng.total_elems * 4 and rep["slot_bytes"] == 2 * sh.slot_elems * 4
