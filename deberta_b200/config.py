@@ -44,7 +44,7 @@ _CHOICES: dict[str, set[str]] = {
     "train.compile.backend": {"inductor", "aot_eager"},
     "train.checkpoint.resume_data_strategy": {"auto", "replay", "restart_epoch"},
     "train.distributed.parallelism": {"ddp", "zero", "fsdp"},
-    "train.distributed.multicast": {"auto", "on", "off"},
+    "train.distributed.nvls": {"auto", "on", "off"},
     "optim.scheduler.type": {"linear", "cosine", "cosine_with_restarts", "polynomial", "constant", "constant_with_warmup"},
     "logging.backend": {"none", "tensorboard"},
     "logging.wandb.watch": {"none", "gradients", "parameters", "all"},
@@ -62,7 +62,7 @@ _ALIASES: dict[str, dict[str, str]] = {
     "train.compile.backend": {"aot-eager": "aot_eager"},
     "train.distributed.parallelism": {"replicated": "ddp", "zero1": "zero", "sharded_optimizer": "zero",
                                       "full_shard": "fsdp", "fsdp2": "fsdp", "zero3": "fsdp"},
-    "train.distributed.multicast": {"true": "on", "1": "on", "yes": "on", "false": "off", "0": "off", "no": "off"},
+    "train.distributed.nvls": {"true": "on", "1": "on", "yes": "on", "false": "off", "0": "off", "no": "off"},
     "logging.wandb.watch": {"off": "none", "disabled": "none", "false": "none", "0": "none", "grad": "gradients",
                             "gradient": "gradients", "weights": "parameters", "params": "parameters",
                             "param": "parameters"},
@@ -424,7 +424,7 @@ class TrainDistributedConfig(Section):
 
     parallelism: str = "zero"       # ddp: replicated optimizer | zero: sharded optimizer state | fsdp: parameters sharded too
     fused_collectives: bool = True  # peer-memory kernels instead of NCCL for gradients / parameters (one node, 2..8 GPUs)
-    multicast: str = "auto"         # NVSwitch multimem path of those kernels: auto = from 4 ranks on
+    nvls: str = "auto"              # in-switch reduction (multimem) path of those kernels: auto = from 4 ranks on
     overlap_backward: bool = True   # reduce gradient buckets on a side stream while backward still runs
     comm_timeout_s: float = 20.0    # longest device-side wait for a peer before the step fails
     step_deadline_s: float = 0.0    # host watchdog: report when no optimizer step completes in this time (0 = off)
@@ -757,7 +757,7 @@ def validate_train_config(cfg: TrainConfig) -> None:
     _set(ck, "resume_data_strategy", normalize_choice("train.checkpoint.resume_data_strategy", ck.resume_data_strategy))
     di = cfg.distributed
     _set(di, "parallelism", normalize_choice("train.distributed.parallelism", di.parallelism))
-    _set(di, "multicast", normalize_choice("train.distributed.multicast", di.multicast))
+    _set(di, "nvls", normalize_choice("train.distributed.nvls", di.nvls))
     for name in ("comm_timeout_s", "step_deadline_s", "heartbeat_s"):
         if float(getattr(di, name)) < 0.0:
             raise ValueError(f"train.distributed.{name} must be >= 0.")

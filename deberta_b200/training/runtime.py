@@ -114,5 +114,5 @@ def build_engine(*, model: torch.nn.Module, ctx: DistContext, train_cfg: TrainCo
                        decoupled=bool(train_cfg.decoupled_training), lr_generator=lr_g, lr_discriminator=lr_d,
                        weight_decay=float(optim_cfg.weight_decay),
                        betas=(float(optim_cfg.adam.beta1), float(optim_cfg.adam.beta2)), eps=eps,
-                       fused_collectives=bool(di.fused_collectives), multicast=str(di.multicast),
+                       fused_collectives=bool(di.fused_collectives), multicast=str(di.nvls),
                        comm_timeout_s=float(di.comm_timeout_s))

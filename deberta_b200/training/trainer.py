@@ -25,6 +25,13 @@ Window-level rules of the reference that therefore run on the device:
   several GPUs the update kernel is gated by the summed token count and the step counter and schedule
   are corrected when the outcome arrives.
 
+Overlap (``train.distributed.overlap_backward``, GPUs only): the discriminator's gradient collective and its
+optimizer kernel are queued on a side stream. Nothing of the next window's generator phase reads a discriminator
+parameter or gradient, so that whole phase — forward, backward, the generator's own collective and update — runs
+while the discriminator's reduce-scatter, AdamW and parameter all-gather are in flight; the main stream waits for
+them where the next discriminator phase (or a checkpoint) begins. The two optimizers' fused collectives share one
+set of flags, so the generator's collective is queued behind the discriminator's.
+
 The outcome also carries the kernels' status word: a bounded wait that ran out anywhere since the
 previous window raises ``KernelError`` here instead of letting the run continue on partial data.
 """
@@ -130,6 +137,11 @@ class Trainer:
         self.skipped_steps = 0
         self.consumed_micro_batches = 0
         self._pending: _PendingOutcome | None = None
+        di = getattr(train_cfg, "distributed", None)
+        self.overlap = bool(getattr(di, "overlap_backward", True)) and engine.device.type == "cuda" and self.decoupled \
+            and not self.synchronous
+        self._side = torch.cuda.Stream(device=engine.device) if self.overlap else None
+        self._disc_done = None  # event: the discriminator's collective + update queued on the side stream have finished
         self.last_outcome: dict[str, float] = {}
         self.on_nonfinite = None  # optional callback(step, norms) for debug artifacts
         self.model.train()
@@ -173,6 +185,7 @@ class Trainer:
         update is skipped too (the whole window is void). ``gate``: see ``TrainEngine.step``.
         """
         eng = self.engine
+        self.wait_for_side_stream()  # the fused collectives of the two optimizers share one set of flags
         penalty = None
         if loss_guard is not None:  # +inf when the window's loss was not finite: every rank then skips the update
             penalty = torch.where(torch.isfinite(loss_guard), 0.0, float("inf")).to(torch.float32).reshape(1)
@@ -183,6 +196,12 @@ class Trainer:
         eng.step(name, lr_scale=self.schedules[name].scale() * self.lr_mult, max_grad_norm=self.max_grad_norm, gate=gate)
         self.schedules[name].step()
         return norm_sq.clone()
+
+    def wait_for_side_stream(self) -> None:
+        """Order the current stream behind the discriminator update that may still run on the side stream."""
+        if self._disc_done is not None:
+            torch.cuda.current_stream(self.engine.device).wait_event(self._disc_done)
+            self._disc_done = None
 
     def resolve_pending(self) -> None:
         """Apply the host-side consequences of the previous step (LR back-off / recovery, gated updates, kernel errors).
@@ -236,7 +255,12 @@ class Trainer:
         zero = lambda: torch.zeros((), dtype=torch.float32, device=dev)  # noqa: E731
         stats = WindowStats(zero(), zero(), zero(), zero(), gen_total, disc_total, input_tokens,
                             zero_gen_window=gen_total <= 0, zero_disc_window=disc_total <= 0)
-        eng.zero_grad()
+        if self.overlap:
+            # the discriminator's range was cleared on the side stream right after its update (which may still be
+            # reading it); the generator's is cleared after its update below, and both start out as zeros
+            pass
+        else:
+            eng.zero_grad()
         norms: dict[str, torch.Tensor] = {}
         if self.decoupled:
             cached = []
@@ -271,6 +295,7 @@ class Trainer:
                 run_disc = bool(has_targets)
             if not run_disc:
                 cached = []
+            self.wait_for_side_stream()  # last window's discriminator update must have landed before its next forward
             for b, mask, corrupted, labels, g_i, d_i in cached:
                 with nvtx_range("discriminator fwd"):
                     out = model(input_ids=b["input_ids"], corrupted_input_ids=corrupted, disc_labels=labels,
@@ -283,7 +308,21 @@ class Trainer:
                 stats.disc_loss_tokens += out.disc_loss_raw.detach().float() * d_i
                 stats.disc_acc_tokens += out.disc_accuracy.float() * d_i
                 stats.disc_pos += out.disc_positive_count.float()
-            if run_disc:
+            if run_disc and self.overlap:
+                main = torch.cuda.current_stream(dev)
+                self._side.wait_stream(main)  # gradients are final, the generator's update has been queued
+                for t in (guard, norms["generator"], device_gate):
+                    if isinstance(t, torch.Tensor):
+                        t.record_stream(self._side)
+                with torch.cuda.stream(self._side), nvtx_range("discriminator optimizer (side stream)"):
+                    norms["discriminator"] = self._finish_optimizer("discriminator", guard, upstream=norms["generator"],
+                                                                    gate=device_gate)
+                    eng.zero_grad("discriminator")
+                    self._pending = _PendingOutcome(self.global_step + 1, norms, False, gate=device_gate)
+                    self._disc_done = torch.cuda.Event()
+                    self._disc_done.record(self._side)
+                norms["discriminator"].record_stream(main)
+            elif run_disc:
                 with nvtx_range("discriminator optimizer"):
                     norms["discriminator"] = self._finish_optimizer("discriminator", guard, upstream=norms["generator"],
                                                                     gate=device_gate)
@@ -308,11 +347,18 @@ class Trainer:
             norms["all"] = self._finish_optimizer("all", guard)
             model.sync_discriminator_embeddings_from_generator()
             eng.zero_grad()
-        stats.grad_norms = {k: v.sqrt() for k, v in norms.items()}
+        if self._disc_done is not None:  # values the caller may read on the main stream
+            with torch.cuda.stream(self._side):
+                stats.grad_norms = {k: v.sqrt() for k, v in norms.items()}
+            for v in stats.grad_norms.values():
+                v.record_stream(torch.cuda.current_stream(dev))
+        else:
+            stats.grad_norms = {k: v.sqrt() for k, v in norms.items()}
         self.global_step += 1
         self.consumed_micro_batches += len(batches)
-        self._pending = _PendingOutcome(self.global_step, norms, self.synchronous,
-                                        gate=device_gate if self.decoupled else None)
+        if self._pending is None:
+            self._pending = _PendingOutcome(self.global_step, norms, self.synchronous,
+                                            gate=device_gate if self.decoupled else None)
         if self.synchronous:
             self.resolve_pending()
         return stats
@@ -320,6 +366,7 @@ class Trainer:
     # ---- state ----------------------------------------------------------------------------------------
     def state_dict(self) -> dict[str, Any]:
         """Host-side training state. Call ``resolve_pending()`` on every rank first (``save_training_state`` does)."""
+        self.wait_for_side_stream()
         self.resolve_pending()
         return {"global_step": self.global_step, "lr_mult": self.lr_mult, "skip_streak": self.skip_streak,
                 "consumed_micro_batches": self.consumed_micro_batches,

@@ -106,6 +106,8 @@ def save_training_state(directory: str | Path, *, engine: Any, trainer: Any, ctx
     d = Path(directory)
     # The outcome of the last window may still be on its way to the host; applying it can roll back an optimizer step,
     # change the LR multiplier or clear the moments, so every rank does it before any rank reads optimizer state.
+    if hasattr(trainer, "wait_for_side_stream"):
+        trainer.wait_for_side_stream()  # an optimizer update queued on the trainer's side stream
     trainer.resolve_pending()
     model_state = engine.model_state_dict()  # collective
     sharded = engine.sharded and ctx.world_size > 1

@@ -129,7 +129,8 @@ def test_one_deberta_v3_base_layer_kernels_match_fp32_modules():
         assert p.grad is not None and _rel(p.grad, grads[name].grad) < 8e-2, name
 
 
-def _tiny_step(precision: str, compile_backend: str | None = None):
+def _tiny_step(precision: str, compile_backend: str | None = None, synchronous: bool = True, overlap: bool = True,
+               windows: int = 2, return_engine: bool = False):
     from deberta_b200.config import Config, DataConfig, ModelConfig, OptimConfig, TrainConfig, validate_config
     from deberta_b200.parallel.dist import DistContext
     from deberta_b200.training.compile import maybe_compile_model
@@ -142,7 +143,8 @@ def _tiny_step(precision: str, compile_backend: str | None = None):
     cfg = Config(model=ModelConfig(hf={"model_size": "xsmall"}, tokenizer={"name_or_path": "synthetic:4096"}),
                  data=DataConfig(dataset_name="synthetic", max_seq_length=256),
                  train=TrainConfig(mixed_precision=precision, per_device_train_batch_size=4, gradient_accumulation_steps=1,
-                                   max_steps=10, dataloader_num_workers=0, **train_kw),
+                                   max_steps=10, dataloader_num_workers=0, distributed={"overlap_backward": overlap},
+                                   **train_kw),
                  optim=OptimConfig(warmup_steps=1))
     import warnings
 
@@ -155,7 +157,7 @@ def _tiny_step(precision: str, compile_backend: str | None = None):
     ctx = DistContext(device=torch.device("cuda", 0))
     engine = build_engine(model=model, ctx=ctx, train_cfg=cfg.train, optim_cfg=cfg.optim)
     trainer = Trainer(model=model, engine=engine, ctx=ctx, train_cfg=cfg.train, optim_cfg=cfg.optim, pad_token_id=0,
-                      synchronous=True)
+                      synchronous=synchronous)
     maybe_compile_model(model, train_cfg=cfg.train, model_cfg=cfg.model, data_cfg=cfg.data)
     g = torch.Generator().manual_seed(5)
     ids = torch.randint(5, 4096, (4, 256), generator=g)
@@ -164,12 +166,31 @@ def _tiny_step(precision: str, compile_backend: str | None = None):
     labels[pick] = ids[pick]
     ids[pick] = tok.mask_token_id
     out = []
-    for _ in range(2):
+    for w in range(windows):
+        torch.manual_seed(50 + w)
         st = trainer.train_window([{"input_ids": ids, "labels": labels}])
+        if not synchronous:
+            continue
         out.append((float(st.gen_loss_tokens) / st.gen_tokens, float(st.disc_loss_tokens) / st.disc_tokens,
                     float(st.grad_norms["generator"]), float(st.grad_norms["discriminator"])))
+    trainer.wait_for_side_stream()
+    trainer.resolve_pending()
     _lib.check_status()
+    if return_engine:
+        return trainer, engine
     return out
+
+
+def test_discriminator_update_on_the_side_stream_matches_the_serial_schedule():
+    """Four windows with the discriminator's collective + AdamW queued on a side stream (outcomes read one window
+    late) end in the same masters and step counters as the fully serial schedule."""
+    t_ser, e_ser = _tiny_step("bf16", synchronous=False, overlap=False, windows=4, return_engine=True)
+    t_ovl, e_ovl = _tiny_step("bf16", synchronous=False, overlap=True, windows=4, return_engine=True)
+    assert t_ovl.overlap and not t_ser.overlap
+    torch.cuda.synchronize()
+    assert torch.equal(e_ser.master, e_ovl.master)
+    assert [o.step for o in e_ser.optimizers.values()] == [o.step for o in e_ovl.optimizers.values()] == [4, 4]
+    assert float(e_ovl.grads.abs().max()) == 0.0  # both ranges were cleared after their updates
 
 
 def test_whole_rtd_step_bf16_kernels_match_fp32_modules():
