@@ -468,6 +468,7 @@ class TrainEngine:
             self.sharder.after_update(None)
 
     def optimizer_state_dict(self) -> dict[str, Any]:
+        """This rank's optimizer state in the engine's own flat form (one entry per optimizer)."""
         return {name: {"step": o.step, "shard": list(o.shard), "range": [o.start, o.end], "names": list(o.names),
                        "exp_avg": o.exp_avg.detach().cpu().clone(), "exp_avg_sq": o.exp_avg_sq.detach().cpu().clone()}
                 for name, o in self.optimizers.items()}
@@ -480,6 +481,78 @@ class TrainEngine:
             o.step = int(s["step"])
             o.exp_avg.copy_(s["exp_avg"].to(self.device))
             o.exp_avg_sq.copy_(s["exp_avg_sq"].to(self.device))
+
+    # ---- optimizer state in the layout of ``torch.optim.AdamW.state_dict()`` --------------------------------
+    def _full_moments(self, o: OptimizerState) -> tuple[torch.Tensor, torch.Tensor]:
+        """Both moment buffers over the whole optimizer range on every rank (collective under sharding)."""
+        if not (self.sharded and self.ctx.world_size > 1):
+            return o.exp_avg, o.exp_avg_sq
+        out = []
+        for part in (o.exp_avg, o.exp_avg_sq):
+            full = torch.empty(o.end - o.start, dtype=torch.float32, device=self.device)
+            dist.all_gather_into_tensor(full, part.contiguous())
+            out.append(full)
+        return out[0], out[1]
+
+    def torch_optimizer_state_dicts(self) -> dict[str, dict[str, Any]]:
+        """Per optimizer, what ``torch.optim.AdamW(param_groups).state_dict()`` of the reference holds
+        (``training/runtime.py:250-296`` there): two parameter groups (decayed, then not decayed), parameters numbered in
+        group order, per-parameter ``step`` / ``exp_avg`` / ``exp_avg_sq`` in the parameter's shape. Collective when the
+        moments are sharded; every rank returns the full state."""
+        out: dict[str, dict[str, Any]] = {}
+        for name, o in self.optimizers.items():
+            m_full, v_full = self._full_moments(o)
+            m_cpu, v_cpu = m_full.detach().cpu(), v_full.detach().cpu()
+            groups, state, idx = [], {}, 0
+            for seg in o.segments:
+                ids = []
+                for pname in o.names:
+                    off, n, shape = self.layout[pname]
+                    if not (seg.start <= off < seg.end):
+                        continue
+                    if o.step > 0:
+                        state[idx] = {"step": torch.tensor(float(o.step)),
+                                      "exp_avg": m_cpu[off - o.start : off - o.start + n].view(shape).clone(),
+                                      "exp_avg_sq": v_cpu[off - o.start : off - o.start + n].view(shape).clone()}
+                    ids.append(idx)
+                    idx += 1
+                groups.append({"lr": seg.base_lr, "betas": tuple(o.betas), "eps": o.eps, "weight_decay": seg.weight_decay,
+                               "amsgrad": False, "maximize": False, "foreach": None, "capturable": False,
+                               "differentiable": False, "fused": None, "decoupled_weight_decay": True, "params": ids})
+            out[name] = {"state": state, "param_groups": groups, "param_names": list(o.names)}
+        return out
+
+    def load_torch_optimizer_state_dicts(self, states: dict[str, dict[str, Any]]) -> None:
+        """Inverse of ``torch_optimizer_state_dicts``; each rank keeps the slice of the moments it owns, so a checkpoint
+        can be resumed with any number of ranks and in any parallelism mode."""
+        for name, o in self.optimizers.items():
+            sd = states[name]
+            names = sd.get("param_names")
+            if names is not None and list(names) != list(o.names):
+                raise RuntimeError(f"optimizer state for {name!r} lists other parameters than the current model")
+            order = [pn for seg in o.segments for pn in o.names if seg.start <= self.layout[pn][0] < seg.end]
+            n_saved = sum(len(g["params"]) for g in sd["param_groups"])
+            if n_saved != len(order):
+                raise RuntimeError(f"optimizer state for {name!r} holds {n_saved} parameters, the model has {len(order)}")
+            s0, s1 = o.shard
+            o.exp_avg.zero_()
+            o.exp_avg_sq.zero_()
+            step = 0
+            for idx, pname in enumerate(order):
+                st = sd["state"].get(idx, sd["state"].get(str(idx)))
+                if st is None:
+                    continue
+                step = max(step, int(float(st["step"])))
+                off, n, shape = self.layout[pname]
+                lo, hi = max(off, s0), min(off + n, s1)
+                if lo >= hi:
+                    continue
+                for key, dst in (("exp_avg", o.exp_avg), ("exp_avg_sq", o.exp_avg_sq)):
+                    src = st[key].reshape(-1).float()
+                    if src.numel() != n:
+                        raise RuntimeError(f"optimizer state of {pname!r} has {src.numel()} elements, expected {n}")
+                    dst[lo - s0 : hi - s0].copy_(src[lo - off : hi - off].to(self.device))
+            o.step = step
 
 
 def _fold_grad_into_main(p: torch.Tensor) -> None:

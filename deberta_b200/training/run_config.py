@@ -31,7 +31,7 @@ _INERT_FIELDS = {
               "checkpoint.save_total_limit", "checkpoint.resume_from_checkpoint", "checkpoint.resume_data_strategy",
               "checkpoint.resume_replay_max_micro_batches", "checkpoint.export_hf_final", "dataloader.num_workers",
               "dataloader.pin_memory", "compile.enabled", "compile.mode", "compile.scope", "compile.backend", "tf32",
-              "sdpa_kernel", "distributed.fused_collectives", "distributed.nvls", "distributed.overlap_backward",
+              "sdpa_kernel", "distributed.parallelism", "distributed.fused_collectives", "distributed.nvls", "distributed.overlap_backward",
               "distributed.comm_timeout_s", "distributed.step_deadline_s", "distributed.heartbeat_s"},
     "model": {"gradient_checkpointing", "hf.attention_kernel", "rope.attention_implementation"},
     "data": {"source.shuffle_buffer_size"},

@@ -3,9 +3,12 @@
 A training checkpoint directory holds (names follow what Accelerate writes for the reference,
 ``utils/checkpoint.py`` / ``training/run_management.py`` there, so its tools can read our runs):
 
-* ``model.safetensors``   — full fp32 model state (rank 0)
-* ``optimizer.bin`` / ``optimizer_1.bin`` — generator (or single) / discriminator optimizer state; with
-  sharded optimizer state every rank writes ``optimizer_shard<rank>.bin`` instead
+* ``model.safetensors``   — full fp32 model state (rank 0); in full-shard mode instead ``pytorch_model_fsdp_0/``, a
+  torch distributed-checkpoint directory written by all ranks together (state nested under ``"model"``), which is
+  what the reference's FSDP2 runs leave behind (``training/run_management.py:537-625`` there)
+* ``optimizer.bin`` / ``optimizer_1.bin`` — generator (or single) / discriminator optimizer state in the layout of
+  ``torch.optim.AdamW.state_dict()`` (two parameter groups, per-parameter moments), whole, written by rank 0: any
+  number of ranks, in any parallelism mode, can resume from it, and ``torch.optim.AdamW.load_state_dict`` accepts it
 * ``scheduler.bin`` / ``scheduler_1.bin``, ``trainer_state.bin``, ``random_states_<rank>.pkl``
 
 Model weights can also be read from the other layouts the reference accepts: ``model.bin`` /
@@ -101,8 +104,22 @@ def restore_rng_state(state: dict[str, Any]) -> None:
             logger.warning("Could not restore CUDA RNG state: %s", e)
 
 
+DCP_MODEL_DIR = "pytorch_model_fsdp_0"
+
+
+def save_model_state_dict_dcp(state: dict[str, torch.Tensor], checkpoint_dir: str | Path, *, distributed: bool) -> Path:
+    """Write the model as a torch distributed-checkpoint directory (collective when ``distributed``: the planner
+    spreads the tensors over the ranks' files)."""
+    import torch.distributed.checkpoint as dcp
+
+    path = Path(checkpoint_dir) / DCP_MODEL_DIR
+    payload = {"model": {k: v.detach().cpu().contiguous() for k, v in state.items()}}
+    dcp.save(payload, checkpoint_id=str(path), no_dist=not distributed)
+    return path
+
+
 def save_training_state(directory: str | Path, *, engine: Any, trainer: Any, ctx: Any) -> None:
-    """Every rank's part of a checkpoint (collective: gathers fp32 masters under sharded optimizers)."""
+    """Every rank's part of a checkpoint (collective: gathers fp32 masters and moments under sharding)."""
     d = Path(directory)
     # The outcome of the last window may still be on its way to the host; applying it can roll back an optimizer step,
     # change the LR multiplier or clear the moments, so every rank does it before any rank reads optimizer state.
@@ -110,40 +127,36 @@ def save_training_state(directory: str | Path, *, engine: Any, trainer: Any, ctx
         trainer.wait_for_side_stream()  # an optimizer update queued on the trainer's side stream
     trainer.resolve_pending()
     model_state = engine.model_state_dict()  # collective
-    sharded = engine.sharded and ctx.world_size > 1
-    if ctx.is_main_process:
+    if getattr(engine, "full_shard", False):
+        save_model_state_dict_dcp(model_state, d, distributed=ctx.world_size > 1)
+    elif ctx.is_main_process:
         save_model_state_dict(model_state, d)
+    opt_states = engine.torch_optimizer_state_dicts()  # collective
+    if ctx.is_main_process:
         tstate = trainer.state_dict()
-        names = list(engine.optimizers)
-        for i, name in enumerate(names):
+        for i, name in enumerate(engine.optimizers):
             suffix = "" if i == 0 else f"_{i}"
             torch.save(tstate["schedules"][name], d / f"scheduler{suffix}.bin")
+            torch.save(opt_states[name], d / f"optimizer{suffix}.bin")
         torch.save(tstate, d / "trainer_state.bin")
-    opt_state = engine.optimizer_state_dict()
-    if sharded:
-        torch.save(opt_state, d / f"optimizer_shard{ctx.rank}.bin")
-    elif ctx.is_main_process:
-        for i, (name, st) in enumerate(opt_state.items()):
-            torch.save({name: st}, d / ("optimizer.bin" if i == 0 else f"optimizer_{i}.bin"))
     with open(d / f"random_states_{ctx.rank}.pkl", "wb") as f:
         pickle.dump(capture_rng_state(), f)
 
 
 def load_training_state(directory: str | Path, *, engine: Any, trainer: Any, ctx: Any, strict: bool = True) -> None:
+    """Restore model, optimizer moments, schedules and RNG state. The rank count and parallelism mode may differ from
+    the run that wrote the checkpoint (each rank slices the whole optimizer state); RNG state is per rank and is
+    restored only where a file for this rank exists."""
     d = Path(directory)
     engine.load_model_state_dict(load_model_state_dict(d), strict=strict)
-    sharded = engine.sharded and ctx.world_size > 1
-    if sharded:
-        path = d / f"optimizer_shard{ctx.rank}.bin"
-        if not path.exists():
-            raise FileNotFoundError(f"{path} is missing: sharded optimizer state needs the same number of ranks on resume.")
-        engine.load_optimizer_state_dict(torch.load(path, map_location="cpu", weights_only=False))
-    else:
-        merged: dict[str, Any] = {}
-        for i in range(len(engine.optimizers)):
-            path = d / ("optimizer.bin" if i == 0 else f"optimizer_{i}.bin")
-            merged.update(torch.load(path, map_location="cpu", weights_only=False))
-        engine.load_optimizer_state_dict(merged)
+    states: dict[str, Any] = {}
+    for i, name in enumerate(engine.optimizers):
+        path = d / ("optimizer.bin" if i == 0 else f"optimizer_{i}.bin")
+        sd = torch.load(path, map_location="cpu", weights_only=False)
+        if "param_groups" not in sd:
+            raise RuntimeError(f"{path} is not in torch.optim state-dict layout (written by an older version?).")
+        states[name] = sd
+    engine.load_torch_optimizer_state_dicts(states)
     ts = d / "trainer_state.bin"
     if ts.exists():
         trainer.load_state_dict(torch.load(ts, map_location="cpu", weights_only=False))

@@ -188,7 +188,8 @@ def test_discriminator_update_on_the_side_stream_matches_the_serial_schedule():
     t_ovl, e_ovl = _tiny_step("bf16", synchronous=False, overlap=True, windows=4, return_engine=True)
     assert t_ovl.overlap and not t_ser.overlap
     torch.cuda.synchronize()
-    assert torch.equal(e_ser.master, e_ovl.master)
+    # (not bit-equal: dQ and the embedding gradients are accumulated with floating-point atomics)
+    assert (e_ser.master - e_ovl.master).abs().max() < 2e-3 and _rel(e_ovl.master, e_ser.master) < 2e-3
     assert [o.step for o in e_ser.optimizers.values()] == [o.step for o in e_ovl.optimizers.values()] == [4, 4]
     assert float(e_ovl.grads.abs().max()) == 0.0  # both ranges were cleared after their updates
 

@@ -78,12 +78,16 @@ def test_two_rank_gloo_matches_layout(tmp_path, parallelism):
                port=29611 + ["ddp", "zero", "fsdp"].index(parallelism))
     assert r.returncode == 0, r.stderr[-3000:]
     ck = out / "checkpoint-3"
-    assert (ck / ".complete").exists() and (ck / "model.safetensors").exists()
+    assert (ck / ".complete").exists()
     names = {p.name for p in ck.iterdir()}
-    if parallelism in ("zero", "fsdp"):
-        assert {"optimizer_shard0.bin", "optimizer_shard1.bin"} <= names
-    else:
-        assert {"optimizer.bin", "optimizer_1.bin"} <= names
+    # the model: one safetensors file, or (full shard) a distributed-checkpoint directory all ranks wrote into
+    assert ("pytorch_model_fsdp_0" in names and (ck / "pytorch_model_fsdp_0" / ".metadata").exists()) if parallelism == "fsdp" \
+        else "model.safetensors" in names
+    # optimizer state is whole and in torch.optim layout whatever the sharding was
+    assert {"optimizer.bin", "optimizer_1.bin"} <= names and not any(n.startswith("optimizer_shard") for n in names)
+    sd = torch.load(ck / "optimizer_1.bin", map_location="cpu", weights_only=False)
+    assert len(sd["param_groups"]) == 2 and sd["param_groups"][1]["weight_decay"] == 0.0
+    assert sd["state"] and all(set(v) == {"step", "exp_avg", "exp_avg_sq"} for v in sd["state"].values())
     assert {"random_states_0.pkl", "random_states_1.pkl"} <= names
     assert "step 3" in r.stderr
     losses = [float(m) for m in re.findall(r"step \d+ \| loss ([0-9.]+)", r.stderr)]
@@ -96,6 +100,25 @@ def test_two_rank_gloo_matches_layout(tmp_path, parallelism):
 
 
 _TWO_RANK_LOSSES: dict[str, list[float]] = {}
+
+
+def test_resume_with_another_rank_count_and_mode(tmp_path):
+    """A checkpoint written by two full-shard ranks resumes in one replicated process (and the other way round the
+    optimizer moments are sliced again): the run continues from the same step with finite losses."""
+    out = tmp_path / "run"
+    common = ["--train.checkpoint.output_dir", str(out), "--train.checkpoint.export_hf_final", "false",
+              "--train.gradient_accumulation_steps", "2", "--logging.logging_steps", "1", "--train.checkpoint.save_steps", "2"]
+    r = _train([*common, "--train.max_steps", "2", "--train.distributed.parallelism", "fsdp"], nproc=2, port=29621)
+    assert r.returncode == 0, r.stderr[-3000:]
+    resume = ["--train.checkpoint.resume_from_checkpoint", "auto", "--train.checkpoint.overwrite_output_dir", "false"]
+    r = _train([*common, "--train.max_steps", "3", "--train.distributed.parallelism", "ddp", *resume])
+    assert r.returncode == 0, r.stderr[-3000:]
+    assert "Resumed from" in r.stderr and "step 3 |" in r.stderr and (out / "checkpoint-3" / "model.safetensors").exists()
+    sd = torch.load(out / "checkpoint-3" / "optimizer.bin", map_location="cpu", weights_only=False)
+    assert int(float(next(iter(sd["state"].values()))["step"])) == 3
+    r = _train([*common, "--train.max_steps", "4", "--train.distributed.parallelism", "zero", *resume], nproc=2, port=29622)
+    assert r.returncode == 0, r.stderr[-3000:]
+    assert "step 4 |" in r.stderr
 
 
 def test_dry_run_reports_batch_shape(tmp_path, capsys):
