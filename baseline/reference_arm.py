@@ -71,19 +71,29 @@ def run_reference(args) -> dict:
         dist.init_process_group("nccl", device_id=device)
     torch.manual_seed(1234)
     if getattr(args, "backbone", "hf_deberta_v2") == "rope":
-        model_cfg = ModelConfig(backbone_type="rope", embedding_sharing="gdes")
+        model_cfg = ModelConfig(backbone_type="rope", embedding_sharing="gdes",
+                                rope={"ffn_type": getattr(args, "rope_ffn", "mlp")},
+                                generator=({"num_hidden_layers": int(args.gen_layers)} if getattr(args, "gen_layers", 0) else {}),
+                                gradient_checkpointing=bool(getattr(args, "grad_ckpt", False)))
     else:
         model_cfg = ModelConfig(profile="deberta_v3_parity", backbone_type="hf_deberta_v2", embedding_sharing="gdes",
-                                hf={"model_size": args.model_size})
+                                hf={"model_size": args.model_size},
+                                generator=({"num_hidden_layers": int(args.gen_layers)} if getattr(args, "gen_layers", 0) else {}),
+                                gradient_checkpointing=bool(getattr(args, "grad_ckpt", False)))
     train_cfg = TrainConfig(per_device_train_batch_size=args.micro_batch, gradient_accumulation_steps=args.ga,
                             mixed_precision="bf16", max_steps=10_000)
     for k, v in dict(learning_rate=2e-4, generator_learning_rate=-1.0, discriminator_learning_rate=-1.0, weight_decay=0.01,
-                     adam_beta1=0.9, adam_beta2=0.98, adam_epsilon=1e-6, warmup_steps=10_000,
+                     adam_beta1=0.9, adam_beta2=0.98, adam_epsilon=1e-6,
+                     warmup_steps=(bench.curve_warmup(args) if getattr(args, "curve", 0) else 10_000),
                      lr_scheduler_type="linear", max_grad_norm=1.0).items():
         object.__setattr__(train_cfg, k, v)
     tok = _StubTokenizer(bench.VOCAB)
     disc_cfg, gen_cfg = build_backbone_configs(model_cfg=model_cfg, tokenizer=tok, max_position_embeddings=args.seq_len)
     disc, gen = build_backbones(model_cfg=model_cfg, disc_config=disc_cfg, gen_config=gen_cfg)
+    if model_cfg.gradient_checkpointing:  # as the reference's entrypoint does (training/entrypoint.py:505-510)
+        for backbone in (disc, gen):
+            if hasattr(backbone, "gradient_checkpointing_enable"):
+                backbone.gradient_checkpointing_enable()
     model = DebertaV3RTDPretrainer(discriminator_backbone=disc, generator_backbone=gen, disc_config=disc_cfg,
                                    gen_config=gen_cfg, embedding_sharing="gdes", tie_generator_word_embeddings=True,
                                    additional_forbidden_token_ids=tok.all_special_ids).to(device)
@@ -95,7 +105,8 @@ def run_reference(args) -> dict:
     model.sync_discriminator_embeddings_from_generator()
     model.train()
     block_docs = bool(getattr(args, "block_docs", False))
-    host = bench.synthetic_batches(args.ga, args.micro_batch, args.seq_len, seed=100 + rank, pin=True, block_docs=block_docs)
+    host = bench.synthetic_batches(args.ga, args.micro_batch, args.seq_len, seed=100 + rank, pin=True, block_docs=block_docs,
+                                   mean_doc_len=getattr(args, "mean_doc_len", 60))
     from deberta.training.compile import _build_doc_block_mask  # the reference loop turns document ids into [B,S,S] masks
 
     def mask_of(b):
@@ -105,6 +116,8 @@ def run_reference(args) -> dict:
     dev = [{k: v.to(device) for k, v in b.items()} for b in host]
     # loss weights as the reference's profile defaults resolve them: 10 for the DeBERTa-v2 backbone, 50 otherwise
     gen_w, disc_w, ga = 1.0, (10.0 if getattr(args, "backbone", "hf_deberta_v2") == "hf_deberta_v2" else 50.0), args.ga
+    if getattr(args, "curve", 0):
+        disc_w = 50.0  # loss curves are compared at the objective weights the other arm uses
 
     def window(batches, counts):
         gen_tot = max(sum(c[0] for c in counts), 1.0)
@@ -155,6 +168,13 @@ def run_reference(args) -> dict:
             dist.barrier()
         torch.cuda.synchronize()
 
+    if getattr(args, "curve", 0):  # fixed-seed loss curve instead of timing: same batches as the other arm
+        rows = []
+        for batches in bench.curve_batches(args, rank):
+            g, d = window(batches, [_count_rtd_tokens_for_batch(b, pad_token_id=0) for b in batches])
+            rows.append(torch.stack([g.float(), d.float()]))
+        vals = torch.stack(rows).cpu().tolist()
+        return bench.curve_report(args, "reference", [v[0] for v in vals], [v[1] for v in vals], world) if rank == 0 else {}
     try:
         for _ in range(args.warmup):
             window(dev, counts)

@@ -38,6 +38,14 @@ SEQ_LEN = 512
 MICRO_BATCH = 32
 VOCAB = 128_100
 BASELINE_TOKENS_PER_S = None  # the reference publishes no number
+# Secondary configurations (per-GPU micro-batch as named; grad-accum 2 keeps a run short).
+PRESETS = {
+    "v3-small": dict(model_size="small", micro_batch=64, ga=2, parallelism="ddp"),
+    "rope-2048": dict(backbone="rope", seq_len=2048, micro_batch=8, ga=2, rope_ffn="swiglu", gen_layers=6, block_docs=True,
+                      mean_doc_len=600),
+    "rope-4096": dict(backbone="rope", seq_len=4096, micro_batch=4, ga=2, rope_ffn="swiglu", gen_layers=6, block_docs=True,
+                      mean_doc_len=1200, grad_ckpt=True),
+}
 
 
 def parse_args() -> argparse.Namespace:
@@ -56,7 +64,19 @@ def parse_args() -> argparse.Namespace:
     p.add_argument("--block-docs", action="store_true",
                    help="rope backbone only: packed documents do not attend to each other (data.packing."
                         "block_cross_document_attention); the collator then emits document ids")
-    return p.parse_args()
+    p.add_argument("--rope-ffn", choices=("mlp", "swiglu"), default="mlp", help="feed-forward type of the rope backbone")
+    p.add_argument("--gen-layers", type=int, default=0, help="generator depth (0: derived from the discriminator)")
+    p.add_argument("--grad-ckpt", action="store_true", help="activation checkpointing per layer (both arms)")
+    p.add_argument("--mean-doc-len", type=int, default=60, help="mean length of the synthetic documents (tokens)")
+    p.add_argument("--preset", choices=tuple(PRESETS), default=None,
+                   help="one of the secondary benchmark configurations (sets the flags above)")
+    p.add_argument("--curve", type=int, default=0,
+                   help="instead of timing: train this many steps at a fixed seed and print the loss curve (JSON)")
+    args = p.parse_args()
+    if args.preset:
+        for k, v in PRESETS[args.preset].items():
+            setattr(args, k, v)
+    return args
 
 
 class ClockSampler:
@@ -105,13 +125,13 @@ class ClockSampler:
 
 
 def synthetic_batches(n: int, micro_batch: int, seq_len: int, seed: int, pin: bool,
-                      block_docs: bool = False) -> list[dict[str, torch.Tensor]]:
+                      block_docs: bool = False, mean_doc_len: int = 60) -> list[dict[str, torch.Tensor]]:
     """``n`` collated micro-batches from the synthetic corpus through the real packer + collator."""
     from deberta_b200.data import DebertaV3ElectraCollator, MLMConfig, PackedStreamingConfig, PackedStreamingDataset
     from deberta_b200.data.synthetic import SyntheticTextDataset, SyntheticTokenizer
 
     tok = SyntheticTokenizer(VOCAB)
-    ds = PackedStreamingDataset(hf_dataset=SyntheticTextDataset(vocab_size=VOCAB, zipf_s=1.1, mean_doc_len=60, seed=seed),
+    ds = PackedStreamingDataset(hf_dataset=SyntheticTextDataset(vocab_size=VOCAB, zipf_s=1.1, mean_doc_len=int(mean_doc_len), seed=seed),
                                 tokenizer=tok, cfg=PackedStreamingConfig(max_seq_length=seq_len, seed=seed))
     col = DebertaV3ElectraCollator(tokenizer=tok, cfg=MLMConfig(mlm_probability=0.15, mask_token_prob=1.0,
                                                                 random_token_prob=0.0), packed_sequences=True,
@@ -127,6 +147,35 @@ def synthetic_batches(n: int, micro_batch: int, seq_len: int, seed: int, pin: bo
     return out
 
 
+def curve_warmup(args: argparse.Namespace) -> int:
+    """Warm-up length of a loss-curve run (a tenth of it), the same in both arms."""
+    return max(1, int(args.curve) // 10)
+
+
+def curve_batches(args: argparse.Namespace, rank: int):
+    """The micro-batches of a loss-curve run, window by window: the same stream in both arms."""
+    per = 64  # windows generated at a time
+    done = 0
+    while done < args.curve:
+        n = min(per, args.curve - done)
+        chunk = synthetic_batches(n * args.ga, args.micro_batch, args.seq_len, seed=5000 + 97 * rank + done, pin=False,
+                                  block_docs=getattr(args, "block_docs", False), mean_doc_len=args.mean_doc_len)
+        for w in range(n):
+            yield chunk[w * args.ga:(w + 1) * args.ga]
+        done += n
+
+
+def curve_report(args: argparse.Namespace, impl: str, gen: list[float], disc: list[float], world: int) -> dict:
+    """One JSON object for ``--curve``: per-step generator loss, 100-step means of both losses."""
+    mean = lambda xs: sum(xs) / max(len(xs), 1)  # noqa: E731
+    return {"impl": impl, "curve_steps": len(gen), "n_gpus": world, "seed": 1234,
+            "config": {"model_size": args.model_size, "backbone": args.backbone, "micro_batch": args.micro_batch,
+                       "grad_accum": args.ga, "seq_len": args.seq_len, "lr": 2e-4, "warmup_steps": curve_warmup(args)},
+            "gen_loss": [round(x, 5) for x in gen], "disc_loss": [round(x, 5) for x in disc],
+            "gen_loss_mean100": [round(mean(gen[i:i + 100]), 5) for i in range(0, len(gen), 100)],
+            "disc_loss_mean100": [round(mean(disc[i:i + 100]), 5) for i in range(0, len(disc), 100)]}
+
+
 def build_config(args: argparse.Namespace):
     from deberta_b200.config import Config, DataConfig, ModelConfig, OptimConfig, TrainConfig, validate_config
 
@@ -134,18 +183,35 @@ def build_config(args: argparse.Namespace):
         model=(ModelConfig(profile="deberta_v3_parity", backbone_type="hf_deberta_v2", embedding_sharing="gdes",
                            hf={"model_size": args.model_size}, tokenizer={"name_or_path": f"synthetic:{VOCAB}"})
                if args.backbone == "hf_deberta_v2" else
-               ModelConfig(backbone_type="rope", embedding_sharing="gdes", tokenizer={"name_or_path": f"synthetic:{VOCAB}"})),
+               ModelConfig(backbone_type="rope", embedding_sharing="gdes", tokenizer={"name_or_path": f"synthetic:{VOCAB}"},
+                           rope={"ffn_type": args.rope_ffn})),
         data=DataConfig(dataset_name="synthetic", dataset_config_name=f"zipf1.1-mean60-vocab{VOCAB}",
                         max_seq_length=args.seq_len),
         train=TrainConfig(per_device_train_batch_size=args.micro_batch, gradient_accumulation_steps=args.ga,
                           mixed_precision="bf16", max_steps=10_000, disc_loss_weight=50.0, mask_token_prob=1.0,
                           random_token_prob=0.0, dataloader_num_workers=0),
-        optim=OptimConfig(learning_rate=2e-4, adam_beta2=0.98, adam_epsilon=1e-6, warmup_steps=10_000),
+        optim=OptimConfig(learning_rate=2e-4, adam_beta2=0.98, adam_epsilon=1e-6,
+                          warmup_steps=curve_warmup(args) if args.curve else 10_000),
     )
+    from deberta_b200.config import apply_dotted_override
+
+    if args.gen_layers > 0:
+        cfg = apply_dotted_override(cfg, f"model.generator.num_hidden_layers={int(args.gen_layers)}")
+    if args.grad_ckpt:
+        cfg = apply_dotted_override(cfg, "model.gradient_checkpointing=true")
+    if args.block_docs:
+        cfg = apply_dotted_override(cfg, "data.packing.block_cross_document_attention=true")
     with warnings.catch_warnings():
         warnings.simplefilter("ignore")
         validate_config(cfg)
     return cfg
+
+
+def describe_model(args: argparse.Namespace) -> str:
+    if args.backbone == "hf_deberta_v2":
+        return f"deberta-v3-{args.model_size} RTD (GDES, EMD" + (f", {args.gen_layers}L gen" if args.gen_layers else "") + ")"
+    return (f"rope RTD (12L, {args.rope_ffn} FFN, " + (f"{args.gen_layers}L gen" if args.gen_layers else "derived gen") +
+            (", activation checkpointing" if args.grad_ckpt else "") + ", GDES)")
 
 
 def run_ours(args: argparse.Namespace) -> dict:
@@ -164,8 +230,19 @@ def run_ours(args: argparse.Namespace) -> dict:
     engine = build_engine(model=model, ctx=ctx, train_cfg=cfg.train, optim_cfg=cfg.optim, parallelism=args.parallelism)
     trainer = Trainer(model=model, engine=engine, ctx=ctx, train_cfg=cfg.train, optim_cfg=cfg.optim,
                       pad_token_id=tok.pad_token_id)
+    if args.curve:
+        rows = []
+        for window in curve_batches(args, ctx.rank):
+            st = trainer.train_window(window)
+            rows.append(torch.stack([st.gen_loss_tokens / max(st.gen_tokens, 1.0), st.disc_loss_tokens / max(st.disc_tokens, 1.0)]))
+        trainer.wait_for_side_stream()
+        trainer.resolve_pending()
+        vals = torch.stack(rows).cpu().tolist()
+        _lib.check_status()
+        ctx.shutdown()
+        return curve_report(args, "ours", [v[0] for v in vals], [v[1] for v in vals], ctx.world_size) if ctx.is_main_process else {}
     host = synthetic_batches(args.ga, args.micro_batch, args.seq_len, seed=100 + ctx.rank, pin=True,
-                             block_docs=getattr(args, "block_docs", False))
+                             block_docs=getattr(args, "block_docs", False), mean_doc_len=args.mean_doc_len)
     dev = [{k: v.to(ctx.device) for k, v in b.items()} for b in host]
     tokens_per_step = args.ga * args.micro_batch * args.seq_len
     h2d = sum(v.numel() * v.element_size() for b in host for v in b.values())
@@ -212,8 +289,10 @@ def run_ours(args: argparse.Namespace) -> dict:
         "n_gpus": ctx.world_size, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic packed Zipf(1.1) token streams, random-init weights", "impl": "ours",
-        "config": {"model": (f"deberta-v3-{args.model_size} RTD (12L disc + 6L gen, GDES, EMD)" if args.backbone == "hf_deberta_v2"
-                             else "rope RTD (config defaults, GDES)"),
+        "config": {"model": ("deberta-v3-base RTD (12L disc + 6L gen, GDES, EMD)"
+                             if (args.backbone == "hf_deberta_v2" and args.model_size == "base" and not args.gen_layers)
+                             else describe_model(args)),
+                   "preset": args.preset, "mean_doc_len": args.mean_doc_len,
                    "global_batch": args.micro_batch * args.ga * ctx.world_size, "micro_batch": args.micro_batch,
                    "grad_accum": args.ga, "seq_len": args.seq_len, "block_cross_document_attention": bool(args.block_docs),
                    "parallelism": f"dp{ctx.world_size}" + {"zero": "-zero1", "fsdp": "-fullshard", "ddp": "-replicated"}[args.parallelism],

@@ -243,10 +243,24 @@ class ModelTokenizerConfig(Section):
 
 
 @_cfg
+class ModelHFScratchConfig(Section):
+    """Shape overrides for a from-scratch ``hf_deberta_v2`` discriminator (all optional). The reference's schema only
+    offers the size presets, and builds its tiny test models in code (``tests/test_smoke.py:1773-1851``); these leaves
+    make such a model expressible in a config file (``configs/tiny_cpu_smoke_hf_deberta_v2.yaml``)."""
+
+    hidden_size: int | None = None
+    num_hidden_layers: int | None = None
+    num_attention_heads: int | None = None
+    intermediate_size: int | None = None
+    position_buckets: int | None = None
+
+
+@_cfg
 class ModelHFConfig(Section):
     model_size: str = "base"
     attention_kernel: str = "dynamic"
     max_position_embeddings: int | None = None
+    scratch: ModelHFScratchConfig = field(default_factory=ModelHFScratchConfig)
 
 
 @_cfg
@@ -647,6 +661,15 @@ def validate_model_config(cfg: ModelConfig) -> None:
             raise ValueError(
                 "model.hf.max_position_embeddings is only supported when model.from_scratch=true for hf_deberta_v2 runs."
             )
+        sc = cfg.hf.scratch
+        given = {k: v for k, v in asdict(sc).items() if v is not None}
+        if given and not cfg.from_scratch:
+            raise ValueError("model.hf.scratch.* is only supported when model.from_scratch=true.")
+        for k, v in given.items():
+            if int(v) <= 0:
+                raise ValueError(f"model.hf.scratch.{k} must be > 0 when provided.")
+        if sc.hidden_size is not None and sc.num_attention_heads is not None and int(sc.hidden_size) % int(sc.num_attention_heads):
+            raise ValueError("model.hf.scratch.hidden_size must be divisible by model.hf.scratch.num_attention_heads.")
         if asdict(cfg.rope) != asdict(d.rope):
             raise ValueError("These options are only valid when model.backbone_type='rope': model.rope.*")
     else:

@@ -2,8 +2,8 @@
 // This entry point has no counterpart in the reference implementation.
 //
 // Who it is for: code that calls this library from a place where device memory cannot be
-// requested — a callback running while a stream is being captured into a CUDA graph, a host
-// function enqueued on a stream, a real-time serving loop with a fixed memory plan, or an
+// requested — a host function enqueued on a stream (cudaLaunchHostFunc callbacks must not call
+// the allocator), a real-time serving loop that runs on a memory plan fixed at start-up, or an
 // embedding application whose allocator this library must not touch. The regular entry point
 // (db200_gemm_bf16 with EPI_CE_FWD followed by db200_ce_combine) needs a caller-provided scratch
 // buffer of 4 * ceil(vocab / tile) * rows + rows floats; callers like the ones above often have
@@ -21,8 +21,9 @@
 //
 // Set-up: the first call on each device looks up the device address of the array (the host-side
 // name of a __device__ array is not a device pointer) and caches it; that first call should be
-// made before any stream capture begins. No call allocates or frees memory, neither through the
-// CUDA runtime nor through any library.
+// made before any stream capture begins. The caches are plain variables: make the first call on
+// a device from one host thread (later calls only read them). No call allocates or frees memory,
+// neither through the CUDA runtime nor through any library.
 #pragma once
 
 #ifdef __cplusplus

@@ -290,6 +290,13 @@ def build_backbone_configs(*, model_cfg: ModelConfig, tokenizer: Any, max_positi
         d = src.discriminator
         disc = (build_repo_hf_deberta_v2_config(model_cfg.hf.model_size) if d.config_source is None
                 else _load_config(DebertaV2Config, d.config_source, "discriminator HF", d.config_origin))
+        if d.config_source is None:  # optional shape overrides of a from-scratch model (model.hf.scratch.*)
+            sc = model_cfg.hf.scratch
+            for key in ("hidden_size", "num_hidden_layers", "num_attention_heads", "intermediate_size", "position_buckets"):
+                if getattr(sc, key) is not None:
+                    setattr(disc, key, int(getattr(sc, key)))
+            if sc.hidden_size is not None:
+                disc.pooler_hidden_size = int(sc.hidden_size)
         g = src.generator
         if g.config_source is None:
             gen = _derive_generator_config(disc, model_cfg)

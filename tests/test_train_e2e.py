@@ -16,7 +16,7 @@ ROOT = Path(__file__).resolve().parents[1]
 CFG = ROOT / "configs" / "tiny_cpu_smoke_synthetic.yaml"
 
 
-def _train(args: list[str], env: dict | None = None, nproc: int = 1, port: int = 29611) -> subprocess.CompletedProcess:
+def _train(args: list[str], env: dict | None = None, nproc: int = 1, port: int = 29611, cfg: Path | None = None) -> subprocess.CompletedProcess:
     base = [sys.executable]
     if nproc > 1:
         base += ["-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
@@ -26,7 +26,7 @@ def _train(args: list[str], env: dict | None = None, nproc: int = 1, port: int =
         base += ["-m", "deberta_b200"]
     e = dict(os.environ, DEBERTA_FAST_EXIT_AFTER_TRAIN="0", PYTHONPATH=str(ROOT), CUDA_VISIBLE_DEVICES="")
     e.update(env or {})
-    return subprocess.run(base + ["train", str(CFG), *args], capture_output=True, text=True, cwd=ROOT, env=e, timeout=600)
+    return subprocess.run(base + ["train", str(cfg or CFG), *args], capture_output=True, text=True, cwd=ROOT, env=e, timeout=600)
 
 
 def test_train_resume_export(tmp_path):
@@ -128,3 +128,17 @@ def test_dry_run_reports_batch_shape(tmp_path, capsys):
     text = capsys.readouterr().out
     assert "Dry-run preflight OK" in text and "sample_batch_shape=(4, 128)" in text
     assert not (tmp_path / "never").exists()
+
+
+@pytest.mark.parametrize("nproc", [1, 2])
+def test_tiny_hf_deberta_v2_smoke_config_trains(tmp_path, nproc):
+    """The 2-layer / 64-wide DeBERTa-v2 family model with the 128 100-entry vocabulary: one process, and two gloo ranks."""
+    cfg = ROOT / "configs" / "tiny_cpu_smoke_hf_deberta_v2.yaml"
+    r = _train(["--train.checkpoint.output_dir", str(tmp_path / "run"), "--train.max_steps", "3"], nproc=nproc, port=29631,
+               cfg=cfg)
+    assert r.returncode == 0, r.stderr[-3000:]
+    rows = re.findall(r"step (\d+) \| loss ([0-9.]+) \| gen ([0-9.]+) \| disc ([0-9.]+)", r.stderr)
+    assert [int(x[0]) for x in rows] == [1, 2, 3]
+    gen = [float(x[2]) for x in rows]
+    assert all(11.0 < g < 12.5 for g in gen)  # ln(128100) = 11.76 at initialisation
+    assert abs(float(rows[0][1]) - (float(rows[0][2]) + 50.0 * float(rows[0][3]))) < 2e-3 * float(rows[0][1])  # loss = gen + 50 disc

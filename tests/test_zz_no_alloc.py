@@ -48,13 +48,17 @@ def _noalloc(x, w, b, labels, forb, temperature, seed):
     lse = torch.empty(N, dtype=torch.float32, device="cuda")
     loss = torch.empty(N, dtype=torch.float32, device="cuda")
     sampled = torch.empty(N, dtype=torch.int64, device="cuda")
-    before = torch.cuda.memory_allocated()
+    torch.cuda.synchronize()
+    before, free_before = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]
     rc = fn(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(w.data_ptr()), ctypes.c_void_p(b.data_ptr()),
             ctypes.c_void_p(labels.data_ptr()), ctypes.c_void_p(forb.data_ptr()), ctypes.c_int(N),
             ctypes.c_int(w.shape[0]), ctypes.c_int(E), ctypes.c_float(temperature), ctypes.c_ulonglong(seed),
             ctypes.c_void_p(lse.data_ptr()), ctypes.c_void_p(loss.data_ptr()), ctypes.c_void_p(sampled.data_ptr()),
             ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
-    assert torch.cuda.memory_allocated() == before
+    torch.cuda.synchronize()
+    # neither torch's caching allocator nor the driver handed out memory during the call (cudaMemGetInfo also sees a
+    # cudaMalloc made behind torch's back)
+    assert torch.cuda.memory_allocated() == before and torch.cuda.mem_get_info()[0] >= free_before
     return rc, lse, loss, sampled
 
 
@@ -78,7 +82,9 @@ def test_noalloc_entry_point_matches_regular_entry_point_twice():
         want = _regular(*prob, 1.0, 1234 + call)
         rc, *got = _noalloc(*prob, 1.0, 1234 + call)
         torch.cuda.synchronize()
-        assert rc == 0, _lib.lib().db200_noalloc_strerror
+        strerror = _lib.lib().db200_noalloc_strerror
+        strerror.restype = ctypes.c_char_p
+        assert rc == 0, strerror(rc).decode()
         _lib.check_status()
         torch.testing.assert_close(got[0], want[0], atol=1e-5, rtol=1e-5)
         torch.testing.assert_close(got[1], want[1], atol=1e-5, rtol=1e-5)
