@@ -81,17 +81,21 @@ def main() -> int:
     peak_fsdp = torch.cuda.max_memory_allocated()
     dl = max(abs(a - b) / max(abs(a), 1e-6) for ra, rb in zip(ref_losses, losses) for a, b in zip(ra, rb))
     dm = float((master - ref_master).abs().max())
-    # both arms accumulate dQ / embedding gradients with floating-point atomics and run in bf16: equal up to that noise
-    ok = dl < 2e-2 and dm < 1e-2
+    dmean = float((master - ref_master).abs().mean())
+    # Both arms sum dQ / embedding gradients with floating-point atomics and run in bf16, and Adam turns a sign flip of a
+    # tiny gradient into a full learning-rate step: single elements may differ by a few learning rates, the bulk may not.
+    ok = dl < 2e-2 and dmean < 2e-5 and dm < 2e-2
     flag = torch.tensor([1 if ok else 0], device=ctx.device)
     torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
     if ctx.is_main_process:
         sh = eng.sharder
         print(json.dumps({"ok": bool(int(flag)), "world": ctx.world_size, "max_rel_loss_diff": dl, "max_master_diff": dm,
+                          "mean_master_diff": dmean,
                           "gathers": sh.gathers, "bytes_from_peers": sh.bytes_gathered, "units": len(sh.units),
                           "fused_collectives": eng.comm is not None, "memory": sh.memory_report(),
                           "step_ms": {"zero": ref_t * 1e3, "fsdp": t * 1e3},
-                          "peak_bytes": {"zero": peak_zero, "fsdp": peak_fsdp}, "losses": losses[-1]}))
+                          "peak_bytes": {"zero": peak_zero, "fsdp": peak_fsdp}, "losses": losses[-1],
+                          "reference_losses": ref_losses[-1]}), flush=True)
     ctx.shutdown()
     return 0 if bool(int(flag)) else 1
 

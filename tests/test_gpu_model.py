@@ -185,11 +185,16 @@ def test_discriminator_update_on_the_side_stream_matches_the_serial_schedule():
     """Four windows with the discriminator's collective + AdamW queued on a side stream (outcomes read one window
     late) end in the same masters and step counters as the fully serial schedule."""
     t_ser, e_ser = _tiny_step("bf16", synchronous=False, overlap=False, windows=4, return_engine=True)
+    _, e_again = _tiny_step("bf16", synchronous=False, overlap=False, windows=4, return_engine=True)
     t_ovl, e_ovl = _tiny_step("bf16", synchronous=False, overlap=True, windows=4, return_engine=True)
     assert t_ovl.overlap and not t_ser.overlap
     torch.cuda.synchronize()
-    # (not bit-equal: dQ and the embedding gradients are accumulated with floating-point atomics)
-    assert (e_ser.master - e_ovl.master).abs().max() < 2e-3 and _rel(e_ovl.master, e_ser.master) < 2e-3
+    # Two serial runs already differ: dQ and embedding gradients are summed with floating-point atomics, and Adam turns
+    # a sign flip of a tiny gradient into a full learning-rate step. The side-stream schedule must stay inside that noise.
+    noise = (e_ser.master - e_again.master).abs()
+    diff = (e_ser.master - e_ovl.master).abs()
+    assert float(diff.mean()) <= 3 * float(noise.mean()) + 1e-7, (float(diff.mean()), float(noise.mean()))
+    assert float(diff.max()) <= 3 * float(noise.max()) + 1e-4, (float(diff.max()), float(noise.max()))
     assert [o.step for o in e_ser.optimizers.values()] == [o.step for o in e_ovl.optimizers.values()] == [4, 4]
     assert float(e_ovl.grads.abs().max()) == 0.0  # both ranges were cleared after their updates
 
