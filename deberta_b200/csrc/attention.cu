@@ -279,7 +279,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // padding masks are all-ones for most tiles: those skip the per-element selects
       tile_all_keep = __syncthreads_and(MASK == 1 && tile_meta != 0) != 0;
     }
-    if (!mbar_wait(bar_s, j & 1, abort_flag, p.status, kErrAccFullWait)) { ok = false; break; }
+    // A wait that ran out must not let this thread leave the loop alone (the others would meet it at different
+    // barriers): its answer is combined at the next block barrier and the whole block leaves together.
+    const bool got_s = mbar_wait(bar_s, j & 1, abort_flag, p.status, kErrAccFullWait);
     tc_fence_after();
 
     float s[32];  // unscaled scores of this thread's 32 keys
@@ -337,7 +339,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     for (int k = 0; k < 32; ++k) tmax = fmaxf(tmax, s[k]);
     red[part * kTile + row] = tmax;
     tc_fence_before();
-    __syncthreads();  // every thread has read its scores of tile j: the score accumulator is free again
+    // every thread has read its scores of tile j: the score accumulator is free again
+    if (!__syncthreads_and(got_s)) { ok = false; break; }
     if (tid == 0 && j + 1 < nkt) {  // scores of the next tile run on the tensor core during this tile's softmax
       const int nb = (j + 1) & 1;
       if (mbar_wait(&bar_k[nb], ((j + 1) >> 1) & 1, abort_flag, p.status, kErrFullWait)) {
@@ -364,11 +367,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     l_part = l_part * alpha + lsum;
     m_run = m_new;
 
+    bool got_o = true;
     if (j > 0) {
-      if (!mbar_wait(bar_o, (j - 1) & 1, abort_flag, p.status, kErrAccFullWait)) { ok = false; break; }
+      got_o = __all_sync(0xffffffffu, mbar_wait(bar_o, (j - 1) & 1, abort_flag, p.status, kErrAccFullWait));
       tc_fence_after();
       // rescale the running output (16 of its 64 columns per thread) when a row of this warp raised its maximum
-      if (__any_sync(0xffffffffu, alpha != 1.f)) {
+      if (got_o && __any_sync(0xffffffffu, alpha != 1.f)) {
         uint32_t r[16];
         tmem_ld_32x32b_x16(t_o + lane_addr + part * 16, r);
         tmem_ld_wait();
@@ -396,7 +400,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     fence_proxy_async();
     tc_fence_before();
-    __syncthreads();
+    if (!__syncthreads_and(got_o)) { ok = false; break; }
     if (tid == 0) {
       const bool v_ok = mbar_wait(&bar_v[j & 1], (j >> 1) & 1, abort_flag, p.status, kErrFullWait);
       tc_fence_after();
@@ -640,14 +644,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
       for (int g8 = 0; g8 < 4; ++g8) bias_cur[g8] = __ldg(bias_row + part * 4 + g8);
     }
-    if (!mbar_wait(bar_s, i & 1, abort_flag, p.status, kErrAccFullWait)) { ok = false; break; }
+    bool got_g = true;
+    // (a wait that ran out is reported at the next block barrier, where the whole block leaves the loop together)
+    const bool got_s = mbar_wait(bar_s, i & 1, abort_flag, p.status, kErrAccFullWait);
     tc_fence_after();
     uint32_t rs[32], rd[32];  // this thread's 32 scores and 32 dP values of tile i
     tmem_ld_32x32b_x32(t_s + lane_addr + part * 32, rs);
     tmem_ld_32x32b_x32(t_dp + lane_addr + part * 32, rd);
     tmem_ld_wait();
     tc_fence_before();
-    __syncthreads();  // both accumulators are in registers: the tensor core may start on tile i+1
+    // both accumulators are in registers: the tensor core may start on tile i+1
+    if (!__syncthreads_and(got_s)) { ok = false; break; }
     if (tid == 0 && i + 1 < nqt) {
       const int nb = (i + 1) % 3;
       if (mbar_wait(&bar_qd[nb], ((i + 1) / 3) & 1, abort_flag, p.status, kErrFullWait)) {
@@ -716,15 +723,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       // the previous tile's gradient MMAs must retire before its P / dS tiles and dQ accumulator are reused
       if (i > 0) {
-        if (!mbar_wait(bar_g, (i - 1) & 1, abort_flag, p.status, kErrAccFullWait)) { ok = false; break; }
+        got_g = __all_sync(0xffffffffu, mbar_wait(bar_g, (i - 1) & 1, abort_flag, p.status, kErrAccFullWait));
         tc_fence_after();
-        if (tid == 0 && i + 2 < nqt) {  // buffer (i+2)%3 held tile i-1
+        if (tid == 0 && got_g && i + 2 < nqt) {  // buffer (i+2)%3 held tile i-1
           const int nb = (i + 2) % 3;
           mbar_expect_tx(&bar_qd[nb], 2 * kTileBytes);
           tma_load_3d(sQ + nb * kTileBytes, &tm_q, &bar_qd[nb], h * kD, q0 + 2 * kTile, b);
           tma_load_3d(sdO + nb * kTileBytes, &tm_do, &bar_qd[nb], h * kD, q0 + 2 * kTile, b);
         }
-        flush_dq(ib + i - 1);
+        if (got_g) flush_dq(ib + i - 1);
       } else if (tid == 0 && nqt > 2) {
         mbar_expect_tx(&bar_qd[2], 2 * kTileBytes);
         tma_load_3d(sQ + 2 * kTileBytes, &tm_q, &bar_qd[2], h * kD, (ib + 2) * kTile, b);
@@ -756,7 +763,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     fence_proxy_async();
     tc_fence_before();
-    __syncthreads();
+    if (!__syncthreads_and(got_g)) { ok = false; break; }
     if (tid == 0) {
       tc_fence_after();
       const uint32_t sp = smem_u32(sP), sds = smem_u32(sdS), sq = smem_u32(sQ + buf * kTileBytes),

@@ -368,8 +368,11 @@ class Trainer:
         """Host-side training state. Call ``resolve_pending()`` on every rank first (``save_training_state`` does)."""
         self.wait_for_side_stream()
         self.resolve_pending()
+        from deberta_b200.ops import heads_cuda
+
         return {"global_step": self.global_step, "lr_mult": self.lr_mult, "skip_streak": self.skip_streak,
                 "consumed_micro_batches": self.consumed_micro_batches,
+                "sampler_calls": int(heads_cuda._SEED_STATE["counter"]),  # position of the fused sampler's noise stream
                 "schedules": {n: s.state_dict() for n, s in self.schedules.items()}}
 
     def load_state_dict(self, state: dict[str, Any]) -> None:
@@ -377,6 +380,10 @@ class Trainer:
         self.lr_mult = float(state.get("lr_mult", 1.0))
         self.skip_streak = int(state.get("skip_streak", 0))
         self.consumed_micro_batches = int(state.get("consumed_micro_batches", 0))
+        if "sampler_calls" in state:
+            from deberta_b200.ops import heads_cuda
+
+            heads_cuda._SEED_STATE["counter"] = int(state["sampler_calls"])
         for n, s in self.schedules.items():
             if n in state.get("schedules", {}):
                 s.load_state_dict(state["schedules"][n])
