@@ -125,6 +125,40 @@ cast_rows_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, lon
   }
 }
 
+// Masked-row gather: out[n, :] = x[idx[n], :] (16 bytes per thread), and inv[idx[n]] = n for the backward pass.
+__global__ void __launch_bounds__(256)
+rows_gather_kernel(const __nv_bfloat16* __restrict__ x, long long ld_x, const long long* __restrict__ idx,
+                   __nv_bfloat16* __restrict__ out, int* __restrict__ inv, long long n_rows, int cols) {
+  const int vpr = cols / 8;
+  const long long total = n_rows * vpr;
+  for (long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * 256) {
+    const long long n = i / vpr;
+    const int c = static_cast<int>(i % vpr) * 8;
+    const long long src = idx[n];
+    *reinterpret_cast<uint4*>(out + n * cols + c) = *reinterpret_cast<const uint4*>(x + src * ld_x + c);
+    if (c == 0 && inv) inv[src] = static_cast<int>(n);
+  }
+}
+
+// Its gradient: dx[m, :] = dout[inv[m], :] for selected rows and 0 elsewhere; every row of dx is written once, so the
+// destination needs no clearing pass.
+__global__ void __launch_bounds__(256)
+rows_scatter_kernel(const __nv_bfloat16* __restrict__ dout, long long ld_do, const int* __restrict__ inv,
+                    __nv_bfloat16* __restrict__ dx, long long m_rows, int cols) {
+  const int vpr = cols / 8;
+  const long long total = m_rows * vpr;
+  for (long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * 256) {
+    const long long m = i / vpr;
+    const int c = static_cast<int>(i % vpr) * 8;
+    const int n = inv[m];
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (n >= 0) v = *reinterpret_cast<const uint4*>(dout + static_cast<long long>(n) * ld_do + c);
+    *reinterpret_cast<uint4*>(dx + m * cols + c) = v;
+  }
+}
+
 int ew_grid(long long vecs) {
   long long blocks = (vecs + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
@@ -443,5 +477,25 @@ extern "C" int db200_rtd_tail_bwd(const void* a, long long lda, const void* pre,
       static_cast<const __nv_bfloat16*>(a), lda, static_cast<const __nv_bfloat16*>(pre), ldp,
       static_cast<const __nv_bfloat16*>(w), logits, labels, active, grad, stats, static_cast<__nv_bfloat16*>(d_pre), ldd, dw,
       db, tokens, H);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int db200_rows_gather(const void* x, long long ld_x, const long long* idx, void* out, int* inv, long long m_rows,
+                                 long long n_rows, int cols, void* stream) {
+  if (cols <= 0 || (cols % 8) || (ld_x % 8) || !al16(x) || !al16(out)) return -10;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (inv && m_rows > 0 && cudaMemsetAsync(inv, 0xFF, static_cast<size_t>(m_rows) * sizeof(int), st) != cudaSuccess) return -4;
+  if (n_rows <= 0) return 0;
+  rows_gather_kernel<<<ew_grid(n_rows * (cols / 8)), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), ld_x, idx,
+                                                                    static_cast<__nv_bfloat16*>(out), inv, n_rows, cols);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int db200_rows_scatter(const void* dout, long long ld_do, const int* inv, void* dx, long long m_rows, int cols,
+                                  void* stream) {
+  if (m_rows <= 0) return 0;
+  if (cols <= 0 || (cols % 8) || (ld_do % 8) || !al16(dout) || !al16(dx) || !inv) return -10;
+  rows_scatter_kernel<<<ew_grid(m_rows * (cols / 8)), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(dout), ld_do, inv, static_cast<__nv_bfloat16*>(dx), m_rows, cols);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

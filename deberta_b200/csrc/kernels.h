@@ -87,6 +87,13 @@ int db200_embed_fwd(const long long* ids, const void* table, const void* delta, 
 int db200_embed_bwd(const long long* ids, const void* dout, long long ld_do, float* grad, long long tokens, int H,
                     long long vocab, long long padding_idx, void* stream);
 
+// Masked-row gather out[n] = x[idx[n]] over bf16 rows of `cols` features (idx: distinct int64 rows of x); `inv`
+// (int32 [m_rows], may be null) receives the inverse map (-1 = row not selected). Its gradient writes every row of dx:
+// dx[m] = dout[inv[m]] or 0, so dx needs no clearing.
+int db200_rows_gather(const void* x, long long ld_x, const long long* idx, void* out, int* inv, long long m_rows,
+                      long long n_rows, int cols, void* stream);
+int db200_rows_scatter(const void* dout, long long ld_do, const int* inv, void* dx, long long m_rows, int cols, void* stream);
+
 // Tail of the replaced-token-detection head. Forward: logit[t] = a[t,:].w + bias (rounded to bf16), and
 // stats[0..3] += {BCE-with-logits summed over active tokens, correct predictions, active tokens, positive labels}.
 // Backward: d_pre[t,:] = dz[t] * w * gelu'(pre[t,:]) (pre null: no activation derivative), dw += sum dz * a[t,:],

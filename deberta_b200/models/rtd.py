@@ -16,6 +16,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from deberta_b200.ops.gather import gather_rows
 from deberta_b200.ops.heads import gumbel_sample, mlm_loss_and_sample, rtd_loss
 from deberta_b200.ops.linear import linear
 from deberta_b200.ops.norm import layer_norm
@@ -178,9 +179,9 @@ class EnhancedMaskDecoder(nn.Module):
             )
         masked_idx = torch.nonzero(masked_positions.reshape(-1), as_tuple=False).squeeze(-1)
         if masked_idx.numel() == 0 or self.position_biased_input:
-            return hs[-1].reshape(-1, hs[-1].shape[-1]).index_select(0, masked_idx)
+            return gather_rows(hs[-1].reshape(-1, hs[-1].shape[-1]), masked_idx)
         final = self.decode(hs[-2], attention_mask, embeddings, encoder, position_ids, relative_pos)
-        return final.reshape(-1, final.shape[-1]).index_select(0, masked_idx)
+        return gather_rows(final.reshape(-1, final.shape[-1]), masked_idx)
 
     def decode(self, kv_states, attention_mask, embeddings, encoder, position_ids=None, relative_pos=None):
         """Full-sequence ``[B,S,H]`` output of the EMD passes."""
@@ -443,7 +444,7 @@ class DebertaV3RTDPretrainer(nn.Module):
             )
         else:
             last = gen_out.last_hidden_state
-            hidden = last.reshape(-1, last.shape[-1]).index_select(0, masked_idx)
+            hidden = gather_rows(last.reshape(-1, last.shape[-1]), masked_idx)
         masked_labels = labels.view(-1).index_select(0, masked_idx)
         head = self.generator_lm_head
         w, b = head.projection(self._get_generator_word_embedding_weight() if head.tie_word_embeddings else None)

@@ -113,3 +113,22 @@ def test_rtd_head_kernel_matches_composition():
     want = [xr.grad] + [p.grad for p in ps]
     for g, w in zip(got, want):
         assert (g - w).abs().max() <= 6e-2 * w.abs().max() + 1e-5, (float((g - w).abs().max()), float(w.abs().max()))
+
+
+@pytest.mark.parametrize("M,H,frac", [(4096, 768, 0.15), (1000, 64, 0.5), (512, 256, 0.0)])
+def test_masked_row_gather_matches_index_select(M, H, frac):
+    """Forward equals ``index_select`` bit for bit; the gradient equals the zero-filled ``index_add`` of the reference
+    and covers every row (the unselected ones are exact zeros), also for a strided source and an empty selection."""
+    from deberta_b200.ops.gather import gather_rows
+
+    torch.manual_seed(4)
+    base = (torch.randn(M, H + 8, device="cuda")).to(torch.bfloat16)
+    x = base[:, :H].detach().requires_grad_(True)  # row stride H + 8
+    idx = torch.nonzero(torch.rand(M, device="cuda") < frac).flatten()
+    out = gather_rows(x, idx)
+    assert torch.equal(out, x.detach().index_select(0, idx))
+    dout = torch.randn(idx.numel(), H, device="cuda").to(torch.bfloat16)
+    out.backward(dout)
+    _lib.check_status()
+    ref = torch.zeros(M, H, device="cuda", dtype=torch.bfloat16).index_add_(0, idx, dout)
+    assert torch.equal(x.grad, ref)
