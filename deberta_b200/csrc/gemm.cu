@@ -69,6 +69,7 @@ struct DevParams {
   const float* row_lse;             // [M] natural-log log-sum-exp (backward)
   float gscale;                     // dLoss/dlogit scale (backward)
   const float* gscale_ptr;          // optional device scalar multiplied into gscale
+  float* a_sum;                     // [M] fp32 or null: += sum_k A[m,k] (fp32 output with M-major A: bias gradients)
 };
 
 // Counter-based uniform in (0,1) from (seed, row, column): 32-bit multiply-xorshift mixing (two rounds), the seed's
@@ -134,6 +135,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   constexpr bool kTwoOut = kEpi == EPI_GELU || kEpi == EPI_GELU_GRAD;  // second output: gelu of the pre-activation
   constexpr bool kAuxMul = kEpi == EPI_DGELU || kEpi == EPI_MUL;       // accumulator times a function of `aux`
   constexpr bool kOutF32 = MODE == 3;
+  // Row sums of A on the tensor cores (the bias gradient of a linear layer inside its weight-gradient GEMM): the
+  // work items of the first column tile multiply every A tile by a 16-column tile of ones as well, into 16 spare
+  // TMEM columns. With BN = 256 the two accumulator buffers fill the tensor memory, so such a launch runs on one
+  // buffer (weight gradients are split along K into about one work item per CTA, so nothing is lost).
+  constexpr bool kRowSum = kOutF32 && A_MN;
+  constexpr uint32_t kSumCol = 256;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
@@ -145,7 +152,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  constexpr uint32_t kTmemCols = 2 * BN;  // 256 or 512: powers of two
+  constexpr uint32_t kTmemCols = kRowSum ? 512 : 2 * BN;  // 256 or 512: powers of two
+  const bool want_sum = kRowSum && p.a_sum != nullptr;
+  const int acc_stages = (want_sum && BN == 256) ? 1 : 2;
+  if (want_sum) {  // bf16 ones: identical under every swizzle, so the tile needs no layout
+    uint32_t* ones = reinterpret_cast<uint32_t*>(smem + L::kStagingOffset);
+    for (int i = threadIdx.x; i < 512; i += kThreads) ones[i] = 0x3F803F80u;
+    fence_proxy_async();
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::kStages; ++s) {
@@ -221,6 +235,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // ------------------------------- MMA issuer ---------------------------------
     if (elect_one()) {
       constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      constexpr uint32_t idesc_sum = make_idesc_bf16(BM, 16, A_MN, false);
+      const uint64_t d_ones = make_smem_desc(smem_u32(smem + L::kStagingOffset), 16, 1024);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -233,6 +249,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.status, kErrAccEmptyWait)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
+        const bool do_sum = want_sum && ((w / p.splits) % tiles_per_batch) / p.tiles_m == 0;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, kErrFullWait)) { ok = false; break; }
           tc_fence_after();
@@ -247,13 +264,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, BK * 128, 1024)
                                      : make_smem_desc(sb + k * 32, 16, 1024);
             umma_bf16(d_tmem, da, db, idesc, (kb > kb0) || (k > 0));
+            if (kRowSum && do_sum) umma_bf16(tmem_base + kSumCol + acc * 16, da, d_ones, idesc_sum, (kb > kb0) || (k > 0));
           }
           umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
           if (++stage == L::kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         umma_commit(&acc_full[acc]);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        if (++acc == acc_stages) { acc = 0; acc_phase ^= 1; }
       }
     }
   } else {
@@ -604,10 +622,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
       }
       }
+      if constexpr (kRowSum) {
+        if (want_sum && n0 == 0 && half == 0 && z == 0) {  // warp-uniform
+          uint32_t sum_bits;
+          asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];"
+                       : "=r"(sum_bits)
+                       : "r"(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kSumCol + acc * 16));
+          tmem_ld_wait();
+          if (row_ok && !empty_split) atomicAdd(p.a_sum + row, __uint_as_float(sum_bits));
+        }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
-      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      if (++acc == acc_stages) { acc = 0; acc_phase ^= 1; }
       }  // regular (non-CE) epilogue
     }
     if (lane == 0) tma_store_wait_all();  // shared memory must outlive the bulk stores that read it
@@ -822,6 +850,8 @@ extern "C" int db200_gemm_bf16(const GemmArgs* a, void* stream_) {
   p.row_lse = a->row_lse;
   p.gscale = a->gscale;
   p.gscale_ptr = a->gscale_ptr;
+  p.a_sum = a->a_sum;
+  if (p.a_sum && (!a->out_f32 || !a->a_mn || a->batch != 1)) return -11;
   if ((p.epi == EPI_CE_FWD) && (!p.labels || !p.ce_part || !p.label_logit || a->batch != 1)) return -11;
   if ((p.epi == EPI_CE_BWD) && (!p.labels || !p.row_lse || p.out_f32 || a->batch != 1)) return -11;
   const bool two_out = p.epi == EPI_GELU || p.epi == EPI_GELU_GRAD;

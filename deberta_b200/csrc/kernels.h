@@ -42,6 +42,7 @@ typedef struct GemmArgs {
   const float* row_lse;      // fp32 [M]                       (EPI_CE_BWD)
   float gscale;              // scale of the logit gradient     (EPI_CE_BWD)
   const float* gscale_ptr;   // optional device scalar multiplied into gscale
+  float* a_sum;              // fp32 [M] or null: a_sum[m] += sum_k A[m,k] (needs out_f32, a_mn, batch 1); alpha is not applied
 } GemmArgs;
 
 int db200_gemm_bf16(const GemmArgs* args, void* stream);

@@ -80,6 +80,7 @@ class GemmArgs(ctypes.Structure):
         ("row_lse", c_void_p),
         ("gscale", c_float),
         ("gscale_ptr", c_void_p),
+        ("a_sum", c_void_p),
     ]
 
 

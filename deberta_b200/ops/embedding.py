@@ -82,14 +82,10 @@ class _Embed(torch.autograd.Function):
 def embedding_lookup(ids: torch.Tensor, table: torch.Tensor, delta: torch.Tensor | None = None,
                      padding_idx: int | None = None) -> torch.Tensor:
     """``table[ids] (+ delta[ids])``; gradients of trainable tables go to their ``main_grad`` on the kernel path."""
+    # Under a compiler the lookup is F.embedding (the kernel path scatters into the engine's gradient buffers, and ops that
+    # mutate views of the flat gradient storage do not go into a compiled graph: see ops/linear.py:linear).
     if _usable(table) and _usable(delta) and table.is_cuda and _grad_ready(table) and _grad_ready(delta) and \
-            (delta is None or delta.shape == table.shape):
-        if torch.compiler.is_compiling():
-            from . import library
-
-            tg = table.main_grad if table.requires_grad else None
-            dg = delta.main_grad if (delta is not None and delta.requires_grad) else None
-            return library.embed(ids, table, delta, -1 if padding_idx is None else int(padding_idx), tg, dg)
+            (delta is None or delta.shape == table.shape) and not torch.compiler.is_compiling():
         if torch.is_grad_enabled() and (table.requires_grad or (delta is not None and delta.requires_grad)):
             return _Embed.apply(ids, table, delta, padding_idx)
         return embed_forward(ids, table, delta)

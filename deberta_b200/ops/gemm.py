@@ -94,13 +94,16 @@ def gemm(
     out_dtype: torch.dtype | None = None,
     accumulate: bool = False,
     split_k: bool = True,
+    a_sum: torch.Tensor | None = None,
 ):
     """``out = epilogue(alpha * A·Bᵀ)``; returns ``out``, ``(z, gelu(z))`` for ``EPI_GELU`` or ``(gelu'(z), gelu(z))``
     for ``EPI_GELU_GRAD`` (``EPI_MUL`` with that first output as ``aux`` is then the whole GELU backward).
 
     ``a``: [M,K] (``a_mn=False``) or [K,M] (``a_mn=True``); ``b``: [N,K] or [K,N]
     likewise; optional leading batch dim on both. ``accumulate`` adds into an fp32
-    ``out`` (used for weight gradients accumulated across micro-batches).
+    ``out`` (used for weight gradients accumulated across micro-batches). ``a_sum`` (fp32 [M], only with ``a_mn`` and an
+    fp32 ``out``) receives ``+= Σ_k A[m, k]`` from the same launch: the bias gradient of a linear layer comes out of its
+    weight-gradient GEMM.
     """
     use_kernel = a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     if not use_kernel:
@@ -119,8 +122,9 @@ def gemm(
                 out.add_(res.to(out.dtype))
             else:
                 out.copy_(res)
-            return out
-        return res
+        if a_sum is not None:
+            a_sum.add_((a.float().sum(dim=-2) if a_mn else a.float().sum(dim=-1)).to(a_sum.dtype))
+        return res if out is None else out
 
     batched = a.dim() == 3
     M = a.shape[-1] if a_mn else a.shape[-2]
@@ -163,6 +167,9 @@ def gemm(
     args.ldr, args.bs_res = _ld(residual) if residual is not None else (0, 0)
     args.ldaux, args.bs_aux = _ld(aux) if aux is not None else (0, 0)
     args.bs_bias = bias.stride(0) if (bias is not None and bias.dim() == 2) else 0
+    if a_sum is not None and (a_sum.dtype != torch.float32 or not a_sum.is_contiguous() or a_sum.numel() != M):
+        raise ValueError("a_sum must be a dense fp32 vector of M elements")
+    args.a_sum = a_sum.data_ptr() if a_sum is not None else None
     for t in (bias, residual, aux, out, out2):
         if t is not None and t.data_ptr() % 16:
             raise ValueError("GEMM epilogue tensors must be 16-byte aligned")

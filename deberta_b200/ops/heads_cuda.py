@@ -128,7 +128,7 @@ class _RTDHead(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_loss, *_unused):
-        from .linear import _bias_grad, _weight_grad
+        from .linear import _param_grads
 
         x, dense_w, pre, act, logits, labels, active, stats = ctx.saved_tensors
         dense_b, cls_w, cls_b = ctx.refs
@@ -144,8 +144,7 @@ class _RTDHead(torch.autograd.Function):
                   _lib.ptr(g), _lib.ptr(stats), _lib.ptr(d_pre), ctypes.c_longlong(d_pre.stride(0)), _lib.ptr(dw), _lib.ptr(db),
                   ctypes.c_longlong(T), ctypes.c_int(H), _lib.stream_ptr())
         dx = gemm(d_pre, dense_w, b_mn=True) if ctx.needs_input_grad[0] else None
-        d_dense_w = _weight_grad(d_pre, x, dense_w) if dense_w.requires_grad else None
-        d_dense_b = _bias_grad(d_pre, dense_b) if (dense_b is not None and dense_b.requires_grad) else None
+        d_dense_w, d_dense_b = _param_grads(d_pre, x, dense_w, dense_b)
         d_cls_w = None if dw_main is not None else dw.view(1, H).to(cls_w.dtype)
         d_cls_b = None if (cls_b is None or db_main is not None) else db.to(cls_b.dtype)
         return dx, d_dense_w, d_dense_b, d_cls_w, d_cls_b, None, None

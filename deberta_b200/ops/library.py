@@ -12,7 +12,12 @@ a compiler is tracing (``torch.compiler.is_compiling()``).
 Conventions
 * Gradients of parameters that the engine owns go straight into their fp32 ``main_grad`` buffers; those buffers are
   explicit, mutated arguments of the backward ops (``mutates_args``), and the autograd formula then returns ``None``
-  for the parameter. Without a buffer the gradient tensor is returned instead.
+  for the parameter. Without a buffer the gradient tensor is returned instead. The public operator functions pass NO
+  buffers while a compiler traces: the engine's buffers are views at offsets inside one flat storage, and Inductor
+  handles a mutated graph input that is such a view by copying ``offset + size`` elements starting at the view's own
+  address, which runs past the end of the storage (seen as an illegal address in a generated copy kernel). Gradients then
+  flow back as tensors and the engine's post-accumulate hook adds them to the buffers. Buffers that own their storage
+  (as in the tests of this module) are fine.
 * On bf16 CUDA tensors the ops launch the sm_100a kernels; on anything else they evaluate the PyTorch statement of the
   same operator, which is what ``torch.library.opcheck`` exercises on a machine without a GPU.
 """
@@ -60,15 +65,14 @@ def _(x, w, b, residual, w_grad, b_grad):
 def linear_bwd(dy: Tensor, x: Tensor, w: Tensor, w_grad: Tensor | None, b_grad: Tensor | None, has_bias: bool,
                need_dx: bool) -> tuple[Tensor, Tensor, Tensor]:
     """(dx, dw, db); a gradient that went into its buffer comes back as an empty tensor."""
-    from .linear import bias_grad_into, weight_grad_into
+    from .linear import param_grads_into
 
     dy = dy.contiguous()
     if _kernels(dy):
         dx = gemm(dy, w, b_mn=True) if need_dx else dy.new_empty(_EMPTY)
     else:
         dx = (dy @ w.to(dy.dtype)) if need_dx else dy.new_empty(_EMPTY)
-    dw = weight_grad_into(dy, x, w, w_grad)
-    db = bias_grad_into(dy, b_grad, w.dtype) if has_bias else None
+    dw, db = param_grads_into(dy, x, w, w_grad, b_grad, True, has_bias)
     return dx, (dw if dw is not None else w.new_empty(_EMPTY)), (db if db is not None else w.new_empty(_EMPTY))
 
 
@@ -115,15 +119,14 @@ def _(x, wq, bq, w_grad, b_grad):
 
 @custom_op("db200::linear_qkv_bwd", mutates_args=("w_grad", "b_grad"))
 def linear_qkv_bwd(dqkv: Tensor, x: Tensor, wq: Tensor, w_grad: Tensor, b_grad: Tensor | None, need_dx: bool) -> Tensor:
-    from .linear import _span3, colsum_into
+    from .linear import _span3
 
     n, k = wq.shape
     if dqkv.stride(1) != 1 or dqkv.stride(0) % 8 or dqkv.data_ptr() % 16:
         dqkv = dqkv.contiguous()
     dx = gemm(dqkv, _span3(wq, (3 * n, k)), b_mn=True) if need_dx else dqkv.new_empty(_EMPTY)
-    gemm(dqkv, x, a_mn=True, b_mn=True, out=_span3(w_grad, (3 * n, k)), accumulate=True)
-    if b_grad is not None:
-        colsum_into(dqkv, _span3(b_grad, (3 * n,)))
+    gemm(dqkv, x, a_mn=True, b_mn=True, out=_span3(w_grad, (3 * n, k)), accumulate=True,
+         a_sum=None if b_grad is None else _span3(b_grad, (3 * n,)))
     return dx
 
 
@@ -175,16 +178,14 @@ def ffn_gelu_bwd(dy: Tensor, x: Tensor, w1: Tensor, w2: Tensor, g: Tensor, a: Te
                  b1_grad: Tensor | None, w2_grad: Tensor | None, b2_grad: Tensor | None, has_b1: bool, has_b2: bool,
                  need_dx: bool) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor]:
     from .gemm import gemm_reference
-    from .linear import bias_grad_into, weight_grad_into
+    from .linear import param_grads_into
 
     dy = dy.contiguous()
     mm = gemm if _kernels(dy) else gemm_reference
     dz = mm(dy, w2, b_mn=True, epi=EPI_MUL, aux=g)
-    dw2 = weight_grad_into(dy, a, w2, w2_grad)
-    db2 = bias_grad_into(dy, b2_grad, w2.dtype) if has_b2 else None
+    dw2, db2 = param_grads_into(dy, a, w2, w2_grad, b2_grad, True, has_b2)
     dx = mm(dz, w1, b_mn=True) if need_dx else dy.new_empty(_EMPTY)
-    dw1 = weight_grad_into(dz, x, w1, w1_grad)
-    db1 = bias_grad_into(dz, b1_grad, w1.dtype) if has_b1 else None
+    dw1, db1 = param_grads_into(dz, x, w1, w1_grad, b1_grad, True, has_b1)
     e = lambda t, like: t if t is not None else like.new_empty(_EMPTY)  # noqa: E731
     return dx, e(dw1, w1), e(db1, w1), e(dw2, w2), e(db2, w2)
 

@@ -68,6 +68,25 @@ def _bias_grad(dy: torch.Tensor, b: torch.Tensor | None) -> torch.Tensor | None:
     return bias_grad_into(dy, getattr(b, "main_grad", None), b.dtype)
 
 
+def param_grads_into(dy, x, w, w_main, b_main, want_w: bool = True, want_b: bool = True, b_dtype=None):
+    """(dW, db) of ``y = x·Wᵀ + b`` from ``dy``. With fp32 accumulation buffers for both, ONE launch produces them: the
+    weight-gradient GEMM also sums ``dy`` over the tokens on the tensor cores (no separate column-sum pass)."""
+    fused = (want_w and want_b and w_main is not None and b_main is not None and dy.is_cuda and dy.dtype == torch.bfloat16
+             and x.dtype == torch.bfloat16 and dy.dim() == 2 and b_main.is_contiguous())
+    if fused:
+        gemm(dy, x, a_mn=True, b_mn=True, out=w_main, accumulate=True, a_sum=b_main)
+        return None, None
+    dw = weight_grad_into(dy, x, w, w_main) if want_w else None
+    db = bias_grad_into(dy, b_main, b_dtype or w.dtype) if want_b else None
+    return dw, db
+
+
+def _param_grads(dy, x, w, b):
+    want_b = b is not None and b.requires_grad
+    return param_grads_into(dy, x, w, getattr(w, "main_grad", None), getattr(b, "main_grad", None) if want_b else None,
+                            w.requires_grad, want_b, b.dtype if b is not None else None)
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, b, residual):
@@ -82,8 +101,7 @@ class _Linear(torch.autograd.Function):
         x, w = ctx.saved_tensors
         dy = dy.contiguous()
         dx = gemm(dy, w, b_mn=True) if ctx.needs_input_grad[0] else None
-        dw = _weight_grad(dy, x, w) if w.requires_grad else None
-        db = _bias_grad(dy, ctx.bias_ref) if (ctx.has_bias and ctx.bias_ref.requires_grad) else None
+        dw, db = _param_grads(dy, x, w, ctx.bias_ref if ctx.has_bias else None)
         dres = dy if ctx.has_res else None
         return dx, dw, db, dres
 
@@ -103,7 +121,11 @@ def linear(
     if torch.compiler.is_compiling():
         from . import library
 
-        out = library.linear(x2, w, b, r2, getattr(w, "main_grad", None), None if b is None else getattr(b, "main_grad", None))
+        # No gradient buffers under a compiler: a buffer is a view at an offset inside the engine's flat fp32 storage, and an
+        # op that mutates such a graph input makes the compiler copy "its base" (offset + size elements, read from the
+        # view's own address: past the end of the storage). The parameter gradients come back as tensors instead and
+        # the engine's post-accumulate hook adds them to the buffers.
+        out = library.linear(x2, w, b, r2, None, None)
     else:
         out = _Linear.apply(x2, w, b, r2)
     return out.view(*lead, w.shape[0])
@@ -131,11 +153,9 @@ class _FFNGelu(torch.autograd.Function):
         b1, b2 = ctx.params
         dy = dy.contiguous()
         dz = gemm(dy, w2, b_mn=True, epi=EPI_MUL, aux=g)
-        dw2 = _weight_grad(dy, a, w2) if w2.requires_grad else None
-        db2 = _bias_grad(dy, b2) if (b2 is not None and b2.requires_grad) else None
+        dw2, db2 = _param_grads(dy, a, w2, b2)
         dx = gemm(dz, w1, b_mn=True) if ctx.needs_input_grad[0] else None
-        dw1 = _weight_grad(dz, x, w1) if w1.requires_grad else None
-        db1 = _bias_grad(dz, b1) if (b1 is not None and b1.requires_grad) else None
+        dw1, db1 = _param_grads(dz, x, w1, b1)
         return dx, dw1, db1, dw2, db2, (dy if ctx.has_res else None)
 
 
@@ -151,8 +171,7 @@ def ffn_gelu(x, w1, b1, w2, b2, residual=None):
     if torch.compiler.is_compiling():
         from . import library
 
-        mg = lambda t: None if t is None else getattr(t, "main_grad", None)  # noqa: E731
-        out = library.ffn_gelu(x2, w1, b1, w2, b2, r2, mg(w1), mg(b1), mg(w2), mg(b2))[0]
+        out = library.ffn_gelu(x2, w1, b1, w2, b2, r2, None, None, None, None)[0]  # no buffers: see linear()
     else:
         out = _FFNGelu.apply(x2, w1, b1, w2, b2, r2)
     return out.view(*lead, w2.shape[0])
@@ -209,9 +228,9 @@ class _LinearQKV(torch.autograd.Function):
         if dqkv.stride(1) != 1 or dqkv.stride(0) % 8 or dqkv.data_ptr() % 16:
             dqkv = dqkv.contiguous()
         dx = gemm(dqkv, _span3(wq, (3 * n, k)), b_mn=True) if ctx.needs_input_grad[0] else None
-        gemm(dqkv, x, a_mn=True, b_mn=True, out=_span3(wq.main_grad, (3 * n, k)), accumulate=True)
-        if ctx.bq is not None and ctx.bq.requires_grad:
-            colsum_into(dqkv, _span3(ctx.bq.main_grad, (3 * n,)))
+        want_b = ctx.bq is not None and ctx.bq.requires_grad
+        gemm(dqkv, x, a_mn=True, b_mn=True, out=_span3(wq.main_grad, (3 * n, k)), accumulate=True,
+             a_sum=_span3(ctx.bq.main_grad, (3 * n,)) if want_b else None)
         return dx, None, None
 
 

@@ -131,8 +131,8 @@ def _norm_apply(x2, weight, bias, eps: float, rms: bool, rk):
     if torch.compiler.is_compiling():
         from . import library
 
-        return library.norm(x2, weight, bias, rk, float(eps), rms, getattr(weight, "main_grad", None),
-                            None if bias is None else getattr(bias, "main_grad", None))[0]
+        # (no gradient buffers under a compiler: see ops/linear.py:linear)
+        return library.norm(x2, weight, bias, rk, float(eps), rms, None, None)[0]
     return _Norm.apply(x2, weight, bias, float(eps), rms, rk)
 
 

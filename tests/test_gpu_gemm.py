@@ -106,6 +106,29 @@ def test_gemm_fp32_accumulate_split_k():
     _lib.check_status()
 
 
+@pytest.mark.parametrize("M,N,K", [(768, 768, 16384), (3072, 768, 4096), (768, 3072, 2048), (200, 96, 1000), (2304, 768, 512),
+                                   (4000, 520, 192)])
+def test_weight_gradient_gemm_also_sums_its_first_operand(M, N, K):
+    """dW = dyᵀ·x with ``a_sum``: the bias gradient Σ_tokens dy comes out of the same launch, is added to what the
+    buffer held, and matches an fp32 column sum; covers split-K, both tile widths, ragged edges and several work
+    items per CTA (the single-buffer accumulator path)."""
+    torch.manual_seed(5)
+    dy = (torch.randn(K, M, device="cuda") * 0.5 + 0.1).to(torch.bfloat16)
+    x = torch.randn(K, N, device="cuda").to(torch.bfloat16)
+    w_acc = torch.randn(M, N, device="cuda")
+    b_acc = torch.randn(M, device="cuda")
+    w0, b0 = w_acc.clone(), b_acc.clone()
+    gemm(dy, x, a_mn=True, b_mn=True, out=w_acc, accumulate=True, a_sum=b_acc)
+    _lib.check_status()
+    ref_w = w0 + dy.float().t() @ x.float()
+    ref_b = b0 + dy.float().sum(0)
+    assert (w_acc - ref_w).abs().max().item() < 2e-3 * ref_w.abs().max().item() + 1e-3
+    assert (b_acc - ref_b).abs().max().item() < 1e-4 * ref_b.abs().max().item() + 1e-3
+    # a second call keeps accumulating (no hidden state between launches)
+    gemm(dy, x, a_mn=True, b_mn=True, out=w_acc, accumulate=True, a_sum=b_acc)
+    assert (b_acc - (ref_b + dy.float().sum(0))).abs().max().item() < 1e-4 * ref_b.abs().max().item() + 2e-3
+
+
 def test_gemm_batched_strided():
     torch.manual_seed(3)
     B, T, H, d, P = 3, 256, 4, 64, 512
