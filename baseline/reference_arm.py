@@ -92,8 +92,14 @@ def run_reference(args) -> dict:
     disc, gen = build_backbones(model_cfg=model_cfg, disc_config=disc_cfg, gen_config=gen_cfg)
     if model_cfg.gradient_checkpointing:  # as the reference's entrypoint does (training/entrypoint.py:505-510)
         for backbone in (disc, gen):
-            if hasattr(backbone, "gradient_checkpointing_enable"):
+            try:
                 backbone.gradient_checkpointing_enable()
+            except (TypeError, AttributeError):
+                # transformers >= 5 walks the tree with nn.Module.apply(fn), which the reference's RotaryEmbedding shadows
+                # with its own apply(q, k); the encoder's forward only reads this flag (modeling/rope_encoder.py:474-475)
+                for mod in backbone.modules():
+                    if hasattr(mod, "gradient_checkpointing"):
+                        mod.gradient_checkpointing = True
     model = DebertaV3RTDPretrainer(discriminator_backbone=disc, generator_backbone=gen, disc_config=disc_cfg,
                                    gen_config=gen_cfg, embedding_sharing="gdes", tie_generator_word_embeddings=True,
                                    additional_forbidden_token_ids=tok.all_special_ids).to(device)

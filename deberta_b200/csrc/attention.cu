@@ -103,19 +103,27 @@ __device__ __forceinline__ void store_bf16x16(__nv_bfloat16* dst, const uint32_t
 // --------------------------------------------------------------------------------------------
 // forward
 // --------------------------------------------------------------------------------------------
+// KT = keys per tile. 128: one CTA of 512 threads per SM. 64: 256 threads and ~67 KB, so two CTAs share an SM and
+// each one's barrier, TMEM and TMA latencies hide behind the other's arithmetic (short sequences give a CTA only a
+// few key tiles to pipeline over).
+template <int KT>
 struct FwdSmem {
+  static constexpr int kKVBytes = KT * kD * 2;        // one K or V tile
   static constexpr int kQ = 0;
   static constexpr int kK = kQ + kTileBytes;          // 2 buffers
-  static constexpr int kV = kK + 2 * kTileBytes;      // 2 buffers
-  static constexpr int kP = kV + 2 * kTileBytes;      // 128x128 bf16
-  static constexpr int kBar = kP + 2 * kTileBytes;
-  static constexpr int kMeta = kBar + 128;            // 128 ints of key metadata
-  static constexpr int kRed = kMeta + 512;            // 4 x 128 floats: per column-group row statistics
-  static constexpr int kLut = kRed + 2048;            // 2 * (2S-1) uint16
+  static constexpr int kV = kK + 2 * kKVBytes;        // 2 buffers
+  static constexpr int kP = kV + 2 * kKVBytes;        // 128 x KT bf16 in 64-key blocks of 16 KB
+  static constexpr int kBar = kP + (KT / 64) * kTileBytes;
+  static constexpr int kMeta = kBar + 128;            // KT ints of key metadata
+  static constexpr int kRed = kMeta + KT * 4;         // (KT / 32) x 128 floats: per column-group row statistics
+  static constexpr int kLut = kRed + (KT / 32) * 512; // 2 * (2S-1) uint16
   static int total(int S, bool pos) { return kLut + (pos ? 2 * (2 * S) * 2 : 0) + 1024; }
 };
 
-constexpr int kFwdThreads = 512;  // 16 warps: warp w owns rows of TMEM quadrant (w & 3), key columns 32*(w >> 2)...
+// warp w owns the rows of TMEM lane quadrant (w & 3) and the key columns 32 * (w >> 2) .. of a tile
+template <int KT>
+constexpr int fwd_threads() { return KT * 4; }
+
 
 __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -135,30 +143,48 @@ __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+      "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+      "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
 // Four threads share a query row (one per 32-key column group of the tile); the row maximum is
 // exchanged through shared memory, the running sum stays per thread until the end.
 // MASK: 0 = no mask (only the sequence end), 1 = key padding, 2 = document ids.
 // POS: 0 = content scores only, 1 = key-indexed bias tensor, 2 = gathers from the bucket-indexed tables.
-template <int MASK, int POS>
-__global__ void __launch_bounds__(kFwdThreads, 1)
+template <int MASK, int POS, int KT>
+__global__ void __launch_bounds__(KT * 4, KT == 64 ? 2 : 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnDev p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem + FwdSmem::kQ;
-  uint8_t* sK = smem + FwdSmem::kK;
-  uint8_t* sV = smem + FwdSmem::kV;
-  uint8_t* sP = smem + FwdSmem::kP;
-  uint64_t* bar_q = reinterpret_cast<uint64_t*>(smem + FwdSmem::kBar);
+  using L = FwdSmem<KT>;
+  constexpr int kThreads = KT * 4;
+  constexpr int kParts = KT / 32;          // column groups of a tile = threads per query row
+  constexpr int kOCols = kD / kParts;      // output columns a thread rescales and stores
+  constexpr int kKV = L::kKVBytes;
+  constexpr uint32_t kTmemCols = KT == 64 ? 128 : 256;
+  uint8_t* sQ = smem + L::kQ;
+  uint8_t* sK = smem + L::kK;
+  uint8_t* sV = smem + L::kV;
+  uint8_t* sP = smem + L::kP;
+  uint64_t* bar_q = reinterpret_cast<uint64_t*>(smem + L::kBar);
   uint64_t* bar_k = bar_q + 1;  // [2]
   uint64_t* bar_v = bar_q + 3;  // [2]
   uint64_t* bar_s = bar_q + 5;
   uint64_t* bar_o = bar_q + 6;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 7);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* kmeta = reinterpret_cast<int*>(smem + FwdSmem::kMeta);
-  float* red = reinterpret_cast<float*>(smem + FwdSmem::kRed);  // [4][128] row maxima / sums per column group
-  unsigned short* lutc = reinterpret_cast<unsigned short*>(smem + FwdSmem::kLut);
+  int* kmeta = reinterpret_cast<int*>(smem + L::kMeta);
+  float* red = reinterpret_cast<float*>(smem + L::kRed);  // [kParts][128] row maxima / sums per column group
+  unsigned short* lutc = reinterpret_cast<unsigned short*>(smem + L::kLut);
   unsigned short* lutp = lutc + 2 * p.S;
 
   const int tid = threadIdx.x;
@@ -172,7 +198,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int b = blockIdx.z;
   const int S = p.S;
   int jb = 0, nkt = (S + kTile - 1) / kTile;  // first key tile and number of key tiles this CTA visits
-  if (MASK == 2) doc_tile_run(p.doc_tiles, b, nkt, blockIdx.x, lane, jb, nkt);
+  if (MASK == 2) doc_tile_run(p.doc_tiles, b, nkt, blockIdx.x, lane, jb, nkt);  // in 128-token tiles
+  if (KT == 64) {
+    jb *= 2;
+    nkt = min(nkt * 2, (S + KT - 1) / KT - jb);
+  }
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
@@ -186,11 +216,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     fence_barrier_init();
   }
   if (warp == 0) {
-    tmem_alloc(tmem_slot, 256);
+    tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
   }
   if (POS == 2) {
-    for (int i = tid; i < 2 * S - 1; i += kFwdThreads) {
+    for (int i = tid; i < 2 * S - 1; i += kThreads) {
       lutc[i] = p.lut_c2p[i];
       lutp[i] = p.lut_p2c[i];
     }
@@ -199,8 +229,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t t_s = tmem_base;          // 128 columns: scores
-  const uint32_t t_o = tmem_base + 128;    // 64 columns: output accumulator
+  const uint32_t t_s = tmem_base;          // KT columns: scores
+  const uint32_t t_o = tmem_base + KT;     // 64 columns: output accumulator
   const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
 
   if (tid == 0) {
@@ -209,15 +239,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tma_prefetch_desc(&tm_v);
     mbar_expect_tx(bar_q, kTileBytes);
     tma_load_3d(sQ, &tm_q, bar_q, h * kD, q0, b);
-    mbar_expect_tx(&bar_k[0], kTileBytes);
-    tma_load_3d(sK, &tm_k, &bar_k[0], h * kD, jb * kTile, b);
-    mbar_expect_tx(&bar_v[0], kTileBytes);
-    tma_load_3d(sV, &tm_v, &bar_v[0], h * kD, jb * kTile, b);
+    mbar_expect_tx(&bar_k[0], kKV);
+    tma_load_3d(sK, &tm_k, &bar_k[0], h * kD, jb * KT, b);
+    mbar_expect_tx(&bar_v[0], kKV);
+    tma_load_3d(sV, &tm_v, &bar_v[0], h * kD, jb * KT, b);
     if (nkt > 1) {  // second tile of K and V straight away: both buffers start empty
-      mbar_expect_tx(&bar_k[1], kTileBytes);
-      tma_load_3d(sK + kTileBytes, &tm_k, &bar_k[1], h * kD, (jb + 1) * kTile, b);
-      mbar_expect_tx(&bar_v[1], kTileBytes);
-      tma_load_3d(sV + kTileBytes, &tm_v, &bar_v[1], h * kD, (jb + 1) * kTile, b);
+      mbar_expect_tx(&bar_k[1], kKV);
+      tma_load_3d(sK + kKV, &tm_k, &bar_k[1], h * kD, (jb + 1) * KT, b);
+      mbar_expect_tx(&bar_v[1], kKV);
+      tma_load_3d(sV + kKV, &tm_v, &bar_v[1], h * kD, (jb + 1) * KT, b);
     }
   }
 
@@ -237,7 +267,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                                          p.bias + ((static_cast<long long>(b) * p.heads + h) * S + (q_valid ? q : 0)) * p.ldb)
                                    : nullptr;
 
-  constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+  constexpr uint32_t idesc_s = make_idesc_bf16(128, KT, false, false);
   constexpr uint32_t idesc_o = make_idesc_bf16(128, 64, false, true);
   bool ok = true;
 
@@ -259,14 +289,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint4 bias_pf[4] = {};
   if (POS == 1) {
 #pragma unroll
-    for (int g = 0; g < 4; ++g) bias_pf[g] = __ldg(bias_row + ((jb * kTile + part * 32) >> 3) + g);
+    for (int g = 0; g < 4; ++g) bias_pf[g] = __ldg(bias_row + ((jb * KT + part * 32) >> 3) + g);
   }
   for (int j = 0; j < nkt; ++j) {  // j counts visited tiles (buffers and barrier phases follow it)
-    const int k0 = (jb + j) * kTile;
+    const int k0 = (jb + j) * KT;
     bool tile_all_keep = false;
     if (MASK != 0) {
       int tile_meta = 1;
-      if (tid < kTile) {  // key metadata of this tile: 0 = masked, otherwise doc id (or 1)
+      if (tid < KT) {  // key metadata of this tile: 0 = masked, otherwise doc id (or 1)
         const int kk = k0 + tid;
         int meta = 0;
         if (kk < S) {
@@ -307,7 +337,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       if (j + 1 < nkt) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) bias_pf[g] = __ldg(bias_row + ((kb + kTile) >> 3) + g);
+        for (int g = 0; g < 4; ++g) bias_pf[g] = __ldg(bias_row + ((kb + KT) >> 3) + g);
       }
     } else if (POS == 2) {
       const int dbase = q - kb + S - 1;  // lut index for the first key
@@ -323,7 +353,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
     if (MASK == 0) {
-      if (k0 + kTile > S) {  // last, partial tile (block-uniform)
+      if (k0 + KT > S) {  // last, partial tile (block-uniform)
 #pragma unroll
         for (int k = 0; k < 32; ++k) s[k] = (kb + k < S) ? s[k] : -INFINITY;
       }
@@ -345,7 +375,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int nb = (j + 1) & 1;
       if (mbar_wait(&bar_k[nb], ((j + 1) >> 1) & 1, abort_flag, p.status, kErrFullWait)) {
         tc_fence_after();
-        const uint32_t kb2 = smem_u32(sK + nb * kTileBytes);
+        const uint32_t kb2 = smem_u32(sK + nb * kKV);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           umma_bf16(t_s, make_smem_desc(smem_u32(sQ) + ks * 32, 16, 1024), make_smem_desc(kb2 + ks * 32, 16, 1024),
@@ -353,7 +383,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       umma_commit(bar_s);
     }
-    tmax = fmaxf(fmaxf(red[row], red[kTile + row]), fmaxf(red[2 * kTile + row], red[3 * kTile + row]));
+    tmax = fmaxf(red[row], red[kTile + row]);
+    if (kParts == 4) tmax = fmaxf(tmax, fmaxf(red[2 * kTile + row], red[3 * kTile + row]));
     const float m_new = fmaxf(m_run, tmax);  // running maximum of the unscaled scores
     const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
     const float alpha = (m_run == -INFINITY) ? 0.f : ex2((m_run - m_use) * p.scale_log2);
@@ -371,22 +402,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (j > 0) {
       got_o = __all_sync(0xffffffffu, mbar_wait(bar_o, (j - 1) & 1, abort_flag, p.status, kErrAccFullWait));
       tc_fence_after();
-      // rescale the running output (16 of its 64 columns per thread) when a row of this warp raised its maximum
+      // rescale the running output (this thread's share of its 64 columns) when a row of this warp raised its maximum
       if (got_o && __any_sync(0xffffffffu, alpha != 1.f)) {
-        uint32_t r[16];
-        tmem_ld_32x32b_x16(t_o + lane_addr + part * 16, r);
+        uint32_t r[kOCols];
+        if constexpr (kOCols == 16) tmem_ld_32x32b_x16(t_o + lane_addr + part * kOCols, r);
+        else tmem_ld_32x32b_x32(t_o + lane_addr + part * kOCols, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-        tmem_st_32x32b_x16(t_o + lane_addr + part * 16, r);
+        for (int i = 0; i < kOCols; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+        if constexpr (kOCols == 16) tmem_st_32x32b_x16(t_o + lane_addr + part * kOCols, r);
+        else tmem_st_32x32b_x32(t_o + lane_addr + part * kOCols, r);
         tmem_st_wait();
       }
     }
     if (tid == 0 && j > 0 && j + 1 < nkt) {
       // P·V of tile j-1 and the scores of tile j have retired: buffer (j+1)&1 of V and of K is free for tile j+1
       const int nb = (j + 1) & 1;
-      mbar_expect_tx(&bar_v[nb], kTileBytes);
-      tma_load_3d(sV + nb * kTileBytes, &tm_v, &bar_v[nb], h * kD, k0 + kTile, b);
+      mbar_expect_tx(&bar_v[nb], kKV);
+      tma_load_3d(sV + nb * kKV, &tm_v, &bar_v[nb], h * kD, k0 + KT, b);
     }
     // this thread's 32 probabilities: 4 chunks of 8 bf16 in 64-key block (part >> 1)
 #pragma unroll
@@ -404,17 +437,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (tid == 0) {
       const bool v_ok = mbar_wait(&bar_v[j & 1], (j >> 1) & 1, abort_flag, p.status, kErrFullWait);
       tc_fence_after();
-      const uint32_t pv = smem_u32(sV + (j & 1) * kTileBytes);
+      const uint32_t pv = smem_u32(sV + (j & 1) * kKV);
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
+      for (int ks = 0; ks < KT / 16; ++ks) {
         if (!v_ok) break;
         umma_bf16(t_o, make_smem_desc(smem_u32(sP) + (ks >> 2) * kTileBytes + (ks & 3) * 32, 16, 1024),
                   make_smem_desc(pv + ks * 2048, 8192, 1024), idesc_o, (j > 0) || (ks > 0));
       }
       umma_commit(bar_o);
       if (j + 2 < nkt) {  // K buffer j&1 was read by the scores of tile j (retired before this tile's softmax ended)
-        mbar_expect_tx(&bar_k[j & 1], kTileBytes);
-        tma_load_3d(sK + (j & 1) * kTileBytes, &tm_k, &bar_k[j & 1], h * kD, k0 + 2 * kTile, b);
+        mbar_expect_tx(&bar_k[j & 1], kKV);
+        tma_load_3d(sK + (j & 1) * kKV, &tm_k, &bar_k[j & 1], h * kD, k0 + 2 * KT, b);
       }
     }
   }
@@ -423,19 +456,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   red[part * kTile + row] = l_part;
   __syncthreads();
-  const float l_run = red[row] + red[kTile + row] + red[2 * kTile + row] + red[3 * kTile + row];
+  float l_run = red[row] + red[kTile + row];
+  if (kParts == 4) l_run += red[2 * kTile + row] + red[3 * kTile + row];
   if (ok && mbar_wait(bar_o, (nkt - 1) & 1, abort_flag, p.status, kErrAccFullWait)) {
     tc_fence_after();
     const float inv = (q_live && l_run > 0.f) ? 1.f / l_run : 0.f;
-    __nv_bfloat16* o = p.out + tq * p.ldo + h * kD + part * 16;
-    uint32_t r[16];
-    tmem_ld_32x32b_x16(t_o + lane_addr + part * 16, r);
+    __nv_bfloat16* o = p.out + tq * p.ldo + h * kD + part * kOCols;
+    uint32_t r[kOCols];
+    if constexpr (kOCols == 16) tmem_ld_32x32b_x16(t_o + lane_addr + part * kOCols, r);
+    else tmem_ld_32x32b_x32(t_o + lane_addr + part * kOCols, r);
     tmem_ld_wait();
     if (q_valid) {
-      uint32_t w[8];
+      uint32_t w[kOCols / 2];
 #pragma unroll
-      for (int g = 0; g < 8; ++g) w[g] = pack_bf16(__uint_as_float(r[2 * g]) * inv, __uint_as_float(r[2 * g + 1]) * inv);
+      for (int g = 0; g < kOCols / 2; ++g)
+        w[g] = pack_bf16(__uint_as_float(r[2 * g]) * inv, __uint_as_float(r[2 * g + 1]) * inv);
       store_bf16x16(o, w);
+      if constexpr (kOCols == 32) store_bf16x16(o + 16, w + 8);
     }
     if (q_valid && part == 0 && p.lse)
       p.lse[(static_cast<long long>(b) * p.heads + h) * S + q] =
@@ -445,7 +482,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -871,10 +908,13 @@ attn_doc_tiles_kernel(const int* __restrict__ doc_ids, int* __restrict__ tiles, 
   }
 }
 
-int make_head_map(CUtensorMap* m, const void* ptr, const AttnArgs* a, long long ld) {
+int make_head_map(CUtensorMap* m, const void* ptr, const AttnArgs* a, long long ld, int box_rows = kTile) {
   return db200_make_tmap_bf16(m, ptr, static_cast<long long>(a->heads) * kD, a->S, a->B, ld,
-                              static_cast<long long>(a->S) * ld, kTile);
+                              static_cast<long long>(a->S) * ld, box_rows);
 }
+
+// Keys per tile of the forward kernel: 64 (two 256-thread CTAs per SM) or 128 (one 512-thread CTA).
+int g_fwd_key_tile = 64;
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -890,9 +930,10 @@ extern "C" int db200_attn_fwd(const AttnArgs* a, void* stream_) {
   if (pos && (a->S > 4096 || a->span2 > 65535 || !a->lut_c2p || !a->lut_p2c)) return -12;
   CUtensorMap tq, tk, tv;
   int rc;
+  const int kt = g_fwd_key_tile == 128 ? 128 : 64;
   if ((rc = make_head_map(&tq, a->q, a, a->ldq))) return rc;
-  if ((rc = make_head_map(&tk, a->k, a, a->ldk))) return rc;
-  if ((rc = make_head_map(&tv, a->v, a, a->ldv))) return rc;
+  if ((rc = make_head_map(&tk, a->k, a, a->ldk, kt))) return rc;
+  if ((rc = make_head_map(&tv, a->v, a, a->ldv, kt))) return rc;
   AttnDev d{};
   d.B = a->B; d.S = a->S; d.heads = a->heads; d.span2 = a->span2;
   d.scale_log2 = 1.4426950408889634f / a->scale;
@@ -913,23 +954,27 @@ extern "C" int db200_attn_fwd(const AttnArgs* a, void* stream_) {
   d.status = db200_status_ptr();
   const int pos_mode = d.bias ? 1 : (pos ? 2 : 0);
   const int mask_mode = d.doc_ids ? 2 : (d.key_keep ? 1 : 0);
-  const int smem = FwdSmem::total(a->S, pos_mode == 2);
+  const int wide = kt == 128 ? 1 : 0;
+  const int smem = wide ? FwdSmem<128>::total(a->S, pos_mode == 2) : FwdSmem<64>::total(a->S, pos_mode == 2);
   using FwdKernel = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, AttnDev);
-  static const FwdKernel kernels[3][3] = {
-      {attn_fwd_kernel<0, 0>, attn_fwd_kernel<0, 1>, attn_fwd_kernel<0, 2>},
-      {attn_fwd_kernel<1, 0>, attn_fwd_kernel<1, 1>, attn_fwd_kernel<1, 2>},
-      {attn_fwd_kernel<2, 0>, attn_fwd_kernel<2, 1>, attn_fwd_kernel<2, 2>}};
-  static int configured[16][3][3] = {};  // per device: the opt-in to large shared memory is a per-device attribute
+  static const FwdKernel kernels[2][3][3] = {
+      {{attn_fwd_kernel<0, 0, 64>, attn_fwd_kernel<0, 1, 64>, attn_fwd_kernel<0, 2, 64>},
+       {attn_fwd_kernel<1, 0, 64>, attn_fwd_kernel<1, 1, 64>, attn_fwd_kernel<1, 2, 64>},
+       {attn_fwd_kernel<2, 0, 64>, attn_fwd_kernel<2, 1, 64>, attn_fwd_kernel<2, 2, 64>}},
+      {{attn_fwd_kernel<0, 0, 128>, attn_fwd_kernel<0, 1, 128>, attn_fwd_kernel<0, 2, 128>},
+       {attn_fwd_kernel<1, 0, 128>, attn_fwd_kernel<1, 1, 128>, attn_fwd_kernel<1, 2, 128>},
+       {attn_fwd_kernel<2, 0, 128>, attn_fwd_kernel<2, 1, 128>, attn_fwd_kernel<2, 2, 128>}}};
+  static int configured[16][2][3][3] = {};  // per device: the opt-in to large shared memory is a per-device attribute
   int dev = 0;
   cudaGetDevice(&dev);
   dev = (dev >= 0 && dev < 16) ? dev : 0;
-  const FwdKernel kern = kernels[mask_mode][pos_mode];
-  if (configured[dev][mask_mode][pos_mode] < smem) {
+  const FwdKernel kern = kernels[wide][mask_mode][pos_mode];
+  if (configured[dev][wide][mask_mode][pos_mode] < smem) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
-    configured[dev][mask_mode][pos_mode] = smem;
+    configured[dev][wide][mask_mode][pos_mode] = smem;
   }
   dim3 grid((a->S + kTile - 1) / kTile, a->heads, a->B);
-  kern<<<grid, kFwdThreads, smem, stream>>>(tq, tk, tv, d);
+  kern<<<grid, kt * 4, smem, stream>>>(tq, tk, tv, d);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -1011,4 +1056,11 @@ extern "C" int db200_attn_doc_tiles(const void* doc_ids, void* tiles, int B, int
   attn_doc_tiles_kernel<<<grid, kTile, 0, reinterpret_cast<cudaStream_t>(stream)>>>(static_cast<const int*>(doc_ids),
                                                                                    static_cast<int*>(tiles), S);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// 64 or 128 keys per tile in the forward kernel (anything else selects 64); returns the previous value.
+extern "C" int db200_attn_set_fwd_key_tile(int keys) {
+  const int old = g_fwd_key_tile;
+  g_fwd_key_tile = keys == 128 ? 128 : 64;
+  return old;
 }

@@ -807,6 +807,18 @@ ce_combine_kernel(const float* __restrict__ part, const float* __restrict__ labe
   }
 }
 
+// Load the code of the cross-entropy forward path (both tile widths and the combine kernel) on the current device
+// without launching anything: under CUDA's lazy module loading a kernel's code reaches the device on first use, and
+// that is a device-memory request made by the driver. Callers that must not cause one later call this at start-up.
+extern "C" int db200_gemm_preload_ce(void) {
+  cudaFuncAttributes attr;
+  if (cudaFuncGetAttributes(&attr, gemm_kernel<256, false, false, 4>) != cudaSuccess) return -3;
+  if (cudaFuncGetAttributes(&attr, gemm_kernel<128, false, false, 4>) != cudaSuccess) return -3;
+  if (cudaFuncGetAttributes(&attr, ce_combine_kernel) != cudaSuccess) return -3;
+  (void)num_sms();
+  return get_encode_fn() ? 0 : -1;
+}
+
 extern "C" int db200_ce_combine(const float* part, const float* label_logit, int tiles_n, int M, float* lse,
                                 float* loss_rows, long long* sampled, void* stream) {
   if (M <= 0) return 0;

@@ -46,6 +46,7 @@ typedef struct GemmArgs {
 } GemmArgs;
 
 int db200_gemm_bf16(const GemmArgs* args, void* stream);
+int db200_gemm_preload_ce(void);  // loads the EPI_CE_FWD kernels and db200_ce_combine's kernel on the current device, launches nothing
 int db200_gemm_tile_n(int N);  // width of the vocabulary range one EPI_CE_FWD partial covers
 int db200_ce_combine(const float* part, const float* label_logit, int tiles_n, int M, float* lse, float* loss_rows,
                      long long* sampled, void* stream);

@@ -31,6 +31,11 @@ float* scratch_for_current_device() {
 
 }  // namespace
 
+extern "C" int db200_noalloc_prepare(void) {
+  if (!scratch_for_current_device()) return DB200_NOALLOC_NO_DEVICE;
+  return db200_gemm_preload_ce() == 0 ? DB200_NOALLOC_OK : DB200_NOALLOC_NO_DEVICE;
+}
+
 extern "C" int db200_vocab_ce_forward_noalloc(const void* x, const void* weight, const void* bias,
                                               const long long* labels, const unsigned char* forbidden, int rows,
                                               int vocab, int hidden, float temperature, unsigned long long seed,

@@ -2,9 +2,9 @@
 // This entry point has no counterpart in the reference implementation.
 //
 // Who it is for: code that calls this library from a place where device memory cannot be
-// requested — a host function enqueued on a stream (cudaLaunchHostFunc callbacks must not call
-// the allocator), a real-time serving loop that runs on a memory plan fixed at start-up, or an
-// embedding application whose allocator this library must not touch. The regular entry point
+// requested: a real-time serving loop that runs on a memory plan fixed at start-up, an embedding
+// application whose allocator this library must not touch, a latency-critical section that cannot
+// afford the device-wide synchronisation a cudaMalloc or cudaFree may imply. The regular entry point
 // (db200_gemm_bf16 with EPI_CE_FWD followed by db200_ce_combine) needs a caller-provided scratch
 // buffer of 4 * ceil(vocab / tile) * rows + rows floats; callers like the ones above often have
 // nowhere to get one from. Here the scratch lives inside the library instead.
@@ -19,11 +19,18 @@
 // whose kernels overlap on the GPU (different streams without ordering, or two host threads)
 // race on the scratch and produce garbage: order them.
 //
-// Set-up: the first call on each device looks up the device address of the array (the host-side
-// name of a __device__ array is not a device pointer) and caches it; that first call should be
-// made before any stream capture begins. The caches are plain variables: make the first call on
-// a device from one host thread (later calls only read them). No call allocates or frees memory,
-// neither through the CUDA runtime nor through any library.
+// Set-up, once per device, from a place where device memory may still be requested: db200_noalloc_prepare().
+// It looks up the device address of the array (the host-side name of a __device__ array is not a device pointer),
+// caches it, and loads the kernels of this path. Both are moments at which the CUDA driver itself takes device
+// memory: with lazy module loading (the default since CUDA 12) a library's device image, the scratch array in it and
+// each kernel's code reach the GPU on first use, not when the library is opened; measured on a B200, free device
+// memory drops by 34 MiB (the array, rounded up by the driver) at the first use. An entry-point call on a device that
+// was not prepared does the same set-up itself, so that first call is NOT allocation-free. Make the set-up from one
+// host thread (the caches are plain variables; later calls only read them).
+// After the set-up no call allocates or frees device memory, neither through the CUDA runtime nor through any
+// library, and the driver has nothing left to load for it. (Host side: a thread's first GEMM launch creates that
+// thread's table of encoded tensor maps, about 600 KB of heap; db200_noalloc_prepare() on the same thread does not
+// cover it, a first call does.)
 #pragma once
 
 #ifdef __cplusplus
@@ -47,6 +54,9 @@ int db200_vocab_ce_forward_noalloc(const void* x, const void* weight, const void
                                    const unsigned char* forbidden, int rows, int vocab, int hidden, float temperature,
                                    unsigned long long seed, float* lse, float* loss_rows, long long* sampled,
                                    void* stream);
+
+// One-time set-up on the current device (see above). Idempotent; returns DB200_NOALLOC_OK or DB200_NOALLOC_NO_DEVICE.
+int db200_noalloc_prepare(void);
 
 // Human-readable text for the codes above (and for the launcher codes passed through unchanged).
 const char* db200_noalloc_strerror(int code);

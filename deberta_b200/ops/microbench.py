@@ -65,15 +65,21 @@ def bench_attention(a) -> None:
     H = h * 64
     q, k, v = (_rand(a.batch, a.seq, H, grad=True) for _ in range(3))
     pk, pq = (_rand(2 * span, H, grad=True) for _ in range(2))
+    from deberta_b200.ops.attention_cuda import set_forward_key_tile
+
     kw = dict(heads=h, scale_factor=3, bucket_size=256, max_position=512, att_span=span)
-    for name, pkk, pqq in (("content only", None, None), ("disentangled", pk, pq)):
-        f = lambda: disentangled_attention(q, k, v, pkk, pqq, **kw)  # noqa: E731
-        g = torch.randn_like(f())
-        fwd = _time(f, a.iters)
-        both = _time(lambda: f().backward(g), a.iters)
-        flops = 4 * a.batch * h * a.seq * a.seq * 64
-        print(f"attention [{name}] B={a.batch} S={a.seq} h={h}: fwd {fwd:.0f} us ({flops / fwd / 1e6:.0f} TFLOP/s), "
-              f"fwd+bwd {both:.0f} us")
+    for tile in ((64, 128) if a.key_tile == 0 else (a.key_tile,)):
+        set_forward_key_tile(tile)
+        for name, pkk, pqq in (("content only", None, None), ("disentangled", pk, pq)):
+            f = lambda: disentangled_attention(q, k, v, pkk, pqq, **kw)  # noqa: E731
+            g = torch.randn_like(f())
+            with torch.no_grad():
+                fwd = _time(f, a.iters)
+            both = _time(lambda: f().backward(g), a.iters)
+            flops = 4 * a.batch * h * a.seq * a.seq * 64
+            print(f"attention [{name}, {tile} keys per tile] B={a.batch} S={a.seq} h={h}: fwd {fwd:.0f} us "
+                  f"({flops / fwd / 1e6:.0f} TFLOP/s), fwd+bwd {both:.0f} us")
+    set_forward_key_tile(64)
 
 
 def bench_posbias(a) -> None:
@@ -142,6 +148,7 @@ def main() -> None:
     p.add_argument("--seq", type=int, default=512)
     p.add_argument("--heads", type=int, default=12)
     p.add_argument("--iters", type=int, default=5)
+    p.add_argument("--key-tile", type=int, default=0, help="attention forward: 64 or 128 keys per tile (0: both)")
     a = p.parse_args()
     {"gemm": bench_gemm, "ffn": bench_ffn, "attention": bench_attention, "posbias": bench_posbias, "vocab_ce": bench_vocab_ce, "layer": bench_layer}[a.op](a)
 

@@ -12,6 +12,16 @@ from deberta_b200.ops.attention import (disentangled_attention, disentangled_att
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=[64, 128], ids=["kt64", "kt128"])
+def forward_key_tile(request):
+    """Every case runs on both forward kernels: 64 keys per tile (two CTAs per SM) and 128 (one CTA per SM)."""
+    from deberta_b200.ops.attention_cuda import set_forward_key_tile
+
+    old = set_forward_key_tile(request.param)
+    yield request.param
+    set_forward_key_tile(old)
+
+
 def _rel_err(got, ref):
     return (got.float() - ref.float()).abs().max().item() / (ref.float().abs().max().item() + 1e-6)
 
