@@ -220,7 +220,11 @@ def run_reference(args) -> dict:
         "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic packed Zipf(1.1) token streams, random-init weights", "impl": "reference",
-        "config": {"model": f"deberta-v3-{args.model_size} RTD (reference modules, eager, bf16 autocast)",
+        "config": {"model": ((f"deberta-v3-{args.model_size} RTD" if getattr(args, "backbone", "hf_deberta_v2") == "hf_deberta_v2"
+                              else f"rope RTD ({getattr(args, 'rope_ffn', 'mlp')} FFN"
+                                   + (", activation checkpointing" if getattr(args, "grad_ckpt", False) else "") + ")")
+                             + " (reference modules, eager, bf16 autocast)"),
+                   "preset": getattr(args, "preset", None), "mean_doc_len": getattr(args, "mean_doc_len", 60),
                    "global_batch": args.micro_batch * args.ga * world, "micro_batch": args.micro_batch,
                    "grad_accum": args.ga, "seq_len": args.seq_len, "block_cross_document_attention": block_docs,
                    "parallelism": f"ddp{world}",

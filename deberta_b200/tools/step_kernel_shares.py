@@ -3,11 +3,13 @@
 Usage::
 
     python -m deberta_b200.tools.step_kernel_shares [--backbone hf_deberta_v2|rope] [--model-size base] [--seq-len 512]
-        [--micro-batch 32] [--ga 2] [--top 40]
+        [--micro-batch 32] [--ga 2] [--top 40] [--callers]
 
 Builds the RTD pretrainer from the config defaults on synthetic packed data, runs three warm-up windows, profiles the
 fourth and prints, per kernel name, the launch count, total and mean device time and the share of the window. The
-shares say where a step spends its time; absolute times under the profiler are not benchmark numbers. The reference
+shares say where a step spends its time; absolute times under the profiler are not benchmark numbers. ``--callers``
+also lists the ATen operators that launched kernels (fills, adds, copies: what is left outside the library's own
+kernels) with the line of this package that called each of them. The reference
 has no counterpart (it ships no profiling hooks; its closest tool is ``tools/compile_drift_probe.py:363-366``, which
 times whole steps).
 """
@@ -60,6 +62,7 @@ def main(argv: list[str] | None = None) -> int:
     p.add_argument("--micro-batch", type=int, default=32)
     p.add_argument("--ga", type=int, default=2)
     p.add_argument("--top", type=int, default=40)
+    p.add_argument("--callers", action="store_true", help="attribute ATen kernels to the package line that launched them")
     a = p.parse_args(argv)
     if not torch.cuda.is_available():
         print("step_kernel_shares needs a CUDA device")
@@ -81,7 +84,10 @@ def main(argv: list[str] | None = None) -> int:
     for _ in range(3):
         trainer.train_window(window)
     torch.cuda.synchronize()
-    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+    extra = {}
+    if a.callers:  # Python stacks are only recorded with the verbose collector
+        extra = dict(with_stack=True, experimental_config=torch._C._profiler._ExperimentalConfig(verbose=True))
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU], **extra) as prof:
         trainer.train_window(window)
         torch.cuda.synchronize()
     agg: dict[str, list[float]] = collections.defaultdict(lambda: [0, 0.0])
@@ -95,6 +101,19 @@ def main(argv: list[str] | None = None) -> int:
     print(f"window of {a.ga} micro-batches ({a.micro_batch} x {a.seq_len}): {total / 1e3:.1f} ms of device time over {launches} launches")
     for name, (n, t) in sorted(agg.items(), key=lambda kv: -kv[1][1])[: a.top]:
         print(f"{t / total * 100:5.1f} %  {t / 1e3:8.2f} ms  n={int(n):5d}  mean {t / n:8.1f} us  {name}")
+    if a.callers:
+        rows: dict[tuple[str, str], list[float]] = collections.defaultdict(lambda: [0, 0.0])
+        for ev in prof.key_averages(group_by_stack_n=24):
+            if not ev.key.startswith("aten::") or ev.self_device_time_total <= 0:
+                continue
+            site = next((f.strip() for f in ev.stack if "deberta_b200" in f and "step_kernel_shares" not in f),
+                        "(autograd engine or outside the package)")
+            slot = rows[(ev.key, site[-110:])]
+            slot[0] += ev.count
+            slot[1] += ev.self_device_time_total
+        print("ATen operators that launched kernels, by calling line:")
+        for (op, site), (n, t) in sorted(rows.items(), key=lambda kv: -kv[1][1])[: a.top]:
+            print(f"{t / 1e3:8.2f} ms  n={int(n):5d}  {op:28s} {site}")
     ctx.shutdown()
     return 0
 
