@@ -72,6 +72,8 @@ def parse_args() -> argparse.Namespace:
                    help="one of the secondary benchmark configurations (sets the flags above)")
     p.add_argument("--curve", type=int, default=0,
                    help="instead of timing: train this many steps at a fixed seed and print the loss curve (JSON)")
+    p.add_argument("--no-dependent-launch", action="store_true",
+                   help="launch every kernel the ordinary way (A/B switch for programmatic dependent launch)")
     args = p.parse_args()
     if args.preset:
         for k, v in PRESETS[args.preset].items():
@@ -223,6 +225,8 @@ def run_ours(args: argparse.Namespace) -> dict:
     ctx = init_distributed()
     if ctx.device.type != "cuda":
         raise SystemExit("bench.py needs a CUDA device")
+    if getattr(args, "no_dependent_launch", False):
+        _lib.set_dependent_launch(False)
     cfg = build_config(args)
     torch.manual_seed(1234)
     tok = build_tokenizer(cfg.model)
@@ -243,7 +247,7 @@ def run_ours(args: argparse.Namespace) -> dict:
         return curve_report(args, "ours", [v[0] for v in vals], [v[1] for v in vals], ctx.world_size) if ctx.is_main_process else {}
     host = synthetic_batches(args.ga, args.micro_batch, args.seq_len, seed=100 + ctx.rank, pin=True,
                              block_docs=getattr(args, "block_docs", False), mean_doc_len=args.mean_doc_len)
-    dev = [{k: v.to(ctx.device) for k, v in b.items()} for b in host]
+    dev = [trainer.stage_batch(b) for b in host]  # device-resident inputs with their host-side token counts attached
     tokens_per_step = args.ga * args.micro_batch * args.seq_len
     h2d = sum(v.numel() * v.element_size() for b in host for v in b.values())
 

@@ -197,12 +197,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int S = p.S;
-  int jb = 0, nkt = (S + kTile - 1) / kTile;  // first key tile and number of key tiles this CTA visits
-  if (MASK == 2) doc_tile_run(p.doc_tiles, b, nkt, blockIdx.x, lane, jb, nkt);  // in 128-token tiles
-  if (KT == 64) {
-    jb *= 2;
-    nkt = min(nkt * 2, (S + KT - 1) / KT - jb);
-  }
+  pdl_launch_dependents();
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
@@ -218,6 +213,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (warp == 0) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
+  }
+  pdl_wait();  // shared memory, barriers and TMEM are set up; everything below may touch global memory
+  int jb = 0, nkt = (S + kTile - 1) / kTile;  // first key tile and number of key tiles this CTA visits
+  if (MASK == 2) doc_tile_run(p.doc_tiles, b, nkt, blockIdx.x, lane, jb, nkt);  // in 128-token tiles
+  if (KT == 64) {
+    jb *= 2;
+    nkt = min(nkt * 2, (S + KT - 1) / KT - jb);
   }
   if (POS == 2) {
     for (int i = tid; i < 2 * S - 1; i += kThreads) {
@@ -565,8 +567,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int S = p.S;
-  int ib = 0, nqt = (S + kTile - 1) / kTile;  // first query tile and number of query tiles this CTA visits
-  if (MASK == 2) doc_tile_run(p.doc_tiles, b, nqt, blockIdx.x, lane, ib, nqt);
+  pdl_launch_dependents();
 
   if (tid == 0) {
     mbar_init(bar_kv, 1);
@@ -582,6 +583,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
+  pdl_wait();  // set-up done; everything below may touch global memory
+  int ib = 0, nqt = (S + kTile - 1) / kTile;  // first query tile and number of query tiles this CTA visits
+  if (MASK == 2) doc_tile_run(p.doc_tiles, b, nqt, blockIdx.x, lane, ib, nqt);
   if (POS == 2) {
     for (int i = tid; i < 2 * S - 1; i += kBwdThreads) {
       lutc[i] = p.lut_c2p[i];
@@ -855,6 +859,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, long long ld_do, const __nv_bfloat16* __restrict__ out,
                   long long ldo, float* __restrict__ delta, int B, int S, int heads) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long gid = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
   const long long pair = gid >> 3;  // (token, head)
   const int sub = static_cast<int>(gid & 7);
@@ -974,8 +980,7 @@ extern "C" int db200_attn_fwd(const AttnArgs* a, void* stream_) {
     configured[dev][wide][mask_mode][pos_mode] = smem;
   }
   dim3 grid((a->S + kTile - 1) / kTile, a->heads, a->B);
-  kern<<<grid, kt * 4, smem, stream>>>(tq, tk, tv, d);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return launch_pdl(kern, grid, dim3(kt * 4), smem, stream, tq, tk, tv, d) == cudaSuccess ? 0 : -4;
 }
 
 extern "C" int db200_attn_bwd(const AttnArgs* a, void* stream_) {
@@ -1035,7 +1040,7 @@ extern "C" int db200_attn_bwd(const AttnArgs* a, void* stream_) {
     configured[dev][mask_mode][pos_mode] = smem;
   }
   dim3 grid((a->S + kTile - 1) / kTile, a->heads, a->B);
-  kern<<<grid, kBwdThreads, smem, stream>>>(tq, tk, tv, tdo, d);
+  if (launch_pdl(kern, grid, dim3(kBwdThreads), smem, stream, tq, tk, tv, tdo, d) != cudaSuccess) return -4;
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -1044,9 +1049,9 @@ extern "C" int db200_attn_delta(const void* dout, long long ld_do, const void* o
   if (B <= 0 || S <= 0 || heads <= 0) return 0;
   if (!aligned16(dout) || !aligned16(out) || (ld_do % 8) || (ldo % 8)) return -10;
   const long long threads = static_cast<long long>(B) * S * heads * 8;
-  attn_delta_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(dout), ld_do, static_cast<const __nv_bfloat16*>(out), ldo, delta, B, S, heads);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return launch_pdl(attn_delta_kernel, dim3(static_cast<unsigned>((threads + 255) / 256)), dim3(256), 0,
+                    reinterpret_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(dout), ld_do,
+                    static_cast<const __nv_bfloat16*>(out), ldo, delta, B, S, heads) == cudaSuccess ? 0 : -4;
 }
 
 extern "C" int db200_attn_doc_tiles(const void* doc_ids, void* tiles, int B, int S, void* stream) {

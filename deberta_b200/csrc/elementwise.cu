@@ -4,6 +4,7 @@
 //   db200_swiglu_fwd  : out = silu(gate) * up           with [gate | up] the two halves of one row
 //   db200_swiglu_bwd  : d[gate | up] from d(out)         (silu'(g) = s * (1 + g * (1 - s)), s = sigmoid(g))
 #include "kernels.h"
+#include "tc05.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -113,6 +114,8 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_in, const _
 // (two 16-byte loads, one 16-byte store), grid-stride over rows * cols / 8 vectors.
 __global__ void __launch_bounds__(256)
 cast_rows_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, long long ld_y, long long rows, int cols) {
+  tc05::pdl_launch_dependents();
+  tc05::pdl_wait();
   const int vpr = cols / 8;
   const long long total = rows * vpr;
   for (long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; i < total;
@@ -184,8 +187,8 @@ extern "C" int db200_rotary_bf16(const void* x, void* y, long long ldx, long lon
 extern "C" int db200_cast_f32_bf16(const float* x, void* y, long long ld_y, long long rows, int cols, void* stream) {
   if (rows <= 0 || cols <= 0) return 0;
   if (!al16(x) || !al16(y) || (ld_y % 8) || (cols % 8) || ld_y < cols) return -10;
-  cast_rows_kernel<<<ew_grid(rows * (cols / 8)), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      x, static_cast<__nv_bfloat16*>(y), ld_y, rows, cols);
+  tc05::launch_pdl(cast_rows_kernel, dim3(ew_grid(rows * (cols / 8))), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+                   x, static_cast<__nv_bfloat16*>(y), ld_y, rows, cols);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

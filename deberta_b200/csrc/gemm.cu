@@ -142,6 +142,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   constexpr bool kRowSum = kOutF32 && A_MN;
   constexpr uint32_t kSumCol = 256;
   extern __shared__ uint8_t smem_raw[];
+  pdl_launch_dependents();
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
   uint64_t* empty_bar = full_bar + L::kStages;
@@ -181,6 +182,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // set-up done; from here on global memory is touched
 
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
   const int total_work = tiles_per_batch * p.batch * p.splits;
@@ -696,8 +698,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, 
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal) != cudaSuccess) return -3;
     configured[dev] = true;
   }
-  kern<<<grid, kThreads, L::kTotal, stream>>>(ta, tb, to, to2, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return launch_pdl(kern, dim3(grid), dim3(kThreads), L::kTotal, stream, ta, tb, to, to2, p) == cudaSuccess ? 0 : -4;
 }
 
 }  // namespace

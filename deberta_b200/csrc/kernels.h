@@ -11,7 +11,10 @@ extern "C" {
 // ----- status word written by kernels whose bounded waits ran out -------------------
 int* db200_status_ptr(void);          // device address of the status word (lazily allocated)
 int db200_status_read_and_clear(void);  // synchronises the device; 0 = no error recorded
-int db200_status_snapshot(int* dst, void* stream);  // stream-ordered copy of the word into device / pinned memory
+int db200_status_snapshot(int* dst, void* stream);
+// Programmatic dependent launch (overlap of a kernel's set-up with its predecessor's tail) for the kernels that support it.
+int db200_pdl_enabled(void);
+int db200_set_pdl(int on);  // returns the previous setting  // stream-ordered copy of the word into device / pinned memory
 
 // ----- GEMM ---------------------------------------------------------------------------
 enum { EPI_NONE = 0, EPI_GELU = 1, EPI_DGELU = 2, EPI_CE_FWD = 3, EPI_CE_BWD = 4,

@@ -4,6 +4,7 @@
 // gradients in registers across the rows a warp visits and flushes them once per block
 // with fp32 atomics (directly into the optimizer's fp32 gradient buffer when given).
 #include "kernels.h"
+#include "tc05.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -42,6 +43,8 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
                 const __nv_bfloat16* __restrict__ beta, const unsigned char* __restrict__ row_keep,
                 __nv_bfloat16* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
                 int H, float eps) {
+  tc05::pdl_launch_dependents();
+  tc05::pdl_wait();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int nvec = H >> 3;
@@ -110,6 +113,8 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
                 const float* __restrict__ rstd_in, const unsigned char* __restrict__ row_keep,
                 __nv_bfloat16* __restrict__ dx, float* __restrict__ dgamma, float* __restrict__ dbeta, int rows, int H) {
   __shared__ float red[kWarpsPerBlock][32 * 8 + 1];
+  tc05::pdl_launch_dependents();
+  tc05::pdl_wait();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int nvec = H >> 3;
@@ -194,9 +199,9 @@ int launch_fwd(const void* x, const void* g, const void* b, const void* keep, vo
   auto B = static_cast<const __nv_bfloat16*>(b);
   auto K = static_cast<const unsigned char*>(keep);
   auto Y = static_cast<__nv_bfloat16*>(y);
-  if (H <= 256) norm_fwd_kernel<1, RMS><<<blocks, kWarpsPerBlock * 32, 0, st>>>(X, G, B, K, Y, mean, rstd, rows, H, eps);
-  else if (H <= 1024) norm_fwd_kernel<4, RMS><<<blocks, kWarpsPerBlock * 32, 0, st>>>(X, G, B, K, Y, mean, rstd, rows, H, eps);
-  else if (H <= 2048) norm_fwd_kernel<8, RMS><<<blocks, kWarpsPerBlock * 32, 0, st>>>(X, G, B, K, Y, mean, rstd, rows, H, eps);
+  if (H <= 256) tc05::launch_pdl(norm_fwd_kernel<1, RMS>, dim3(blocks), dim3(kWarpsPerBlock * 32), 0, st, X, G, B, K, Y, mean, rstd, rows, H, eps);
+  else if (H <= 1024) tc05::launch_pdl(norm_fwd_kernel<4, RMS>, dim3(blocks), dim3(kWarpsPerBlock * 32), 0, st, X, G, B, K, Y, mean, rstd, rows, H, eps);
+  else if (H <= 2048) tc05::launch_pdl(norm_fwd_kernel<8, RMS>, dim3(blocks), dim3(kWarpsPerBlock * 32), 0, st, X, G, B, K, Y, mean, rstd, rows, H, eps);
   else return -12;
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -210,11 +215,11 @@ int launch_bwd(const void* dy, const void* x, const void* g, const float* mean, 
   auto G = static_cast<const __nv_bfloat16*>(g);
   auto K = static_cast<const unsigned char*>(keep);
   auto DX = static_cast<__nv_bfloat16*>(dx);
-  if (H <= 256) norm_bwd_kernel<1, RMS><<<blocks, kWarpsPerBlock * 32, 0, st>>>(DY, X, G, mean, rstd, K, DX, dgamma, dbeta, rows, H);
-  else if (H <= 512) norm_bwd_kernel<2, RMS><<<blocks, kWarpsPerBlock * 32, 0, st>>>(DY, X, G, mean, rstd, K, DX, dgamma, dbeta, rows, H);
-  else if (H <= 768) norm_bwd_kernel<3, RMS><<<blocks, kWarpsPerBlock * 32, 0, st>>>(DY, X, G, mean, rstd, K, DX, dgamma, dbeta, rows, H);
-  else if (H <= 1024) norm_bwd_kernel<4, RMS><<<blocks, kWarpsPerBlock * 32, 0, st>>>(DY, X, G, mean, rstd, K, DX, dgamma, dbeta, rows, H);
-  else if (H <= 2048) norm_bwd_kernel<8, RMS><<<blocks, kWarpsPerBlock * 32, 0, st>>>(DY, X, G, mean, rstd, K, DX, dgamma, dbeta, rows, H);
+  if (H <= 256) tc05::launch_pdl(norm_bwd_kernel<1, RMS>, dim3(blocks), dim3(kWarpsPerBlock * 32), 0, st, DY, X, G, mean, rstd, K, DX, dgamma, dbeta, rows, H);
+  else if (H <= 512) tc05::launch_pdl(norm_bwd_kernel<2, RMS>, dim3(blocks), dim3(kWarpsPerBlock * 32), 0, st, DY, X, G, mean, rstd, K, DX, dgamma, dbeta, rows, H);
+  else if (H <= 768) tc05::launch_pdl(norm_bwd_kernel<3, RMS>, dim3(blocks), dim3(kWarpsPerBlock * 32), 0, st, DY, X, G, mean, rstd, K, DX, dgamma, dbeta, rows, H);
+  else if (H <= 1024) tc05::launch_pdl(norm_bwd_kernel<4, RMS>, dim3(blocks), dim3(kWarpsPerBlock * 32), 0, st, DY, X, G, mean, rstd, K, DX, dgamma, dbeta, rows, H);
+  else if (H <= 2048) tc05::launch_pdl(norm_bwd_kernel<8, RMS>, dim3(blocks), dim3(kWarpsPerBlock * 32), 0, st, DY, X, G, mean, rstd, K, DX, dgamma, dbeta, rows, H);
   else return -12;
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -10,6 +10,7 @@
 // transposition is needed, so that every global access is a coalesced run of table entries or
 // bias columns.
 #include "kernels.h"
+#include "tc05.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -224,6 +225,8 @@ __global__ void __launch_bounds__(256)
 posbias_rowscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __restrict__ ranges,
                        __nv_bfloat16* __restrict__ dtab, int S, int ldb, int heads, int span2) {
   extern __shared__ float sm[];
+  tc05::pdl_launch_dependents();
+  tc05::pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stride = (S + 1) + ((S + 1) >> 3) + 1;
   // P[i] = sum of the first i keys, kept at word i + i/8: the lanes of the scan write 8 words apart
@@ -287,6 +290,8 @@ __global__ void __launch_bounds__(256)
 posbias_colscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __restrict__ ranges,
                        __nv_bfloat16* __restrict__ dtab, int S, int ldb, int heads, int span2, int stride, int per, int sh) {
   extern __shared__ float sm[];
+  tc05::pdl_launch_dependents();
+  tc05::pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int* edge = reinterpret_cast<int*>(sm);  // E_0 .. E_span2, 16-byte aligned for vector loads
   float* tb = sm + ((span2 + 4) & ~3);     // T[KEYS][stride]
@@ -453,7 +458,8 @@ extern "C" int db200_posbias_scatter_ranges(const void* dbias, const void* range
     else if (per == 32) kern = posbias_colscan_kernel<32, kColKeys>;
     else if (per == 4) kern = posbias_colscan_kernel<4, kColKeys>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) != cudaSuccess) return -3;
-    kern<<<dim3((S + kColKeys - 1) / kColKeys, heads, B), 256, smem, st>>>(db, rg, dt, S, ldb, heads, span2, stride, per, sh);
+    tc05::launch_pdl(kern, dim3((S + kColKeys - 1) / kColKeys, heads, B), dim3(256), smem, st, db, rg, dt, S, ldb, heads, span2,
+                     stride, per, sh);
   } else {
     const int smem = 8 * ((S + 1) + ((S + 1) >> 3) + 1) * 4 + 2 * span2 * 4;
     if (smem > kMaxSmem) return -12;
@@ -463,7 +469,7 @@ extern "C" int db200_posbias_scatter_ranges(const void* dbias, const void* range
         return -3;
       cfg = true;
     }
-    posbias_rowscan_kernel<<<dim3((S + 7) / 8, heads, B), 256, smem, st>>>(db, rg, dt, S, ldb, heads, span2);
+    tc05::launch_pdl(posbias_rowscan_kernel, dim3((S + 7) / 8, heads, B), dim3(256), smem, st, db, rg, dt, S, ldb, heads, span2);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -115,6 +115,7 @@ posbias_tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int row = quad * 32 + lane;
   const int ti = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int q0 = ti * kTile;
+  pdl_launch_dependents();
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
@@ -129,9 +130,10 @@ posbias_tc_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   }
   for (int x = tid; x < lut_len - 1; x += kThreads) {
     const int d = min(max(x - (nt * kTile - 1) + (S - 1), 0), 2 * S - 2);
-    if (HAS_C) lutc[x] = p.lut_c2p[d];
+    if (HAS_C) lutc[x] = p.lut_c2p[d];  // (the bucket maps are written once, when the model is built)
     if (HAS_P) lutp[x] = p.lut_p2c[d];
   }
+  pdl_wait();  // set-up done; Q, K, the position tables and the bias are touched only from here on
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -322,8 +324,7 @@ extern "C" int db200_posbias_tc_fwd(const PosBiasArgs* a, void* stream_) {
                             : posbias_tc_fwd_kernel<false, true>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
   dim3 grid(nt, a->heads, a->B);
-  kern<<<grid, kThreads, smem, stream>>>(tq, tk, tpk, tpq, d);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  return launch_pdl(kern, grid, dim3(kThreads), smem, stream, tq, tk, tpk, tpq, d) == cudaSuccess ? 0 : -4;
 }
 
 

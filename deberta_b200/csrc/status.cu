@@ -10,6 +10,17 @@ constexpr int kMaxDevices = 16;
 int* g_status_addr[kMaxDevices] = {nullptr};
 }  // namespace
 
+// Programmatic dependent launch for the kernels that support it (tc05.cuh); on by default.
+namespace {
+int g_pdl = 1;
+}
+extern "C" int db200_pdl_enabled(void) { return g_pdl; }
+extern "C" int db200_set_pdl(int on) {
+  const int old = g_pdl;
+  g_pdl = on ? 1 : 0;
+  return old;
+}
+
 extern "C" int* db200_status_ptr(void) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;

@@ -47,6 +47,39 @@ __device__ __forceinline__ bool elect_one() {
 }
 
 // ---------------------------------------------------------------------------
+// programmatic dependent launch
+//
+// Back-to-back kernels of one stream normally leave the GPU idle for a few microseconds at every boundary (the last
+// CTAs drain, the next grid is launched, its CTAs set themselves up). A kernel launched through launch_pdl() may
+// become resident as soon as every CTA of its predecessor has called pdl_launch_dependents() (or exited), runs its
+// set-up (barrier init, TMEM allocation, descriptor prefetch) under the predecessor's tail and then blocks in
+// pdl_wait() until the predecessor has completed and its writes are visible. Rules kept by every kernel that uses
+// it: pdl_wait() is executed by ALL threads before the first access to global memory (reads of what a predecessor
+// wrote and writes to what it may still read alike), and pdl_launch_dependents() is issued at the top of the kernel.
+// Both instructions are no-ops for grids launched the ordinary way.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+extern "C" int db200_pdl_enabled(void);
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = db200_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+// ---------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {

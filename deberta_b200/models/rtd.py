@@ -170,14 +170,15 @@ class EnhancedMaskDecoder(nn.Module):
             raise ValueError("num_last_layer_passes must be >= 1")
 
     def forward(self, *, encoder_hidden_states, masked_positions, attention_mask, embeddings, encoder,
-                position_ids=None, relative_pos=None) -> torch.Tensor:
+                position_ids=None, relative_pos=None, masked_idx=None) -> torch.Tensor:
         hs = list(encoder_hidden_states)
         if len(hs) < 2:
             raise RuntimeError(
                 "EnhancedMaskDecoder requires output_hidden_states=True on the generator "
                 "so we can access penultimate-layer states."
             )
-        masked_idx = torch.nonzero(masked_positions.reshape(-1), as_tuple=False).squeeze(-1)
+        if masked_idx is None:  # (data-dependent size: the host waits for the device here)
+            masked_idx = torch.nonzero(masked_positions.reshape(-1), as_tuple=False).squeeze(-1)
         if masked_idx.numel() == 0 or self.position_biased_input:
             return gather_rows(hs[-1].reshape(-1, hs[-1].shape[-1]), masked_idx)
         final = self.decode(hs[-2], attention_mask, embeddings, encoder, position_ids, relative_pos)
@@ -417,13 +418,18 @@ class DebertaV3RTDPretrainer(nn.Module):
         return self.use_enhanced_mask_decoder and (not pos_biased) and z_steps <= 1
 
     def forward_generator_phase(self, *, input_ids, attention_mask=None, labels, token_type_ids=None,
-                                sampling_temperature: float = 1.0) -> RTDGeneratorPhaseOutput:
-        """Generator MLM loss on masked rows + sampled corruption for the discriminator (``:988-1093``)."""
+                                sampling_temperature: float = 1.0, masked_idx=None) -> RTDGeneratorPhaseOutput:
+        """Generator MLM loss on masked rows + sampled corruption for the discriminator (``:988-1093``).
+
+        ``masked_idx`` (optional): the flat positions where ``labels != -100``, already on the device. The training
+        loop computes them on the host copy of the batch, so that the forward never has to wait for the device to
+        learn how many rows are masked; without it they come from ``torch.nonzero`` (one host-device round trip)."""
         if labels is None:
             raise ValueError("labels must be provided (MLM labels with -100 for unmasked positions)")
         masked_positions = labels.ne(-100)
         masked_flat = masked_positions.view(-1)
-        masked_idx = torch.nonzero(masked_flat, as_tuple=False).squeeze(-1)
+        if masked_idx is None:
+            masked_idx = torch.nonzero(masked_flat, as_tuple=False).squeeze(-1)
         gen_token_count = masked_flat.sum().to(torch.float32)
         use_emd = self._uses_emd()
         kw: dict[str, Any] = {"input_ids": input_ids, "attention_mask": attention_mask,
@@ -441,6 +447,7 @@ class DebertaV3RTDPretrainer(nn.Module):
             hidden = self.enhanced_mask_decoder(
                 encoder_hidden_states=gen_out.hidden_states, masked_positions=masked_positions,
                 attention_mask=attention_mask, embeddings=self.generator.embeddings, encoder=self.generator.encoder,
+                masked_idx=masked_idx,
             )
         else:
             last = gen_out.last_hidden_state
@@ -477,7 +484,7 @@ class DebertaV3RTDPretrainer(nn.Module):
 
     def forward(self, *, input_ids, attention_mask=None, labels=None, token_type_ids=None,
                 sampling_temperature: float = 1.0, gen_loss_weight: float = 1.0, disc_loss_weight: float = 50.0,
-                phase: str = "both", corrupted_input_ids=None, disc_labels=None):
+                phase: str = "both", corrupted_input_ids=None, disc_labels=None, masked_idx=None):
         """``phase='generator' | 'discriminator'`` run one branch; ``'both'`` returns the weighted ``RTDOutput``."""
         phase = str(phase or "both").strip().lower()
         if phase == "generator":
@@ -485,7 +492,7 @@ class DebertaV3RTDPretrainer(nn.Module):
                 raise ValueError("labels must be provided for phase='generator'.")
             return self.forward_generator_phase(input_ids=input_ids, attention_mask=attention_mask, labels=labels,
                                                 token_type_ids=token_type_ids,
-                                                sampling_temperature=sampling_temperature)
+                                                sampling_temperature=sampling_temperature, masked_idx=masked_idx)
         if phase == "discriminator":
             if corrupted_input_ids is None:
                 raise ValueError("corrupted_input_ids must be provided for phase='discriminator'.")
@@ -499,7 +506,8 @@ class DebertaV3RTDPretrainer(nn.Module):
         if labels is None:
             raise ValueError("labels must be provided for phase='both'.")
         g = self.forward_generator_phase(input_ids=input_ids, attention_mask=attention_mask, labels=labels,
-                                         token_type_ids=token_type_ids, sampling_temperature=sampling_temperature)
+                                         token_type_ids=token_type_ids, sampling_temperature=sampling_temperature,
+                                         masked_idx=masked_idx)
         if not g.has_masked_targets:
             zero = torch.zeros((), device=input_ids.device, dtype=torch.float32)
             return RTDOutput(loss=float(gen_loss_weight) * g.gen_loss_raw, gen_loss=g.gen_loss_raw.detach(),

@@ -126,6 +126,13 @@ def check_status() -> None:
         raise KernelError(f"device status {code}: {STATUS_NAMES.get(code, 'unknown')}")
 
 
+def set_dependent_launch(on: bool) -> bool:
+    """Programmatic dependent launch for the kernels that support it (GEMM, norms, attention, position bias, casts): a
+    kernel's set-up runs under the tail of its predecessor in the stream and it waits, before touching global memory,
+    until the predecessor has completed. On by default; returns the previous setting."""
+    return bool(lib().db200_set_pdl(ctypes.c_int(1 if on else 0)))
+
+
 LAUNCH_COUNT = 0
 
 

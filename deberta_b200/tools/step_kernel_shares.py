@@ -3,13 +3,15 @@
 Usage::
 
     python -m deberta_b200.tools.step_kernel_shares [--backbone hf_deberta_v2|rope] [--model-size base] [--seq-len 512]
-        [--micro-batch 32] [--ga 2] [--top 40] [--callers]
+        [--micro-batch 32] [--ga 2] [--top 40] [--callers] [--gaps]
 
 Builds the RTD pretrainer from the config defaults on synthetic packed data, runs three warm-up windows, profiles the
 fourth and prints, per kernel name, the launch count, total and mean device time and the share of the window. The
 shares say where a step spends its time; absolute times under the profiler are not benchmark numbers. ``--callers``
 also lists the ATen operators that launched kernels (fills, adds, copies: what is left outside the library's own
-kernels) with the line of this package that called each of them. The reference
+kernels) with the line of this package that called each of them; ``--gaps`` lists where the GPU sat idle inside the
+window (time between the end of one kernel and the start of the next, grouped by the pair of kernels around it; the
+profiler slows the host down, so these are upper bounds). The reference
 has no counterpart (it ships no profiling hooks; its closest tool is ``tools/compile_drift_probe.py:363-366``, which
 times whole steps).
 """
@@ -51,7 +53,7 @@ def _batches(a: argparse.Namespace, device: torch.device) -> list[dict[str, torc
     col = DebertaV3ElectraCollator(tokenizer=tok, cfg=MLMConfig(mask_token_prob=1.0, random_token_prob=0.0),
                                    packed_sequences=True, block_cross_document_attention=False)
     torch.manual_seed(100)
-    return [{k: v.to(device) for k, v in col([next(ds) for _ in range(a.micro_batch)]).items()} for _ in range(a.ga)]
+    return [dict(col([next(ds) for _ in range(a.micro_batch)])) for _ in range(a.ga)]  # host batches
 
 
 def main(argv: list[str] | None = None) -> int:
@@ -63,6 +65,7 @@ def main(argv: list[str] | None = None) -> int:
     p.add_argument("--ga", type=int, default=2)
     p.add_argument("--top", type=int, default=40)
     p.add_argument("--callers", action="store_true", help="attribute ATen kernels to the package line that launched them")
+    p.add_argument("--gaps", action="store_true", help="list the idle intervals of the GPU inside the window")
     a = p.parse_args(argv)
     if not torch.cuda.is_available():
         print("step_kernel_shares needs a CUDA device")
@@ -80,14 +83,17 @@ def main(argv: list[str] | None = None) -> int:
     model, _, _ = build_model(model_cfg=cfg.model, tokenizer=tok, max_seq_length=a.seq_len)
     engine = build_engine(model=model, ctx=ctx, train_cfg=cfg.train, optim_cfg=cfg.optim, parallelism="zero")
     trainer = Trainer(model=model, engine=engine, ctx=ctx, train_cfg=cfg.train, optim_cfg=cfg.optim, pad_token_id=tok.pad_token_id)
-    window = _batches(a, ctx.device)
+    window = [trainer.stage_batch(b) for b in _batches(a, ctx.device)]
     for _ in range(3):
         trainer.train_window(window)
     torch.cuda.synchronize()
     extra = {}
     if a.callers:  # Python stacks are only recorded with the verbose collector
         extra = dict(with_stack=True, experimental_config=torch._C._profiler._ExperimentalConfig(verbose=True))
-    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU], **extra) as prof:
+    # host-side events are only needed to name callers; without them the profiler barely slows the launching thread,
+    # which is what the idle-gap report wants
+    acts = [ProfilerActivity.CUDA] + ([ProfilerActivity.CPU] if a.callers else [])
+    with profile(activities=acts, **extra) as prof:
         trainer.train_window(window)
         torch.cuda.synchronize()
     agg: dict[str, list[float]] = collections.defaultdict(lambda: [0, 0.0])
@@ -101,6 +107,23 @@ def main(argv: list[str] | None = None) -> int:
     print(f"window of {a.ga} micro-batches ({a.micro_batch} x {a.seq_len}): {total / 1e3:.1f} ms of device time over {launches} launches")
     for name, (n, t) in sorted(agg.items(), key=lambda kv: -kv[1][1])[: a.top]:
         print(f"{t / total * 100:5.1f} %  {t / 1e3:8.2f} ms  n={int(n):5d}  mean {t / n:8.1f} us  {name}")
+    if a.gaps:
+        spans = sorted((ev.time_range.start, ev.time_range.end, ev.name) for ev in prof.events()
+                       if ev.device_type == torch.autograd.DeviceType.CUDA)
+        idle: dict[tuple[str, str], list[float]] = collections.defaultdict(lambda: [0, 0.0])
+        busy_until, prev = spans[0][1], spans[0][2]
+        for start, end, name in spans[1:]:
+            if start > busy_until + 1.0:  # more than a microsecond with nothing running
+                slot = idle[(prev[:60], name[:60])]
+                slot[0] += 1
+                slot[1] += start - busy_until
+            if end > busy_until:
+                busy_until, prev = end, name
+        gap_total = sum(v[1] for v in idle.values())
+        print(f"GPU idle inside the window: {gap_total / 1e3:.2f} ms in {int(sum(v[0] for v in idle.values()))} intervals "
+              f"({gap_total / (spans[-1][1] - spans[0][0]) * 100:.1f} % of its span)")
+        for (before, after), (n, t) in sorted(idle.items(), key=lambda kv: -kv[1][1])[: a.top]:
+            print(f"{t / 1e3:8.2f} ms  n={int(n):4d}  after {before}  before {after}")
     if a.callers:
         rows: dict[tuple[str, str], list[float]] = collections.defaultdict(lambda: [0, 0.0])
         for ev in prof.key_averages(group_by_stack_n=24):

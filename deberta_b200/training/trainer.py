@@ -157,8 +157,25 @@ class Trainer:
         return {n: s.get_last_lr()[0] * self.lr_mult for n, s in self.schedules.items()}
 
     def _to_device(self, batch: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+        """Copy a micro-batch to the device. A batch that is still on the host also gets ``masked_idx``, the flat
+        positions of its MLM targets: found here on the CPU (16 k integers), they spare the generator phase its two
+        ``nonzero`` calls, each of which would stall the host until the device had drained its queue."""
         dev = self.engine.device
-        return {k: (v.to(dev, non_blocking=True) if isinstance(v, torch.Tensor) else v) for k, v in batch.items()}
+        out = {k: (v.to(dev, non_blocking=True) if isinstance(v, torch.Tensor) else v) for k, v in batch.items()}
+        labels = batch.get("labels")
+        if isinstance(labels, torch.Tensor) and not labels.is_cuda and dev.type == "cuda" and "masked_idx" not in out:
+            idx = torch.nonzero(labels.reshape(-1).ne(-100), as_tuple=False).squeeze(-1)
+            out["masked_idx"] = idx.pin_memory().to(dev, non_blocking=True)
+        return out
+
+    def stage_batch(self, batch: dict[str, torch.Tensor]) -> dict[str, Any]:
+        """A host micro-batch made device-resident ahead of time (prefetching loaders, benchmarks that keep their inputs
+        on the GPU): the copy of :meth:`_to_device` plus ``_counts``, the token counts that :meth:`train_window`
+        would otherwise have to read back from the device, one blocking ``.item()`` each."""
+        counts = (*count_rtd_tokens_for_batch(batch, pad_token_id=self.pad_token_id), count_input_tokens_for_batch(batch))
+        out: dict[str, Any] = self._to_device(batch)
+        out["_counts"] = counts
+        return out
 
     @staticmethod
     def _mask_of(batch: dict[str, torch.Tensor]):
@@ -247,8 +264,10 @@ class Trainer:
         self.resolve_pending()
         eng, model, dev = self.engine, self.model, self.engine.device
         device_gate = None
-        counts = [count_rtd_tokens_for_batch(b, pad_token_id=self.pad_token_id) for b in batches]
-        input_tokens = sum(count_input_tokens_for_batch(b) for b in batches)
+        staged = [b.get("_counts") for b in batches]  # batches from stage_batch() carry their host-side counts
+        counts = [c[:2] if c is not None else count_rtd_tokens_for_batch(b, pad_token_id=self.pad_token_id)
+                  for b, c in zip(batches, staged)]
+        input_tokens = sum(c[2] if c is not None else count_input_tokens_for_batch(b) for b, c in zip(batches, staged))
         gen_total, disc_total = sum(c[0] for c in counts), sum(c[1] for c in counts)
         gen_den, disc_den, has_targets = self._window_denominators(gen_total, disc_total)
         scale = micro_loss_scale(ga_steps=len(batches), token_weighted_ga=self.token_weighted)
@@ -271,7 +290,7 @@ class Trainer:
                 with nvtx_range("generator fwd"):
                     out = model(input_ids=b["input_ids"], attention_mask=mask, labels=b["labels"],
                                 token_type_ids=b.get("token_type_ids"), sampling_temperature=self.temperature,
-                                phase="generator")
+                                phase="generator", masked_idx=b.get("masked_idx"))
                 w = (g_i / gen_den) if self.token_weighted else 1.0
                 with nvtx_range("generator bwd"):
                     (out.gen_loss_raw * (self.gen_w * scale) * w).backward()
@@ -333,7 +352,7 @@ class Trainer:
                 b = self._to_device(b)
                 out = model(input_ids=b["input_ids"], attention_mask=self._mask_of(b), labels=b["labels"],
                             token_type_ids=b.get("token_type_ids"), sampling_temperature=self.temperature,
-                            gen_loss_weight=self.gen_w, disc_loss_weight=self.disc_w)
+                            gen_loss_weight=self.gen_w, disc_loss_weight=self.disc_w, masked_idx=b.get("masked_idx"))
                 if self.token_weighted:
                     obj = self.gen_w * (g_i / gen_den) * out.gen_loss_raw + self.disc_w * (d_i / disc_den) * out.disc_loss_raw
                 else:

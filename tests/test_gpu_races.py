@@ -171,3 +171,39 @@ def test_norm_and_vocab_head_repeat_bit_for_bit():
     l2, _ = mlm_loss_and_sample(h, table, None, labels, None, 1.0)
     assert torch.equal(l1, l2)  # the loss does not depend on the sampling seed, and its reduction order is fixed
     _lib.check_status()
+
+
+def test_dependent_launch_chains_match_ordinary_launches_bit_for_bit():
+    """A chain of short kernels in which each one reads what the previous one wrote and overwrites what the one before
+    that read (GEMM -> LayerNorm -> GEMM -> cast, ping-ponging two buffers, 40 rounds, plus a backward chain): with
+    programmatic dependent launch the kernels' set-up overlaps their predecessors, and the results must still be the
+    ones of ordinary stream-ordered launches, bit for bit, every time."""
+    from deberta_b200.ops.linear import linear
+    from deberta_b200.ops.norm import layer_norm
+
+    T, H = 2048, 768
+    x0 = _rand(T, H, seed=3)
+    w1, w2 = _rand(H, H, scale=0.03, seed=4), _rand(H, H, scale=0.03, seed=5)
+    b1 = _rand(H, scale=0.1, seed=6)
+    gamma, beta = _rand(H, seed=7) * 0 + 1, _rand(H, scale=0.1, seed=8)
+
+    def chain():
+        torch.manual_seed(0)
+        x = x0.clone().requires_grad_(True)
+        h = x
+        for _ in range(40):
+            h = layer_norm(linear(h, w1, b1, residual=h), gamma, beta, 1e-6)
+            h = linear(h, w2, None)
+        (h.float().square().mean()).backward()
+        return h.detach().clone(), x.grad.detach().clone()
+
+    old = _lib.set_dependent_launch(False)
+    try:
+        ref = chain()
+        _lib.set_dependent_launch(True)
+        for _ in range(3):
+            got = chain()
+            assert torch.equal(got[0], ref[0]) and torch.equal(got[1], ref[1])
+    finally:
+        _lib.set_dependent_launch(old)
+    _lib.check_status()
