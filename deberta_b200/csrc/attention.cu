@@ -195,7 +195,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int row = quad * 32 + lane; // query row inside the tile
   const int q0 = blockIdx.x * kTile;
   const int h = blockIdx.y;
-  const int b = blockIdx.z;
+  // The bias tensor was written batch by batch just before this launch and is larger than the L2 at training sizes:
+  // walking the batch backwards starts with the part that is still cached.
+  const int b = POS == 1 ? static_cast<int>(gridDim.z - 1 - blockIdx.z) : static_cast<int>(blockIdx.z);
   const int S = p.S;
   pdl_launch_dependents();
 

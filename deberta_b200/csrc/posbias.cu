@@ -235,7 +235,9 @@ posbias_rowscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __res
   for (int i = threadIdx.x; i <= span2; i += 256) edge[i] = ranges[i + 1];
   const float sign = ranges[0] >= 0 ? 1.f : -1.f;
   __syncthreads();
-  const int q = blockIdx.x * 8 + warp, h = blockIdx.y, b = blockIdx.z;
+  // (batch walked backwards: the attention backward wrote dbias in ascending order and its tail is still in the L2;
+  // the column scan that follows walks forwards again and finds this kernel's tail)
+  const int q = blockIdx.x * 8 + warp, h = blockIdx.y, b = gridDim.z - 1 - blockIdx.z;
   if (q >= S) return;
   const __nv_bfloat16* src = dbias + ((static_cast<long long>(b) * heads + h) * S + q) * ldb;
   float carry = 0.f;

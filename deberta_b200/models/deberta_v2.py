@@ -108,7 +108,9 @@ class DisentangledSelfAttention(nn.Module):
 
     def project_positions(self, rel_embeddings: torch.Tensor, *, use_query: bool) -> torch.Tensor:
         """``[2·span, H]`` projection of the relative-embedding table with the key/query weights."""
-        rel = rel_embeddings[: 2 * self.pos_ebd_size]
+        # (a slice of the whole table is still an autograd node: its backward would zero-fill and copy a full table per layer)
+        rows = 2 * self.pos_ebd_size
+        rel = rel_embeddings if rel_embeddings.shape[0] == rows else rel_embeddings[:rows]
         proj = (self.query_proj if self.share_att_key else self.pos_query_proj) if use_query else (
             self.key_proj if self.share_att_key else self.pos_key_proj
         )

@@ -407,8 +407,9 @@ def disentangled_attention_cuda(q, k, v, pos_k, pos_q, *, heads, scale_factor, b
     scale = math.sqrt(float(d * scale_factor))
     luts = None
     if pos_k is not None or pos_q is not None:
-        pos_k = None if pos_k is None else pos_k[: 2 * att_span].contiguous()
-        pos_q = None if pos_q is None else pos_q[: 2 * att_span].contiguous()
+        # (no slice when the table already has 2·span rows: the slice's backward would zero-fill and copy it)
+        trim = lambda t: t if t is None or (t.shape[0] == 2 * att_span and t.is_contiguous()) else t[: 2 * att_span].contiguous()  # noqa: E731
+        pos_k, pos_q = trim(pos_k), trim(pos_q)
     if torch.compiler.is_compiling():
         from . import library
 

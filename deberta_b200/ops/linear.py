@@ -139,12 +139,15 @@ class _FFNGelu(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, w1, b1, w2, b2, residual):
+    def forward(ctx, x, w1, b1, w2, b2, residual, residual_is_x):
+        if residual_is_x:  # the usual transformer block: y = FFN(x) + x
+            residual = x
         g, a = gemm(x, w1, bias=b1, epi=EPI_GELU_GRAD)
         y = gemm(a, w2, bias=b2, residual=residual)
         ctx.save_for_backward(x, w1, w2, g, a)
         ctx.params = (b1, b2)
-        ctx.has_res = residual is not None
+        ctx.has_res = residual is not None and not residual_is_x
+        ctx.res_is_x = bool(residual_is_x)
         return y
 
     @staticmethod
@@ -154,9 +157,10 @@ class _FFNGelu(torch.autograd.Function):
         dy = dy.contiguous()
         dz = gemm(dy, w2, b_mn=True, epi=EPI_MUL, aux=g)
         dw2, db2 = _param_grads(dy, a, w2, b2)
-        dx = gemm(dz, w1, b_mn=True) if ctx.needs_input_grad[0] else None
+        # with y = FFN(x) + x the two gradients of x meet in the epilogue of the W1 data-gradient GEMM (no add kernel)
+        dx = gemm(dz, w1, b_mn=True, residual=dy if ctx.res_is_x else None) if ctx.needs_input_grad[0] else None
         dw1, db1 = _param_grads(dz, x, w1, b1)
-        return dx, dw1, db1, dw2, db2, (dy if ctx.has_res else None)
+        return dx, dw1, db1, dw2, db2, (dy if ctx.has_res else None), None
 
 
 def ffn_gelu(x, w1, b1, w2, b2, residual=None):
@@ -173,7 +177,8 @@ def ffn_gelu(x, w1, b1, w2, b2, residual=None):
 
         out = library.ffn_gelu(x2, w1, b1, w2, b2, r2, None, None, None, None)[0]  # no buffers: see linear()
     else:
-        out = _FFNGelu.apply(x2, w1, b1, w2, b2, r2)
+        same = residual is x and x.requires_grad
+        out = _FFNGelu.apply(x2, w1, b1, w2, b2, None if same else r2, same)
     return out.view(*lead, w2.shape[0])
 
 
