@@ -686,6 +686,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (POS == 1) {
 #pragma unroll
       for (int g8 = 0; g8 < 4; ++g8) bias_cur[g8] = __ldg(bias_row + part * 4 + g8);
+      // the same 64 bytes of the next query tile's row: fetched into the L2 now (no registers to spare for a
+      // tile-ahead copy here), so that the next iteration's load does not wait for DRAM
+      if (i + 1 < nqt && q + kTile < S)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.bias + brow_off + static_cast<long long>(kTile) * p.ldb + part * 32));
     }
     bool got_g = true;
     // (a wait that ran out is reported at the next block barrier, where the whole block leaves the loop together)
