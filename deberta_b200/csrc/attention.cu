@@ -491,6 +491,330 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 // --------------------------------------------------------------------------------------------
+// forward, warp-specialised (64 keys per tile, no document ids, no in-kernel table gathers)
+// --------------------------------------------------------------------------------------------
+// Same arithmetic as attn_fwd_kernel<MASK, POS, 64>, different choreography. A ninth warp owns every TMA load and
+// every MMA; the eight softmax warps never meet at a block-wide barrier inside the loop. What orders them:
+//   bar_s[2]      (tcgen05.commit)  scores of a tile are in TMEM buffer j & 1 (two buffers: the next tile's scores are
+//                                   computed while this tile's are still being read)
+//   bar_sfree[2]  (8 warp arrivals) every softmax warp has copied its scores of that buffer into registers
+//   bar_pair[4]   (2 warp arrivals) the two warps that share query rows have published their partial row maxima
+//   bar_p         (8 warp arrivals) P of the tile is in shared memory and the running output has been rescaled
+//   bar_o         (tcgen05.commit)  P·V of a tile has retired: P may be overwritten, O may be rescaled or read
+// Every wait is bounded; a wait that runs out raises the CTA's abort flag, which ends every other role's waits too.
+struct FwdWsSmem {
+  static constexpr int kQ = 0;
+  static constexpr int kK = kQ + kTileBytes;       // 2 x 8 KB
+  static constexpr int kV = kK + kTileBytes;       // 2 x 8 KB
+  static constexpr int kP = kV + kTileBytes;       // 128 x 64 bf16
+  static constexpr int kBar = kP + kTileBytes;     // 16 barriers + TMEM slot + abort flag
+  static constexpr int kRed = kBar + 256;          // [2 tiles][2 column groups][128 rows] floats
+  static constexpr int kTotal = kRed + 2048 + 1024;
+};
+constexpr int kFwdWsThreads = 288;  // warps 0-7: softmax (quadrant w & 3, 32-key column group w >> 2); warp 8: TMA + MMA
+
+template <int MASK, int POS>  // MASK 0 | 1, POS 0 | 1
+__global__ void __launch_bounds__(kFwdWsThreads, 2)
+attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const AttnDev p) {
+  constexpr int KT = 64;
+  constexpr int kKV = KT * kD * 2;
+  extern __shared__ uint8_t smem_raw[];
+  pdl_launch_dependents();
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + FwdWsSmem::kQ;
+  uint8_t* sK = smem + FwdWsSmem::kK;
+  uint8_t* sV = smem + FwdWsSmem::kV;
+  uint8_t* sP = smem + FwdWsSmem::kP;
+  uint64_t* bar_q = reinterpret_cast<uint64_t*>(smem + FwdWsSmem::kBar);
+  uint64_t* bar_k = bar_q + 1;      // [2]
+  uint64_t* bar_v = bar_q + 3;      // [2]
+  uint64_t* bar_s = bar_q + 5;      // [2]
+  uint64_t* bar_sfree = bar_q + 7;  // [2]
+  uint64_t* bar_pair = bar_q + 9;   // [4]
+  uint64_t* bar_p = bar_q + 13;
+  uint64_t* bar_o = bar_q + 14;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* red = reinterpret_cast<float*>(smem + FwdWsSmem::kRed);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int q0 = blockIdx.x * kTile;
+  const int h = blockIdx.y;
+  const int b = POS == 1 ? static_cast<int>(gridDim.z - 1 - blockIdx.z) : static_cast<int>(blockIdx.z);  // see attn_fwd_kernel
+  const int S = p.S;
+  const int nkt = (S + KT - 1) / KT;
+
+  if (tid == 0) {
+    mbar_init(bar_q, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar_k[i], 1);
+      mbar_init(&bar_v[i], 1);
+      mbar_init(&bar_s[i], 1);
+      mbar_init(&bar_sfree[i], 8);
+    }
+    for (int i = 0; i < 4; ++i) mbar_init(&bar_pair[i], 2);
+    mbar_init(bar_p, 8);
+    mbar_init(bar_o, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  pdl_wait();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_o = tmem_base + 128;  // scores: columns [0, 64) and [64, 128)
+
+  if (warp == 8) {
+    // ------------------------------------ TMA + MMA ------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, KT, false, false);
+      constexpr uint32_t idesc_o = make_idesc_bf16(128, 64, false, true);
+      auto issue_scores = [&](int buf) {
+        const uint32_t kaddr = smem_u32(sK + buf * kKV);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_bf16(tmem_base + buf * KT, make_smem_desc(smem_u32(sQ) + ks * 32, 16, 1024),
+                    make_smem_desc(kaddr + ks * 32, 16, 1024), idesc_s, ks > 0);
+        umma_commit(&bar_s[buf]);
+      };
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      mbar_expect_tx(bar_q, kTileBytes);
+      tma_load_3d(sQ, &tm_q, bar_q, h * kD, q0, b);
+      for (int t = 0; t < 2 && t < nkt; ++t) {
+        mbar_expect_tx(&bar_k[t], kKV);
+        tma_load_3d(sK + t * kKV, &tm_k, &bar_k[t], h * kD, t * KT, b);
+        mbar_expect_tx(&bar_v[t], kKV);
+        tma_load_3d(sV + t * kKV, &tm_v, &bar_v[t], h * kD, t * KT, b);
+      }
+      bool ok = mbar_wait(bar_q, 0, abort_flag, p.status, kErrFullWait) &&
+                mbar_wait(&bar_k[0], 0, abort_flag, p.status, kErrFullWait);
+      if (ok) {
+        tc_fence_after();
+        issue_scores(0);
+        if (nkt > 1) {
+          ok = mbar_wait(&bar_k[1], 0, abort_flag, p.status, kErrFullWait);
+          if (ok) {
+            tc_fence_after();
+            issue_scores(1);
+          }
+        }
+      }
+      for (int j = 0; j < nkt && ok; ++j) {
+        const int sb = j & 1;
+        const uint32_t use = (j >> 1) & 1;  // parity of the j-th tile's use of a double-buffered resource
+        if (j + 2 < nkt) {  // K buffer sb is free once the scores of tile j have retired
+          ok = mbar_wait(&bar_s[sb], use, abort_flag, p.status, kErrAccFullWait);
+          if (!ok) break;
+          mbar_expect_tx(&bar_k[sb], kKV);
+          tma_load_3d(sK + sb * kKV, &tm_k, &bar_k[sb], h * kD, (j + 2) * KT, b);
+        }
+        if (j >= 1 && j + 1 < nkt) {  // V buffer (j+1) & 1 held tile j-1: free once its P·V has retired
+          ok = mbar_wait(bar_o, (j - 1) & 1, abort_flag, p.status, kErrAccFullWait);
+          if (!ok) break;
+          const int vb = (j + 1) & 1;
+          mbar_expect_tx(&bar_v[vb], kKV);
+          tma_load_3d(sV + vb * kKV, &tm_v, &bar_v[vb], h * kD, (j + 1) * KT, b);
+        }
+        ok = mbar_wait(bar_p, j & 1, abort_flag, p.status, kErrAccEmptyWait) &&
+             mbar_wait(&bar_v[sb], use, abort_flag, p.status, kErrFullWait);
+        if (!ok) break;
+        tc_fence_after();
+        {
+          const uint32_t pv = smem_u32(sV + sb * kKV);
+#pragma unroll
+          for (int ks = 0; ks < KT / 16; ++ks)
+            umma_bf16(t_o, make_smem_desc(smem_u32(sP) + ks * 32, 16, 1024), make_smem_desc(pv + ks * 2048, 8192, 1024),
+                      idesc_o, (j > 0) || (ks > 0));
+          umma_commit(bar_o);
+        }
+        if (j + 2 < nkt) {  // scores of tile j+2 into the buffer every softmax warp has emptied
+          ok = mbar_wait(&bar_k[sb], ((j + 2) >> 1) & 1, abort_flag, p.status, kErrFullWait) &&
+               mbar_wait(&bar_sfree[sb], use, abort_flag, p.status, kErrAccEmptyWait);
+          if (!ok) break;
+          tc_fence_after();
+          issue_scores(sb);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------ softmax ------------------------------------
+    const int quad = warp & 3;
+    const int part = warp >> 2;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const int q = q0 + row;
+    const bool q_valid = q < S;
+    const long long tq = static_cast<long long>(b) * S + (q_valid ? q : 0);
+    bool q_live = q_valid;
+    if (MASK == 1 && q_valid) q_live = p.key_keep[tq] != 0;
+    const uint4* bias_row = POS == 1 ? reinterpret_cast<const uint4*>(
+                                           p.bias + ((static_cast<long long>(b) * p.heads + h) * S + (q_valid ? q : 0)) * p.ldb)
+                                     : nullptr;
+    float m_run = -INFINITY, l_part = 0.f;
+    uint4 bias_pf[4] = {};
+    if (POS == 1) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) bias_pf[g] = __ldg(bias_row + ((part * 32) >> 3) + g);
+    }
+    // a wait's answer is agreed by the whole warp: the TMEM loads, votes and arrivals below are warp-collective
+    auto wait_all = [&](uint64_t* bar, uint32_t parity, int err) {
+      return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, p.status, err)) != 0;
+    };
+    bool ok = true;
+    for (int j = 0; j < nkt; ++j) {
+      const int sb = j & 1;
+      const int kb = j * KT + part * 32;  // first key of this thread's column group
+      uint4 keep_lo = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u), keep_hi = keep_lo;
+      if (MASK == 1) {  // this thread's 32 keep bytes (keys past the end read as dropped)
+        const unsigned char* kp = p.key_keep + static_cast<long long>(b) * S + kb;
+        if (kb + 32 <= S && ((reinterpret_cast<uintptr_t>(kp) & 15) == 0)) {
+          keep_lo = __ldg(reinterpret_cast<const uint4*>(kp));
+          keep_hi = __ldg(reinterpret_cast<const uint4*>(kp) + 1);
+        } else {
+          unsigned int w[8] = {};
+          for (int k = 0; k < 32; ++k)
+            if (kb + k < S && kp[k]) w[k >> 2] |= 1u << (8 * (k & 3));
+          keep_lo = make_uint4(w[0], w[1], w[2], w[3]);
+          keep_hi = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+      }
+      if (!wait_all(&bar_s[sb], (j >> 1) & 1, kErrAccFullWait)) { ok = false; break; }
+      tc_fence_after();
+      float s[32];
+      {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_base + sb * KT + lane_addr + part * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(r[i]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_sfree[sb]);
+      if (POS == 1) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const uint4 bvec = bias_pf[g];
+          const uint32_t w[4] = {bvec.x, bvec.y, bvec.z, bvec.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            s[g * 8 + 2 * e] += __uint_as_float(w[e] << 16);
+            s[g * 8 + 2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+          }
+        }
+        if (j + 1 < nkt) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) bias_pf[g] = __ldg(bias_row + ((kb + KT) >> 3) + g);
+        }
+      }
+      if (MASK == 0) {
+        if (j * KT + KT > S) {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) s[k] = (kb + k < S) ? s[k] : -INFINITY;
+        }
+      } else {
+        const uint32_t kw[8] = {keep_lo.x, keep_lo.y, keep_lo.z, keep_lo.w, keep_hi.x, keep_hi.y, keep_hi.z, keep_hi.w};
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const bool keep = ((kw[k >> 2] >> (8 * (k & 3))) & 0xffu) != 0 && (kb + k < S);
+          s[k] = keep ? s[k] : -INFINITY;
+        }
+      }
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int k = 0; k < 32; ++k) tmax = fmaxf(tmax, s[k]);
+      float* red_t = red + sb * 256;  // per-tile-parity copy: the partner may still be reading the previous tile's
+      red_t[part * kTile + row] = tmax;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_pair[quad]);
+      if (!wait_all(&bar_pair[quad], j & 1, kErrGeneric)) { ok = false; break; }
+      tmax = fmaxf(red_t[row], red_t[kTile + row]);
+      const float m_new = fmaxf(m_run, tmax);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = (m_run == -INFINITY) ? 0.f : ex2((m_run - m_use) * p.scale_log2);
+      const float neg_ms = -m_use * p.scale_log2;
+      float lsum = 0.f;
+#pragma unroll
+      for (int k = 0; k < 32; ++k) {
+        s[k] = ex2(fmaf(s[k], p.scale_log2, neg_ms));
+        lsum += s[k];
+      }
+      l_part = l_part * alpha + lsum;
+      m_run = m_new;
+      if (j > 0) {  // P·V of the previous tile retired: its P is consumed and O is stable
+        if (!wait_all(bar_o, (j - 1) & 1, kErrAccFullWait)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_o + lane_addr + part * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st_32x32b_x32(t_o + lane_addr + part * 32, r);
+          tmem_st_wait();
+        }
+      }
+#pragma unroll
+      for (int g4 = 0; g4 < 4; ++g4) {
+        uint4 u;
+        u.x = pack_bf16(s[g4 * 8 + 0], s[g4 * 8 + 1]);
+        u.y = pack_bf16(s[g4 * 8 + 2], s[g4 * 8 + 3]);
+        u.z = pack_bf16(s[g4 * 8 + 4], s[g4 * 8 + 5]);
+        u.w = pack_bf16(s[g4 * 8 + 6], s[g4 * 8 + 7]);
+        *reinterpret_cast<uint4*>(sP + swz128(row, part * 4 + g4)) = u;
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_p);
+    }
+    // row sums of the two column groups, then the output
+    if (ok) {
+      float* red_t = red + (nkt & 1) * 256;
+      red_t[part * kTile + row] = l_part;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_pair[quad]);
+      ok = wait_all(&bar_pair[quad], nkt & 1, kErrGeneric);
+      const float l_run = red_t[row] + red_t[kTile + row];
+      if (ok && wait_all(bar_o, (nkt - 1) & 1, kErrAccFullWait)) {
+        tc_fence_after();
+        const float inv = (q_live && l_run > 0.f) ? 1.f / l_run : 0.f;
+        __nv_bfloat16* o = p.out + tq * p.ldo + h * kD + part * 32;
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_o + lane_addr + part * 32, r);
+        tmem_ld_wait();
+        if (q_valid) {
+          uint32_t w[16];
+#pragma unroll
+          for (int g = 0; g < 16; ++g) w[g] = pack_bf16(__uint_as_float(r[2 * g]) * inv, __uint_as_float(r[2 * g + 1]) * inv);
+          store_bf16x16(o, w);
+          store_bf16x16(o + 16, w + 8);
+        }
+        if (q_valid && part == 0 && p.lse)
+          p.lse[(static_cast<long long>(b) * p.heads + h) * S + q] =
+              (q_live && l_run > 0.f) ? (m_run * p.scale_log2 + log2f(l_run)) : INFINITY;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+// --------------------------------------------------------------------------------------------
 // backward
 // --------------------------------------------------------------------------------------------
 struct AttnBwdDev {
@@ -927,6 +1251,9 @@ int make_head_map(CUtensorMap* m, const void* ptr, const AttnArgs* a, long long 
 
 // Keys per tile of the forward kernel: 64 (two 256-thread CTAs per SM) or 128 (one 512-thread CTA).
 int g_fwd_key_tile = 64;
+// With 64-key tiles and neither document ids nor in-kernel table gathers: the warp-specialised kernel (a dedicated
+// TMA/MMA warp, mbarriers instead of block-wide barriers).
+int g_fwd_specialised = 1;
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -966,6 +1293,22 @@ extern "C" int db200_attn_fwd(const AttnArgs* a, void* stream_) {
   d.status = db200_status_ptr();
   const int pos_mode = d.bias ? 1 : (pos ? 2 : 0);
   const int mask_mode = d.doc_ids ? 2 : (d.key_keep ? 1 : 0);
+  if (kt == 64 && g_fwd_specialised && mask_mode != 2 && pos_mode != 2) {
+    using WsKernel = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, AttnDev);
+    static const WsKernel ws[2][2] = {{attn_fwd_ws_kernel<0, 0>, attn_fwd_ws_kernel<0, 1>},
+                                      {attn_fwd_ws_kernel<1, 0>, attn_fwd_ws_kernel<1, 1>}};
+    static bool ws_configured[16][2][2] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    dev = (dev >= 0 && dev < 16) ? dev : 0;
+    const WsKernel kern = ws[mask_mode][pos_mode];
+    if (!ws_configured[dev][mask_mode][pos_mode]) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdWsSmem::kTotal) != cudaSuccess) return -3;
+      ws_configured[dev][mask_mode][pos_mode] = true;
+    }
+    dim3 grid((a->S + kTile - 1) / kTile, a->heads, a->B);
+    return launch_pdl(kern, grid, dim3(kFwdWsThreads), FwdWsSmem::kTotal, stream, tq, tk, tv, d) == cudaSuccess ? 0 : -4;
+  }
   const int wide = kt == 128 ? 1 : 0;
   const int smem = wide ? FwdSmem<128>::total(a->S, pos_mode == 2) : FwdSmem<64>::total(a->S, pos_mode == 2);
   using FwdKernel = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, AttnDev);
@@ -1070,8 +1413,10 @@ extern "C" int db200_attn_doc_tiles(const void* doc_ids, void* tiles, int B, int
 }
 
 // 64 or 128 keys per tile in the forward kernel (anything else selects 64); returns the previous value.
+// 65 selects 64-key tiles on the kernel without warp specialisation (A/B comparisons, tests).
 extern "C" int db200_attn_set_fwd_key_tile(int keys) {
-  const int old = g_fwd_key_tile;
+  const int old = g_fwd_key_tile == 128 ? 128 : (g_fwd_specialised ? 64 : 65);
   g_fwd_key_tile = keys == 128 ? 128 : 64;
+  g_fwd_specialised = keys == 65 ? 0 : 1;
   return old;
 }

@@ -64,8 +64,9 @@ _TC_REJECTED = -13  # launcher: this bucket map / table size needs the table pat
 
 
 def set_forward_key_tile(keys: int) -> int:
-    """Keys per tile of the forward kernel: 64 (256-thread CTAs, two per SM; the default) or 128 (one 512-thread CTA per
-    SM). Returns the previous setting. The results agree to rounding; the choice is about latency hiding."""
+    """Keys per tile of the forward kernel: 64 (two CTAs per SM; warp-specialised where the mask / position mode allows
+    it: the default), 65 (64-key tiles without warp specialisation) or 128 (one 512-thread CTA per SM). Returns the
+    previous setting. The results agree to rounding; the choice is about latency hiding."""
     return int(_lib.lib().db200_attn_set_fwd_key_tile(c_int(int(keys))))
 
 

@@ -68,7 +68,7 @@ def bench_attention(a) -> None:
     from deberta_b200.ops.attention_cuda import set_forward_key_tile
 
     kw = dict(heads=h, scale_factor=3, bucket_size=256, max_position=512, att_span=span)
-    for tile in ((64, 128) if a.key_tile == 0 else (a.key_tile,)):
+    for tile in ((64, 65, 128) if a.key_tile == 0 else (a.key_tile,)):
         set_forward_key_tile(tile)
         for name, pkk, pqq in (("content only", None, None), ("disentangled", pk, pq)):
             f = lambda: disentangled_attention(q, k, v, pkk, pqq, **kw)  # noqa: E731
@@ -148,7 +148,7 @@ def main() -> None:
     p.add_argument("--seq", type=int, default=512)
     p.add_argument("--heads", type=int, default=12)
     p.add_argument("--iters", type=int, default=5)
-    p.add_argument("--key-tile", type=int, default=0, help="attention forward: 64 or 128 keys per tile (0: both)")
+    p.add_argument("--key-tile", type=int, default=0, help="attention forward: 64 (warp-specialised), 65 (64 keys, block barriers) or 128 keys per tile (0: all)")
     a = p.parse_args()
     {"gemm": bench_gemm, "ffn": bench_ffn, "attention": bench_attention, "posbias": bench_posbias, "vocab_ce": bench_vocab_ce, "layer": bench_layer}[a.op](a)
 

@@ -12,9 +12,10 @@ from deberta_b200.ops.attention import (disentangled_attention, disentangled_att
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=[64, 128], ids=["kt64", "kt128"])
+@pytest.fixture(autouse=True, params=[64, 65, 128], ids=["kt64ws", "kt64", "kt128"])
 def forward_key_tile(request):
-    """Every case runs on both forward kernels: 64 keys per tile (two CTAs per SM) and 128 (one CTA per SM)."""
+    """Every case runs on the three forward kernels: 64 keys per tile with a dedicated TMA/MMA warp (the default where
+    it applies), 64 keys per tile with block-wide barriers (65), and 128 keys per tile (one CTA per SM)."""
     from deberta_b200.ops.attention_cuda import set_forward_key_tile
 
     old = set_forward_key_tile(request.param)
