@@ -70,6 +70,7 @@ struct DevParams {
   float gscale;                     // dLoss/dlogit scale (backward)
   const float* gscale_ptr;          // optional device scalar multiplied into gscale
   float* a_sum;                     // [M] fp32 or null: += sum_k A[m,k] (fp32 output with M-major A: bias gradients)
+  int half_n;                       // SwiGLU epilogues: F, the width of the gate (and of the up) half
 };
 
 // Counter-based uniform in (0,1) from (seed, row, column): 32-bit multiply-xorshift mixing (two rounds), the seed's
@@ -123,7 +124,9 @@ __device__ __forceinline__ float dgelu_erf(float x) {
 // MODE selects the epilogue at compile time (one lean code path per instantiation):
 // 0 bf16 output (+bias, +residual), 1 GELU (two outputs), 2 GELU derivative, 3 fp32 output (store / accumulate /
 // split-K), 4 cross-entropy forward, 5 cross-entropy backward, 6 GELU with its derivative as the first output,
-// 7 product with a stored operand (the backward partner of 6: no transcendental in the epilogue).
+// 7 product with a stored operand (the backward partner of 6: no transcendental in the epilogue),
+// 8 SwiGLU forward (a tile = 128 gate columns and the 128 up columns that go with them; three outputs' worth of
+// stores), 9 SwiGLU backward.
 template <int BN, bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -131,7 +134,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             const DevParams p) {
   using L = SmemLayout<BN>;
   constexpr int kEpi = MODE == 1 ? EPI_GELU : MODE == 2 ? EPI_DGELU : MODE == 4 ? EPI_CE_FWD : MODE == 5 ? EPI_CE_BWD
-                       : MODE == 6 ? EPI_GELU_GRAD : MODE == 7 ? EPI_MUL : EPI_NONE;
+                       : MODE == 6 ? EPI_GELU_GRAD : MODE == 7 ? EPI_MUL : MODE == 8 ? EPI_SWIGLU
+                       : MODE == 9 ? EPI_SWIGLU_BWD : EPI_NONE;
+  constexpr bool kSwigluFwd = MODE == 8;  // needs BN == 256 and a K-major B (instantiated only that way)
   constexpr bool kTwoOut = kEpi == EPI_GELU || kEpi == EPI_GELU_GRAD;  // second output: gelu of the pre-activation
   constexpr bool kAuxMul = kEpi == EPI_DGELU || kEpi == EPI_MUL;       // accumulator times a function of `aux`
   constexpr bool kOutF32 = MODE == 3;
@@ -218,7 +223,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               tma_load_3d(sa + c * (BK * 128), &tmap_a, &full_bar[stage], m0 + c * 64, kb * BK, z);
           }
           if (!B_MN) {
-            if (BN == 256) {
+            if (kSwigluFwd) {  // 128 gate rows of W12 and the 128 up rows of the same hidden columns
+              tma_load_3d(sb, &tmap_b, &full_bar[stage], kb * BK, n0 / 2, z);
+              tma_load_3d(sb + 128 * 128, &tmap_b, &full_bar[stage], kb * BK, p.half_n + n0 / 2, z);
+            } else if (BN == 256) {
               tma_load_3d(sb, &tmap_b, &full_bar[stage], kb * BK, n0, z);
               tma_load_3d(sb + 128 * 128, &tmap_b, &full_bar[stage], kb * BK, n0 + 128, z);
             } else {
@@ -441,6 +449,115 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[acc]);
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      } else if constexpr (kEpi == EPI_SWIGLU) {
+        // accumulator columns [0, 128) = gate, [128, 256) = up of hidden columns j0 .. j0 + 127; a warp takes two
+        // 32-column chunks of both halves
+        const int j0 = n0 / 2;
+        __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldo;
+        __nv_bfloat16* hrow = p.out2 + static_cast<long long>(row) * p.ldo2;
+#pragma unroll 1
+        for (int cc = half * 2; cc < half * 2 + 2; ++cc) {
+          const int jc = j0 + cc * 32;
+          if (jc >= p.half_n) continue;  // warp-uniform
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32b_x32(t_row + cc * 32, rg);
+          tmem_ld_32x32b_x32(t_row + 128 + cc * 32, ru);
+          tmem_ld_wait();
+          if (!row_ok) continue;
+          const bool full = jc + 32 <= p.half_n;
+          float g[32], u[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            g[j] = __uint_as_float(rg[j]) * p.alpha;
+            u[j] = __uint_as_float(ru[j]) * p.alpha;
+          }
+          if (bias) {
+            for (int j = 0; j < 32; ++j) {
+              if (jc + j < p.half_n) {
+                g[j] += __bfloat162float(bias[jc + j]);
+                u[j] += __bfloat162float(bias[p.half_n + jc + j]);
+              }
+            }
+          }
+          float hv[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {  // from the bf16-rounded halves, as a separate activation pass would see them
+            const float gr = __bfloat162float(__float2bfloat16(g[j])), ur = __bfloat162float(__float2bfloat16(u[j]));
+            float sig;
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(sig) : "f"(1.0f + ex2_approx(gr * -1.4426950408889634f)));
+            hv[j] = gr * sig * ur;
+          }
+          const bool vec = full && (p.ldo % 8 == 0) && (p.half_n % 8 == 0) && (p.ldo2 % 8 == 0);
+          if (vec) {
+            store_bf16x32(gu + jc, g);
+            store_bf16x32(gu + p.half_n + jc, u);
+            store_bf16x32(hrow + jc, hv);
+          } else {
+            for (int j = 0; j < 32; ++j) {
+              if (jc + j < p.half_n) {
+                gu[jc + j] = __float2bfloat16(g[j]);
+                gu[p.half_n + jc + j] = __float2bfloat16(u[j]);
+                hrow[jc + j] = __float2bfloat16(hv[j]);
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (++acc == acc_stages) { acc = 0; acc_phase ^= 1; }
+      } else if constexpr (kEpi == EPI_SWIGLU_BWD) {
+        const __nv_bfloat16* gu = p.aux + static_cast<long long>(row) * p.ldaux;
+        __nv_bfloat16* dgu = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldo;
+#pragma unroll 1
+        for (int c = half * kChunksPerHalf; c < (half + 1) * kChunksPerHalf; ++c) {
+          const int nc = n0 + c * 32;
+          if (nc >= p.N) continue;  // warp-uniform (N = F here)
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_row + c * 32, r);
+          const bool full = nc + 32 <= p.N;
+          const bool vec = full && row_ok && (p.ldaux % 8 == 0) && (p.ldo % 8 == 0) && (p.half_n % 8 == 0);
+          uint32_t gw[16], uw[16];
+          if (vec) {
+            load_bf16x32(gu + nc, gw);
+            load_bf16x32(gu + p.half_n + nc, uw);
+          }
+          tmem_ld_wait();
+          if (!row_ok) continue;
+          float dg[32], du[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float gate, up;
+            if (vec) {
+              gate = (j & 1) ? bf16_hi(gw[j >> 1]) : bf16_lo(gw[j >> 1]);
+              up = (j & 1) ? bf16_hi(uw[j >> 1]) : bf16_lo(uw[j >> 1]);
+            } else {
+              const bool in = nc + j < p.N;
+              gate = in ? __bfloat162float(gu[nc + j]) : 0.f;
+              up = in ? __bfloat162float(gu[p.half_n + nc + j]) : 0.f;
+            }
+            const float dh = __uint_as_float(r[j]) * p.alpha;
+            float sig;
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(sig) : "f"(1.0f + ex2_approx(gate * -1.4426950408889634f)));
+            dg[j] = dh * up * sig * fmaf(gate, 1.0f - sig, 1.0f);
+            du[j] = dh * gate * sig;
+          }
+          if (vec) {
+            store_bf16x32(dgu + nc, dg);
+            store_bf16x32(dgu + p.half_n + nc, du);
+          } else {
+            for (int j = 0; j < 32; ++j) {
+              if (nc + j < p.N) {
+                dgu[nc + j] = __float2bfloat16(dg[j]);
+                dgu[p.half_n + nc + j] = __float2bfloat16(du[j]);
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (++acc == acc_stages) { acc = 0; acc_phase ^= 1; }
       } else {
 #pragma unroll 1
       for (int cp = half * (kChunksPerHalf / 2); cp < (half + 1) * (kChunksPerHalf / 2); ++cp) {
@@ -870,6 +987,12 @@ extern "C" int db200_gemm_bf16(const GemmArgs* a, void* stream_) {
   const bool two_out = p.epi == EPI_GELU || p.epi == EPI_GELU_GRAD;
   if (two_out && (p.out_f32 || !p.out2)) return -11;
   if ((p.epi == EPI_DGELU || p.epi == EPI_MUL) && (p.out_f32 || !p.aux)) return -11;
+  if (p.epi == EPI_SWIGLU && (p.out_f32 || !p.out2 || a->batch != 1 || (a->N % 2) || a->a_mn || a->b_mn || a->N <= 128 ||
+                              a->residual))
+    return -11;
+  if (p.epi == EPI_SWIGLU_BWD && (p.out_f32 || !p.aux || a->batch != 1 || a->a_mn || !a->b_mn || a->residual)) return -11;
+  p.half_n = p.epi == EPI_SWIGLU ? a->N / 2 : (p.epi == EPI_SWIGLU_BWD ? a->N : 0);
+  if (p.epi == EPI_SWIGLU) p.tiles_n = (p.half_n + 127) / 128;  // a tile = 128 gate columns + their 128 up columns
 
   const int tiles = p.tiles_m * p.tiles_n * p.batch;
   int splits = 1;
@@ -911,7 +1034,8 @@ extern "C" int db200_gemm_bf16(const GemmArgs* a, void* stream_) {
     return ptr && !(reinterpret_cast<uintptr_t>(ptr) & 15) && (ld % 8 == 0) && (a->batch == 1 || bs % 8 == 0);
   };
   p.tma_out = 0;
-  if (!p.out_f32 && splits == 1 && p.epi != EPI_CE_FWD && p.epi != EPI_CE_BWD && tma_ok(a->out, a->ldo, a->bs_out) &&
+  if (!p.out_f32 && splits == 1 && p.epi != EPI_CE_FWD && p.epi != EPI_CE_BWD && p.epi != EPI_SWIGLU &&
+      p.epi != EPI_SWIGLU_BWD && tma_ok(a->out, a->ldo, a->bs_out) &&
       (!two_out || tma_ok(a->out2, a->ldo2, a->bs_out2))) {
     if (db200_make_tmap_bf16(&to, a->out, a->N, a->M, a->batch, a->ldo, a->bs_out, 32) == 0 &&
         (!two_out || db200_make_tmap_bf16(&to2, a->out2, a->N, a->M, a->batch, a->ldo2, a->bs_out2, 32) == 0))
@@ -921,6 +1045,10 @@ extern "C" int db200_gemm_bf16(const GemmArgs* a, void* stream_) {
   const int grid = min(tiles * splits, num_sms());
   const int mode = p.out_f32 ? 3 : p.epi == EPI_GELU ? 1 : p.epi == EPI_DGELU ? 2 : p.epi == EPI_CE_FWD ? 4
                    : p.epi == EPI_CE_BWD ? 5 : p.epi == EPI_GELU_GRAD ? 6 : p.epi == EPI_MUL ? 7 : 0;
+  if (p.epi == EPI_SWIGLU) return launch<256, false, false, 8>(ta, tb, to, to2, p, grid, stream);
+  if (p.epi == EPI_SWIGLU_BWD)
+    return BN == 256 ? launch<256, false, true, 9>(ta, tb, to, to2, p, grid, stream)
+                     : launch<128, false, true, 9>(ta, tb, to, to2, p, grid, stream);
 #define DISPATCH_MODE(BN_, AM_, BM_)                                                         \
   switch (mode) {                                                                            \
     case 0: return launch<BN_, AM_, BM_, 0>(ta, tb, to, to2, p, grid, stream);               \

@@ -19,7 +19,12 @@ int db200_set_pdl(int on);  // returns the previous setting  // stream-ordered c
 // ----- GEMM ---------------------------------------------------------------------------
 enum { EPI_NONE = 0, EPI_GELU = 1, EPI_DGELU = 2, EPI_CE_FWD = 3, EPI_CE_BWD = 4,
        EPI_GELU_GRAD = 5,  // out = gelu'(z), out2 = gelu(z): the backward pass then needs no transcendental
-       EPI_MUL = 6 };      // out = acc * aux (aux = the gelu'(z) written by EPI_GELU_GRAD)
+       EPI_MUL = 6,        // out = acc * aux (aux = the gelu'(z) written by EPI_GELU_GRAD)
+       // SwiGLU inside the GEMMs around it. B = W12 [2F, K] (gate rows, then up rows), N = 2F:
+       // out [M, 2F] = [gate | up] (kept for the backward pass), out2 [M, F] = silu(gate) * up.
+       EPI_SWIGLU = 7,
+       // its backward: A·B = dh [M, F] (N = F), aux = [gate | up] [M, 2F]; out [M, 2F] = [dh*up*silu'(gate) | dh*silu(gate)]
+       EPI_SWIGLU_BWD = 8 };
 
 typedef struct GemmArgs {
   const void* A;     // bf16

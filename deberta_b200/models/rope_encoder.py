@@ -17,8 +17,7 @@ from transformers import PretrainedConfig, PreTrainedModel
 from transformers.modeling_outputs import BaseModelOutput
 
 from deberta_b200.ops.attention import rope_attention
-from deberta_b200.ops.elementwise import swiglu
-from deberta_b200.ops.linear import ffn_gelu, linear
+from deberta_b200.ops.linear import ffn_gelu, ffn_swiglu, linear
 
 from .activations import get_act_fn
 from .mask_utils import AttnMask
@@ -165,7 +164,7 @@ class DebertaRoPEMLP(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.ffn_type == "swiglu":
-            return linear(swiglu(linear(x, self.w12.weight, self.w12.bias)), self.w3.weight, self.w3.bias)
+            return ffn_swiglu(x, self.w12.weight, self.w12.bias, self.w3.weight, self.w3.bias)
         if self.act_name == "gelu":
             return ffn_gelu(x, self.dense_in.weight, self.dense_in.bias, self.dense_out.weight, self.dense_out.bias)
         return linear(self.act(linear(x, self.dense_in.weight, self.dense_in.bias)),

@@ -21,7 +21,7 @@ c_int = ctypes.c_int
 c_ll = ctypes.c_longlong
 c_float = ctypes.c_float
 
-EPI_NONE, EPI_GELU, EPI_DGELU, EPI_CE_FWD, EPI_CE_BWD, EPI_GELU_GRAD, EPI_MUL = 0, 1, 2, 3, 4, 5, 6
+EPI_NONE, EPI_GELU, EPI_DGELU, EPI_CE_FWD, EPI_CE_BWD, EPI_GELU_GRAD, EPI_MUL, EPI_SWIGLU, EPI_SWIGLU_BWD = range(9)
 
 STATUS_NAMES = {
     0: "ok",

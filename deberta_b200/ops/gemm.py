@@ -15,9 +15,10 @@ import ctypes
 import torch
 
 from . import _lib
-from ._lib import EPI_DGELU, EPI_GELU, EPI_GELU_GRAD, EPI_MUL, EPI_NONE
+from ._lib import EPI_DGELU, EPI_GELU, EPI_GELU_GRAD, EPI_MUL, EPI_NONE, EPI_SWIGLU, EPI_SWIGLU_BWD
 
-__all__ = ["gemm", "gemm_reference", "EPI_NONE", "EPI_GELU", "EPI_DGELU", "EPI_GELU_GRAD", "EPI_MUL"]
+__all__ = ["gemm", "gemm_reference", "EPI_NONE", "EPI_GELU", "EPI_DGELU", "EPI_GELU_GRAD", "EPI_MUL", "EPI_SWIGLU",
+           "EPI_SWIGLU_BWD"]
 
 
 def _gelu(x: torch.Tensor) -> torch.Tensor:
@@ -61,6 +62,16 @@ def gemm_reference(
     if epi == EPI_GELU:
         z = acc.to(out_dtype)
         return z, _gelu(z.float()).to(out_dtype)
+    if epi == EPI_SWIGLU:  # ([gate | up], silu(gate) * up) with the activation taken from the rounded halves
+        gu = acc.to(out_dtype)
+        f = gu.shape[-1] // 2
+        return gu, (torch.nn.functional.silu(gu[..., :f].float()) * gu[..., f:].float()).to(out_dtype)
+    if epi == EPI_SWIGLU_BWD:  # acc = dh [M, F], aux = [gate | up]
+        assert aux is not None
+        f = acc.shape[-1]
+        gate, up = aux[..., :f].float(), aux[..., f:].float()
+        sig = torch.sigmoid(gate)
+        return torch.cat([acc * up * sig * (1 + gate * (1 - sig)), acc * gate * sig], dim=-1).to(out_dtype)
     if epi == EPI_GELU_GRAD:  # (gelu'(z), gelu(z)) of the rounded pre-activation
         z = acc.to(out_dtype).float()
         return _dgelu(z).to(out_dtype), _gelu(z).to(out_dtype)
@@ -112,7 +123,7 @@ def gemm(
             out_dtype=out_dtype or (out.dtype if out is not None else None),
         )
         if out is not None:
-            if epi in (EPI_GELU, EPI_GELU_GRAD):
+            if epi in (EPI_GELU, EPI_GELU_GRAD, EPI_SWIGLU):
                 out.copy_(res[0])
                 if out2 is not None:
                     out2.copy_(res[1])
@@ -136,7 +147,8 @@ def gemm(
     batch = a.shape[0] if batched else 1
     if out is None:
         dt = out_dtype or torch.bfloat16
-        shape = (batch, M, N) if batched else (M, N)
+        n_out = 2 * N if epi == EPI_SWIGLU_BWD else N  # the SwiGLU backward writes both halves of [d_gate | d_up]
+        shape = (batch, M, n_out) if batched else (M, n_out)
         out = torch.empty(shape, dtype=dt, device=a.device)
         if accumulate:
             out.zero_()
@@ -144,6 +156,8 @@ def gemm(
         raise ValueError("GEMM output must be bf16 or fp32")
     if epi in (EPI_GELU, EPI_GELU_GRAD) and out2 is None:
         out2 = torch.empty_like(out)
+    if epi == EPI_SWIGLU and out2 is None:
+        out2 = torch.empty((M, N // 2), dtype=out.dtype, device=a.device)
 
     args = GemmArgsCache.get()
     lda, bsa = _ld(a)
@@ -174,7 +188,7 @@ def gemm(
         if t is not None and t.data_ptr() % 16:
             raise ValueError("GEMM epilogue tensors must be 16-byte aligned")
     _lib.call("db200_gemm_bf16", ctypes.byref(args), _lib.stream_ptr())
-    if epi in (EPI_GELU, EPI_GELU_GRAD):
+    if epi in (EPI_GELU, EPI_GELU_GRAD, EPI_SWIGLU):
         return out, out2
     return out
 

@@ -13,9 +13,9 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
-from .gemm import EPI_DGELU, EPI_GELU, EPI_GELU_GRAD, EPI_MUL, gemm
+from .gemm import EPI_DGELU, EPI_GELU, EPI_GELU_GRAD, EPI_MUL, EPI_SWIGLU, EPI_SWIGLU_BWD, gemm
 
-__all__ = ["linear", "linear_qkv", "ffn_gelu", "use_kernels"]
+__all__ = ["linear", "linear_qkv", "ffn_gelu", "ffn_swiglu", "use_kernels"]
 
 
 def use_kernels(x: torch.Tensor) -> bool:
@@ -180,6 +180,52 @@ def ffn_gelu(x, w1, b1, w2, b2, residual=None):
         same = residual is x and x.requires_grad
         out = _FFNGelu.apply(x2, w1, b1, w2, b2, None if same else r2, same)
     return out.view(*lead, w2.shape[0])
+
+
+class _FFNSwiGLU(torch.autograd.Function):
+    """``W3·(silu(gate) ⊙ up) + b3`` with ``[gate | up] = W12·x + b12``: the activation and its derivative run in the
+    epilogues of the GEMMs next to them (``EPI_SWIGLU`` writes ``[gate | up]`` and the product from one accumulator
+    tile; ``EPI_SWIGLU_BWD`` turns ``dh = dy·W3`` into ``[d_gate | d_up]`` before it leaves the SM), so the forward has no
+    pass that re-reads the ``[tokens, 2F]`` projection and the backward none that writes and re-reads ``dh``."""
+
+    @staticmethod
+    def forward(ctx, x, w12, b12, w3, b3, residual):
+        gu, h = gemm(x, w12, bias=b12, epi=EPI_SWIGLU)
+        y = gemm(h, w3, bias=b3, residual=residual)
+        ctx.save_for_backward(x, w12, w3, gu, h)
+        ctx.params = (b12, b3)
+        ctx.has_res = residual is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w12, w3, gu, h = ctx.saved_tensors
+        b12, b3 = ctx.params
+        dy = dy.contiguous()
+        dgu = gemm(dy, w3, b_mn=True, epi=EPI_SWIGLU_BWD, aux=gu)
+        dw3, db3 = _param_grads(dy, h, w3, b3)
+        dx = gemm(dgu, w12, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw12, db12 = _param_grads(dgu, x, w12, b12)
+        return dx, dw12, db12, dw3, db3, (dy if ctx.has_res else None)
+
+
+def ffn_swiglu(x, w12, b12, w3, b3, residual=None):
+    """SwiGLU feed-forward block ``W3·(silu(gate) ⊙ up) + b3 (+ residual)``, ``[gate | up] = W12·x + b12``
+    (the reference's ``modeling/rope_encoder.py:290-343``)."""
+    f = w12.shape[0] // 2
+    fused = (use_kernels(x) and w12.dtype == torch.bfloat16 and w3.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0
+             and f % 8 == 0 and w12.shape[0] == 2 * f and f >= 64 and w3.shape[0] % 8 == 0
+             and not torch.compiler.is_compiling())
+    if not fused:
+        from .elementwise import swiglu
+
+        return linear(swiglu(linear(x, w12, b12)), w3, b3, residual)
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 or x2.stride(0) % 8:
+        x2 = x2.contiguous()
+    r2 = None if residual is None else residual.reshape(-1, w3.shape[0]).contiguous()
+    return _FFNSwiGLU.apply(x2, w12, b12, w3, b3, r2).view(*lead, w3.shape[0])
 
 
 # ---- fused query / key / value projection ------------------------------------------------------------

@@ -184,3 +184,21 @@ def test_compiled_backbones_train_step_matches_eager_on_cpu():
     loss_c, w_c = run(True)
     assert abs(loss_e - loss_c) < 1e-4 * max(1.0, abs(loss_e))
     torch.testing.assert_close(w_c, w_e, rtol=1e-4, atol=1e-6)
+
+
+def test_gemm_reference_swiglu_epilogues_are_consistent_with_autograd():
+    """The fp32 statements of the two SwiGLU epilogues (the oracle of the GPU test): forward halves and product, and a
+    backward that equals autograd's through ``silu(gate) * up``."""
+    from deberta_b200.ops.gemm import EPI_SWIGLU, EPI_SWIGLU_BWD, gemm_reference
+
+    torch.manual_seed(2)
+    x, w12, b12 = _t(5, 8), _t(12, 8), _t(12)
+    gu, h = gemm_reference(x, w12, bias=b12, epi=EPI_SWIGLU)
+    ref_gu = torch.nn.functional.linear(x, w12, b12)
+    torch.testing.assert_close(gu, ref_gu)
+    torch.testing.assert_close(h, torch.nn.functional.silu(ref_gu[:, :6]) * ref_gu[:, 6:])
+    dy, w3 = _t(5, 4), _t(4, 6)
+    dgu = gemm_reference(dy, w3, b_mn=True, epi=EPI_SWIGLU_BWD, aux=gu)
+    gu_ad = ref_gu.clone().requires_grad_(True)
+    (torch.nn.functional.silu(gu_ad[:, :6]) * gu_ad[:, 6:] @ w3.t() * dy).sum().backward()
+    torch.testing.assert_close(dgu, gu_ad.grad, rtol=1e-4, atol=1e-5)

@@ -196,3 +196,28 @@ def test_fused_qkv_projection_matches_three_linears():
         assert (ws[i].main_grad - want_w).abs().max() <= 3e-2 * want_w.abs().max()
         want_b = g.float().reshape(-1, n).sum(0)
         assert (bs[i].main_grad - want_b).abs().max() <= 3e-2 * want_b.abs().max()
+
+
+@pytest.mark.parametrize("T,H,F,bias", [(1024, 768, 2048, False), (300, 256, 200, True), (640, 768, 3072, True)])
+def test_swiglu_ffn_in_gemm_epilogues_matches_pytorch(T, H, F, bias):
+    """SwiGLU forward inside the W12 GEMM (writes [gate | up] and silu(gate)·up) and its backward inside the W3
+    data-gradient GEMM, against the fp32 statement; ragged F exercises the scalar tails."""
+    from deberta_b200.ops.linear import ffn_swiglu
+
+    torch.manual_seed(11)
+    x = _rand(T, H, scale=0.5).requires_grad_(True)
+    w12, w3 = _rand(2 * F, H, scale=0.05).requires_grad_(True), _rand(H, F, scale=0.05).requires_grad_(True)
+    b12 = _rand(2 * F, scale=0.1).requires_grad_(True) if bias else None
+    b3 = _rand(H, scale=0.1).requires_grad_(True) if bias else None
+    y = ffn_swiglu(x, w12, b12, w3, b3)
+    ref_in = [t.detach().float().requires_grad_(True) if t is not None else None for t in (x, w12, b12, w3, b3)]
+    xr, w12r, b12r, w3r, b3r = ref_in
+    gu = torch.nn.functional.linear(xr, w12r, b12r)
+    yr = torch.nn.functional.linear(torch.nn.functional.silu(gu[:, :F]) * gu[:, F:], w3r, b3r)
+    _close(y, yr, tol=3e-2)
+    g = torch.randn_like(yr)
+    y.backward(g.to(torch.bfloat16))
+    yr.backward(g)
+    _lib.check_status()
+    for got, ref in ((x, xr), (w12, w12r), (w3, w3r)) + (((b12, b12r), (b3, b3r)) if bias else ()):
+        _close(got.grad, ref.grad, tol=4e-2)
