@@ -716,6 +716,9 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
           for (int g = 0; g < 4; ++g) bias_pf[g] = __ldg(bias_row + ((kb + KT) >> 3) + g);
         }
+        // a 64-key tile is too short to hide a DRAM access behind: the 64 bytes of the tile after the next one are
+        // asked into the L2 already
+        if (j + 2 < nkt) asm volatile("prefetch.global.L2 [%0];" ::"l"(bias_row + ((kb + 2 * KT) >> 3)));
       }
       if (MASK == 0) {
         if (j * KT + KT > S) {

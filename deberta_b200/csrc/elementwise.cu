@@ -21,7 +21,7 @@ __device__ __forceinline__ unsigned int pack2(float a, float b) {
 // One thread rotates 4 pairs (8 features, 16 bytes). cos/sin: fp32 [S, rotary_dim] with every frequency stored twice
 // (entries 2i and 2i+1 equal), as the rotary cache of the model keeps them.
 __global__ void __launch_bounds__(256)
-rotary_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, long long ldx, long long ldy,
+rotary_kernel(const __nv_bfloat16* x, __nv_bfloat16* y, long long ldx, long long ldy,  // y may be x (in place)
               const float* __restrict__ cos_t, const float* __restrict__ sin_t, long long tokens, int S, int heads,
               int head_dim, int rotary_dim, float sign) {
   const int vec_per_head = head_dim / 8;

@@ -17,7 +17,7 @@ from transformers import PretrainedConfig, PreTrainedModel
 from transformers.modeling_outputs import BaseModelOutput
 
 from deberta_b200.ops.attention import rope_attention
-from deberta_b200.ops.linear import ffn_gelu, ffn_swiglu, linear
+from deberta_b200.ops.linear import ffn_gelu, ffn_swiglu, linear, split_qkv
 
 from .activations import get_act_fn
 from .mask_utils import AttnMask
@@ -128,19 +128,21 @@ class DebertaRoPESelfAttention(nn.Module):
             if self.rotary_dim > 0 else None
         )
 
-    def forward(self, x: torch.Tensor, attention_mask) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, attention_mask, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``out_proj(attention(x)) (+ residual)``; the residual is added in the projection's epilogue."""
         mask = AttnMask.from_any(attention_mask)
-        H = self.hidden_size
-        qkv = linear(x, self.qkv.weight, self.qkv.bias)
-        q, k, v = qkv[..., :H], qkv[..., H : 2 * H], qkv[..., 2 * H :]
+        q, k, v = split_qkv(linear(x, self.qkv.weight, self.qkv.bias))
         cos = sin = None
         if self.rope is not None:
             cos, sin = self.rope.get_cos_sin(x.shape[1], device=x.device, dtype=torch.float32)
         ctx = rope_attention(q, k, v, cos, sin, heads=self.num_heads, rotary_dim=self.rotary_dim,
                              dropout_p=self.attn_dropout, training=self.training, **mask.kwargs())
-        out = linear(ctx, self.out_proj.weight, self.out_proj.bias)
         keep = mask.token_keep()
-        return out if keep is None else out * keep[:, :, None].to(out.dtype)
+        if keep is None or self.out_proj.bias is None:
+            # (rows of inactive queries leave the attention as zeros: without a bias the projection keeps them zero)
+            return linear(ctx, self.out_proj.weight, self.out_proj.bias, residual=residual)
+        out = linear(ctx, self.out_proj.weight, self.out_proj.bias) * keep[:, :, None].to(ctx.dtype)
+        return out if residual is None else out + residual
 
 
 class DebertaRoPEMLP(nn.Module):
@@ -162,13 +164,15 @@ class DebertaRoPEMLP(nn.Module):
         else:
             raise ValueError(f"Unsupported ffn_type: {self.ffn_type}")
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``FFN(x) (+ residual)``; the residual is added in the epilogue of the second GEMM."""
         if self.ffn_type == "swiglu":
-            return ffn_swiglu(x, self.w12.weight, self.w12.bias, self.w3.weight, self.w3.bias)
+            return ffn_swiglu(x, self.w12.weight, self.w12.bias, self.w3.weight, self.w3.bias, residual=residual)
         if self.act_name == "gelu":
-            return ffn_gelu(x, self.dense_in.weight, self.dense_in.bias, self.dense_out.weight, self.dense_out.bias)
+            return ffn_gelu(x, self.dense_in.weight, self.dense_in.bias, self.dense_out.weight, self.dense_out.bias,
+                            residual=residual)
         return linear(self.act(linear(x, self.dense_in.weight, self.dense_in.bias)),
-                      self.dense_out.weight, self.dense_out.bias)
+                      self.dense_out.weight, self.dense_out.bias, residual=residual)
 
 
 class _KEELAlpha(nn.Module):
@@ -205,6 +209,12 @@ class DebertaRoPELayer(nn.Module):
 
     def forward(self, x: torch.Tensor, attention_mask) -> torch.Tensor:
         d = lambda h: _drop(h, self.dropout_p, self.training)  # noqa: E731
+        if not (self.training and self.dropout_p > 0.0):  # residual sums inside the GEMM epilogues
+            if self.norm_arch == "post":
+                x = self.norm1(self.attn(x, attention_mask, residual=x))
+                return self.norm2(self.mlp(x, residual=x))
+            x = self.outer_norm1(self.attn(self.inner_norm1(x), attention_mask, residual=self.alpha1(x) * x))
+            return self.outer_norm2(self.mlp(self.inner_norm2(x), residual=self.alpha2(x) * x))
         if self.norm_arch == "post":
             x = self.norm1(x + d(self.attn(x, attention_mask)))
             return self.norm2(x + d(self.mlp(x)))

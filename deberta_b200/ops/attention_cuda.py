@@ -421,17 +421,70 @@ def disentangled_attention_cuda(q, k, v, pos_k, pos_q, *, heads, scale_factor, b
     return _FlashAttention.apply(q, k, v, pos_k, pos_q, heads, scale, luts, key_keep, doc_ids)
 
 
+def _rotate_rows(x2, out, cos, sin, S: int, heads: int, head_dim: int, rotary_dim: int, inverse: bool) -> None:
+    """Rotary kernel over ``[rows, heads·head_dim]`` row views (``out`` may be ``x2``: in place)."""
+    _lib.call("db200_rotary_bf16", _lib.ptr(x2), _lib.ptr(out), ctypes.c_longlong(x2.stride(0)),
+              ctypes.c_longlong(out.stride(0)), _lib.ptr(cos), _lib.ptr(sin), ctypes.c_longlong(x2.shape[0]), c_int(S),
+              c_int(heads), c_int(head_dim), c_int(rotary_dim), c_int(int(inverse)), _lib.stream_ptr())
+
+
+class _RopeAttention(torch.autograd.Function):
+    """Rotation of q and k + flash attention as one autograd node. Forward: q and k, which a fused QKV projection
+    leaves side by side, are rotated by ONE launch into a ``[tokens, 2H]`` buffer. Backward: the attention kernel writes
+    dQ | dK | dV side by side and the inverse rotation runs in place on the first two thirds of that buffer, so the QKV
+    projection's backward receives one ``[tokens, 3H]`` tensor without a concatenation."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cos, sin, heads, rotary_dim, key_keep, doc_ids):
+        q, k, v = _token_major(q), _token_major(k), _token_major(v)
+        B, S, H = q.shape
+        T, d = B * S, H // heads
+        rows = lambda t: t.as_strided((T, H), (t.stride(1), 1), t.storage_offset())  # noqa: E731
+        qk = torch.empty((T, 2 * H), dtype=q.dtype, device=q.device)
+        if q.stride(1) == k.stride(1) and k.data_ptr() == q.data_ptr() + H * q.element_size():
+            both = q.as_strided((T, 2 * H), (q.stride(1), 1), q.storage_offset())
+            _rotate_rows(both, qk, cos, sin, S, 2 * heads, d, rotary_dim, False)
+        else:
+            _rotate_rows(rows(q), qk[:, :H], cos, sin, S, heads, d, rotary_dim, False)
+            _rotate_rows(rows(k), qk[:, H:], cos, sin, S, heads, d, rotary_dim, False)
+        qr = qk.as_strided((B, S, H), (S * 2 * H, 2 * H, 1), 0)
+        kr = qk.as_strided((B, S, H), (S * 2 * H, 2 * H, 1), H)
+        inner = _Ctx()
+        out = _FlashAttention.forward(inner, qr, kr, v, None, None, heads, math.sqrt(float(d)), None, key_keep, doc_ids)
+        ctx.inner = inner
+        ctx.rot = (cos, sin, heads, rotary_dim)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        cos, sin, heads, rotary_dim = ctx.rot
+        dq, dk, dv = _FlashAttention.backward(ctx.inner, dout)[:3]
+        B, S, H = dq.shape
+        # dq and dk are the first two column blocks of one [tokens, 3H] buffer: rotate both back where they are
+        both = dq.as_strided((B * S, 2 * H), (dq.stride(1), 1), dq.storage_offset())
+        _rotate_rows(both, both, cos, sin, S, 2 * heads, H // heads, rotary_dim, True)
+        return dq, dk, dv, None, None, None, None, None, None
+
+
 def rope_attention_cuda(q, k, v, cos, sin, *, heads, rotary_dim, key_keep=None, doc_ids=None) -> torch.Tensor:
     """Rotary attention: interleaved-pair rotation of q and k, then the same flash kernel without position tables."""
     B, S, H = q.shape
     d = H // heads
+    if torch.compiler.is_compiling():
+        from . import library
+        from .elementwise import rotary_tokens
+
+        if rotary_dim > 0:
+            q = rotary_tokens(q, cos, sin, heads=heads, rotary_dim=rotary_dim)
+            k = rotary_tokens(k, cos, sin, heads=heads, rotary_dim=rotary_dim)
+        return library.flash_attn(q, k, v, None, None, key_keep, doc_ids, heads, math.sqrt(float(d)), 0, 0, 0)[0]
+    if rotary_dim > 0 and d % 8 == 0 and rotary_dim % 2 == 0:
+        c = cos.detach().to(torch.float32).contiguous()
+        s = sin.detach().to(torch.float32).contiguous()
+        return _RopeAttention.apply(q, k, v, c, s, heads, rotary_dim, key_keep, doc_ids)
     if rotary_dim > 0:
         from .elementwise import rotary_tokens
 
         q = rotary_tokens(q, cos, sin, heads=heads, rotary_dim=rotary_dim)
         k = rotary_tokens(k, cos, sin, heads=heads, rotary_dim=rotary_dim)
-    if torch.compiler.is_compiling():
-        from . import library
-
-        return library.flash_attn(q, k, v, None, None, key_keep, doc_ids, heads, math.sqrt(float(d)), 0, 0, 0)[0]
     return _FlashAttention.apply(q, k, v, None, None, heads, math.sqrt(float(d)), None, key_keep, doc_ids)

@@ -15,7 +15,7 @@ import torch.nn.functional as F
 
 from .gemm import EPI_DGELU, EPI_GELU, EPI_GELU_GRAD, EPI_MUL, EPI_SWIGLU, EPI_SWIGLU_BWD, gemm
 
-__all__ = ["linear", "linear_qkv", "ffn_gelu", "ffn_swiglu", "use_kernels"]
+__all__ = ["linear", "linear_qkv", "split_qkv", "ffn_gelu", "ffn_swiglu", "use_kernels"]
 
 
 def use_kernels(x: torch.Tensor) -> bool:
@@ -305,6 +305,17 @@ class _SplitQKV(torch.autograd.Function):
         if side_by_side:
             return dq.as_strided((dq.shape[0], 3 * n), (3 * n, 1), dq.storage_offset())
         return torch.cat([dq, dk, dv], dim=-1)
+
+
+def split_qkv(qkv: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``[..., 3N]`` → three ``[..., N]`` column views. Unlike three slices, whose backward passes would each zero-fill
+    and copy a full ``[..., 3N]`` tensor and then be added up, the backward hands the three gradients back as one tensor
+    (without any copy when they already sit side by side, as the attention backward writes them)."""
+    lead = qkv.shape[:-1]
+    q, k, v = _SplitQKV.apply(qkv.reshape(-1, qkv.shape[-1]))
+    if len(lead) == 1:
+        return q, k, v
+    return tuple(t.unflatten(0, lead) for t in (q, k, v))
 
 
 def linear_qkv(x, wq, bq, wk, bk, wv, bv):

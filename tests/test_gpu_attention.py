@@ -109,6 +109,32 @@ def test_rope_forward_backward(S, mask):
         assert _rel_err(a.grad, b.grad) < 4e-2, name
 
 
+@pytest.mark.parametrize("rotary_dim", [64, 32])
+def test_rope_attention_on_side_by_side_qkv_rotates_in_one_launch_and_in_place(rotary_dim):
+    """q, k, v as the three column blocks of one [B, S, 3H] projection (what the fused QKV GEMM produces): the rotation
+    of q and k is one launch, the gradients come back as views of one [tokens, 3H] buffer (rotated back in place), and
+    both match the fp32 statement, also with a partial rotary dimension."""
+    B, S, heads = 2, 384, 3
+    H = heads * 64
+    g = torch.Generator(device="cuda").manual_seed(9)
+    qkv = (torch.randn(B, S, 3 * H, device="cuda", generator=g) * 0.5).to(torch.bfloat16).requires_grad_(True)
+    q, k, v = qkv[..., :H], qkv[..., H:2 * H], qkv[..., 2 * H:]
+    inv = 1.0 / (10000 ** (torch.arange(0, rotary_dim, 2, device="cuda").float() / rotary_dim))
+    ang = torch.repeat_interleave(torch.outer(torch.arange(S, device="cuda").float(), inv), 2, dim=-1)
+    cos, sin = ang.cos(), ang.sin()
+    out = rope_attention(q, k, v, cos, sin, heads=heads, rotary_dim=rotary_dim)
+    ref_qkv = qkv.detach().float().requires_grad_(True)
+    ref = rope_attention_reference(ref_qkv[..., :H], ref_qkv[..., H:2 * H], ref_qkv[..., 2 * H:], cos, sin, heads=heads,
+                                   rotary_dim=rotary_dim)
+    assert _rel_err(out, ref) < 2e-2
+    w = torch.randn_like(ref)
+    (out.float() * w).sum().backward()
+    (ref * w).sum().backward()
+    _lib.check_status()
+    for lo, name in ((0, "q"), (H, "k"), (2 * H, "v")):
+        assert _rel_err(qkv.grad[..., lo:lo + H], ref_qkv.grad[..., lo:lo + H]) < 4e-2, name
+
+
 def _packed_doc_ids(B, S, mean_len, seed, tail_pad=0, shuffle_ids=False):
     g = torch.Generator().manual_seed(seed)
     doc = torch.zeros(B, S, dtype=torch.long)
