@@ -338,17 +338,16 @@ class _FlashAttention(torch.autograd.Function):
             g = g_c2p.permute(1, 0, 2)  # [heads, T, span2]
             # dQ += dC2P · PosK ; dPosK = dC2Pᵀ · Q   (per head)
             gemm(g, _heads_view(pos_k, heads), b_mn=True, out=_heads_view(dq_acc, heads), accumulate=True)
-            d_pos_k = torch.zeros(pos_k.shape, dtype=torch.float32, device=dev)
-            gemm(g, _heads_view(q2, heads), a_mn=True, b_mn=True, out=_heads_view(d_pos_k, heads), accumulate=True)
-            d_pos_k = d_pos_k.to(pos_k.dtype)
+            # (bf16 straight from the fp32 accumulators: no zero-filled fp32 table, no split-K partial sums, no cast)
+            d_pos_k = torch.empty(pos_k.shape, dtype=pos_k.dtype, device=dev)
+            gemm(g, _heads_view(q2, heads), a_mn=True, b_mn=True, out=_heads_view(d_pos_k, heads))
         if g_p2c is not None:
             g = g_p2c.permute(1, 0, 2)
             # dK += dP2C · PosQ (per head), added in the GEMM epilogue
             dkh = _heads_view(dk, heads)
             gemm(g, _heads_view(pos_q, heads), b_mn=True, residual=dkh, out=dkh)
-            d_pos_q = torch.zeros(pos_q.shape, dtype=torch.float32, device=dev)
-            gemm(g, _heads_view(k2, heads), a_mn=True, b_mn=True, out=_heads_view(d_pos_q, heads), accumulate=True)
-            d_pos_q = d_pos_q.to(pos_q.dtype)
+            d_pos_q = torch.empty(pos_q.shape, dtype=pos_q.dtype, device=dev)
+            gemm(g, _heads_view(k2, heads), a_mn=True, b_mn=True, out=_heads_view(d_pos_q, heads))
         dq = dqkv[:, :H]
         _lib.call("db200_cast_f32_bf16", _lib.ptr(dq_acc), _lib.ptr(dq), ctypes.c_longlong(3 * H), ctypes.c_longlong(T),
                   c_int(H), _lib.stream_ptr())
@@ -451,14 +450,21 @@ class _RopeAttention(torch.autograd.Function):
         kr = qk.as_strided((B, S, H), (S * 2 * H, 2 * H, 1), H)
         inner = _Ctx()
         out = _FlashAttention.forward(inner, qr, kr, v, None, None, heads, math.sqrt(float(d)), None, key_keep, doc_ids)
-        ctx.inner = inner
-        ctx.rot = (cos, sin, heads, rotary_dim)
+        # through save_for_backward, not as attributes: the saved set contains this node's own output, and an attribute
+        # would close a reference cycle (node -> output -> node) that only the garbage collector could free
+        ctx.save_for_backward(cos, sin, *inner.saved_tensors)
+        ctx.inner_meta = inner.meta
+        ctx.rot = (heads, rotary_dim)
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        cos, sin, heads, rotary_dim = ctx.rot
-        dq, dk, dv = _FlashAttention.backward(ctx.inner, dout)[:3]
+        heads, rotary_dim = ctx.rot
+        cos, sin, *saved = ctx.saved_tensors
+        inner = _Ctx()
+        inner.saved_tensors = tuple(saved)
+        inner.meta = ctx.inner_meta
+        dq, dk, dv = _FlashAttention.backward(inner, dout)[:3]
         B, S, H = dq.shape
         # dq and dk are the first two column blocks of one [tokens, 3H] buffer: rotate both back where they are
         both = dq.as_strided((B * S, 2 * H), (dq.stride(1), 1), dq.storage_offset())
