@@ -39,6 +39,18 @@ def bench_gemm(a) -> None:
         us = _time(lambda: gemm(x, w), a.iters)
         ref = _time(lambda: x @ w.t(), a.iters)
         print(f"gemm {M}x{N}x{K}: tcgen05 {us:.1f} us ({2 * M * N * K / us / 1e6:.0f} TFLOP/s) | cuBLAS {ref:.1f} us")
+        # the two gradients of the same layer: dX = dY·W (bf16) and dW += dYᵀ·X with the bias gradient from the same launch
+        dy = _rand(M, N)
+        us = _time(lambda: gemm(dy, w, b_mn=True), a.iters)
+        ref = _time(lambda: dy @ w, a.iters)
+        print(f"  dgrad {M}x{K}x{N}: tcgen05 {us:.1f} us ({2 * M * N * K / us / 1e6:.0f} TFLOP/s) | cuBLAS {ref:.1f} us")
+        dw, db = torch.zeros(N, K, device="cuda"), torch.zeros(N, device="cuda")
+        us = _time(lambda: gemm(dy, x, a_mn=True, b_mn=True, out=dw, accumulate=True, a_sum=db), a.iters)
+        plain = _time(lambda: gemm(dy, x, a_mn=True, b_mn=True, out=dw, accumulate=True), a.iters)
+        dw16 = torch.zeros(N, K, device="cuda", dtype=torch.bfloat16)
+        ref = _time(lambda: (torch.addmm(dw16, dy.t(), x, out=dw16), dy.sum(0)), a.iters)
+        print(f"  wgrad {N}x{K}x{M}: tcgen05 with bias sum {us:.1f} us ({2 * M * N * K / us / 1e6:.0f} TFLOP/s), without "
+              f"{plain:.1f} us | cuBLAS bf16 addmm + column sum {ref:.1f} us")
 
 
 def bench_ffn(a) -> None:
