@@ -81,10 +81,24 @@ def _export_component(*, name: str, out_dir: Path, config: Any, own_sd: dict, di
     model = _build_export_backbone(backbone_type, config)
     state = dict(own_sd)
     if name == "discriminator" and mode == "gdes":
-        # GDES stores (frozen base, trainable delta) instead of .weight: both are folded in below
-        state = {k: v for k, v in state.items() if not (k.endswith(".base_weight") or
-                                                        (k.startswith("embeddings.") and k.endswith("_embeddings.bias")))}
-    missing, unexpected = load_intersection_state_dict(model, state, strict=not cfg.allow_partial_export)
+        # GDES checkpoints hold (frozen base, trainable delta) per shared table instead of one weight. The base stands in
+        # for the weight during the strict load (every key of the export backbone is then accounted for) and the merge
+        # below replaces it by base + delta; the delta ("bias") tensors only feed that merge.
+        wanted = set(model.state_dict().keys())
+        state = {}
+        for k, v in own_sd.items():
+            if k.startswith("embeddings.") and k.endswith(".base_weight"):
+                target = k[: -len("base_weight")] + "weight"
+                if target in wanted and target not in own_sd:
+                    state[target] = v
+            elif k.startswith("embeddings.") and k.endswith("_embeddings.bias") and k not in wanted:
+                continue
+            else:
+                state[k] = v
+    # the stock HF backbone has no absolute-position table when `position_biased_input` is off; the pretrainer keeps one
+    # for its Enhanced Mask Decoder. It is not part of the exported encoder, so it is not an unexpected key either.
+    missing, unexpected = load_intersection_state_dict(model, state, strict=not cfg.allow_partial_export,
+                                                       ignore_unexpected=("embeddings.position_embeddings.weight",))
     if name == "discriminator":
         merge_embeddings_into_export_backbone(export_model=model, disc_sd=disc_sd, gen_sd=gen_sd, mode=mode)
         missing = [k for k in missing if not (mode in {"es", "gdes"} and k.startswith("embeddings.") and k.endswith(".weight"))]

@@ -142,3 +142,31 @@ def test_tiny_hf_deberta_v2_smoke_config_trains(tmp_path, nproc):
     gen = [float(x[2]) for x in rows]
     assert all(11.0 < g < 12.5 for g in gen)  # ln(128100) = 11.76 at initialisation
     assert abs(float(rows[0][1]) - (float(rows[0][2]) + 50.0 * float(rows[0][3]))) < 2e-3 * float(rows[0][1])  # loss = gen + 50 disc
+
+
+def test_hf_deberta_v2_checkpoint_exports_with_stock_transformers_classes(tmp_path):
+    """``deberta export`` on a GDES checkpoint of the DeBERTa-v2 family, strict mode, both components: the artifacts load
+    with ``transformers.AutoModel`` and the discriminator's word embeddings are generator table + delta (the checkpoint
+    itself only holds ``base_weight`` / ``bias`` for shared tables, and the pretrainer's absolute-position table, which
+    the stock backbone does not have, is not an unexpected key)."""
+    cfg = ROOT / "configs" / "tiny_cpu_smoke_hf_deberta_v2.yaml"
+    out = tmp_path / "run"
+    r = _train(["--train.checkpoint.output_dir", str(out), "--train.max_steps", "2", "--train.checkpoint.save_steps", "2",
+                "--train.checkpoint.export_hf_final", "false"], cfg=cfg)
+    assert r.returncode == 0, r.stderr[-3000:]
+    env = dict(os.environ, PYTHONPATH=str(ROOT), CUDA_VISIBLE_DEVICES="")
+    exp = tmp_path / "exported"
+    r = subprocess.run([sys.executable, "-m", "deberta_b200", "export", str(out / "checkpoint-2"), "--what", "both",
+                        "--output-dir", str(exp)], capture_output=True, text=True, cwd=ROOT, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-3000:]
+    from safetensors.torch import load_file
+    from transformers import AutoModel
+
+    disc = AutoModel.from_pretrained(str(exp / "discriminator"))
+    gen = AutoModel.from_pretrained(str(exp / "generator"))
+    ck = load_file(str(out / "checkpoint-2" / "model.safetensors"))
+    want = ck["generator.embeddings.word_embeddings.weight"].float() + ck["discriminator.embeddings.word_embeddings.bias"].float()
+    torch.testing.assert_close(disc.embeddings.word_embeddings.weight.data.float(), want)
+    torch.testing.assert_close(gen.embeddings.word_embeddings.weight.data, ck["generator.embeddings.word_embeddings.weight"])
+    meta = json.loads((exp / "export_meta.json").read_text())
+    assert meta["components"]["discriminator"]["unexpected_keys"] == [] and meta["components"]["discriminator"]["missing_keys"] == []
