@@ -1191,10 +1191,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 // Eight lanes share one (token, head): 16 bytes of dO and of O each.
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, long long ld_do, const __nv_bfloat16* __restrict__ out,
-                  long long ldo, float* __restrict__ delta, int B, int S, int heads) {
+                  long long ldo, float* __restrict__ delta, float* __restrict__ zero_f32, int B, int S, int heads) {
   pdl_launch_dependents();
   pdl_wait();
   const long long gid = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  // the dQ accumulator of the backward kernel that follows has exactly 8 floats per thread of this grid
+  // ([tokens, heads * 64]): clearing it here saves a fill launch per layer
+  if (zero_f32 && gid < static_cast<long long>(B) * S * heads * 8) {
+    float4* z = reinterpret_cast<float4*>(zero_f32 + gid * 8);
+    z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   const long long pair = gid >> 3;  // (token, head)
   const int sub = static_cast<int>(gid & 7);
   const long long total = static_cast<long long>(B) * S * heads;
@@ -1396,14 +1403,14 @@ extern "C" int db200_attn_bwd(const AttnArgs* a, void* stream_) {
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-extern "C" int db200_attn_delta(const void* dout, long long ld_do, const void* out, long long ldo, float* delta, int B,
-                                int S, int heads, void* stream) {
+extern "C" int db200_attn_delta(const void* dout, long long ld_do, const void* out, long long ldo, float* delta,
+                                float* zero_f32, int B, int S, int heads, void* stream) {
   if (B <= 0 || S <= 0 || heads <= 0) return 0;
-  if (!aligned16(dout) || !aligned16(out) || (ld_do % 8) || (ldo % 8)) return -10;
+  if (!aligned16(dout) || !aligned16(out) || (ld_do % 8) || (ldo % 8) || !aligned16(zero_f32)) return -10;
   const long long threads = static_cast<long long>(B) * S * heads * 8;
   return launch_pdl(attn_delta_kernel, dim3(static_cast<unsigned>((threads + 255) / 256)), dim3(256), 0,
                     reinterpret_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(dout), ld_do,
-                    static_cast<const __nv_bfloat16*>(out), ldo, delta, B, S, heads) == cudaSuccess ? 0 : -4;
+                    static_cast<const __nv_bfloat16*>(out), ldo, delta, zero_f32, B, S, heads) == cudaSuccess ? 0 : -4;
 }
 
 extern "C" int db200_attn_doc_tiles(const void* doc_ids, void* tiles, int B, int S, void* stream) {

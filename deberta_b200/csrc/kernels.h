@@ -212,9 +212,10 @@ int db200_posbias_tc_bwd(const PosBiasArgs* args, void* stream);
 
 int db200_attn_fwd(const AttnArgs* args, void* stream);
 int db200_attn_bwd(const AttnArgs* args, void* stream);
-// delta[b,h,s] = sum over the head dim of dO * O (fp32 [B, heads, S]); input of db200_attn_bwd.
-int db200_attn_delta(const void* dout, long long ld_do, const void* out, long long ldo, float* delta, int B, int S,
-                     int heads, void* stream);
+// delta[b,h,s] = sum over the head dim of dO * O (fp32 [B, heads, S]); input of db200_attn_bwd. `zero_f32` (may be
+// null): a dense fp32 [B*S, heads*64] buffer that the same launch clears (the dQ accumulator of db200_attn_bwd).
+int db200_attn_delta(const void* dout, long long ld_do, const void* out, long long ldo, float* delta, float* zero_f32,
+                     int B, int S, int heads, void* stream);
 // tiles[b, t] = (smallest, largest) non-zero document id of tokens [128 t, 128 t + 128) of row b (int32 [B, tiles, 2]).
 int db200_attn_doc_tiles(const void* doc_ids, void* tiles, int B, int S, void* stream);
 

@@ -270,9 +270,9 @@ class _FlashAttention(torch.autograd.Function):
         dev = q.device
         dout = dout.contiguous()
         delta = torch.empty((B, heads, S), dtype=torch.float32, device=dev)
+        dq_acc = torch.empty((T, H), dtype=torch.float32, device=dev)  # cleared by the delta kernel
         _lib.call("db200_attn_delta", _lib.ptr(dout), ctypes.c_longlong(H), _lib.ptr(out), ctypes.c_longlong(H),
-                  _lib.ptr(delta), c_int(B), c_int(S), c_int(heads), _lib.stream_ptr())
-        dq_acc = torch.zeros((T, H), dtype=torch.float32, device=dev)
+                  _lib.ptr(delta), _lib.ptr(dq_acc), c_int(B), c_int(S), c_int(heads), _lib.stream_ptr())
         # dQ | dK | dV side by side in one [T, 3H] buffer: a fused QKV projection takes it as is
         dqkv = torch.empty((T, 3 * H), dtype=torch.bfloat16, device=dev)
         dk, dv = dqkv[:, H : 2 * H], dqkv[:, 2 * H :]
