@@ -3,7 +3,7 @@
 Usage::
 
     python -m deberta_b200.tools.step_kernel_shares [--backbone hf_deberta_v2|rope] [--model-size base] [--seq-len 512]
-        [--micro-batch 32] [--ga 2] [--top 40] [--callers] [--gaps]
+        [--micro-batch 32] [--ga 2] [--top 40] [--callers] [--gaps] [--no-dependent-launch]
 
 Builds the RTD pretrainer from the config defaults on synthetic packed data, runs three warm-up windows, profiles the
 fourth and prints, per kernel name, the launch count, total and mean device time and the share of the window. The
@@ -66,6 +66,9 @@ def main(argv: list[str] | None = None) -> int:
     p.add_argument("--top", type=int, default=40)
     p.add_argument("--callers", action="store_true", help="attribute ATen kernels to the package line that launched them")
     p.add_argument("--gaps", action="store_true", help="list the idle intervals of the GPU inside the window")
+    p.add_argument("--no-dependent-launch", action="store_true",
+                   help="ordinary launches: with programmatic dependent launch a kernel's recorded duration includes its "
+                        "wait for the predecessor, which inflates the per-kernel shares")
     a = p.parse_args(argv)
     if not torch.cuda.is_available():
         print("step_kernel_shares needs a CUDA device")
@@ -77,6 +80,10 @@ def main(argv: list[str] | None = None) -> int:
     from deberta_b200.training.trainer import Trainer
 
     ctx = init_distributed()
+    if a.no_dependent_launch:
+        from deberta_b200.ops import _lib
+
+        _lib.set_dependent_launch(False)
     cfg = _config(a)
     torch.manual_seed(1234)
     tok = build_tokenizer(cfg.model)
