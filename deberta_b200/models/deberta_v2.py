@@ -19,7 +19,7 @@ from transformers import DebertaV2Config, PreTrainedModel
 from transformers.modeling_outputs import BaseModelOutput
 
 from deberta_b200.ops.attention import disentangled_attention
-from deberta_b200.ops.linear import ffn_gelu, linear, linear_qkv
+from deberta_b200.ops.linear import ResidualGradSink, ffn_gelu, linear, linear_qkv
 from deberta_b200.ops.norm import layer_norm
 
 from .activations import get_act_fn
@@ -125,10 +125,12 @@ class DisentangledSelfAttention(nn.Module):
         query_states: torch.Tensor | None = None,
         relative_pos: torch.Tensor | None = None,
         rel_embeddings: torch.Tensor | None = None,
+        residual_sink=None,
     ) -> torch.Tensor:
         if query_states is None:
             q, k, v = linear_qkv(hidden_states, self.query_proj.weight, self.query_proj.bias, self.key_proj.weight,
-                                 self.key_proj.bias, self.value_proj.weight, self.value_proj.bias)
+                                 self.key_proj.bias, self.value_proj.weight, self.value_proj.bias,
+                                 residual_sink=residual_sink)
         else:
             q = linear(query_states, self.query_proj.weight, self.query_proj.bias)
             k = linear(hidden_states, self.key_proj.weight, self.key_proj.bias)
@@ -201,11 +203,12 @@ class DebertaV2SelfOutput(nn.Module):
         self.LayerNorm = nn.LayerNorm(int(config.hidden_size), eps=float(config.layer_norm_eps))
         self.dropout_p = float(config.hidden_dropout_prob)
 
-    def forward(self, hidden_states: torch.Tensor, input_tensor: torch.Tensor) -> torch.Tensor:
+    def forward(self, hidden_states: torch.Tensor, input_tensor: torch.Tensor, residual_sink=None) -> torch.Tensor:
         if self.training and self.dropout_p > 0.0:
             x = _drop(linear(hidden_states, self.dense.weight, self.dense.bias), self.dropout_p, True) + input_tensor
         else:
-            x = linear(hidden_states, self.dense.weight, self.dense.bias, residual=input_tensor)
+            x = linear(hidden_states, self.dense.weight, self.dense.bias, residual=input_tensor,
+                       residual_sink=residual_sink)
         return _ln(self.LayerNorm, x)
 
 
@@ -216,9 +219,15 @@ class DebertaV2Attention(nn.Module):
         self.output = DebertaV2SelfOutput(config)
 
     def forward(self, hidden_states, mask: AttnMask, query_states=None, relative_pos=None, rel_embeddings=None):
-        ctx = self.self(hidden_states, mask, query_states=query_states, relative_pos=relative_pos,
-                        rel_embeddings=rel_embeddings)
-        return self.output(ctx, hidden_states if query_states is None else query_states)
+        if query_states is not None:
+            ctx = self.self(hidden_states, mask, query_states=query_states, relative_pos=relative_pos,
+                            rel_embeddings=rel_embeddings)
+            return self.output(ctx, query_states)
+        # x feeds the QKV projection and the block's residual: the residual's gradient rides into the QKV projection's
+        # data-gradient GEMM instead of meeting it in a separate add (ops/linear.py::ResidualGradSink)
+        sink = ResidualGradSink()
+        ctx = self.self(hidden_states, mask, relative_pos=relative_pos, rel_embeddings=rel_embeddings, residual_sink=sink)
+        return self.output(ctx, hidden_states, residual_sink=sink)
 
 
 class DebertaV2Intermediate(nn.Module):

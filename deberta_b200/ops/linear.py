@@ -15,7 +15,7 @@ import torch.nn.functional as F
 
 from .gemm import EPI_DGELU, EPI_GELU, EPI_GELU_GRAD, EPI_MUL, EPI_SWIGLU, EPI_SWIGLU_BWD, gemm
 
-__all__ = ["linear", "linear_qkv", "split_qkv", "ffn_gelu", "ffn_swiglu", "use_kernels"]
+__all__ = ["linear", "linear_qkv", "split_qkv", "ffn_gelu", "ffn_swiglu", "use_kernels", "ResidualGradSink"]
 
 
 def use_kernels(x: torch.Tensor) -> bool:
@@ -87,13 +87,28 @@ def _param_grads(dy, x, w, b):
                             w.requires_grad, want_b, b.dtype if b is not None else None)
 
 
+class ResidualGradSink:
+    """Carries the gradient of a residual branch from the projection that closes a block to the projection that opened
+    it, when both read the same tensor: ``y = W_o·f(W_qkv·x) + x``. Autograd would add the two gradients of ``x`` with a
+    separate kernel; instead the closing projection's backward parks its residual gradient here (and reports none), and
+    the opening projection's backward, which autograd necessarily runs later, adds it in the epilogue of its
+    data-gradient GEMM. ``armed`` is set by the opening projection once it is certain to collect."""
+
+    __slots__ = ("armed", "grad")
+
+    def __init__(self) -> None:
+        self.armed = False
+        self.grad = None
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, b, residual):
+    def forward(ctx, x, w, b, residual, sink):
         ctx.save_for_backward(x, w)
         ctx.has_bias = b is not None
         ctx.bias_ref = b
         ctx.has_res = residual is not None
+        ctx.sink = sink if (sink is not None and sink.armed and residual is not None) else None
         return gemm(x, w, bias=b, residual=residual)
 
     @staticmethod
@@ -103,13 +118,17 @@ class _Linear(torch.autograd.Function):
         dx = gemm(dy, w, b_mn=True) if ctx.needs_input_grad[0] else None
         dw, db = _param_grads(dy, x, w, ctx.bias_ref if ctx.has_bias else None)
         dres = dy if ctx.has_res else None
-        return dx, dw, db, dres
+        if ctx.sink is not None and dres is not None:
+            ctx.sink.grad, dres = dres, None
+        return dx, dw, db, dres, None
 
 
 def linear(
-    x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None, residual: torch.Tensor | None = None
+    x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None, residual: torch.Tensor | None = None,
+    residual_sink: ResidualGradSink | None = None,
 ) -> torch.Tensor:
-    """``x @ wᵀ + b (+ residual)`` over the last dim of ``x`` (any leading shape)."""
+    """``x @ wᵀ + b (+ residual)`` over the last dim of ``x`` (any leading shape). ``residual_sink``: see
+    :class:`ResidualGradSink` (only an armed sink is used)."""
     if not (use_kernels(x) and w.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0):
         out = F.linear(x, w.to(x.dtype) if w.dtype != x.dtype else w, None if b is None else b.to(x.dtype))
         return out if residual is None else out + residual
@@ -127,7 +146,7 @@ def linear(
         # the engine's post-accumulate hook adds them to the buffers.
         out = library.linear(x2, w, b, r2, None, None)
     else:
-        out = _Linear.apply(x2, w, b, r2)
+        out = _Linear.apply(x2, w, b, r2, residual_sink)
     return out.view(*lead, w.shape[0])
 
 
@@ -264,12 +283,13 @@ class _LinearQKV(torch.autograd.Function):
     """``x @ [Wq; Wk; Wv]ᵀ + [bq; bk; bv]`` as one GEMM when the three parameter sets are adjacent in memory."""
 
     @staticmethod
-    def forward(ctx, x, wq, bq):
+    def forward(ctx, x, wq, bq, sink):
         n, k = wq.shape
         w_all = _span3(wq, (3 * n, k))
         b_all = None if bq is None else _span3(bq, (3 * n,))
         ctx.save_for_backward(x, wq)
         ctx.bq = bq
+        ctx.sink = sink
         return gemm(x, w_all, bias=b_all)
 
     @staticmethod
@@ -278,11 +298,16 @@ class _LinearQKV(torch.autograd.Function):
         n, k = wq.shape
         if dqkv.stride(1) != 1 or dqkv.stride(0) % 8 or dqkv.data_ptr() % 16:
             dqkv = dqkv.contiguous()
-        dx = gemm(dqkv, _span3(wq, (3 * n, k)), b_mn=True) if ctx.needs_input_grad[0] else None
+        parked = None
+        if ctx.sink is not None:  # the block's residual gradient, parked by the projection that closed the block
+            parked, ctx.sink.grad = ctx.sink.grad, None
+            if parked is not None and (parked.shape != x.shape or not parked.is_contiguous()):
+                parked = parked.reshape(x.shape).contiguous()
+        dx = gemm(dqkv, _span3(wq, (3 * n, k)), b_mn=True, residual=parked) if ctx.needs_input_grad[0] else None
         want_b = ctx.bq is not None and ctx.bq.requires_grad
         gemm(dqkv, x, a_mn=True, b_mn=True, out=_span3(wq.main_grad, (3 * n, k)), accumulate=True,
              a_sum=_span3(ctx.bq.main_grad, (3 * n,)) if want_b else None)
-        return dx, None, None
+        return dx, None, None, None
 
 
 class _SplitQKV(torch.autograd.Function):
@@ -318,11 +343,13 @@ def split_qkv(qkv: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tens
     return tuple(t.unflatten(0, lead) for t in (q, k, v))
 
 
-def linear_qkv(x, wq, bq, wk, bk, wv, bv):
+def linear_qkv(x, wq, bq, wk, bk, wv, bv, residual_sink: ResidualGradSink | None = None):
     """Query, key and value projections of the same input: ``(q, k, v)`` with ``x``'s leading shape.
 
     One GEMM with a three times wider output when the engine laid the three weights (and biases, and their fp32
-    gradient buffers) out back to back, three GEMMs otherwise.
+    gradient buffers) out back to back, three GEMMs otherwise. ``residual_sink``: when the fused form runs and ``x``
+    needs a gradient, the sink is armed and this projection's backward collects what the block's closing projection
+    parks there (:class:`ResidualGradSink`).
     """
     if torch.compiler.is_compiling() or not _qkv_fusable(x, wq, bq, wk, bk, wv, bv):
         # (the fused form compares storage addresses of parameters, which a tracing compiler cannot see)
@@ -331,7 +358,10 @@ def linear_qkv(x, wq, bq, wk, bk, wv, bv):
     x2 = x.reshape(-1, x.shape[-1])
     if x2.stride(-1) != 1 or x2.stride(0) % 8:
         x2 = x2.contiguous()
-    q, k, v = _SplitQKV.apply(_LinearQKV.apply(x2, wq, bq))
+    sink = residual_sink if (residual_sink is not None and x.requires_grad and torch.is_grad_enabled()) else None
+    if sink is not None:
+        sink.armed = True
+    q, k, v = _SplitQKV.apply(_LinearQKV.apply(x2, wq, bq, sink))
     if len(lead) == 1:
         return q, k, v
     return tuple(t.unflatten(0, lead) for t in (q, k, v))

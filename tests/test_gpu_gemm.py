@@ -198,6 +198,50 @@ def test_fused_qkv_projection_matches_three_linears():
         assert (bs[i].main_grad - want_b).abs().max() <= 3e-2 * want_b.abs().max()
 
 
+def test_residual_gradient_rides_into_the_qkv_data_gradient_gemm():
+    """y = W_o·(q + k + v) + x with (q, k, v) from the fused projection of x: with a ResidualGradSink the closing
+    projection reports no gradient for its residual and the opening projection's backward adds it in its GEMM epilogue.
+    The gradient of x must equal the one autograd builds with its own add, and the fp32 statement."""
+    from deberta_b200.ops.linear import ResidualGradSink, linear, linear_qkv
+
+    dev = torch.device("cuda")
+    torch.manual_seed(3)
+    n, t = 128, 320
+    flat_w = (torch.randn(3 * n * n, device=dev) * 0.05).to(torch.bfloat16)
+    gw = torch.zeros(3 * n * n, device=dev)
+    ws = []
+    for i in range(3):
+        w = torch.nn.Parameter(flat_w[i * n * n:(i + 1) * n * n].view(n, n))
+        w.main_grad = gw[i * n * n:(i + 1) * n * n].view(n, n)
+        ws.append(w)
+    wo = (torch.randn(n, n, device=dev) * 0.05).to(torch.bfloat16)
+    x0 = (torch.randn(2, t // 2, n, device=dev) * 0.5).to(torch.bfloat16)
+    gy = torch.randn(2, t // 2, n, device=dev).to(torch.bfloat16)
+
+    def run(with_sink):
+        x = x0.clone().requires_grad_(True)
+        sink = ResidualGradSink() if with_sink else None
+        q, k, v = linear_qkv(x, ws[0], None, ws[1], None, ws[2], None, residual_sink=sink)
+        assert (sink is None) or sink.armed
+        y = linear(q + k + v, wo, None, residual=x, residual_sink=sink)
+        y.backward(gy)
+        assert sink is None or sink.grad is None  # collected
+        return y.detach(), x.grad.detach()
+
+    y_a, g_a = run(False)
+    y_b, g_b = run(True)
+    assert torch.equal(y_a, y_b)
+    xr = x0.float().requires_grad_(True)
+    h = sum(torch.nn.functional.linear(xr, w.detach().float()) for w in ws)
+    yr = torch.nn.functional.linear(h, wo.float()) + xr
+    yr.backward(gy.float())
+    for g in (g_a, g_b):
+        assert (g.float() - xr.grad).abs().max() <= 3e-2 * xr.grad.abs().max()
+    # fused: one rounding of (dx + residual gradient); unfused: each rounded, then added and rounded again
+    assert (g_a.float() - g_b.float()).abs().max() <= 2e-2 * xr.grad.abs().max()
+    _lib.check_status()
+
+
 @pytest.mark.parametrize("T,H,F,bias", [(1024, 768, 2048, False), (300, 256, 200, True), (640, 768, 3072, True)])
 def test_swiglu_ffn_in_gemm_epilogues_matches_pytorch(T, H, F, bias):
     """SwiGLU forward inside the W12 GEMM (writes [gate | up] and silu(gate)·up) and its backward inside the W3
