@@ -288,10 +288,9 @@ posbias_rowscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __res
 constexpr int kColKeys = 16;
 
 template <int PER, int KEYS>  // PER > 0: ceil(S/32) known at compile time (the run of a lane lives in registers); 0: any S
-__global__ void __launch_bounds__(256, PER <= 16 ? 4 : 1)
+__global__ void __launch_bounds__(256)
 posbias_colscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __restrict__ ranges,
-                       __nv_bfloat16* __restrict__ dtab, int S, int ldb, int heads, int span2, int stride, int per, int sh,
-                       int strips_per_block) {
+                       __nv_bfloat16* __restrict__ dtab, int S, int ldb, int heads, int span2, int stride, int per, int sh) {
   extern __shared__ float sm[];
   tc05::pdl_launch_dependents();
   tc05::pdl_wait();
@@ -300,119 +299,82 @@ posbias_colscan_kernel(const __nv_bfloat16* __restrict__ dbias, const int* __res
   float* tb = sm + ((span2 + 4) & ~3);     // T[KEYS][stride]
   for (int i = tid; i <= span2; i += 256) edge[i] = ranges[i + 1];
   const float sign = ranges[0] >= 0 ? 1.f : -1.f;
-  const int h = blockIdx.y, b = blockIdx.z;
-  const __nv_bfloat16* src_bh = dbias + (static_cast<long long>(b) * heads + h) * S * ldb;
+  const int k0 = blockIdx.x * KEYS, h = blockIdx.y, b = blockIdx.z;
+  const __nv_bfloat16* src = dbias + (static_cast<long long>(b) * heads + h) * S * ldb + k0;
   constexpr int kGroups = KEYS / 8, kRowsPerPass = 256 / kGroups;
   const int cg = tid % kGroups;  // 8-key group of this thread
-  const long long row_stride = static_cast<long long>(heads) * span2;
-  // A block walks `strips_per_block` neighbouring key strips. When a strip is one pass of loads (S <= 4 * rows per
-  // pass) the next strip is copied into a raw staging area with cp.async before this strip's scan, so that the scan
-  // runs under the loads' latency (asynchronous copies: the prefetch costs no registers).
-  const bool one_pass = S <= 4 * kRowsPerPass;
-  uint4* raw = reinterpret_cast<uint4*>(tb + KEYS * stride);  // [4][256] 16-byte vectors, slot = t * 256 + tid
-  auto prefetch = [&](int k0) {
+  for (int qb = tid / kGroups; qb < S; qb += 4 * kRowsPerPass) {  // four independent 16-byte loads in flight per thread
+    uint4 u[4];
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
-      const int q = tid / kGroups + kRowsPerPass * t;
-      if (q < S && k0 < S) {
-        const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(raw + t * 256 + tid));
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst),
-                     "l"(src_bh + static_cast<long long>(q) * ldb + k0 + cg * 8)
-                     : "memory");
+      const int q = qb + kRowsPerPass * t;
+      u[t] = q < S ? *reinterpret_cast<const uint4*>(src + static_cast<long long>(q) * ldb + cg * 8) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const int q = qb + kRowsPerPass * t;
+      if (q < S) {
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&u[t]);
+        const int w = (q + 1) + ((q + 1) >> sh);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) tb[(cg * 8 + j) * stride + w] = __bfloat162float(e[j]);
       }
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  };
-  auto scatter_vec = [&](const uint4& v, int q) {
-    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
-    const int w = (q + 1) + ((q + 1) >> sh);
+  }
+  if (tid < KEYS) tb[tid * stride] = 0.f;
+  __syncthreads();
+  const long long row_stride = static_cast<long long>(heads) * span2;
+  for (int kk = warp * (KEYS / 8); kk < (warp + 1) * (KEYS / 8); ++kk) {
+    const int k = k0 + kk;
+    if (k >= S) break;  // warp-uniform
+    float* T = tb + kk * stride;  // T[phys(i)] = sum of the first i queries
+    // lane owns prefixes i = lane*per + 1 .. lane*per + per
+    const int first = lane * per + 1;
+    if (PER > 0) {
+      float x[PER > 0 ? PER : 1];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) tb[(cg * 8 + j) * stride + w] = __bfloat162float(e[j]);
-  };
-  const int strip0 = blockIdx.x * strips_per_block;
-  if (one_pass) prefetch(strip0 * KEYS);
-  for (int sidx = 0; sidx < strips_per_block; ++sidx) {
-    const int k0 = (strip0 + sidx) * KEYS;
-    if (k0 >= S) break;  // block-uniform
-    if (one_pass) {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");  // every thread reads back the vectors it copied itself
+      for (int o = 0; o < PER; ++o) {
+        const int i = first + o;
+        x[o] = (i <= S) ? T[i + (i >> sh)] : 0.f;
+      }
 #pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const int q = tid / kGroups + kRowsPerPass * t;
-        if (q < S) scatter_vec(raw[t * 256 + tid], q);
+      for (int o = 1; o < PER; ++o) x[o] += x[o - 1];
+      const float run = x[PER > 0 ? PER - 1 : 0];
+      const float off = warp_inclusive_scan(run, lane) - run;
+#pragma unroll
+      for (int o = 0; o < PER; ++o) {
+        const int i = first + o;
+        if (i <= S) T[i + (i >> sh)] = x[o] + off;
       }
     } else {
-      for (int qb = tid / kGroups; qb < S; qb += 4 * kRowsPerPass) {  // four independent 16-byte loads in flight
-        uint4 u[4];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const int q = qb + kRowsPerPass * t;
-          u[t] = q < S ? *reinterpret_cast<const uint4*>(src_bh + static_cast<long long>(q) * ldb + k0 + cg * 8)
-                       : make_uint4(0, 0, 0, 0);
+      float run = 0.f;
+      for (int o = 0; o < per; ++o) {
+        const int i = first + o;
+        if (i <= S) {
+          run += T[i + (i >> sh)];
+          T[i + (i >> sh)] = run;
         }
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const int q = qb + kRowsPerPass * t;
-          if (q < S) scatter_vec(u[t], q);
-        }
+      }
+      const float off = warp_inclusive_scan(run, lane) - run;
+      for (int o = 0; o < per; ++o) {
+        const int i = first + o;
+        if (i <= S) T[i + (i >> sh)] += off;
       }
     }
-    if (tid < KEYS) tb[tid * stride] = 0.f;
-    __syncthreads();
-    if (one_pass && sidx + 1 < strips_per_block) prefetch(k0 + KEYS);  // lands during the scan below
-    for (int kk = warp * (KEYS / 8); kk < (warp + 1) * (KEYS / 8); ++kk) {
-      const int k = k0 + kk;
-      if (k >= S) break;  // warp-uniform
-      float* T = tb + kk * stride;  // T[phys(i)] = sum of the first i queries
-      // lane owns prefixes i = lane*per + 1 .. lane*per + per
-      const int first = lane * per + 1;
-      if (PER > 0) {
-        float x[PER > 0 ? PER : 1];
+    __syncwarp();
+    __nv_bfloat16* dst = dtab + (static_cast<long long>(b) * S + k) * row_stride + h * span2;
+    // queries with offset q-k < E are the first k+E queries: g = T[clamp(k + E)], and bucket j is sign * (g_{j+1} - g_j)
+    for (int j = lane * 8; j < span2; j += 256) {
+      const int4 e0 = *reinterpret_cast<const int4*>(edge + j), e1 = *reinterpret_cast<const int4*>(edge + j + 4);
+      const int e[9] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w, edge[j + 8]};
+      float g[9];
 #pragma unroll
-        for (int o = 0; o < PER; ++o) {
-          const int i = first + o;
-          x[o] = (i <= S) ? T[i + (i >> sh)] : 0.f;
-        }
-#pragma unroll
-        for (int o = 1; o < PER; ++o) x[o] += x[o - 1];
-        const float run = x[PER > 0 ? PER - 1 : 0];
-        const float off = warp_inclusive_scan(run, lane) - run;
-#pragma unroll
-        for (int o = 0; o < PER; ++o) {
-          const int i = first + o;
-          if (i <= S) T[i + (i >> sh)] = x[o] + off;
-        }
-      } else {
-        float run = 0.f;
-        for (int o = 0; o < per; ++o) {
-          const int i = first + o;
-          if (i <= S) {
-            run += T[i + (i >> sh)];
-            T[i + (i >> sh)] = run;
-          }
-        }
-        const float off = warp_inclusive_scan(run, lane) - run;
-        for (int o = 0; o < per; ++o) {
-          const int i = first + o;
-          if (i <= S) T[i + (i >> sh)] += off;
-        }
+      for (int t = 0; t < 9; ++t) {
+        const int i = min(max(k + e[t], 0), S);
+        g[t] = T[i + (i >> sh)];
       }
-      __syncwarp();
-      __nv_bfloat16* dst = dtab + (static_cast<long long>(b) * S + k) * row_stride + h * span2;
-      // queries with offset q-k < E are the first k+E queries: g = T[clamp(k + E)], and bucket j is sign * (g_{j+1} - g_j)
-      for (int j = lane * 8; j < span2; j += 256) {
-        const int4 e0 = *reinterpret_cast<const int4*>(edge + j), e1 = *reinterpret_cast<const int4*>(edge + j + 4);
-        const int e[9] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w, edge[j + 8]};
-        float g[9];
-#pragma unroll
-        for (int t = 0; t < 9; ++t) {
-          const int i = min(max(k + e[t], 0), S);
-          g[t] = T[i + (i >> sh)];
-        }
-        store_edge_diffs(dst + j, g, sign);
-      }
+      store_edge_diffs(dst + j, g, sign);
     }
-    __syncthreads();  // the strip's prefix table is consumed: the next strip may overwrite it
   }
 }
 
@@ -489,7 +451,7 @@ extern "C" int db200_posbias_scatter_ranges(const void* dbias, const void* range
     while ((1 << sh) < per) ++sh;
     int stride = (S + 1) + ((S + 1) >> sh) + 1;
     stride |= 1;  // odd: the 32 key rows start on different banks
-    const int smem = kColKeys * stride * 4 + ((span2 + 4) & ~3) * 4 + 4 * 256 * 16 + 16;  // prefix tables, edges, raw staging
+    const int smem = kColKeys * stride * 4 + 2 * span2 * 4;
     if (smem > kMaxSmem) return -12;
     // 16 keys per block measured fastest (228 us against 253 / 492 us for 32 / 64 keys at B=32, S=512, 12 heads)
     auto kern = posbias_colscan_kernel<0, kColKeys>;
@@ -498,10 +460,8 @@ extern "C" int db200_posbias_scatter_ranges(const void* dbias, const void* range
     else if (per == 32) kern = posbias_colscan_kernel<32, kColKeys>;
     else if (per == 4) kern = posbias_colscan_kernel<4, kColKeys>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmem) != cudaSuccess) return -3;
-    const int strips = (S + kColKeys - 1) / kColKeys;
-    const int spb = strips >= 16 ? 4 : 1;  // strips per block (neighbouring strips, loads of the next one prefetched)
-    tc05::launch_pdl(kern, dim3((strips + spb - 1) / spb, heads, B), dim3(256), smem, st, db, rg, dt, S, ldb, heads, span2,
-                     stride, per, sh, spb);
+    tc05::launch_pdl(kern, dim3((S + kColKeys - 1) / kColKeys, heads, B), dim3(256), smem, st, db, rg, dt, S, ldb, heads, span2,
+                     stride, per, sh);
   } else {
     const int smem = 8 * ((S + 1) + ((S + 1) >> 3) + 1) * 4 + 2 * span2 * 4;
     if (smem > kMaxSmem) return -12;
