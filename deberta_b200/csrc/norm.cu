@@ -118,39 +118,60 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int nvec = H >> 3;
-  float g[V][8];
+  uint4 gq[V];  // gamma stays packed (bf16): the registers go to the next row's loads
   float dg[V][8], db[V][8];
 #pragma unroll
   for (int i = 0; i < V; ++i) {
     const int c = lane + i * 32;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { dg[i][j] = 0.f; db[i][j] = 0.f; g[i][j] = 0.f; }
-    if (c < nvec) unpack8(reinterpret_cast<const uint4*>(gamma)[c], g[i]);
+    for (int j = 0; j < 8; ++j) { dg[i][j] = 0.f; db[i][j] = 0.f; }
+    gq[i] = c < nvec ? reinterpret_cast<const uint4*>(gamma)[c] : make_uint4(0, 0, 0, 0);
   }
-  for (long long row = static_cast<long long>(blockIdx.x) * kWarpsPerBlock + warp; row < rows;
-       row += static_cast<long long>(gridDim.x) * kWarpsPerBlock) {
-    const float keep = (row_keep == nullptr || row_keep[row]) ? 1.f : 0.f;
-    const float mean = RMS ? 0.f : mean_in[row];
-    const float rstd = rstd_in[row];
-    const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
-    const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * H);
-    float xh[V][8], dyv[V][8];
+  // The rows of a warp are processed one after the other and each needs two row reductions before it can be written,
+  // so the loads of the NEXT row are issued before the current row's arithmetic: their latency hides behind it.
+  const long long row_step = static_cast<long long>(gridDim.x) * kWarpsPerBlock;
+  long long row = static_cast<long long>(blockIdx.x) * kWarpsPerBlock + warp;
+  uint4 xq[V], dq[V];  // raw bf16 vectors of the current row
+  float keep = 0.f, mean = 0.f, rstd = 0.f;
+  auto fetch = [&](long long r, uint4 (&xo)[V], uint4 (&dout)[V], float& k, float& m, float& rs) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + r * H);
+    const uint4* dyr = reinterpret_cast<const uint4*>(dy + r * H);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const int c = lane + i * 32;
+      if (c < nvec) {
+        xo[i] = xr[c];
+        dout[i] = dyr[c];
+      }
+    }
+    k = (row_keep == nullptr || row_keep[r]) ? 1.f : 0.f;
+    m = RMS ? 0.f : mean_in[r];
+    rs = rstd_in[r];
+  };
+  if (row < rows) fetch(row, xq, dq, keep, mean, rstd);
+  for (; row < rows; row += row_step) {
+    uint4 xn[V], dn[V];
+    float keep_n = 0.f, mean_n = 0.f, rstd_n = 0.f;
+    constexpr bool kAhead = V <= 4;  // (wider rows have no registers to spare: they fetch at the bottom of the loop)
+    if (kAhead && row + row_step < rows) fetch(row + row_step, xn, dn, keep_n, mean_n, rstd_n);
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < V; ++i) {
       const int c = lane + i * 32;
       if (c < nvec) {
-        unpack8(xr[c], xh[i]);
-        unpack8(dyr[c], dyv[i]);
+        float xh[8], dyv[8], g[8];
+        unpack8(xq[i], xh);
+        unpack8(dq[i], dyv);
+        unpack8(gq[i], g);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          xh[i][j] = (xh[i][j] - mean) * rstd;
-          dyv[i][j] *= keep;
-          const float dxh = dyv[i][j] * g[i][j];
+          const float xn_ = (xh[j] - mean) * rstd;
+          const float d = dyv[j] * keep;
+          const float dxh = d * g[j];
           s1 += dxh;
-          s2 += dxh * xh[i][j];
-          dg[i][j] += dyv[i][j] * xh[i][j];
-          db[i][j] += dyv[i][j];
+          s2 += dxh * xn_;
+          dg[i][j] += d * xn_;
+          db[i][j] += d;
         }
       }
     }
@@ -161,12 +182,25 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     for (int i = 0; i < V; ++i) {
       const int c = lane + i * 32;
       if (c < nvec) {
-        float o[8];
+        float xh[8], dyv[8], g[8], o[8];
+        unpack8(xq[i], xh);  // (unpacked again rather than kept: the registers hold the next row's loads instead)
+        unpack8(dq[i], dyv);
+        unpack8(gq[i], g);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rstd * (dyv[i][j] * g[i][j] - s1 - xh[i][j] * s2);
+        for (int j = 0; j < 8; ++j)
+          o[j] = rstd * (dyv[j] * keep * g[j] - s1 - (xh[j] - mean) * rstd * s2);
         dxr[c] = pack8(o);
       }
     }
+    if (!kAhead && row + row_step < rows) fetch(row + row_step, xn, dn, keep_n, mean_n, rstd_n);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      xq[i] = xn[i];
+      dq[i] = dn[i];
+    }
+    keep = keep_n;
+    mean = mean_n;
+    rstd = rstd_n;
   }
   // block-level reduction of the parameter gradients, one vector slot at a time
 #pragma unroll
