@@ -130,7 +130,7 @@ def test_one_deberta_v3_base_layer_kernels_match_fp32_modules():
 
 
 def _tiny_step(precision: str, compile_backend: str | None = None, synchronous: bool = True, overlap: bool = True,
-               windows: int = 2, return_engine: bool = False):
+               windows: int = 2, return_engine: bool = False, grad_ckpt: bool = False):
     from deberta_b200.config import Config, DataConfig, ModelConfig, OptimConfig, TrainConfig, validate_config
     from deberta_b200.parallel.dist import DistContext
     from deberta_b200.training.compile import maybe_compile_model
@@ -140,7 +140,8 @@ def _tiny_step(precision: str, compile_backend: str | None = None, synchronous: 
     train_kw = {}
     if compile_backend:
         train_kw = dict(torch_compile=True, torch_compile_backend=compile_backend, torch_compile_scope="backbones")
-    cfg = Config(model=ModelConfig(hf={"model_size": "xsmall"}, tokenizer={"name_or_path": "synthetic:4096"}),
+    cfg = Config(model=ModelConfig(hf={"model_size": "xsmall"}, tokenizer={"name_or_path": "synthetic:4096"},
+                                   gradient_checkpointing=grad_ckpt),
                  data=DataConfig(dataset_name="synthetic", max_seq_length=256),
                  train=TrainConfig(mixed_precision=precision, per_device_train_batch_size=4, gradient_accumulation_steps=1,
                                    max_steps=10, dataloader_num_workers=0, distributed={"overlap_backward": overlap},
@@ -204,6 +205,17 @@ def test_whole_rtd_step_bf16_kernels_match_fp32_modules():
     for (gl, dl, gn, dn), (rgl, rdl, rgn, rdn) in zip(fast, ref):
         assert abs(gl - rgl) < 2e-2 * rgl and abs(dl - rdl) < 5e-2 * rdl
         assert abs(gn - rgn) < 0.15 * rgn and abs(dn - rdn) < 0.25 * rdn  # the discriminator sees sampled tokens
+
+
+def test_activation_checkpointing_leaves_the_step_unchanged():
+    """Per-layer recomputation (non-reentrant checkpoints) with the fused blocks: the residual-gradient hand-over
+    between the attention block's two projections, the side-by-side QKV gradients and the saved position bias all have
+    to survive a forward that runs twice. Losses and gradient norms must match the plain step within atomics noise."""
+    plain = _tiny_step("bf16")
+    ckpt = _tiny_step("bf16", grad_ckpt=True)
+    for (gl, dl, gn, dn), (cgl, cdl, cgn, cdn) in zip(plain, ckpt):
+        assert abs(gl - cgl) < 5e-3 * gl and abs(dl - cdl) < 1e-2 * dl
+        assert abs(gn - cgn) < 3e-2 * gn and abs(dn - cdn) < 3e-2 * dn
 
 
 @pytest.mark.parametrize("backend", ["aot_eager", "inductor"])
