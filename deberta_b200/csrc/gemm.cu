@@ -64,7 +64,7 @@ struct DevParams {
   const unsigned char* forbidden;   // [N] ids that may not be sampled, or null
   float inv_temp;                   // 1 / sampling temperature
   unsigned long long seed;
-  float* ce_part;                   // [4, tiles_n, M]: tile max, tile sum-exp, best noisy logit, its index
+  float* ce_part;                   // [4, tiles_n, M]: tile max, tile sum-exp, largest sampling key, its candidate id
   float* label_logit;               // [M]
   const float* row_lse;             // [M] natural-log log-sum-exp (backward)
   float gscale;                     // dLoss/dlogit scale (backward)
@@ -74,7 +74,7 @@ struct DevParams {
 };
 
 // Counter-based uniform in (0,1) from (seed, row, column): 32-bit multiply-xorshift mixing (two rounds), the seed's
-// halves entering before and between the rounds. One value per logit, so it has to be cheap: ~10 integer operations.
+// halves entering before and between the rounds; ~10 integer operations. The sampler draws two per 32 logits.
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -336,8 +336,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const __nv_bfloat16* bias = p.bias ? p.bias + z * p.bs_bias : nullptr;
       if constexpr (kEpi == EPI_CE_FWD || kEpi == EPI_CE_BWD) {
         // One thread owns one row of logits. Forward: tile-local max / sum-exp / label logit and the
-        // Gumbel-max candidate (logit/T + noise, forbidden ids excluded); partial results of every
-        // vocabulary tile are combined by a second small kernel. Backward: softmax minus one-hot.
+        // sampling candidate (an id drawn inside each 32-column chunk, the chunks competing through Gumbel-max
+        // keys over their masses; forbidden ids excluded); partial results of every vocabulary tile are
+        // combined by a second small kernel, which keeps the candidate with the largest key. Backward: softmax
+        // minus one-hot.
         const long long label = row_ok ? p.labels[row] : -1;
         const float lse = (kEpi == EPI_CE_BWD && row_ok) ? p.row_lse[row] : 0.f;
         const float gs = p.gscale * ((kEpi == EPI_CE_BWD && p.gscale_ptr) ? *p.gscale_ptr : 1.f);
@@ -350,6 +352,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           uint32_t r[32];
           tmem_ld_32x32b_x32(t_row + c * 32, r);
           tmem_ld_wait();
+          const bool label_here = kEpi == EPI_CE_FWD && __any_sync(0xffffffffu, label >= nc && label < nc + 32);
           if (!row_ok) continue;
           float v[32];
           float cmax = -INFINITY;
@@ -386,40 +389,81 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
           }
           if (kEpi == EPI_CE_FWD) {
-            const float m_new = fmaxf(t_max, cmax);
-            float acc = 0.f;
-            // forbidden-id flags of the chunk as one bit mask (two 16-byte loads when the chunk is complete)
+            // forbidden-id flags of the chunk as one bit mask (two 16-byte loads when the chunk is complete);
+            // every lane sees the same columns, so the mask is warp-uniform
             unsigned int ban_mask = 0;
             if (p.forbidden) {
               if (nc + 32 <= p.N && ((reinterpret_cast<uintptr_t>(p.forbidden) + nc) & 15) == 0) {
                 const uint4 f0 = __ldg(reinterpret_cast<const uint4*>(p.forbidden + nc));
                 const uint4 f1 = __ldg(reinterpret_cast<const uint4*>(p.forbidden + nc) + 1);
                 const unsigned int fw[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+                if ((f0.x | f0.y | f0.z | f0.w | f1.x | f1.y | f1.z | f1.w) != 0u) {  // few chunks hold a forbidden id
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  ban_mask |= ((fw[j >> 2] >> ((j & 3) * 8)) & 0xffu) ? (1u << j) : 0u;
+                  for (int j = 0; j < 32; ++j)
+                    ban_mask |= ((fw[j >> 2] >> ((j & 3) * 8)) & 0xffu) ? (1u << j) : 0u;
+                }
               } else {
                 for (int j = 0; j < 32; ++j)
                   if (nc + j < p.N && p.forbidden[nc + j]) ban_mask |= 1u << j;
               }
             }
-            const long long label_off = label - nc;  // position of the label inside this chunk, if it falls there
-            const float m_l2 = m_new * 1.4426950408889634f;
+            if (label_here) {  // some row of this warp has its label in this chunk (about one chunk in a hundred)
+              const long long label_off = label - nc;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int n = nc + j;
-              acc += ex2_approx(fmaf(v[j], 1.4426950408889634f, -m_l2));
-              if (label_off == j) p.label_logit[row] = v[j];
-              if (full_chunk || n < p.N) {
-                const bool banned = (ban_mask >> j) & 1u;
-                // u is an odd multiple of 2^-24: never 0 or 1, so both logarithms are finite.
-                // Gumbel noise -ln(-ln u) = -ln2 * lg2(-ln2 * lg2 u), one MUFU per logarithm
-                const float u = hash_uniform(p.seed, static_cast<unsigned int>(row), static_cast<unsigned int>(n));
-                const float cand = (banned ? -1e9f : v[j] * p.inv_temp) - 0.69314718f * lg2_approx(-0.69314718f * lg2_approx(u));
-                if (cand > best) { best = cand; best_idx = n; }
+              for (int j = 0; j < 32; ++j)
+                if (label_off == j) p.label_logit[row] = v[j];
+            }
+            // Sampling from softmax(logits / T) over the allowed ids, exactly, with two uniforms per chunk instead of
+            // one per logit: the chunk competes with the others through a Gumbel-max key over its total mass
+            // (ln of the sum of exp(logit/T) plus Gumbel noise), and the id inside the chunk is drawn by inverting
+            // the running sum of the same terms. Columns past N hold -inf and weigh nothing.
+            constexpr float kLog2e = 1.4426950408889634f;
+            const bool unit_temp = p.inv_temp == 1.f;
+            const float c_l2 = cmax * kLog2e;
+            float s_all = 0.f;  // sum over the chunk of exp(logit - cmax): the loss's share
+            if (unit_temp) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = ex2_approx(fmaf(v[j], kLog2e, -c_l2));
+              if (ban_mask) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) s_all += v[j];
+              }
+            } else {
+              const float c1 = p.inv_temp * kLog2e;
+              const float c_t = cmax * c1;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                s_all += ex2_approx(fmaf(v[j], kLog2e, -c_l2));
+                v[j] = ex2_approx(fmaf(v[j], c1, -c_t));
               }
             }
-            t_sum = t_sum * __expf(t_max - m_new) + acc;
+            if (ban_mask) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if ((ban_mask >> j) & 1u) v[j] = 0.f;
+            }
+            // running sums in place; the last one is the mass of the chunk
+#pragma unroll
+            for (int j = 1; j < 32; ++j) v[j] += v[j - 1];
+            const float mass = v[31];
+            if (unit_temp && !ban_mask) s_all = mass;
+            if (mass > 0.f) {
+              // u is an odd multiple of 2^-24: never 0 or 1, so every logarithm below is finite
+              const float u_in = hash_uniform(p.seed, static_cast<unsigned int>(row), static_cast<unsigned int>(nc));
+              const float u_key = hash_uniform(p.seed, static_cast<unsigned int>(row), static_cast<unsigned int>(nc) + 1u);
+              // strictly below the total: the count of partial sums <= target is then at most 31, and the chosen
+              // column is one whose term moved the sum, i.e. an allowed id with non-zero weight
+              const float target = fminf(u_in * mass, __uint_as_float(__float_as_uint(mass) - 1u));
+              int pick = 0;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) pick += v[j] <= target ? 1 : 0;
+              // ln(sum_j exp(logit_j / T)) - ln(-ln u): lg2 is one MUFU each
+              const float key = fmaf(cmax, p.inv_temp, 0.69314718f * lg2_approx(mass)) -
+                                0.69314718f * lg2_approx(-0.69314718f * lg2_approx(u_key));
+              if (key > best) { best = key; best_idx = nc + pick; }
+            }
+            const float m_new = fmaxf(t_max, cmax);
+            t_sum = t_sum * __expf(t_max - m_new) + s_all * __expf(cmax - m_new);
             t_max = m_new;
           } else {
             __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldo + nc;
@@ -883,9 +927,9 @@ int db200_make_tmap_bf16(CUtensorMap* out, const void* ptr, long long inner, lon
 extern "C" int db200_gemm_tile_n(int N) { return (N > 128) ? 128 : 64; }
 
 // Combine the per-vocabulary-tile partials of EPI_CE_FWD: per row log-sum-exp (natural log),
-// cross-entropy against the label logit, and the arg-max of the noisy logits (the sample).
+// cross-entropy against the label logit, and the candidate id with the largest sampling key (the sample).
 // block (32 rows, 16 tile slices): every thread folds the tiles t = slice, slice + 16, ... of its row, the slices are
-// then combined through shared memory (online log-sum-exp, arg-max of the noisy logits).
+// then combined through shared memory (online log-sum-exp, arg-max of the sampling keys).
 __global__ void __launch_bounds__(512)
 ce_combine_kernel(const float* __restrict__ part, const float* __restrict__ label_logit, int tiles_n, int M,
                   float* __restrict__ lse_out, float* __restrict__ loss_rows, long long* __restrict__ sampled) {
@@ -910,7 +954,7 @@ ce_combine_kernel(const float* __restrict__ part, const float* __restrict__ labe
   s_m[slice][rl] = m; s_s[slice][rl] = sum; s_b[slice][rl] = best; s_i[slice][rl] = idx;
   __syncthreads();
   if (slice == 0 && row < M) {
-    // slices are folded in a fixed order; ties of the noisy maximum go to the lowest tile index seen first
+    // slices are folded in a fixed order; ties of the largest key go to the lowest tile index seen first
     for (int k = 1; k < kSlices; ++k) {
       const float tm = s_m[k][rl], ts = s_s[k][rl];
       const float nm = fmaxf(m, tm);

@@ -1,8 +1,10 @@
-"""Fused vocabulary projection + cross-entropy + Gumbel-max sampling on the tcgen05 GEMM.
+"""Fused vocabulary projection + cross-entropy + sampling from ``softmax(logits / T)`` on the tcgen05 GEMM.
 
 Forward: one sweep over vocabulary tiles of the tied embedding table; each tile's epilogue
-reduces its logits to (max, sum-exp, label logit, best noisy logit) per row, a small kernel
-combines the tiles. The ``[N, V]`` logits are never written. Backward recomputes the logits
+reduces its logits to (max, sum-exp, label logit, sampling candidate) per row, a small kernel
+combines the tiles. The candidate is exact two-level sampling: inside every 32-column group an id is drawn by
+inverting the running sum of ``exp(logit / T)`` over the allowed ids, and the groups compete through Gumbel-max keys
+``ln(group mass) + Gumbel noise``, so a row costs two uniforms per 32 logits instead of a Gumbel draw per logit. The ``[N, V]`` logits are never written. Backward recomputes the logits
 tile by tile and writes ``softmax − onehot`` once in bf16, which feeds the two gradient GEMMs.
 """
 

@@ -237,18 +237,21 @@ def test_compiled_train_step_has_no_graph_breaks_and_matches_eager(backend):
     dynamo.reset()
 
 
-def test_fused_sampler_frequencies_follow_softmax_chi_square():
-    """V = 64 with forbidden ids: the sample frequencies of 40 000 draws must pass a chi-square test against
-    ``softmax(logits / T)`` renormalised over the allowed ids."""
+@pytest.mark.parametrize("V,T,banned", [(64, 0.7, True), (64, 1.0, True), (1000, 1.0, False), (1000, 1.3, True)])
+def test_fused_sampler_frequencies_follow_softmax_chi_square(V, T, banned):
+    """The sample frequencies of 40 000 draws must pass a chi-square test against ``softmax(logits / T)`` renormalised
+    over the allowed ids: one and several vocabulary tiles (V = 1000 ends in a ragged 8-column chunk), unit and other
+    temperatures (two code paths in the kernel), with and without forbidden ids."""
     from deberta_b200.ops.heads import mlm_loss_and_sample
 
     torch.manual_seed(3)
-    V, E, T = 64, 64, 0.7
+    E = 64
     w = (torch.randn(V, E, device="cuda") * 0.3).to(torch.bfloat16)
     b = (torch.randn(V, device="cuda") * 0.5).to(torch.bfloat16)
     x_row = (torch.randn(E, device="cuda") * 0.5).to(torch.bfloat16)
     forb = torch.zeros(V, dtype=torch.bool, device="cuda")
-    forb[[0, 1, 2, 3, 17, 40]] = True
+    if banned:
+        forb[[0, 1, 2, 3, 17, 40]] = True
     logits = (x_row.float() @ w.float().t() + b.float()) / T
     probs = torch.softmax(logits.masked_fill(forb, -1e9), dim=-1).double().cpu()
     N, rounds = 4000, 10
@@ -256,7 +259,7 @@ def test_fused_sampler_frequencies_follow_softmax_chi_square():
     labels = torch.full((N,), 5, device="cuda")
     counts = torch.zeros(V, dtype=torch.float64)
     for _ in range(rounds):
-        _, s = mlm_loss_and_sample(x, w, b, labels, forb, T)
+        _, s = mlm_loss_and_sample(x, w, b, labels, forb if banned else None, T)
         counts += torch.bincount(s.cpu(), minlength=V).double()
     _lib.check_status()
     assert float(counts[forb.cpu()].sum()) == 0.0
