@@ -27,19 +27,31 @@ using namespace tc05;
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int kEpilogueWarps = 8;  // two per TMEM lane quadrant, each owning half of the tile's columns
-constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+// Epilogue warps per CTA: a warp may read only its own TMEM lane quadrant (warp id mod 4), so the warps come in sets
+// of four and each set owns an equal share of the tile's columns. Two sets cover every epilogue that hides behind the
+// MMAs; the ones that do real arithmetic per element (cross-entropy with sampling, GELU with two outputs) and would
+// otherwise set the kernel's pace with two warps per scheduler get four sets on the wide tile.
+template <int BN, int MODE>
+__host__ __device__ constexpr int epilogue_warps() { return (BN == 256 && (MODE == 4 || MODE == 5 || MODE == 6)) ? 16 : 8; }
+template <int BN, int MODE>
+__host__ __device__ constexpr int gemm_threads() { return 64 + 32 * epilogue_warps<BN, MODE>(); }
 
-template <int BN>
+template <int BN, int MODE>
 struct SmemLayout {
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kEpilogueWarps = epilogue_warps<BN, MODE>();
+  // the cross-entropy epilogues write from registers and need no staging tiles (2 KB stay for alignment's sake)
+  static constexpr bool kStaging = !(MODE == 4 || MODE == 5);
+  static constexpr int kStagingBytes = 32 * 128;  // per epilogue warp: 32 rows x 64 bf16, 128B swizzle
+  static constexpr int kStagingTotal = kStaging ? kEpilogueWarps * kStagingBytes : 2048;
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
+  // 16 staging tiles leave room for three operand stages of the wide tile
+  static constexpr int kStages = (BN == 256) ? ((kStaging && kEpilogueWarps == 16) ? 3 : 4) : 6;
   static constexpr int kStagingOffset = kStages * kStageBytes;          // 1024-byte aligned
-  static constexpr int kStagingBytes = 32 * 128;                         // per epilogue warp: 32 rows x 64 bf16, 128B swizzle
-  static constexpr int kBarOffset = kStagingOffset + kEpilogueWarps * kStagingBytes;
+  static constexpr int kBarOffset = kStagingOffset + kStagingTotal;
   static constexpr int kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
+  static_assert(kTotal <= 227 * 1024, "shared memory of one CTA");
 };
 
 struct DevParams {
@@ -128,11 +140,14 @@ __device__ __forceinline__ float dgelu_erf(float x) {
 // 8 SwiGLU forward (a tile = 128 gate columns and the 128 up columns that go with them; three outputs' worth of
 // stores), 9 SwiGLU backward.
 template <int BN, bool A_MN, bool B_MN, int MODE>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(gemm_threads<BN, MODE>(), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_out2,
             const DevParams p) {
-  using L = SmemLayout<BN>;
+  using L = SmemLayout<BN, MODE>;
+  constexpr int kEpilogueWarps = L::kEpilogueWarps;
+  constexpr int kThreads = gemm_threads<BN, MODE>();
+  constexpr int kParts = kEpilogueWarps / 4;  // column shares of a tile (one per set of four warps)
   constexpr int kEpi = MODE == 1 ? EPI_GELU : MODE == 2 ? EPI_DGELU : MODE == 4 ? EPI_CE_FWD : MODE == 5 ? EPI_CE_BWD
                        : MODE == 6 ? EPI_GELU_GRAD : MODE == 7 ? EPI_MUL : MODE == 8 ? EPI_SWIGLU
                        : MODE == 9 ? EPI_SWIGLU_BWD : EPI_NONE;
@@ -287,8 +302,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   } else {
     // ------------------------------- epilogue -----------------------------------
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
-    const int half = (warp - 2) >> 2;  // which half of the tile's columns
-    constexpr int kChunksPerHalf = BN / 64;
+    const int half = (warp - 2) >> 2;  // which share of the tile's columns (a half with two sets of warps)
+    constexpr int kChunksPerHalf = BN / (32 * kParts);  // 32-column chunks of one share
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -479,10 +494,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
           }
         }
-        if (kEpi == EPI_CE_FWD && row_ok && (n0 + half * (BN / 2) < p.N)) {
-          // partial results are kept per half tile: ceil(N / (BN/2)) entries per row
-          const long long tn = (n0 / BN) * 2 + half;
-          const long long plane = static_cast<long long>((p.N + BN / 2 - 1) / (BN / 2)) * p.M;
+        if (kEpi == EPI_CE_FWD && row_ok && (n0 + half * (BN / kParts) < p.N)) {
+          // partial results are kept per column share of a tile (64 columns): ceil(N / 64) entries per row
+          static_assert(kEpi != EPI_CE_FWD || BN / kParts == 64, "db200_gemm_tile_n");
+          const long long tn = (n0 / BN) * kParts + half;
+          const long long plane = static_cast<long long>((p.N + BN / kParts - 1) / (BN / kParts)) * p.M;
           float* dst = p.ce_part + tn * p.M + row;
           dst[0] = t_max;
           dst[plane] = t_sum;
@@ -851,7 +867,8 @@ int num_sms() {  // per device: a process may drive more than one GPU
 template <int BN, bool A_MN, bool B_MN, int MODE>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, const CUtensorMap& to2, const DevParams& p,
            int grid, cudaStream_t stream) {
-  using L = SmemLayout<BN>;
+  using L = SmemLayout<BN, MODE>;
+  constexpr int kThreads = gemm_threads<BN, MODE>();
   static bool configured[kMaxDevices] = {};  // the shared-memory opt-in is a per-device attribute of the function
   auto kern = gemm_kernel<BN, A_MN, B_MN, MODE>;
   const int dev = current_device();
@@ -923,8 +940,9 @@ int db200_make_tmap_bf16(CUtensorMap* out, const void* ptr, long long inner, lon
   return 0;
 }
 
-// Width of the column range one partial result of EPI_CE_FWD covers (half of the GEMM tile).
-extern "C" int db200_gemm_tile_n(int N) { return (N > 128) ? 128 : 64; }
+// Width of the column range one partial result of EPI_CE_FWD covers: the share of a tile that one set of four
+// epilogue warps reduces (a quarter of the 256-column tile, half of the 128-column one).
+extern "C" int db200_gemm_tile_n(int N) { (void)N; return 64; }
 
 // Combine the per-vocabulary-tile partials of EPI_CE_FWD: per row log-sum-exp (natural log),
 // cross-entropy against the label logit, and the candidate id with the largest sampling key (the sample).
