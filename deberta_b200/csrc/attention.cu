@@ -892,10 +892,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int quad = warp & 3;
   const int part = warp >> 2;
   const int row = quad * 32 + lane;  // row of the tile this thread works on (query row, or key row at the end)
-  const int k0 = blockIdx.x * kTile;
-  const int h = blockIdx.y;
-  const int b = blockIdx.z;
   const int S = p.S;
+  // Work items are (batch, head, key tile) triples, key tile fastest. A CTA takes items blockIdx.x, blockIdx.x +
+  // gridDim.x, ...: the launcher starts one CTA per item where items differ in length (document ids) and one per SM
+  // otherwise, so that barriers, tensor memory and the lookup tables are set up once and the loads of the next item
+  // fly while the gradients of the current one leave the tensor memory.
+  const int nkt_all = (S + kTile - 1) / kTile;
+  const int n_items = nkt_all * p.heads * p.B;
   pdl_launch_dependents();
 
   if (tid == 0) {
@@ -913,27 +916,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tmem_relinquish();
   }
   pdl_wait();  // set-up done; everything below may touch global memory
-  int ib = 0, nqt = (S + kTile - 1) / kTile;  // first query tile and number of query tiles this CTA visits
-  if (MASK == 2) doc_tile_run(p.doc_tiles, b, nqt, blockIdx.x, lane, ib, nqt);
   if (POS == 2) {
     for (int i = tid; i < 2 * S - 1; i += kBwdThreads) {
       lutc[i] = p.lut_c2p[i];
       lutp[i] = p.lut_p2c[i];
     }
   }
-  int cta_meta = 1;
-  if (MASK != 0 && tid < kTile) {
-    const int kk = k0 + tid;
-    int meta = 0;
-    if (kk < S) {
-      const long long tk = static_cast<long long>(b) * S + kk;
-      meta = MASK == 1 ? (p.key_keep[tk] ? 1 : 0) : p.doc_ids[tk];
-    }
-    kmeta[tid] = meta;
-    cta_meta = meta;
-  }
   tc_fence_before();
-  const bool tile_all_keep = __syncthreads_and(MASK == 1 && cta_meta != 0) != 0;  // all 128 keys of this CTA are kept
+  __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 320,
@@ -958,26 +948,54 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     umma_commit(bar_s);
   };
 
+  // K, V and the first two (Q, dO) tiles of an item; `g` is the running count of query tiles this CTA has visited,
+  // which names the ring slot (g % 3) and the barrier phase ((g / 3) & 1) of a tile
+  auto issue_item_loads = [&](int b_, int h_, int k0_, int ib_, int nqt_, int g) {
+    mbar_expect_tx(bar_kv, 2 * kTileBytes);
+    tma_load_3d(sK, &tm_k, bar_kv, h_ * kD, k0_, b_);
+    tma_load_3d(sV, &tm_v, bar_kv, h_ * kD, k0_, b_);
+    for (int t = 0; t < 2 && t < nqt_; ++t) {
+      const int slot = (g + t) % 3;
+      mbar_expect_tx(&bar_qd[slot], 2 * kTileBytes);
+      tma_load_3d(sQ + slot * kTileBytes, &tm_q, &bar_qd[slot], h_ * kD, (ib_ + t) * kTile, b_);
+      tma_load_3d(sdO + slot * kTileBytes, &tm_do, &bar_qd[slot], h_ * kD, (ib_ + t) * kTile, b_);
+    }
+  };
   if (tid == 0) {
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
     tma_prefetch_desc(&tm_do);
-    mbar_expect_tx(bar_kv, 2 * kTileBytes);
-    tma_load_3d(sK, &tm_k, bar_kv, h * kD, k0, b);
-    tma_load_3d(sV, &tm_v, bar_kv, h * kD, k0, b);
-    mbar_expect_tx(&bar_qd[0], 2 * kTileBytes);
-    tma_load_3d(sQ, &tm_q, &bar_qd[0], h * kD, ib * kTile, b);
-    tma_load_3d(sdO, &tm_do, &bar_qd[0], h * kD, ib * kTile, b);
-    if (nqt > 1) {
-      mbar_expect_tx(&bar_qd[1], 2 * kTileBytes);
-      tma_load_3d(sQ + kTileBytes, &tm_q, &bar_qd[1], h * kD, (ib + 1) * kTile, b);
-      tma_load_3d(sdO + kTileBytes, &tm_do, &bar_qd[1], h * kD, (ib + 1) * kTile, b);
+  }
+
+  bool ok = true;
+  int g0 = 0;       // query tiles visited by this CTA before the current item
+  int n_done = 0;   // items finished by this CTA (phase of bar_kv)
+  bool loads_issued = false;  // the previous item already asked for this item's operands
+  for (int w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
+  const int k0 = (w % nkt_all) * kTile;
+  const int h = (w / nkt_all) % p.heads;
+  const int b = w / (nkt_all * p.heads);
+  int ib = 0, nqt = nkt_all;  // first query tile and number of query tiles of this item
+  if (MASK == 2) doc_tile_run(p.doc_tiles, b, nkt_all, w % nkt_all, lane, ib, nqt);
+  if (tid == 0 && !loads_issued) issue_item_loads(b, h, k0, ib, nqt, g0);
+  int cta_meta = 1;
+  if (MASK != 0 && tid < kTile) {
+    const int kk = k0 + tid;
+    int meta = 0;
+    if (kk < S) {
+      const long long tk = static_cast<long long>(b) * S + kk;
+      meta = MASK == 1 ? (p.key_keep[tk] ? 1 : 0) : p.doc_ids[tk];
     }
-    if (mbar_wait(bar_kv, 0, abort_flag, p.status, kErrFullWait) &&
-        mbar_wait(&bar_qd[0], 0, abort_flag, p.status, kErrFullWait)) {
+    kmeta[tid] = meta;
+    cta_meta = meta;
+  }
+  const bool tile_all_keep = __syncthreads_and(MASK == 1 && cta_meta != 0) != 0;  // all 128 keys of this item are kept
+  if (tid == 0) {
+    if (mbar_wait(bar_kv, n_done & 1, abort_flag, p.status, kErrFullWait) &&
+        mbar_wait(&bar_qd[g0 % 3], (g0 / 3) & 1, abort_flag, p.status, kErrFullWait)) {
       tc_fence_after();
-      issue_scores(0);
+      issue_scores(g0 % 3);
     } else {
       umma_commit(bar_s);
     }
@@ -997,9 +1015,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   };
 
-  bool ok = true;
-  for (int i = 0; i < nqt; ++i) {  // i counts visited tiles (buffers and barrier phases follow it)
-    const int buf = i % 3;
+  for (int i = 0; i < nqt; ++i) {  // i counts the visited tiles of this item; buffers and barrier phases follow g
+    const int g = g0 + i;
+    const int buf = g % 3;
     const int q0 = (ib + i) * kTile;
     // per-row inputs that do not depend on the scores are requested before the wait: their latency hides behind the MMAs
     const int q = q0 + row;
@@ -1020,7 +1038,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     bool got_g = true;
     // (a wait that ran out is reported at the next block barrier, where the whole block leaves the loop together)
-    const bool got_s = mbar_wait(bar_s, i & 1, abort_flag, p.status, kErrAccFullWait);
+    const bool got_s = mbar_wait(bar_s, g & 1, abort_flag, p.status, kErrAccFullWait);
     tc_fence_after();
     uint32_t rs[32], rd[32];  // this thread's 32 scores and 32 dP values of tile i
     tmem_ld_32x32b_x32(t_s + lane_addr + part * 32, rs);
@@ -1030,8 +1048,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // both accumulators are in registers: the tensor core may start on tile i+1
     if (!__syncthreads_and(got_s)) { ok = false; break; }
     if (tid == 0 && i + 1 < nqt) {
-      const int nb = (i + 1) % 3;
-      if (mbar_wait(&bar_qd[nb], ((i + 1) / 3) & 1, abort_flag, p.status, kErrFullWait)) {
+      const int nb = (g + 1) % 3;
+      if (mbar_wait(&bar_qd[nb], ((g + 1) / 3) & 1, abort_flag, p.status, kErrFullWait)) {
         tc_fence_after();
         issue_scores(nb);
       } else {
@@ -1097,19 +1115,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       // the previous tile's gradient MMAs must retire before its P / dS tiles and dQ accumulator are reused
       if (i > 0) {
-        got_g = __all_sync(0xffffffffu, mbar_wait(bar_g, (i - 1) & 1, abort_flag, p.status, kErrAccFullWait));
+        got_g = __all_sync(0xffffffffu, mbar_wait(bar_g, (g - 1) & 1, abort_flag, p.status, kErrAccFullWait));
         tc_fence_after();
-        if (tid == 0 && got_g && i + 2 < nqt) {  // buffer (i+2)%3 held tile i-1
-          const int nb = (i + 2) % 3;
+        if (tid == 0 && got_g && i + 2 < nqt) {  // slot (g+2)%3 held tile g-1
+          const int nb = (g + 2) % 3;
           mbar_expect_tx(&bar_qd[nb], 2 * kTileBytes);
           tma_load_3d(sQ + nb * kTileBytes, &tm_q, &bar_qd[nb], h * kD, q0 + 2 * kTile, b);
           tma_load_3d(sdO + nb * kTileBytes, &tm_do, &bar_qd[nb], h * kD, q0 + 2 * kTile, b);
         }
         if (got_g) flush_dq(ib + i - 1);
-      } else if (tid == 0 && nqt > 2) {
-        mbar_expect_tx(&bar_qd[2], 2 * kTileBytes);
-        tma_load_3d(sQ + 2 * kTileBytes, &tm_q, &bar_qd[2], h * kD, (ib + 2) * kTile, b);
-        tma_load_3d(sdO + 2 * kTileBytes, &tm_do, &bar_qd[2], h * kD, (ib + 2) * kTile, b);
+      } else if (tid == 0 && nqt > 2) {  // the item's third tile: its slot is free (every earlier MMA has retired)
+        const int nb = (g + 2) % 3;
+        mbar_expect_tx(&bar_qd[nb], 2 * kTileBytes);
+        tma_load_3d(sQ + nb * kTileBytes, &tm_q, &bar_qd[nb], h * kD, (ib + 2) * kTile, b);
+        tma_load_3d(sdO + nb * kTileBytes, &tm_do, &bar_qd[nb], h * kD, (ib + 2) * kTile, b);
       }
       // rows of P and dS for these 32 keys: 4 chunks of 8 bf16 inside 64-key block (c >> 1)
       uint32_t dsw[16];
@@ -1158,8 +1177,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   }
 
-  if (ok && mbar_wait(bar_g, (nqt - 1) & 1, abort_flag, p.status, kErrAccFullWait)) {
-    tc_fence_after();
+  if (!ok) break;
+  const bool fin = mbar_wait(bar_g, (g0 + nqt - 1) & 1, abort_flag, p.status, kErrAccFullWait);
+  tc_fence_after();
+  g0 += nqt;
+  ++n_done;
+  loads_issued = false;
+  if (MASK != 2) {
+    // every MMA of this item has retired: K, V and the (Q, dO) ring are free, and the next item's operands can
+    // travel while this item's gradients are read out of the tensor memory
+    const int wn = w + gridDim.x;
+    if (wn < n_items) {
+      loads_issued = true;
+      if (tid == 0 && fin)
+        issue_item_loads(wn / (nkt_all * p.heads), (wn / nkt_all) % p.heads, (wn % nkt_all) * kTile, 0, nkt_all, g0);
+    }
+  }
+  if (fin) {
     flush_dq(ib + nqt - 1);
     const int kk = k0 + row;
     const long long tk = static_cast<long long>(b) * S + kk;
@@ -1170,13 +1204,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_ld_32x32b_x16((which == 0 ? t_dv : t_dk) + lane_addr + part * 16, r);
       tmem_ld_wait();
       if (kk < S) {
-        uint32_t w[8];
+        uint32_t pk[8];
 #pragma unroll
-        for (int g = 0; g < 8; ++g) w[g] = pack_bf16(__uint_as_float(r[2 * g]), __uint_as_float(r[2 * g + 1]));
-        store_bf16x16(dst, w);
+        for (int e = 0; e < 8; ++e) pk[e] = pack_bf16(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
+        store_bf16x16(dst, pk);
       }
     }
   }
+  // the next item's first gradient MMAs (and its key metadata) may only follow once every thread is done here;
+  // a wait that ran out ends the CTA for all threads together
+  tc_fence_before();
+  if (!__syncthreads_and(fin)) ok = false;
+  tc_fence_after();
+  }  // work items
+
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {
@@ -1264,6 +1305,21 @@ int g_fwd_key_tile = 64;
 // With 64-key tiles and neither document ids nor in-kernel table gathers: the warp-specialised kernel (a dedicated
 // TMA/MMA warp, mbarriers instead of block-wide barriers).
 int g_fwd_specialised = 1;
+// backward: 1 = one CTA per SM walks the (batch, head, key tile) items; 0 = one CTA per item; n > 1 = at most n CTAs
+// (tests: several items per CTA on small inputs)
+int g_bwd_persistent = 1;
+
+int sm_count() {  // per device: a process may drive more than one GPU
+  static int count[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  dev = (dev >= 0 && dev < 16) ? dev : 0;
+  if (count[dev] == 0) {
+    cudaDeviceGetAttribute(&count[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (count[dev] <= 0) count[dev] = 148;
+  }
+  return count[dev];
+}
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -1398,7 +1454,13 @@ extern "C" int db200_attn_bwd(const AttnArgs* a, void* stream_) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -3;
     configured[dev][mask_mode][pos_mode] = smem;
   }
-  dim3 grid((a->S + kTile - 1) / kTile, a->heads, a->B);
+  // one CTA per SM walks the work items; items of different lengths (document ids) get a CTA each, which the
+  // hardware hands out as SMs become free
+  const long long items = static_cast<long long>((a->S + kTile - 1) / kTile) * a->heads * a->B;
+  if (items > 0x7fffffffLL) return -12;
+  const bool persistent = g_bwd_persistent && mask_mode != 2;
+  const int max_ctas = g_bwd_persistent > 1 && g_bwd_persistent < sm_count() ? g_bwd_persistent : sm_count();
+  dim3 grid(static_cast<unsigned>(persistent && items > max_ctas ? max_ctas : items));
   if (launch_pdl(kern, grid, dim3(kBwdThreads), smem, stream, tq, tk, tv, tdo, d) != cudaSuccess) return -4;
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -1420,6 +1482,14 @@ extern "C" int db200_attn_doc_tiles(const void* doc_ids, void* tiles, int B, int
   attn_doc_tiles_kernel<<<grid, kTile, 0, reinterpret_cast<cudaStream_t>(stream)>>>(static_cast<const int*>(doc_ids),
                                                                                    static_cast<int*>(tiles), S);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Backward kernel: 1 = one CTA per SM loops over the work items (default), 0 = one CTA per item, n > 1 = at most n
+// CTAs; returns the previous value (A/B comparisons, tests).
+extern "C" int db200_attn_set_bwd_persistent(int on) {
+  const int old = g_bwd_persistent;
+  g_bwd_persistent = on < 0 ? 0 : on;
+  return old;
 }
 
 // 64 or 128 keys per tile in the forward kernel (anything else selects 64); returns the previous value.

@@ -70,6 +70,16 @@ def set_forward_key_tile(keys: int) -> int:
     return int(_lib.lib().db200_attn_set_fwd_key_tile(c_int(int(keys))))
 
 
+def set_backward_persistent(on: bool | int) -> int:
+    """Backward kernel scheduling: ``True`` (default) starts one CTA per SM that walks the (batch, head, key tile) work
+    items, so barriers and tensor memory are set up once and the next item's operands travel while the current item's
+    gradients leave the tensor memory; ``False`` starts one CTA per item; an integer above 1 caps the number of CTAs
+    (tests use it to give every CTA several items on small inputs). Inputs with document ids always get a CTA per
+    item (their items differ in length). Returns the previous setting; results are identical up to the order of the
+    fp32 additions into the query gradient."""
+    return int(_lib.lib().db200_attn_set_bwd_persistent(c_int(int(on))))
+
+
 _LUT_CACHE: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
 
 

@@ -15,12 +15,16 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(autouse=True, params=[64, 65, 128], ids=["kt64ws", "kt64", "kt128"])
 def forward_key_tile(request):
     """Every case runs on the three forward kernels: 64 keys per tile with a dedicated TMA/MMA warp (the default where
-    it applies), 64 keys per tile with block-wide barriers (65), and 128 keys per tile (one CTA per SM)."""
-    from deberta_b200.ops.attention_cuda import set_forward_key_tile
+    it applies), 64 keys per tile with block-wide barriers (65), and 128 keys per tile (one CTA per SM). The backward
+    kernel runs with one CTA per SM walking the work items (the default), with one CTA per item, and with at most three
+    CTAs, so that on these small inputs every CTA goes through several items."""
+    from deberta_b200.ops.attention_cuda import set_backward_persistent, set_forward_key_tile
 
     old = set_forward_key_tile(request.param)
+    old_bwd = set_backward_persistent({64: 1, 65: 0, 128: 3}[request.param])
     yield request.param
     set_forward_key_tile(old)
+    set_backward_persistent(old_bwd)
 
 
 def _rel_err(got, ref):
