@@ -104,7 +104,10 @@ class ResidualGradSink:
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, b, residual, sink):
-        ctx.save_for_backward(x, w)
+        # Parameters are kept by reference, not through save_for_backward: activation checkpointing hands saved
+        # tensors back as detached copies, which have lost the parameter's ``main_grad`` buffer.
+        ctx.save_for_backward(x)
+        ctx.w_ref = w
         ctx.has_bias = b is not None
         ctx.bias_ref = b
         ctx.has_res = residual is not None
@@ -113,7 +116,8 @@ class _Linear(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        x, w = ctx.saved_tensors
+        (x,) = ctx.saved_tensors
+        w = ctx.w_ref
         dy = dy.contiguous()
         dx = gemm(dy, w, b_mn=True) if ctx.needs_input_grad[0] else None
         dw, db = _param_grads(dy, x, w, ctx.bias_ref if ctx.has_bias else None)
@@ -163,16 +167,16 @@ class _FFNGelu(torch.autograd.Function):
             residual = x
         g, a = gemm(x, w1, bias=b1, epi=EPI_GELU_GRAD)
         y = gemm(a, w2, bias=b2, residual=residual)
-        ctx.save_for_backward(x, w1, w2, g, a)
-        ctx.params = (b1, b2)
+        ctx.save_for_backward(x, g, a)
+        ctx.params = (w1, b1, w2, b2)  # by reference (see _Linear)
         ctx.has_res = residual is not None and not residual_is_x
         ctx.res_is_x = bool(residual_is_x)
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, w1, w2, g, a = ctx.saved_tensors
-        b1, b2 = ctx.params
+        x, g, a = ctx.saved_tensors
+        w1, b1, w2, b2 = ctx.params
         dy = dy.contiguous()
         dz = gemm(dy, w2, b_mn=True, epi=EPI_MUL, aux=g)
         dw2, db2 = _param_grads(dy, a, w2, b2)
@@ -211,15 +215,15 @@ class _FFNSwiGLU(torch.autograd.Function):
     def forward(ctx, x, w12, b12, w3, b3, residual):
         gu, h = gemm(x, w12, bias=b12, epi=EPI_SWIGLU)
         y = gemm(h, w3, bias=b3, residual=residual)
-        ctx.save_for_backward(x, w12, w3, gu, h)
-        ctx.params = (b12, b3)
+        ctx.save_for_backward(x, gu, h)
+        ctx.params = (w12, b12, w3, b3)  # by reference (see _Linear)
         ctx.has_res = residual is not None
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, w12, w3, gu, h = ctx.saved_tensors
-        b12, b3 = ctx.params
+        x, gu, h = ctx.saved_tensors
+        w12, b12, w3, b3 = ctx.params
         dy = dy.contiguous()
         dgu = gemm(dy, w3, b_mn=True, epi=EPI_SWIGLU_BWD, aux=gu)
         dw3, db3 = _param_grads(dy, h, w3, b3)
@@ -287,14 +291,16 @@ class _LinearQKV(torch.autograd.Function):
         n, k = wq.shape
         w_all = _span3(wq, (3 * n, k))
         b_all = None if bq is None else _span3(bq, (3 * n,))
-        ctx.save_for_backward(x, wq)
+        ctx.save_for_backward(x)
+        ctx.wq = wq  # by reference (see _Linear)
         ctx.bq = bq
         ctx.sink = sink
         return gemm(x, w_all, bias=b_all)
 
     @staticmethod
     def backward(ctx, dqkv):
-        x, wq = ctx.saved_tensors
+        (x,) = ctx.saved_tensors
+        wq = ctx.wq
         n, k = wq.shape
         if dqkv.stride(1) != 1 or dqkv.stride(0) % 8 or dqkv.data_ptr() % 16:
             dqkv = dqkv.contiguous()

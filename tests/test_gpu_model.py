@@ -211,7 +211,11 @@ def test_activation_checkpointing_leaves_the_step_unchanged():
     """Per-layer recomputation (non-reentrant checkpoints) with the fused blocks: the residual-gradient hand-over
     between the attention block's two projections, the side-by-side QKV gradients and the saved position bias all have
     to survive a forward that runs twice. Losses and gradient norms must match the plain step within atomics noise."""
+    from deberta_b200.ops import heads_cuda
+
+    heads_cuda._SEED_STATE["counter"] = 0  # both runs draw the same replacement tokens
     plain = _tiny_step("bf16")
+    heads_cuda._SEED_STATE["counter"] = 0
     ckpt = _tiny_step("bf16", grad_ckpt=True)
     for (gl, dl, gn, dn), (cgl, cdl, cgn, cdn) in zip(plain, ckpt):
         assert abs(gl - cgl) < 5e-3 * gl and abs(dl - cdl) < 1e-2 * dl
