@@ -16,7 +16,7 @@ import torch
 
 from . import _lib
 from .gemm import GemmArgsCache, gemm
-from .linear import _weight_grad
+from .linear import _param_grads, weight_grad_into
 
 _SEED_STATE = {"counter": 0}
 
@@ -71,6 +71,7 @@ class _VocabCE(torch.autograd.Function):
                   _lib.ptr(lse), _lib.ptr(loss_rows), _lib.ptr(sampled), _lib.stream_ptr())
         ctx.save_for_backward(x, weight, bias_c, labels, lse)
         ctx.bias_ref = bias
+        ctx.weight_ref = weight  # the parameter itself: a saved tensor may come back without its gradient buffer
         ctx.mark_non_differentiable(sampled)
         return loss_rows.mean(), sampled
 
@@ -85,16 +86,23 @@ class _VocabCE(torch.autograd.Function):
         _ce_gemm(x, weight, bias_c, labels, epi=_lib.EPI_CE_BWD, out=dlogits.data_ptr(), ldo=Vp, row_lse=lse.data_ptr(),
                  gscale=1.0 / N, gscale_ptr=g.data_ptr())
         dx = gemm(dlogits, weight, b_mn=True)
-        dw = _weight_grad(dlogits, x, weight) if weight.requires_grad else None
-        db = None
-        if bias is not None and bias.requires_grad:
-            from .linear import colsum_into
+        want_b = bias is not None and bias.requires_grad
+        w_main = getattr(ctx.weight_ref, "main_grad", None)
+        b_main = getattr(bias, "main_grad", None) if want_b else None
+        if weight.requires_grad and want_b and w_main is not None and b_main is not None:
+            # the table's gradient GEMM sums dlogits over the rows on the tensor cores as well: no column-sum pass
+            # over the [N, V] tensor
+            dw, db = _param_grads(dlogits, x, ctx.weight_ref, bias)
+        else:
+            dw = weight_grad_into(dlogits, x, weight, w_main) if weight.requires_grad else None
+            db = None
+            if want_b:
+                from .linear import colsum_into
 
-            main = getattr(bias, "main_grad", None)
-            gb = main if main is not None else torch.zeros(V, dtype=torch.float32, device=x.device)
-            colsum_into(dlogits, gb)
-            if main is None:
-                db = gb.to(bias.dtype)
+                gb = b_main if b_main is not None else torch.zeros(V, dtype=torch.float32, device=x.device)
+                colsum_into(dlogits, gb)
+                if b_main is None:
+                    db = gb.to(bias.dtype)
         return dx, dw, db, None, None, None
 
 

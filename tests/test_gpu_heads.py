@@ -11,12 +11,18 @@ from deberta_b200.ops.heads import mlm_loss_and_sample, mlm_loss_and_sample_refe
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("buffers", [False, True], ids=["grads", "main_grad"])
 @pytest.mark.parametrize("N,V,E", [(300, 5000, 128), (77, 128100, 768), (130, 1000, 64)])
-def test_vocab_ce_matches_reference(N, V, E):
+def test_vocab_ce_matches_reference(N, V, E, buffers):
+    """``buffers``: the parameters carry the engine's fp32 accumulation buffers, so the table's gradient GEMM also sums
+    the bias gradient (one launch) and both are ADDED to what the buffers held."""
     torch.manual_seed(0)
     x = (torch.randn(N, E, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
     w = (torch.randn(V, E, device="cuda") * 0.2).to(torch.bfloat16).requires_grad_(True)
     b = (torch.randn(V, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_(True)
+    if buffers:
+        w.main_grad = torch.full((V, E), 0.25, dtype=torch.float32, device="cuda")
+        b.main_grad = torch.full((V,), -0.5, dtype=torch.float32, device="cuda")
     labels = torch.randint(5, V, (N,), device="cuda")
     forb = torch.zeros(V, dtype=torch.bool, device="cuda")
     forb[:5] = True
@@ -29,8 +35,14 @@ def test_vocab_ce_matches_reference(N, V, E):
     (loss * 3.0).backward()
     (ref_loss * 3.0).backward()
     _lib.check_status()
-    for name, a, r in (("x", x, xr), ("w", w, wr), ("b", b, br)):
-        err = (a.grad.float() - r.grad).abs().max().item() / (r.grad.abs().max().item() + 1e-9)
+    got = {"x": x.grad.float()}
+    if buffers:
+        assert w.grad is None and b.grad is None
+        got["w"], got["b"] = w.main_grad - 0.25, b.main_grad + 0.5
+    else:
+        got["w"], got["b"] = w.grad.float(), b.grad.float()
+    for name, r in (("x", xr), ("w", wr), ("b", br)):
+        err = (got[name] - r.grad).abs().max().item() / (r.grad.abs().max().item() + 1e-9)
         assert err < 3e-2, (name, err)
 
 
