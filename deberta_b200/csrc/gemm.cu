@@ -643,7 +643,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         // row-indexed epilogue operands are requested before the accumulator wait so that both latencies overlap
         uint32_t resw[16];
         const uint32_t* auxw = auxp[csub];
-        const bool res_vec = !kOutF32 && p.residual && row_ok && full && (p.ldr % 8 == 0);
+        // (the two-output GELU forms take no residual: the launcher refuses it, and its 16 registers stay free)
+        const bool res_vec = !kOutF32 && !kTwoOut && p.residual && row_ok && full && (p.ldr % 8 == 0);
         const bool aux_vec = auxv[csub];
         if (res_vec) load_bf16x32(p.residual + z * p.bs_res + static_cast<long long>(row) * p.ldr + nc, resw);
         tmem_ld_wait();
@@ -699,7 +700,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         // ---- bf16 outputs ----
         const bool vec = full && (p.ldo % 8 == 0);
-        if (p.residual && row_ok) {
+        if (!kTwoOut && p.residual && row_ok) {
           if (res_vec) {
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
@@ -746,8 +747,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 normal_cdf_pdf(z1, c1, d1);
                 act[i] = pack_bf16(z0 * c0, z1 * c1);
                 wds[i] = pack_bf16(fmaf(z0, d0, c0), fmaf(z1, d1, c1));
-                v[2 * i] = fmaf(z0, d0, c0);  // the scalar tail below stores v
-                v[2 * i + 1] = fmaf(z1, d1, c1);
               }
             } else {
 #pragma unroll
@@ -756,10 +755,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             if (row_ok && full) {
               __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + z * p.bs_out + static_cast<long long>(row) * p.ldo + nc;
               store_words16(o, wds);
-            } else if (row_ok) {
-              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + z * p.bs_out + static_cast<long long>(row) * p.ldo + nc;
+            } else if (row_ok) {  // ragged last chunk: element by element, from the packed words (v is dead by now)
+              unsigned short* o = reinterpret_cast<unsigned short*>(p.out) + z * p.bs_out + static_cast<long long>(row) * p.ldo + nc;
+#pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (nc + j < p.N) o[j] = __float2bfloat16(v[j]);
+                if (nc + j < p.N) o[j] = static_cast<unsigned short>((j & 1) ? (wds[j >> 1] >> 16) : (wds[j >> 1] & 0xffffu));
             }
 #pragma unroll
             for (int i = 0; i < 16; ++i) wds[i] = act[i];
@@ -1047,7 +1047,7 @@ extern "C" int db200_gemm_bf16(const GemmArgs* a, void* stream_) {
   if ((p.epi == EPI_CE_FWD) && (!p.labels || !p.ce_part || !p.label_logit || a->batch != 1)) return -11;
   if ((p.epi == EPI_CE_BWD) && (!p.labels || !p.row_lse || p.out_f32 || a->batch != 1)) return -11;
   const bool two_out = p.epi == EPI_GELU || p.epi == EPI_GELU_GRAD;
-  if (two_out && (p.out_f32 || !p.out2)) return -11;
+  if (two_out && (p.out_f32 || !p.out2 || a->residual)) return -11;
   if ((p.epi == EPI_DGELU || p.epi == EPI_MUL) && (p.out_f32 || !p.aux)) return -11;
   if (p.epi == EPI_SWIGLU && (p.out_f32 || !p.out2 || a->batch != 1 || (a->N % 2) || a->a_mn || a->b_mn || a->N <= 128 ||
                               a->residual))
