@@ -107,7 +107,7 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
 }
 
 template <int V, bool RMS>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32, (V <= 3) ? 2 : 1)
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, (V <= 2) ? 2 : 1)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                 const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ mean_in,
                 const float* __restrict__ rstd_in, const unsigned char* __restrict__ row_keep,
@@ -243,7 +243,9 @@ int launch_fwd(const void* x, const void* g, const void* b, const void* keep, vo
 template <bool RMS>
 int launch_bwd(const void* dy, const void* x, const void* g, const float* mean, const float* rstd, const void* keep,
                void* dx, float* dgamma, float* dbeta, int rows, int H, cudaStream_t st) {
-  const int blocks = min((rows + kWarpsPerBlock - 1) / kWarpsPerBlock, 148 * 2);
+  // one resident block per SM from 768 columns on (the parameter-gradient accumulators and the next row's loads
+  // take about 150 registers per thread, and spilling them costs more than the second block brings), two below
+  const int blocks = min((rows + kWarpsPerBlock - 1) / kWarpsPerBlock, 148 * (H <= 512 ? 2 : 1));
   auto DY = static_cast<const __nv_bfloat16*>(dy);
   auto X = static_cast<const __nv_bfloat16*>(x);
   auto G = static_cast<const __nv_bfloat16*>(g);
