@@ -757,16 +757,9 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (j > 0) {  // P·V of the previous tile retired: its P is consumed and O is stable
         if (!wait_all(bar_o, (j - 1) & 1, kErrAccFullWait)) { ok = false; break; }
         tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(t_o + lane_addr + part * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st_32x32b_x32(t_o + lane_addr + part * 32, r);
-          tmem_st_wait();
-        }
       }
+      // P first, then the rescaling of O: the 32 probabilities are dead before the 32 accumulator values arrive, so
+      // the two sets never hold registers at the same time
 #pragma unroll
       for (int g4 = 0; g4 < 4; ++g4) {
         uint4 u;
@@ -775,6 +768,15 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         u.z = pack_bf16(s[g4 * 8 + 4], s[g4 * 8 + 5]);
         u.w = pack_bf16(s[g4 * 8 + 6], s[g4 * 8 + 7]);
         *reinterpret_cast<uint4*>(sP + swz128(row, part * 4 + g4)) = u;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_o + lane_addr + part * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+        tmem_st_32x32b_x32(t_o + lane_addr + part * 32, r);
+        tmem_st_wait();
       }
       fence_proxy_async();
       tc_fence_before();
