@@ -18,6 +18,8 @@
 // Backward: grid (k-tiles, heads, batch); dK/dV accumulate in TMEM, dQ and the gradients of
 //           C2P / P2C are reduced into fp32 buffers with red.global.add.
 #include "tc05.cuh"
+
+#include <type_traits>
 #include "kernels.h"
 
 namespace {
@@ -726,11 +728,20 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           for (int k = 0; k < 32; ++k) s[k] = (kb + k < S) ? s[k] : -INFINITY;
         }
       } else {
-        const uint32_t kw[8] = {keep_lo.x, keep_lo.y, keep_lo.z, keep_lo.w, keep_hi.x, keep_hi.y, keep_hi.z, keep_hi.w};
+        // every lane of the warp looks at the same 32 keys, so "all of them kept" (the usual case: packed batches carry
+        // a mask of ones) is a warp-uniform test that skips the per-score selects
+        const bool all_kept = kb + 32 <= S &&
+                              (keep_lo.x & keep_lo.y & keep_lo.z & keep_lo.w & keep_hi.x & keep_hi.y & keep_hi.z & keep_hi.w) ==
+                                  0x01010101u &&
+                              (keep_lo.x | keep_lo.y | keep_lo.z | keep_lo.w | keep_hi.x | keep_hi.y | keep_hi.z | keep_hi.w) ==
+                                  0x01010101u;
+        if (!all_kept) {
+          const uint32_t kw[8] = {keep_lo.x, keep_lo.y, keep_lo.z, keep_lo.w, keep_hi.x, keep_hi.y, keep_hi.z, keep_hi.w};
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const bool keep = ((kw[k >> 2] >> (8 * (k & 3))) & 0xffu) != 0 && (kb + k < S);
-          s[k] = keep ? s[k] : -INFINITY;
+          for (int k = 0; k < 32; ++k) {
+            const bool keep = ((kw[k >> 2] >> (8 * (k & 3))) & 0xffu) != 0 && (kb + k < S);
+            s[k] = keep ? s[k] : -INFINITY;
+          }
         }
       }
       float tmax = -INFINITY;
@@ -1086,15 +1097,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
       const float delta_s = delta * p.inv_scale;
+      // Two copies of the loop, chosen by a block-uniform test: tiles whose 128 keys are all kept (every full tile of
+      // an unmasked input, and of a padding mask of ones) carry no per-score select and no metadata reads.
+      auto score_loop = [&](auto masked_tag) {
+      constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
       for (int e = 0; e < 32; ++e) {
         const int k = c * 32 + e;
         bool keep = true;
-        if (MASK == 0) {
-          if (k0 + kTile > S) keep = k0 + k < S;  // last, partial key tile
-        } else if (!tile_all_keep) {
-          const int meta = kmeta[k];
-          keep = MASK == 1 ? (meta != 0) : (meta != 0 && meta == q_doc);
+        if (kMasked) {
+          if (MASK == 0) {
+            keep = k0 + k < S;  // last, partial key tile
+          } else {
+            const int meta = kmeta[k];
+            keep = MASK == 1 ? (meta != 0) : (meta != 0 && meta == q_doc);
+          }
         }
         float v = pv[e];
         int ic = 0, ip = 0;
@@ -1114,6 +1131,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (dc2p_row) atomicAdd(dc2p_row + ic, g);
           if (p.d_p2c) atomicAdd(p.d_p2c + kbase + static_cast<long long>(k) * pos_row + ip, g);
         }
+      }
+      };
+      if (MASK == 0 ? (k0 + kTile > S) : !tile_all_keep) {
+        score_loop(std::true_type{});
+      } else {
+        score_loop(std::false_type{});
       }
       // the previous tile's gradient MMAs must retire before its P / dS tiles and dQ accumulator are reused
       if (i > 0) {
