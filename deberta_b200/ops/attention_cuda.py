@@ -344,22 +344,29 @@ class _FlashAttention(torch.autograd.Function):
                     g_p2c = gt
         q2 = q.as_strided((T, H), (q.stride(1), 1), q.storage_offset())
         k2 = k.as_strided((T, H), (k.stride(1), 1), k.storage_offset())
+        # the two table gradients accumulate in fp32 (split-K over the tokens: measured faster than one bf16 pass that can
+        # only use 48 CTAs); side by side in one buffer when both exist, so that one fill serves both
+        both = g_c2p is not None and g_p2c is not None and pos_k.shape == pos_q.shape and pos_k.dtype == pos_q.dtype
+        acc = torch.zeros((2, *pos_k.shape), dtype=torch.float32, device=dev) if both else None
         if g_c2p is not None:
             g = g_c2p.permute(1, 0, 2)  # [heads, T, span2]
             # dQ += dC2P · PosK ; dPosK = dC2Pᵀ · Q   (per head)
             gemm(g, _heads_view(pos_k, heads), b_mn=True, out=_heads_view(dq_acc, heads), accumulate=True)
-            # (fp32 with split-K over the tokens: measured faster than one bf16 pass that can only use 48 CTAs)
-            d_pos_k = torch.zeros(pos_k.shape, dtype=torch.float32, device=dev)
+            d_pos_k = acc[0] if both else torch.zeros(pos_k.shape, dtype=torch.float32, device=dev)
             gemm(g, _heads_view(q2, heads), a_mn=True, b_mn=True, out=_heads_view(d_pos_k, heads), accumulate=True)
-            d_pos_k = d_pos_k.to(pos_k.dtype)
+            if not both:
+                d_pos_k = d_pos_k.to(pos_k.dtype)
         if g_p2c is not None:
             g = g_p2c.permute(1, 0, 2)
             # dK += dP2C · PosQ (per head), added in the GEMM epilogue
             dkh = _heads_view(dk, heads)
             gemm(g, _heads_view(pos_q, heads), b_mn=True, residual=dkh, out=dkh)
-            d_pos_q = torch.zeros(pos_q.shape, dtype=torch.float32, device=dev)
+            d_pos_q = acc[1] if both else torch.zeros(pos_q.shape, dtype=torch.float32, device=dev)
             gemm(g, _heads_view(k2, heads), a_mn=True, b_mn=True, out=_heads_view(d_pos_q, heads), accumulate=True)
-            d_pos_q = d_pos_q.to(pos_q.dtype)
+            if not both:
+                d_pos_q = d_pos_q.to(pos_q.dtype)
+        if both:  # (two casts: the outputs of a custom op must not alias each other)
+            d_pos_k, d_pos_q = acc[0].to(pos_k.dtype), acc[1].to(pos_q.dtype)
         dq = dqkv[:, :H]
         _lib.call("db200_cast_f32_bf16", _lib.ptr(dq_acc), _lib.ptr(dq), ctypes.c_longlong(3 * H), ctypes.c_longlong(T),
                   c_int(H), _lib.stream_ptr())
