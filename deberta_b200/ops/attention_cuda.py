@@ -168,6 +168,27 @@ def _token_major(x: torch.Tensor) -> torch.Tensor:
     return x
 
 
+# Both products of one side of the position-term gradient from ONE pass over the folded gradient table
+# (csrc/posgrad.cu) instead of two batched GEMMs that each read it. Off: the two GEMMs (A/B comparisons, tests).
+POSGRAD_DUAL = True
+
+
+def _posgrad_dual(g, tab, x, out_f32, out_bf16, d_tab, heads: int) -> bool:
+    """``rows += g·tab`` (fp32 ``out_f32`` or bf16 ``out_bf16``) and ``d_tab += gᵀ·x`` per head in one kernel. ``g``:
+    ``[T, heads, W]`` bf16, ``tab``: ``[W, heads*64]``, ``x``: ``[T, heads*64]`` rows (any row stride), ``d_tab``:
+    ``[W, heads*64]`` fp32. Returns False when the shape is not covered (W other than 256 / 512) or the path is off."""
+    T, _, W = g.shape
+    if not POSGRAD_DUAL or W not in (256, 512) or not g.is_contiguous() or tab.shape[0] != W or tab.stride(1) != 1:
+        return False
+    out = out_f32 if out_f32 is not None else out_bf16
+    rc = _lib.call_rc(
+        "db200_posgrad_dual", _lib.ptr(g), c_ll(heads * W), _lib.ptr(tab), c_ll(tab.stride(0)), _lib.ptr(x),
+        c_ll(x.stride(0)), _lib.ptr(out_f32), c_ll(out.stride(0) if out_f32 is not None else 0), _lib.ptr(out_bf16),
+        c_ll(out.stride(0) if out_bf16 is not None else 0), _lib.ptr(d_tab), c_ll(d_tab.stride(0)), c_int(T),
+        c_int(heads), c_int(W), _lib.stream_ptr(), accept=(_TC_REJECTED,))
+    return rc == 0
+
+
 def _heads_view(x2: torch.Tensor, heads: int) -> torch.Tensor:
     """[rows, H] (row stride ld) → [heads, rows, 64] view for the batched GEMM."""
     rows, H = x2.shape
@@ -349,20 +370,22 @@ class _FlashAttention(torch.autograd.Function):
         both = g_c2p is not None and g_p2c is not None and pos_k.shape == pos_q.shape and pos_k.dtype == pos_q.dtype
         acc = torch.zeros((2, *pos_k.shape), dtype=torch.float32, device=dev) if both else None
         if g_c2p is not None:
-            g = g_c2p.permute(1, 0, 2)  # [heads, T, span2]
             # dQ += dC2P · PosK ; dPosK = dC2Pᵀ · Q   (per head)
-            gemm(g, _heads_view(pos_k, heads), b_mn=True, out=_heads_view(dq_acc, heads), accumulate=True)
             d_pos_k = acc[0] if both else torch.zeros(pos_k.shape, dtype=torch.float32, device=dev)
-            gemm(g, _heads_view(q2, heads), a_mn=True, b_mn=True, out=_heads_view(d_pos_k, heads), accumulate=True)
+            if not _posgrad_dual(g_c2p, pos_k, q2, dq_acc, None, d_pos_k, heads):
+                g = g_c2p.permute(1, 0, 2)  # [heads, T, span2]
+                gemm(g, _heads_view(pos_k, heads), b_mn=True, out=_heads_view(dq_acc, heads), accumulate=True)
+                gemm(g, _heads_view(q2, heads), a_mn=True, b_mn=True, out=_heads_view(d_pos_k, heads), accumulate=True)
             if not both:
                 d_pos_k = d_pos_k.to(pos_k.dtype)
         if g_p2c is not None:
-            g = g_p2c.permute(1, 0, 2)
-            # dK += dP2C · PosQ (per head), added in the GEMM epilogue
-            dkh = _heads_view(dk, heads)
-            gemm(g, _heads_view(pos_q, heads), b_mn=True, residual=dkh, out=dkh)
+            # dK += dP2C · PosQ ; dPosQ = dP2Cᵀ · K   (per head)
             d_pos_q = acc[1] if both else torch.zeros(pos_q.shape, dtype=torch.float32, device=dev)
-            gemm(g, _heads_view(k2, heads), a_mn=True, b_mn=True, out=_heads_view(d_pos_q, heads), accumulate=True)
+            if not _posgrad_dual(g_p2c, pos_q, k2, None, dk, d_pos_q, heads):
+                g = g_p2c.permute(1, 0, 2)
+                dkh = _heads_view(dk, heads)
+                gemm(g, _heads_view(pos_q, heads), b_mn=True, residual=dkh, out=dkh)  # added in the GEMM epilogue
+                gemm(g, _heads_view(k2, heads), a_mn=True, b_mn=True, out=_heads_view(d_pos_q, heads), accumulate=True)
             if not both:
                 d_pos_q = d_pos_q.to(pos_q.dtype)
         if both:  # (two casts: the outputs of a custom op must not alias each other)
