@@ -118,7 +118,9 @@ class _Linear(torch.autograd.Function):
     def backward(ctx, dy):
         (x,) = ctx.saved_tensors
         w = ctx.w_ref
-        dy = dy.contiguous()
+        # (a column slice of a wider buffer, e.g. one third of the attention backward's dQ | dK | dV, is read in place)
+        if dy.stride(1) != 1 or dy.stride(0) % 8 or dy.data_ptr() % 16:
+            dy = dy.contiguous()
         dx = gemm(dy, w, b_mn=True) if ctx.needs_input_grad[0] else None
         dw, db = _param_grads(dy, x, w, ctx.bias_ref if ctx.has_bias else None)
         dres = dy if ctx.has_res else None

@@ -198,6 +198,35 @@ def test_fused_qkv_projection_matches_three_linears():
         assert (bs[i].main_grad - want_b).abs().max() <= 3e-2 * want_b.abs().max()
 
 
+def test_linear_backward_reads_a_column_slice_in_place():
+    """The upstream gradient of a projection can be a column slice of a wider buffer (the attention backward writes
+    dQ | dK | dV side by side): data, weight and bias gradients must equal those of a contiguous copy, also into
+    ``main_grad`` buffers."""
+    from deberta_b200.ops.linear import linear
+
+    torch.manual_seed(5)
+    T, K, N = 1000, 256, 384
+    x = (torch.randn(T, K, device="cuda") * 0.5).to(torch.bfloat16)
+    wide = (torch.randn(T, 3 * N, device="cuda") * 0.5).to(torch.bfloat16)
+    results = []
+    for contiguous in (True, False):
+        xx = x.clone().requires_grad_(True)
+        w = torch.nn.Parameter((torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16))
+        b = torch.nn.Parameter(torch.zeros(N, device="cuda", dtype=torch.bfloat16))
+        torch.manual_seed(6)
+        w.data.copy_((torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16))
+        w.main_grad = torch.zeros(N, K, device="cuda")
+        b.main_grad = torch.zeros(N, device="cuda")
+        dy = wide[:, N : 2 * N]
+        assert not dy.is_contiguous()
+        linear(xx, w, b).backward(dy.contiguous() if contiguous else dy)
+        results.append((xx.grad.clone(), w.main_grad.clone(), b.main_grad.clone()))
+    _lib.check_status()
+    assert torch.equal(results[0][0], results[1][0])
+    for a_, b_ in zip(results[0][1:], results[1][1:]):  # split-K adds in fp32: equal up to the order of the additions
+        assert (a_ - b_).abs().max() <= 1e-4 * a_.abs().max()
+
+
 def test_residual_gradient_rides_into_the_qkv_data_gradient_gemm():
     """y = W_o·(q + k + v) + x with (q, k, v) from the fused projection of x: with a ResidualGradSink the closing
     projection reports no gradient for its residual and the opening projection's backward adds it in its GEMM epilogue.
