@@ -365,3 +365,38 @@ def test_position_terms_single_sided_and_long_rows(which, S, span, buckets, maxp
             assert a.grad is None or float(a.grad.abs().max()) == 0.0, name
             continue
         assert _rel_err(a.grad, b.grad) < 4e-2, name
+
+
+@pytest.mark.parametrize("T,heads,W", [(1000, 3, 512), (256, 2, 256), (130, 1, 512)])
+def test_position_gradient_dual_kernel_matches_fp32(T, heads, W):
+    """One pass over the folded gradient table gives both products of a side: rows += g·tab (fp32 accumulator for the
+    query side, bf16 read-modify-write for the key side) and d_tab += gᵀ·x, per head; x and the bf16 rows are column
+    slices of wider buffers, T is not a multiple of the 128-token tile, and what the outputs held before is kept."""
+    from deberta_b200.ops import attention_cuda
+
+    torch.manual_seed(11)
+    H = heads * 64
+    g = (torch.randn(T, heads, W, device="cuda") * 0.3).to(torch.bfloat16)
+    tab = (torch.randn(W, H, device="cuda") * 0.3).to(torch.bfloat16)
+    wide = (torch.randn(T, 3 * H, device="cuda") * 0.5).to(torch.bfloat16)
+    x = wide[:, H : 2 * H]
+    gf, tf, xf = g.float(), tab.float().view(W, heads, 64), x.float().reshape(T, heads, 64)
+    want_rows = torch.einsum("thw,whd->thd", gf, tf).reshape(T, H)
+    want_tab = torch.einsum("thw,thd->whd", gf, xf).reshape(W, H)
+    # query side: fp32 accumulator
+    acc = torch.full((T, H), 0.5, device="cuda")
+    d_tab = torch.full((W, H), -1.0, device="cuda")
+    assert attention_cuda._posgrad_dual(g, tab, x, acc, None, d_tab, heads)
+    _lib.check_status()
+    assert (acc - 0.5 - want_rows).abs().max() <= 2e-2 * want_rows.abs().max()
+    assert (d_tab + 1.0 - want_tab).abs().max() <= 2e-2 * want_tab.abs().max()
+    # key side: bf16 rows inside a wider buffer, everything around them untouched
+    out_wide = (torch.randn(T, 3 * H, device="cuda") * 0.5).to(torch.bfloat16)
+    before = out_wide.clone()
+    d_tab2 = torch.zeros(W, H, device="cuda")
+    assert attention_cuda._posgrad_dual(g, tab, x, None, out_wide[:, H : 2 * H], d_tab2, heads)
+    _lib.check_status()
+    assert torch.equal(out_wide[:, :H], before[:, :H]) and torch.equal(out_wide[:, 2 * H :], before[:, 2 * H :])
+    got = out_wide[:, H : 2 * H].float() - before[:, H : 2 * H].float()
+    assert (got - want_rows).abs().max() <= 3e-2 * want_rows.abs().max()
+    assert (d_tab2 - want_tab).abs().max() <= 2e-2 * want_tab.abs().max()
