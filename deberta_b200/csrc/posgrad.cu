@@ -42,8 +42,10 @@ struct Dev {
   int T, heads, W, halves;      // halves = W / 256
   int tiles, tiles_per_cta;
   float* out_f32;               // [T, ld_of] fp32, += (red.add), or null
-  __nv_bfloat16* out_bf16;      // [T, ld_ob] bf16, += (read-modify-write: every element has one owner), or null
-  long long ld_of, ld_ob;
+  __nv_bfloat16* out_bf16;      // [T, ld_ob] bf16 (every element has one owner), or null: = acc_in + result when
+                                // acc_in is given, else += result (read-modify-write)
+  const float* acc_in;          // [T, ld_ai] fp32 or null
+  long long ld_of, ld_ob, ld_ai;
   float* d_tab;                 // [W, ld_dt] fp32, +=
   long long ld_dt;
   int* status;
@@ -192,16 +194,28 @@ posgrad_dual_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_const
                        __uint_as_float(r[q * 4 + 3]));
         } else {
           uint4* dst = reinterpret_cast<uint4*>(p.out_bf16 + tok * p.ld_ob + h * kD + part * 32);
+          if (p.acc_in) {  // fp32 partial result of another kernel + this one, rounded once
+            const float4* src = reinterpret_cast<const float4*>(p.acc_in + tok * p.ld_ai + h * kD + part * 32);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const uint4 old = dst[q];
-            const uint32_t o[4] = {old.x, old.y, old.z, old.w};
-            uint32_t n[4];
+            for (int q = 0; q < 4; ++q) {
+              const float4 a0 = src[2 * q], a1 = src[2 * q + 1];
+              dst[q] = make_uint4(pack_bf16(a0.x + __uint_as_float(r[q * 8]), a0.y + __uint_as_float(r[q * 8 + 1])),
+                                  pack_bf16(a0.z + __uint_as_float(r[q * 8 + 2]), a0.w + __uint_as_float(r[q * 8 + 3])),
+                                  pack_bf16(a1.x + __uint_as_float(r[q * 8 + 4]), a1.y + __uint_as_float(r[q * 8 + 5])),
+                                  pack_bf16(a1.z + __uint_as_float(r[q * 8 + 6]), a1.w + __uint_as_float(r[q * 8 + 7])));
+            }
+          } else {
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-              n[e] = pack_bf16(bf16_lo(o[e]) + __uint_as_float(r[q * 8 + 2 * e]),
-                               bf16_hi(o[e]) + __uint_as_float(r[q * 8 + 2 * e + 1]));
-            dst[q] = make_uint4(n[0], n[1], n[2], n[3]);
+            for (int q = 0; q < 4; ++q) {
+              const uint4 old = dst[q];
+              const uint32_t o[4] = {old.x, old.y, old.z, old.w};
+              uint32_t n[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                n[e] = pack_bf16(bf16_lo(o[e]) + __uint_as_float(r[q * 8 + 2 * e]),
+                                 bf16_hi(o[e]) + __uint_as_float(r[q * 8 + 2 * e + 1]));
+              dst[q] = make_uint4(n[0], n[1], n[2], n[3]);
+            }
           }
         }
       }
@@ -234,19 +248,21 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 
 }  // namespace
 
-// rows += G·Tab (fp32 red.add into `out_f32`, or bf16 read-modify-write into `out_bf16`; exactly one of the two) and
-// d_tab += Gᵀ·X, per head. g: [T, heads*W] bf16 (row stride ld_g), tab: [W, heads*64] bf16, x: [T, >= heads*64] bf16,
+// rows += G·Tab (fp32 red.add into `out_f32`, or bf16 read-modify-write into `out_bf16`; exactly one of the two; with
+// `acc_in` the bf16 rows are acc_in + G·Tab instead, rounded once) and d_tab += Gᵀ·X, per head. g: [T, heads*W] bf16 (row stride ld_g), tab: [W, heads*64] bf16, x: [T, >= heads*64] bf16,
 // d_tab: [W, heads*64] fp32. W must be 256 or 512. Returns -13 when the shape is not covered (the caller then uses
 // the two GEMMs).
 extern "C" int db200_posgrad_dual(const void* g, long long ld_g, const void* tab, long long ld_tab, const void* x,
                                   long long ld_x, float* out_f32, long long ld_of, void* out_bf16, long long ld_ob,
-                                  float* d_tab, long long ld_dt, int T, int heads, int W, void* stream_) {
+                                  const float* acc_in, long long ld_ai, float* d_tab, long long ld_dt, int T, int heads,
+                                  int W, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (T <= 0 || heads <= 0) return 0;
   if (W != 256 && W != 512) return -13;
   if (!g || !tab || !x || !d_tab || ((out_f32 == nullptr) == (out_bf16 == nullptr))) return -10;
   if (!aligned16(g) || !aligned16(tab) || !aligned16(x) || !aligned16(d_tab) || (ld_g % 8) || (ld_tab % 8) || (ld_x % 8) ||
-      (ld_dt % 4) || (out_f32 && (!aligned16(out_f32) || (ld_of % 4))) || (out_bf16 && (!aligned16(out_bf16) || (ld_ob % 8))))
+      (ld_dt % 4) || (out_f32 && (!aligned16(out_f32) || (ld_of % 4))) || (out_bf16 && (!aligned16(out_bf16) || (ld_ob % 8))) ||
+      (acc_in && (!out_bf16 || !aligned16(acc_in) || (ld_ai % 4))))
     return -10;
   CUtensorMap tg, tt, tx;
   int rc;
@@ -269,6 +285,7 @@ extern "C" int db200_posgrad_dual(const void* g, long long ld_g, const void* tab
   chunks = (d.tiles + d.tiles_per_cta - 1) / d.tiles_per_cta;  // no empty CTA
   d.out_f32 = out_f32; d.ld_of = ld_of;
   d.out_bf16 = static_cast<__nv_bfloat16*>(out_bf16); d.ld_ob = ld_ob;
+  d.acc_in = acc_in; d.ld_ai = ld_ai;
   d.d_tab = d_tab; d.ld_dt = ld_dt;
   d.status = db200_status_ptr();
   static bool configured[16] = {};

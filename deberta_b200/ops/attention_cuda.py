@@ -173,10 +173,11 @@ def _token_major(x: torch.Tensor) -> torch.Tensor:
 POSGRAD_DUAL = True
 
 
-def _posgrad_dual(g, tab, x, out_f32, out_bf16, d_tab, heads: int) -> bool:
+def _posgrad_dual(g, tab, x, out_f32, out_bf16, d_tab, heads: int, acc_in=None) -> bool:
     """``rows += g·tab`` (fp32 ``out_f32`` or bf16 ``out_bf16``) and ``d_tab += gᵀ·x`` per head in one kernel. ``g``:
     ``[T, heads, W]`` bf16, ``tab``: ``[W, heads*64]``, ``x``: ``[T, heads*64]`` rows (any row stride), ``d_tab``:
-    ``[W, heads*64]`` fp32. Returns False when the shape is not covered (W other than 256 / 512) or the path is off."""
+    ``[W, heads*64]`` fp32. With ``acc_in`` (fp32 ``[T, heads*64]``) the bf16 rows become ``acc_in + g·tab``, rounded
+    once. Returns False when the shape is not covered (W other than 256 / 512) or the path is off."""
     T, _, W = g.shape
     if not POSGRAD_DUAL or W not in (256, 512) or not g.is_contiguous() or tab.shape[0] != W or tab.stride(1) != 1:
         return False
@@ -184,7 +185,8 @@ def _posgrad_dual(g, tab, x, out_f32, out_bf16, d_tab, heads: int) -> bool:
     rc = _lib.call_rc(
         "db200_posgrad_dual", _lib.ptr(g), c_ll(heads * W), _lib.ptr(tab), c_ll(tab.stride(0)), _lib.ptr(x),
         c_ll(x.stride(0)), _lib.ptr(out_f32), c_ll(out.stride(0) if out_f32 is not None else 0), _lib.ptr(out_bf16),
-        c_ll(out.stride(0) if out_bf16 is not None else 0), _lib.ptr(d_tab), c_ll(d_tab.stride(0)), c_int(T),
+        c_ll(out.stride(0) if out_bf16 is not None else 0), _lib.ptr(acc_in),
+        c_ll(acc_in.stride(0) if acc_in is not None else 0), _lib.ptr(d_tab), c_ll(d_tab.stride(0)), c_int(T),
         c_int(heads), c_int(W), _lib.stream_ptr(), accept=(_TC_REJECTED,))
     return rc == 0
 
@@ -369,10 +371,13 @@ class _FlashAttention(torch.autograd.Function):
         # only use 48 CTAs); side by side in one buffer when both exist, so that one fill serves both
         both = g_c2p is not None and g_p2c is not None and pos_k.shape == pos_q.shape and pos_k.dtype == pos_q.dtype
         acc = torch.zeros((2, *pos_k.shape), dtype=torch.float32, device=dev) if both else None
+        dq_done = False
         if g_c2p is not None:
             # dQ += dC2P · PosK ; dPosK = dC2Pᵀ · Q   (per head)
             d_pos_k = acc[0] if both else torch.zeros(pos_k.shape, dtype=torch.float32, device=dev)
-            if not _posgrad_dual(g_c2p, pos_k, q2, dq_acc, None, d_pos_k, heads):
+            # (the query rows leave as bf16 = fp32 accumulator of the attention kernel + this product: no cast pass)
+            dq_done = _posgrad_dual(g_c2p, pos_k, q2, None, dqkv[:, :H], d_pos_k, heads, acc_in=dq_acc)
+            if not dq_done:
                 g = g_c2p.permute(1, 0, 2)  # [heads, T, span2]
                 gemm(g, _heads_view(pos_k, heads), b_mn=True, out=_heads_view(dq_acc, heads), accumulate=True)
                 gemm(g, _heads_view(q2, heads), a_mn=True, b_mn=True, out=_heads_view(d_pos_k, heads), accumulate=True)
@@ -391,8 +396,9 @@ class _FlashAttention(torch.autograd.Function):
         if both:  # (two casts: the outputs of a custom op must not alias each other)
             d_pos_k, d_pos_q = acc[0].to(pos_k.dtype), acc[1].to(pos_q.dtype)
         dq = dqkv[:, :H]
-        _lib.call("db200_cast_f32_bf16", _lib.ptr(dq_acc), _lib.ptr(dq), ctypes.c_longlong(3 * H), ctypes.c_longlong(T),
-                  c_int(H), _lib.stream_ptr())
+        if not dq_done:
+            _lib.call("db200_cast_f32_bf16", _lib.ptr(dq_acc), _lib.ptr(dq), ctypes.c_longlong(3 * H), ctypes.c_longlong(T),
+                      c_int(H), _lib.stream_ptr())
         return dq.view(B, S, H), dk.view(B, S, H), dv.view(B, S, H), d_pos_k, d_pos_q, None, None, None, None, None
 
 

@@ -390,6 +390,14 @@ def test_position_gradient_dual_kernel_matches_fp32(T, heads, W):
     _lib.check_status()
     assert (acc - 0.5 - want_rows).abs().max() <= 2e-2 * want_rows.abs().max()
     assert (d_tab + 1.0 - want_tab).abs().max() <= 2e-2 * want_tab.abs().max()
+    # query side as the training step runs it: bf16 rows = fp32 accumulator + product, rounded once
+    acc_in = torch.randn(T, H, device="cuda")
+    rows = torch.zeros(T, 3 * H, device="cuda", dtype=torch.bfloat16)
+    d_tab3 = torch.zeros(W, H, device="cuda")
+    assert attention_cuda._posgrad_dual(g, tab, x, None, rows[:, :H], d_tab3, heads, acc_in=acc_in)
+    _lib.check_status()
+    assert (rows[:, :H].float() - (acc_in + want_rows)).abs().max() <= 2e-2 * (acc_in + want_rows).abs().max()
+    assert float(rows[:, H:].abs().max()) == 0.0
     # key side: bf16 rows inside a wider buffer, everything around them untouched
     out_wide = (torch.randn(T, 3 * H, device="cuda") * 0.5).to(torch.bfloat16)
     before = out_wide.clone()
