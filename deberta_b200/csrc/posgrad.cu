@@ -23,23 +23,24 @@ using namespace tc05;
 
 constexpr int kTok = 128;                    // tokens per tile
 constexpr int kD = 64;                       // head dimension
-constexpr int kHalfW = 256;                  // table rows per load step
+constexpr int kStepW = 128;                  // table rows per load step (one 128-row block of the table gradient)
+constexpr int kStages = 4;                   // one stage per 128-row block of a 512-row table
 constexpr int kBoxBytes = kTok * 64 * 2;     // 16 KB: 128 rows x 64 bf16, 128B swizzle
-constexpr int kStageBytes = 4 * kBoxBytes;   // 64 KB: 128 tokens x 256 table rows
+constexpr int kStageBytes = 2 * kBoxBytes;   // 32 KB: 128 tokens x 128 table rows
 constexpr int kTabBytes = 512 * kD * 2;      // 64 KB: the head's slice of the position table (up to 512 rows)
 constexpr int kThreads = 320;
 
 struct Smem {
   static constexpr int kTab = 0;
-  static constexpr int kG = kTab + kTabBytes;          // two stages: table rows [0, 256) and [256, 512) of a tile
-  static constexpr int kX = kG + 2 * kStageBytes;      // two token tiles of X
+  static constexpr int kG = kTab + kTabBytes;          // four stages: table rows [128 s, 128 s + 128) of a tile
+  static constexpr int kX = kG + kStages * kStageBytes;  // two token tiles of X
   static constexpr int kBar = kX + 2 * kBoxBytes;
   static constexpr int kTotal = kBar + 256 + 1024;
 };
 static_assert(Smem::kTotal <= 227 * 1024, "shared memory of one CTA");
 
 struct Dev {
-  int T, heads, W, halves;      // halves = W / 256
+  int T, heads, W, steps;       // steps = W / 128 (2 or 4)
   int tiles, tiles_per_cta;
   float* out_f32;               // [T, ld_of] fp32, += (red.add), or null
   __nv_bfloat16* out_bf16;      // [T, ld_ob] bf16 (every element has one owner), or null: = acc_in + result when
@@ -64,13 +65,13 @@ posgrad_dual_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_const
   uint8_t* sTab = smem + Smem::kTab;
   uint8_t* sG = smem + Smem::kG;
   uint8_t* sX = smem + Smem::kX;
-  uint64_t* full_g = reinterpret_cast<uint64_t*>(smem + Smem::kBar);  // [2]
-  uint64_t* empty_g = full_g + 2;                                     // [2]
-  uint64_t* acc_full = full_g + 4;                                    // [2]
-  uint64_t* acc_empty = full_g + 6;                                   // [2]
-  uint64_t* tab_full = full_g + 8;
-  uint64_t* pos_full = full_g + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(full_g + 10);
+  uint64_t* full_g = reinterpret_cast<uint64_t*>(smem + Smem::kBar);  // [4]
+  uint64_t* empty_g = full_g + 4;                                     // [4]
+  uint64_t* acc_full = full_g + 8;                                    // [2]
+  uint64_t* acc_empty = full_g + 10;                                  // [2]
+  uint64_t* tab_full = full_g + 12;
+  uint64_t* pos_full = full_g + 13;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(full_g + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -80,9 +81,11 @@ posgrad_dual_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_const
   pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_g[s], 1);
       mbar_init(&empty_g[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&acc_full[s], 1);
       mbar_init(&acc_empty[s], 8);  // one arrival per epilogue warp
     }
@@ -109,21 +112,22 @@ posgrad_dual_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_const
       tma_prefetch_desc(&tm_g);
       tma_prefetch_desc(&tm_tab);
       tma_prefetch_desc(&tm_x);
-      mbar_expect_tx(tab_full, p.halves * (kHalfW * kD * 2));
-      for (int hf = 0; hf < p.halves; ++hf)
-        tma_load_3d(sTab + hf * (kHalfW * kD * 2), &tm_tab, tab_full, h * kD, hf * kHalfW, 0);
+      mbar_expect_tx(tab_full, p.steps * (kStepW * kD * 2));
+      for (int hf = 0; hf < p.steps; ++hf)
+        tma_load_3d(sTab + hf * (kStepW * kD * 2), &tm_tab, tab_full, h * kD, hf * kStepW, 0);
       bool ok = true;
       for (int t = 0; t < ntile && ok; ++t) {
         const int tok0 = (tile0 + t) * kTok;
-        for (int hf = 0; hf < p.halves; ++hf) {
-          // stage hf holds table rows [hf * 256, hf * 256 + 256) of every tile: its k-th use is tile k
+        for (int hf = 0; hf < p.steps; ++hf) {
+          // stage hf holds table rows [hf * 128, hf * 128 + 128) of every tile: its k-th use is tile k. A stage is
+          // asked for again as soon as the MMAs that read it have retired, so up to three are in flight at a time.
           if (!mbar_wait(&empty_g[hf], (t & 1) ^ 1, abort_flag, p.status, kErrEmptyWait)) { ok = false; break; }
           uint8_t* dst = sG + hf * kStageBytes;
           mbar_expect_tx(&full_g[hf], kStageBytes + (hf == 0 ? kBoxBytes : 0));
           if (hf == 0) tma_load_3d(sX + (t & 1) * kBoxBytes, &tm_x, &full_g[0], h * kD, tok0, 0);
 #pragma unroll
-          for (int bx = 0; bx < 4; ++bx)
-            tma_load_3d(dst + bx * kBoxBytes, &tm_g, &full_g[hf], h * p.W + hf * kHalfW + bx * 64, tok0, 0);
+          for (int bx = 0; bx < 2; ++bx)
+            tma_load_3d(dst + bx * kBoxBytes, &tm_g, &full_g[hf], h * p.W + hf * kStepW + bx * 64, tok0, 0);
         }
       }
     }
@@ -138,28 +142,24 @@ posgrad_dual_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_const
         if (!mbar_wait(&acc_empty[a], ((t >> 1) & 1) ^ 1, abort_flag, p.status, kErrAccEmptyWait)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sx = smem_u32(sX + a * kBoxBytes);
-        for (int hf = 0; hf < p.halves; ++hf) {
+        for (int hf = 0; hf < p.steps; ++hf) {
           if (!mbar_wait(&full_g[hf], t & 1, abort_flag, p.status, kErrFullWait)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sg = smem_u32(sG + hf * kStageBytes);
-          const uint32_t st = smem_u32(sTab + hf * (kHalfW * kD * 2));
-          // rows[128 tokens, 64] += G[128, 256] · Tab[256, 64]: 16 steps of 16 table rows; a step is 32 bytes inside
-          // the 128-byte row of one of the four 64-column boxes
+          const uint32_t st = smem_u32(sTab + hf * (kStepW * kD * 2));
+          // rows[128 tokens, 64] += G[128, 128] · Tab[128, 64]: 8 steps of 16 table rows; a step is 32 bytes inside
+          // the 128-byte row of one of the two 64-column boxes
 #pragma unroll
-          for (int ks = 0; ks < 16; ++ks)
+          for (int ks = 0; ks < 8; ++ks)
             umma_bf16(t_rows + a * 64, make_smem_desc(sg + (ks >> 2) * kBoxBytes + (ks & 3) * 32, 16, 1024),
                       make_smem_desc(st + ks * 2048, 8192, 1024), idesc_rows, (hf > 0) || (ks > 0));
-          // dTab[128 table rows, 64] += Gᵀ[128, 128 tokens] · X[128 tokens, 64], one MMA set per 128-row block:
-          // 8 steps of 16 tokens (2048 bytes down the box); the block's two 64-column boxes are 16 KB apart
+          // dTab[128 table rows, 64] += Gᵀ[128, 128 tokens] · X[128 tokens, 64]: 8 steps of 16 tokens (2048 bytes
+          // down the box); the block's two 64-column boxes are 16 KB apart
 #pragma unroll
-          for (int blk = 0; blk < 2; ++blk) {
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks)
-              umma_bf16(t_pos + (hf * 2 + blk) * 64,
-                        make_smem_desc(sg + blk * 2 * kBoxBytes + ks * 2048, kBoxBytes, 1024),
-                        make_smem_desc(sx + ks * 2048, 8192, 1024), idesc_pos, (t > 0) || (ks > 0));
-          }
-          umma_commit(&empty_g[hf]);  // frees the stage (and, after the last half, this tile's X buffer)
+          for (int ks = 0; ks < 8; ++ks)
+            umma_bf16(t_pos + hf * 64, make_smem_desc(sg + ks * 2048, kBoxBytes, 1024),
+                      make_smem_desc(sx + ks * 2048, 8192, 1024), idesc_pos, (t > 0) || (ks > 0));
+          umma_commit(&empty_g[hf]);  // frees the stage (and, after the last step, this tile's X buffer)
         }
         if (!ok) break;
         umma_commit(&acc_full[a]);
@@ -223,7 +223,7 @@ posgrad_dual_kernel(const __grid_constant__ CUtensorMap tm_g, const __grid_const
     // the table gradient of this CTA's tokens, once
     if (ok && __all_sync(0xffffffffu, mbar_wait(pos_full, 0, abort_flag, p.status, kErrAccFullWait)) != 0) {
       tc_fence_after();
-      for (int blk = 0; blk < 2 * p.halves; ++blk) {
+      for (int blk = 0; blk < p.steps; ++blk) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(t_pos + blk * 64 + lane_addr + part * 32, r);
         tmem_ld_wait();
@@ -267,10 +267,10 @@ extern "C" int db200_posgrad_dual(const void* g, long long ld_g, const void* tab
   CUtensorMap tg, tt, tx;
   int rc;
   if ((rc = db200_make_tmap_bf16(&tg, g, static_cast<long long>(heads) * W, T, 1, ld_g, 0, kTok))) return rc;
-  if ((rc = db200_make_tmap_bf16(&tt, tab, static_cast<long long>(heads) * kD, W, 1, ld_tab, 0, kHalfW))) return rc;
+  if ((rc = db200_make_tmap_bf16(&tt, tab, static_cast<long long>(heads) * kD, W, 1, ld_tab, 0, kStepW))) return rc;
   if ((rc = db200_make_tmap_bf16(&tx, x, static_cast<long long>(heads) * kD, T, 1, ld_x, 0, kTok))) return rc;
   Dev d{};
-  d.T = T; d.heads = heads; d.W = W; d.halves = W / kHalfW;
+  d.T = T; d.heads = heads; d.W = W; d.steps = W / kStepW;
   d.tiles = (T + kTok - 1) / kTok;
   int sms = 148;
   {
