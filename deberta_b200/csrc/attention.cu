@@ -919,8 +919,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(&bar_qd[0], 1);
     mbar_init(&bar_qd[1], 1);
     mbar_init(&bar_qd[2], 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_g, 1);
+    // One thread gets a 64- or 128-column MMA out only every 70-100 clocks (about twice what the tensor core needs for
+    // it), and it is blocked while it does. The score MMAs are therefore issued by two threads of different warps and
+    // the gradient MMAs by three, each committing its own: a phase of these barriers takes 2 resp. 3 arrivals.
+    mbar_init(bar_s, 2);
+    mbar_init(bar_g, 3);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -948,16 +951,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   constexpr uint32_t idesc_t = make_idesc_bf16(128, 64, true, true);       // Pᵀ·dO, dSᵀ·Q
   constexpr uint32_t idesc_q = make_idesc_bf16(128, 64, false, true);      // dS·K
 
-  auto issue_scores = [&](int buf) {
-    const uint32_t q = smem_u32(sQ + buf * kTileBytes), d = smem_u32(sdO + buf * kTileBytes);
+  const bool issuer_s = tid == 0, issuer_dp = tid == 32;  // (also: dV and dK; thread 64 issues dQ)
+  auto issue_scores = [&](int buf) {  // called by both issuers, each for its own product
+    if (issuer_s) {
+      const uint32_t q = smem_u32(sQ + buf * kTileBytes);
 #pragma unroll
-    for (int ks = 0; ks < 4; ++ks)
-      umma_bf16(t_s, make_smem_desc(q + ks * 32, 16, 1024), make_smem_desc(smem_u32(sK) + ks * 32, 16, 1024), idesc_s,
-                ks > 0);
+      for (int ks = 0; ks < 4; ++ks)
+        umma_bf16(t_s, make_smem_desc(q + ks * 32, 16, 1024), make_smem_desc(smem_u32(sK) + ks * 32, 16, 1024), idesc_s,
+                  ks > 0);
+    } else {
+      const uint32_t d = smem_u32(sdO + buf * kTileBytes);
 #pragma unroll
-    for (int ks = 0; ks < 4; ++ks)
-      umma_bf16(t_dp, make_smem_desc(d + ks * 32, 16, 1024), make_smem_desc(smem_u32(sV) + ks * 32, 16, 1024), idesc_s,
-                ks > 0);
+      for (int ks = 0; ks < 4; ++ks)
+        umma_bf16(t_dp, make_smem_desc(d + ks * 32, 16, 1024), make_smem_desc(smem_u32(sV) + ks * 32, 16, 1024), idesc_s,
+                  ks > 0);
+    }
     umma_commit(bar_s);
   };
 
@@ -1004,7 +1012,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     cta_meta = meta;
   }
   const bool tile_all_keep = __syncthreads_and(MASK == 1 && cta_meta != 0) != 0;  // all 128 keys of this item are kept
-  if (tid == 0) {
+  if (issuer_s || issuer_dp) {
     if (mbar_wait(bar_kv, n_done & 1, abort_flag, p.status, kErrFullWait) &&
         mbar_wait(&bar_qd[g0 % 3], (g0 / 3) & 1, abort_flag, p.status, kErrFullWait)) {
       tc_fence_after();
@@ -1060,7 +1068,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tc_fence_before();
     // both accumulators are in registers: the tensor core may start on tile i+1
     if (!__syncthreads_and(got_s)) { ok = false; break; }
-    if (tid == 0 && i + 1 < nqt) {
+    if ((issuer_s || issuer_dp) && i + 1 < nqt) {
       const int nb = (g + 1) % 3;
       if (mbar_wait(&bar_qd[nb], ((g + 1) / 3) & 1, abort_flag, p.status, kErrFullWait)) {
         tc_fence_after();
@@ -1182,22 +1190,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     fence_proxy_async();
     tc_fence_before();
     if (!__syncthreads_and(got_g)) { ok = false; break; }
-    if (tid == 0) {
+    if (tid == 0 || tid == 32 || tid == 64) {  // one product each
       tc_fence_after();
       const uint32_t sp = smem_u32(sP), sds = smem_u32(sdS), sq = smem_u32(sQ + buf * kTileBytes),
                      sdo = smem_u32(sdO + buf * kTileBytes), sk = smem_u32(sK);
+      if (tid == 0) {
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks)  // dV[k,d] += sum_q P[q,k] dO[q,d]
-        umma_bf16(t_dv, make_smem_desc(sp + ks * 2048, kTileBytes, 1024), make_smem_desc(sdo + ks * 2048, 8192, 1024),
-                  idesc_t, (i > 0) || (ks > 0));
+        for (int ks = 0; ks < 8; ++ks)  // dV[k,d] += sum_q P[q,k] dO[q,d]
+          umma_bf16(t_dv, make_smem_desc(sp + ks * 2048, kTileBytes, 1024), make_smem_desc(sdo + ks * 2048, 8192, 1024),
+                    idesc_t, (i > 0) || (ks > 0));
+      } else if (tid == 32) {
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks)  // dK[k,d] += sum_q dS[q,k] Q[q,d]
-        umma_bf16(t_dk, make_smem_desc(sds + ks * 2048, kTileBytes, 1024), make_smem_desc(sq + ks * 2048, 8192, 1024),
-                  idesc_t, (i > 0) || (ks > 0));
+        for (int ks = 0; ks < 8; ++ks)  // dK[k,d] += sum_q dS[q,k] Q[q,d]
+          umma_bf16(t_dk, make_smem_desc(sds + ks * 2048, kTileBytes, 1024), make_smem_desc(sq + ks * 2048, 8192, 1024),
+                    idesc_t, (i > 0) || (ks > 0));
+      } else {
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks)  // dQ[q,d] = sum_k dS[q,k] K[k,d]
-        umma_bf16(t_dq, make_smem_desc(sds + (ks >> 2) * kTileBytes + (ks & 3) * 32, 16, 1024),
-                  make_smem_desc(sk + ks * 2048, 8192, 1024), idesc_q, ks > 0);
+        for (int ks = 0; ks < 8; ++ks)  // dQ[q,d] = sum_k dS[q,k] K[k,d]
+          umma_bf16(t_dq, make_smem_desc(sds + (ks >> 2) * kTileBytes + (ks & 3) * 32, 16, 1024),
+                    make_smem_desc(sk + ks * 2048, 8192, 1024), idesc_q, ks > 0);
+      }
       umma_commit(bar_g);
     }
   }
