@@ -1,11 +1,13 @@
 """Objective heads: vocabulary cross-entropy fused with Gumbel-max sampling, and the RTD loss.
 
 ``mlm_loss_and_sample`` evaluates, for the N masked rows only, the tied-embedding
-vocabulary projection, the mean fp32 cross-entropy and one Gumbel-max sample per row
-with forbidden ids excluded — the three steps of ``rtd.py:1066-1078`` of the reference.
-The PyTorch implementation materialises the ``[N, V]`` logits; the sm_100a kernel
-(``csrc/vocab_ce.cu``) sweeps vocabulary tiles once with online log-sum-exp and online
-arg-max so the logits never reach HBM.
+vocabulary projection, the mean fp32 cross-entropy and one sample per row from
+``softmax(logits / T)`` with forbidden ids excluded (the reference draws it by Gumbel-max) — the
+three steps of ``rtd.py:1066-1078`` of the reference. The PyTorch implementation materialises the
+``[N, V]`` logits; the sm_100a kernel (the cross-entropy epilogue of ``csrc/gemm.cu``, behind
+``ops/heads_cuda.py``) sweeps vocabulary tiles once with online log-sum-exp and a two-level exact
+sampler (an id per 32-column chunk by inverse CDF, Gumbel-max over the chunks' masses), so the
+logits never reach HBM.
 
 ``rtd_loss`` is the masked-mean binary cross-entropy of the discriminator with its
 accuracy / count statistics (``rtd.py:1123-1145``).
